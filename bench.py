@@ -1,0 +1,263 @@
+#!/usr/bin/env python3
+"""Headline benchmark: Qwen3-30B-A3B-shaped bf16 greedy decode at batch 1, one persistent launch per token.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layers L] [--prompt P]
+
+A step is one decode step (one token through all layers + lm_head + argmax) at context >= P (default 1024: the
+prompt is fed token by token through the same kernel first, as the reference's host does).  Prints ONE JSON line:
+value = ms per token with every input resident in HBM (K launches back to back, the next token never leaves the
+device), e2e = the same through the C ABI's host-buffer decode (token id host->device and device->host every step),
+roofline = algorithmic bytes of a step / measured launch time against the measured HBM copy peak, cpu_baseline = the
+oracle (numpy restatement of the reference's CPU path) timed on this box's cores on a bounded sample.
+With --impl reference the CPU path itself is the thing measured (same metric / config), on rank 0 only.
+N > 1: N independent replicas (one process per GPU, no collective: tensor / expert parallel sharding is not built yet).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC, UNIT = "decode_ms_per_token_bs1", "ms/token"
+MODEL = "qwen3-30b-a3b"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def oracle_sample(dims_cfg, layers_total: int, context: int, get_layer_weights, lm_head, final_norm, embed_row, seconds: float = 12.0):
+    """Time the oracle on a bounded sample: `ls` layers of the model at `context` prior tokens, a few decode steps, plus
+    the lm_head GEMV; scaled to the whole model (layers_total layers).  Returns (ms per token estimate, description)."""
+    from oracle import ref_decode as O
+    ls = 2
+    od = O.dims_from_config(dims_cfg, MODEL, layers=ls)
+    t = {}
+    for L in range(ls):
+        t.update(get_layer_weights(L))
+    t["model.norm.weight"], t["lm_head.weight"] = final_norm, lm_head
+    t["model.embed_tokens.weight"] = embed_row[None, :]
+    ref = O.Ref(od, O.DictWeights(t), context + 64)
+    rng = np.random.default_rng(0)
+    ref.kc[:, :context] = O.bfr(rng.standard_normal((ls, context, od.NKV, od.HD), dtype=np.float32) * np.float32(0.02))
+    ref.vc[:, :context] = O.bfr(rng.standard_normal((ls, context, od.NKV, od.HD), dtype=np.float32) * np.float32(0.02))
+    x0 = t["model.embed_tokens.weight"][0]
+    xs = O.rmsnorm(x0, final_norm, od.eps)
+    layer_s, head_s, n = [], [], 0
+    t_end = time.perf_counter() + seconds
+    while n < 3 or (time.perf_counter() < t_end and n < 40):
+        a = time.perf_counter()
+        x = x0.copy()
+        for L in range(ls):
+            x = ref.layer(L, x, context + n)
+        b = time.perf_counter()
+        logits = O.bfr(lm_head @ xs)
+        int(np.argmax(logits))
+        c = time.perf_counter()
+        if n >= 1:                                                        # first pass warms the page cache / BLAS threads
+            layer_s.append((b - a) / ls); head_s.append(c - b)
+        n += 1
+    ms = (float(np.median(layer_s)) * layers_total + float(np.median(head_s))) * 1e3
+    return ms, f"{len(layer_s)} decode steps of {ls} layers + lm_head at context {context}, median per-layer time x {layers_total} layers"
+
+
+def blas_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args, rank: int, world: int):
+    """The reference's CPU implementation of the path (its numpy path restated in oracle/) on this box's host cores."""
+    if rank != 0:
+        return
+    from oracle import ref_decode as O
+    cfg = O.QWEN3_30B_A3B
+    layers_total = args.layers or cfg["num_hidden_layers"]
+    od = O.dims_from_config(cfg, MODEL, layers=2)
+    W = O.SyntheticWeights(O.Dims(**{**od.__dict__, "V": 8}), seed=0, gamma="ones")
+    rng = np.random.default_rng(1)
+    lm = O.bfr(rng.standard_normal((cfg["vocab_size"], od.H), dtype=np.float32) * np.float32(0.02))
+
+    def layer_w(L):
+        return {k: v for k, v in W.t.items() if k.startswith(f"model.layers.{L}.")}
+    vals = []
+    for i in range(args.warmup + args.steps):
+        ms, sample = oracle_sample(cfg, layers_total, args.prompt, layer_w, lm, W.t["model.norm.weight"], W.t["model.embed_tokens.weight"][0],
+                                   seconds=max(2.0, 60.0 / max(1, args.warmup + args.steps)))
+        if i >= args.warmup:
+            vals.append(ms)
+    v = float(np.median(vals))
+    cores = blas_threads()
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": v, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"{MODEL} decode bs1, context {args.prompt}, {layers_total} layers", "parallelism": "cpu"},
+                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import etx_megakernel_b200  # noqa: F401
+    from etx_megakernel_b200.models import decode as D
+    from etx_megakernel_b200.models import qwen as Q
+    from oracle import ref_decode as O                                     # cpu_baseline leg and the byte ledger only
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    d = Q.load_dims(MODEL, layers=args.layers or None)
+    P, K, Wm = args.prompt, args.steps, args.warmup
+    maxlen = ((P + Wm + K + 40 + 15) // 16) * 16
+    weights = D.random_packed_weights(d, maxlen, dev, seed=rank, gamma="ones")
+    prog = D.DecodeProgram(d, weights, device=local_rank, maxlen=maxlen, steps=maxlen)
+    prompt = np.random.default_rng(1000 + rank).integers(0, d.V, P)
+    # prefill: the prompt token by token through the same kernel (fills the KV caches), plus W warm-up decode steps
+    tin = torch.zeros_like(prog.buf["token_in"]); tin[:P] = torch.tensor(prompt, dtype=torch.int32)
+    prog.buf["token_in"].copy_(tin)
+    t0 = time.perf_counter()
+    for t in range(P + Wm):
+        prog.step(t, t, write_next=t + 1 >= P, wait=(t % 128 == 127))
+    prog.session.wait(120.0)
+    torch.cuda.synchronize(dev)
+    prefill_s = time.perf_counter() - t0
+    # timed region: exactly K steps, back to back, CUDA events on the launching stream, barrier on both sides
+    stream = torch.cuda.Stream(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    with ClockSampler(local_rank) as clk:
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(K):
+                t = P + Wm + i
+                prog.session.set_step(tok=t, pos=t, write_next=1)
+                prog.session.launch(stream.cuda_stream)
+            e1.record(stream)
+        torch.cuda.synchronize(dev)
+        prog.session.wait(120.0)
+        if dist:
+            dist.barrier()
+        dev_ms = e0.elapsed_time(e1) / K
+        # end to end through the host-buffer entry point: the same K positions, token ids through host memory
+        gen_dev = prog.buf["token_out"][P + Wm - 1:P + Wm + K].cpu().numpy()      # argmax of steps P+Wm-1 .. P+Wm+K-1
+        first = int(gen_dev[0])
+        h0 = time.perf_counter()
+        toks_host, ms_host = prog.session.decode_host(np.asarray([first], np.int32), K, P + Wm)
+        host_ms = (time.perf_counter() - h0) * 1e3 / K
+    clocks = clk.summary()
+    same_tokens = bool(np.array_equal(toks_host, gen_dev[1:K + 1]))
+    times = torch.tensor([dev_ms, host_ms], dtype=torch.float64, device=dev)
+    if dist:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, host_ms = float(times[0]), float(times[1])
+    ctx = P + Wm + K // 2
+    ledger = O.step_bytes(O.dims_from_config(O.QWEN3_30B_A3B, MODEL, layers=d.L), ctx)
+    peak, peak_src = measured_peaks()
+    achieved = ledger["total"] / (dev_ms * 1e-3) / 1e9
+    line = {"metric": METRIC, "value": dev_ms / world, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{MODEL} decode bs1, {d.L} layers, prompt {P} random ids fed through the kernel, then greedy",
+                       "context": ctx, "parallelism": "single" if world == 1 else f"replicas x{world}", "norm_gamma": "ones", "l2": "each step streams 6.2 GB (> 126 MB L2)",
+                       "tokens_per_s": 1000.0 / dev_ms * world, "prefill_s": round(prefill_s, 2), "host_tokens_equal_device_tokens": same_tokens},
+            "e2e": {"value": host_ms / world, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "gpu_launches": K, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": ledger["total"], "kernel": "etxb_megakernel"}}
+    if rank == 0 and world == 1 and not args.no_cpu:
+        def layer_w(L):
+            return Q.unpack_layer_hf(d, lambda n: weights[n].view(torch.int16).cpu().numpy().view(np.uint16), L)
+        f = lambda t: (t.view(torch.int16).cpu().numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)     # noqa: E731
+        ms, sample = oracle_sample(O.QWEN3_30B_A3B, d.L, P, layer_w, f(weights["lm_head"]), f(weights["final_norm"]), f(weights["embed"][int(prompt[0])]))
+        line["cpu_baseline"] = {"value": ms, "unit": UNIT, "cores": blas_threads(), "kind": "port", "sample": sample}
+    prog.close()
+    if rank == 0:
+        print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (debugging only; 0 = all 48)")
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    a = ap.parse_args()
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if a.impl == "reference":
+        run_reference(a, rank, world)
+    else:
+        run_ours(a, rank, world, local)
+
+
+if __name__ == "__main__":
+    main()

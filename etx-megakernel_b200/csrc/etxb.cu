@@ -1,0 +1,470 @@
+// Host side of the C ABI declared in include/etxb200.h: plan blob validation and upload, session lifecycle,
+// cooperative launch of the persistent kernel, bounded waiting, status / trace read-back, the host-buffer decode
+// loop and single-tile launches.
+//
+// Takes over the reference's host launcher etx/runtime/include/etx/host.h (setup 79-210, launch 339-347, watchdog
+// wait 351-417, event dump 545-587) and the token loop of examples/vllm_llm/host.hip:819-894.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <chrono>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "../../include/etxb200.h"
+#include "etxb_kernel.cuh"
+
+static_assert(sizeof(etxb_gemv_args) == 160 && offsetof(etxb_gemv_args, grid) == 144, "GEMV block layout (etx/ops/gemv.py:80-94)");
+static_assert(sizeof(etxb_topk_args) == 64 && offsetof(etxb_topk_args, grid) == 48, "top-k block layout (etx/ops/topk.py:16-23)");
+static_assert(sizeof(etxb_attnprep_args) == 112 && offsetof(etxb_attnprep_args, grid) == 96, "attnprep block layout (etx/ops/attnprep.py:11-15)");
+static_assert(sizeof(etxb_attn_args) == 128 && offsetof(etxb_attn_args, grid) == 112, "attention block layout");
+static_assert(sizeof(etxb_task) == 40 && sizeof(etxb_type) == 48, "plan table layouts");
+static_assert(sizeof(etxb_stepv) == sizeof(etxb_step_params), "step parameter layouts must agree");
+
+static thread_local std::string g_err;
+static int32_t fail(int32_t code, const std::string& msg) { g_err = msg; return code; }
+#define CU(call)                                                                                         \
+  do {                                                                                                   \
+    cudaError_t e_ = (call);                                                                             \
+    if (e_ != cudaSuccess) return fail(ETXB_E_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_)); \
+  } while (0)
+
+struct etxb_session {
+  int device = 0;
+  etxb_blob_header h{};
+  std::vector<etxb_blob_tensor> tensors;
+  std::vector<etxb_type> types;
+  std::vector<int32_t> qbegin, evcount, inwords, outwords;
+  std::vector<etxb_task> tasks;
+  std::vector<void*> tensor_ptr;       // device address of every plan tensor (index 0 = argument pool)
+  // device copies
+  etxb_task* d_tasks = nullptr; int32_t* d_qbegin = nullptr; etxb_type* d_types = nullptr; void** d_type_args = nullptr;
+  int32_t* d_events = nullptr; int32_t* d_evcount = nullptr; int32_t* d_inwords = nullptr; int32_t* d_outwords = nullptr;
+  int32_t* d_ctrl = nullptr; uint64_t* d_trace = nullptr; int32_t* d_exec = nullptr; unsigned char* d_pool = nullptr;
+  int32_t* h_ctrl = nullptr;           // pinned mirror
+  int32_t* h_tok = nullptr;            // pinned staging of the host decode loop
+  bool args_dirty = true, trace = false, launched = false;
+  uint32_t epoch = 0;
+  unsigned long long timeout_ns = 2000000000ull;
+  etxb_stepv step{};
+  cudaStream_t stream = nullptr, own_stream = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float last_ms = 0.f;
+  int workers = 0;
+};
+
+static int g_kernel_ready[64];
+
+static int32_t prepare_kernel(int device, int* workers_out) {
+  CU(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, device));
+  if (device < 64 && !g_kernel_ready[device]) {
+    CU(cudaFuncSetAttribute(etxb::etxb_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ETXB_SMEM_BYTES));
+    g_kernel_ready[device] = 1;
+  }
+  int per_sm = 0;
+  CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, etxb::etxb_megakernel, ETXB_THREADS, ETXB_SMEM_BYTES));
+  if (per_sm < 1) return fail(ETXB_E_RESIDENCY, "the persistent CTA does not fit one SM of this device");
+  *workers_out = prop.multiProcessorCount;
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_version(void) { return ETXB_VERSION; }
+extern "C" const char* etxb_last_error(void) { return g_err.c_str(); }
+
+extern "C" int32_t etxb_device_info(int device, etxb_device_info_t* out) {
+  if (!out) return fail(ETXB_E_ARG, "null out");
+  cudaDeviceProp prop;
+  CU(cudaGetDeviceProperties(&prop, device));
+  int workers = 0;
+  int32_t rc = prepare_kernel(device, &workers);
+  if (rc) return rc;
+  out->sm_count = prop.multiProcessorCount; out->smem_per_block_optin = (int32_t)prop.sharedMemPerBlockOptin;
+  out->l2_bytes = prop.l2CacheSize; out->cc_major = prop.major; out->cc_minor = prop.minor;
+  out->workers = workers; out->threads = ETXB_THREADS; out->smem_bytes = ETXB_SMEM_BYTES; out->hbm_bytes = prop.totalGlobalMem;
+  return ETXB_OK;
+}
+
+// ---- plan blob ------------------------------------------------------------------------------------------------
+static size_t al8(size_t x) { return (x + 7) & ~size_t(7); }
+
+static int32_t parse_plan(etxb_session* s, const unsigned char* b, size_t n) {
+  if (n < sizeof(etxb_blob_header)) return fail(ETXB_E_PLAN, "plan blob shorter than its header");
+  memcpy(&s->h, b, sizeof(s->h));
+  const etxb_blob_header& h = s->h;
+  if (h.magic != ETXB_MAGIC) return fail(ETXB_E_PLAN, "plan blob: bad magic");
+  if (h.version != 1) return fail(ETXB_E_PLAN, "plan blob: unsupported version");
+  if (h.n_workers == 0 || h.n_workers > 4096 || h.n_types == 0 || h.n_tensors == 0) return fail(ETXB_E_PLAN, "plan blob: empty tables");
+  size_t off = al8(sizeof(h));
+  auto take = [&](void* dst, size_t bytes) -> bool {
+    if (off + bytes > n) return false;
+    if (bytes) memcpy(dst, b + off, bytes);
+    off = al8(off + bytes);
+    return true;
+  };
+  s->tensors.resize(h.n_tensors); s->types.resize(h.n_types); s->qbegin.resize(h.n_workers + 1); s->tasks.resize(h.n_tasks);
+  s->evcount.resize(h.n_events); s->inwords.resize(h.n_in); s->outwords.resize(h.n_out);
+  std::vector<unsigned char> pool(h.pool_bytes);
+  if (!take(s->tensors.data(), h.n_tensors * sizeof(etxb_blob_tensor)) || !take(s->types.data(), h.n_types * sizeof(etxb_type)) ||
+      !take(s->qbegin.data(), (h.n_workers + 1) * 4) || !take(s->tasks.data(), h.n_tasks * sizeof(etxb_task)) ||
+      !take(s->evcount.data(), h.n_events * 4) || !take(s->inwords.data(), h.n_in * 4) || !take(s->outwords.data(), h.n_out * 4) ||
+      !take(pool.data(), h.pool_bytes))
+    return fail(ETXB_E_PLAN, "plan blob: truncated");
+  // consistency: queues cover every task once, indices in range, arrivals per event == declared count
+  if (s->qbegin[0] != 0 || s->qbegin[h.n_workers] != (int32_t)h.n_tasks) return fail(ETXB_E_PLAN, "plan blob: queues do not cover the task table");
+  for (uint32_t w = 0; w < h.n_workers; ++w)
+    if (s->qbegin[w] > s->qbegin[w + 1]) return fail(ETXB_E_PLAN, "plan blob: queue bounds not monotone");
+  std::vector<int64_t> arrivals(h.n_events, 0);
+  std::vector<char> seen(h.n_tasks, 0);
+  for (const etxb_task& t : s->tasks) {
+    if (t.type < 0 || t.type >= (int32_t)h.n_types) return fail(ETXB_E_PLAN, "plan blob: task type out of range");
+    if (t.id < 0 || t.id >= (int32_t)h.n_tasks || seen[t.id]) return fail(ETXB_E_PLAN, "plan blob: task ids are not a permutation");
+    seen[t.id] = 1;
+    if (t.in_n < 0 || t.out_n < 0 || t.in_off < 0 || t.out_off < 0 || (uint64_t)t.in_off + t.in_n > h.n_in || (uint64_t)t.out_off + t.out_n > h.n_out)
+      return fail(ETXB_E_PLAN, "plan blob: event list out of range");
+    for (int i = 0; i < t.in_n; ++i)
+      if (s->inwords[t.in_off + i] < 0 || s->inwords[t.in_off + i] >= (int32_t)h.n_events) return fail(ETXB_E_PLAN, "plan blob: wait on an unknown event");
+    for (int i = 0; i < t.out_n; ++i) {
+      const int32_t w = s->outwords[t.out_off + i];
+      if (w < 0 || w >= (int32_t)h.n_events) return fail(ETXB_E_PLAN, "plan blob: arrival on an unknown event");
+      ++arrivals[w];
+    }
+  }
+  for (uint32_t e = 0; e < h.n_events; ++e)
+    if (arrivals[e] != s->evcount[e]) {
+      char m[160];
+      snprintf(m, sizeof m, "plan blob: event %u gets %lld arrivals per step but declares %d", e, (long long)arrivals[e], s->evcount[e]);
+      return fail(ETXB_E_PLAN, m);
+    }
+  for (const etxb_task& t : s->tasks)
+    for (int i = 0; i < t.in_n; ++i)
+      if (s->evcount[s->inwords[t.in_off + i]] <= 0) return fail(ETXB_E_PLAN, "plan blob: a task waits on an event nobody arrives on");
+  for (const etxb_type& ty : s->types) {
+    if (ty.body < 0 || ty.body >= ETXB_BODY_COUNT) return fail(ETXB_E_PLAN, "plan blob: unknown tile body");
+    for (int k = 0; k < ETXB_MAX_ARGS; ++k)
+      if (ty.args[k] >= (int32_t)h.n_tensors) return fail(ETXB_E_PLAN, "plan blob: type names an unknown tensor");
+    if (ty.body >= ETXB_BODY_GEMV && ty.args[0] < 0) return fail(ETXB_E_PLAN, "plan blob: tile without an argument tensor");
+  }
+  if (pool.size() != s->tensors[0].bytes) return fail(ETXB_E_PLAN, "plan blob: tensor 0 must be the argument pool");
+  // upload
+  CU(cudaSetDevice(s->device));
+  auto up = [&](void** d, const void* src, size_t bytes) -> cudaError_t {
+    cudaError_t e = cudaMalloc(d, bytes ? bytes : 8);
+    if (e != cudaSuccess) return e;
+    return bytes ? cudaMemcpy(*d, src, bytes, cudaMemcpyHostToDevice) : cudaSuccess;
+  };
+  CU(up((void**)&s->d_tasks, s->tasks.data(), h.n_tasks * sizeof(etxb_task)));
+  CU(up((void**)&s->d_qbegin, s->qbegin.data(), s->qbegin.size() * 4));
+  CU(up((void**)&s->d_types, s->types.data(), h.n_types * sizeof(etxb_type)));
+  CU(up((void**)&s->d_evcount, s->evcount.data(), h.n_events * 4));
+  CU(up((void**)&s->d_inwords, s->inwords.data(), h.n_in * 4));
+  CU(up((void**)&s->d_outwords, s->outwords.data(), h.n_out * 4));
+  CU(up((void**)&s->d_pool, pool.data(), pool.size()));
+  CU(cudaMalloc((void**)&s->d_type_args, (size_t)h.n_types * ETXB_MAX_ARGS * sizeof(void*)));
+  const size_t evbytes = (size_t)(h.n_events ? h.n_events : 1) * ETXB_EV_STRIDE * 4;
+  CU(cudaMalloc((void**)&s->d_events, evbytes));
+  CU(cudaMemset(s->d_events, 0, evbytes));
+  CU(cudaMalloc((void**)&s->d_ctrl, 64));
+  CU(cudaMemset(s->d_ctrl, 0, 64));
+  CU(cudaMallocHost((void**)&s->h_ctrl, 64));
+  CU(cudaMallocHost((void**)&s->h_tok, 64));
+  s->tensor_ptr.assign(h.n_tensors, nullptr);
+  s->tensor_ptr[0] = s->d_pool;
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_create(const void* plan_blob, size_t bytes, int device, etxb_session** out) {
+  if (!plan_blob || !out) return fail(ETXB_E_ARG, "null argument");
+  *out = nullptr;
+  etxb_session* s = new etxb_session();
+  s->device = device;
+  int32_t rc = prepare_kernel(device, &s->workers);
+  if (rc == ETXB_OK) rc = parse_plan(s, (const unsigned char*)plan_blob, bytes);
+  if (rc == ETXB_OK && (int)s->h.n_workers > s->workers) rc = fail(ETXB_E_RESIDENCY, "plan wants more workers than the device has SMs");
+  if (rc == ETXB_OK) {
+    cudaError_t e = cudaStreamCreateWithFlags(&s->own_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&s->ev0);
+    if (e == cudaSuccess) e = cudaEventCreate(&s->ev1);
+    if (e != cudaSuccess) rc = fail(ETXB_E_CUDA, cudaGetErrorString(e));
+  }
+  if (rc != ETXB_OK) { std::string keep = g_err; etxb_destroy(s); g_err = keep; return rc; }
+  *out = s;
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_destroy(etxb_session* s) {
+  if (!s) return ETXB_OK;
+  cudaSetDevice(s->device);
+  if (s->launched) cudaDeviceSynchronize();
+  void* ptrs[] = {s->d_tasks, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
+                  s->d_ctrl, s->d_trace, s->d_exec, s->d_pool};
+  for (void* p : ptrs) if (p) cudaFree(p);
+  if (s->h_ctrl) cudaFreeHost(s->h_ctrl);
+  if (s->h_tok) cudaFreeHost(s->h_tok);
+  if (s->ev0) cudaEventDestroy(s->ev0);
+  if (s->ev1) cudaEventDestroy(s->ev1);
+  if (s->own_stream) cudaStreamDestroy(s->own_stream);
+  delete s;
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_bind(etxb_session* s, const char* name, void* dev_ptr, size_t bytes) {
+  if (!s || !name) return fail(ETXB_E_ARG, "null argument");
+  for (size_t i = 0; i < s->tensors.size(); ++i)
+    if (strncmp(s->tensors[i].name, name, sizeof(s->tensors[i].name)) == 0) {
+      if (bytes < s->tensors[i].bytes) return fail(ETXB_E_ARG, std::string("bind ") + name + ": buffer smaller than the plan's tensor");
+      s->tensor_ptr[i] = dev_ptr;
+      s->args_dirty = true;
+      return ETXB_OK;
+    }
+  return fail(ETXB_E_ARG, std::string("bind: the plan has no tensor named ") + name);
+}
+
+extern "C" int32_t etxb_set_step(etxb_session* s, const etxb_step_params* p) {
+  if (!s || !p) return fail(ETXB_E_ARG, "null argument");
+  memcpy(&s->step, p, sizeof(s->step));
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_set_option(etxb_session* s, const char* key, int64_t value) {
+  if (!s || !key) return fail(ETXB_E_ARG, "null argument");
+  if (!strcmp(key, "timeout_ms")) { s->timeout_ns = (unsigned long long)(value > 0 ? value : 1) * 1000000ull; return ETXB_OK; }
+  if (!strcmp(key, "trace")) {
+    CU(cudaSetDevice(s->device));
+    s->trace = value != 0;
+    if (s->trace && !s->d_trace) {
+      CU(cudaMalloc((void**)&s->d_trace, (size_t)s->h.n_tasks * 32 + 32));
+      CU(cudaMalloc((void**)&s->d_exec, (size_t)s->h.n_tasks * 4 + 4));
+    }
+    return ETXB_OK;
+  }
+  return fail(ETXB_E_ARG, std::string("unknown option ") + key);
+}
+
+static int32_t upload_type_args(etxb_session* s) {
+  std::vector<void*> ta((size_t)s->h.n_types * ETXB_MAX_ARGS, nullptr);
+  for (size_t t = 0; t < s->types.size(); ++t)
+    for (int k = 0; k < ETXB_MAX_ARGS; ++k) {
+      const int idx = s->types[t].args[k];
+      if (idx < 0) continue;
+      if (!s->tensor_ptr[idx]) return fail(ETXB_E_ARG, std::string("tensor not bound: ") + s->tensors[idx].name);
+      ta[t * ETXB_MAX_ARGS + k] = s->tensor_ptr[idx];
+    }
+  CU(cudaMemcpy(s->d_type_args, ta.data(), ta.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  s->args_dirty = false;
+  return ETXB_OK;
+}
+
+static void fill_params(etxb_session* s, etxb_params& p) {
+  p.tasks = s->d_tasks; p.qbegin = s->d_qbegin; p.types = s->d_types; p.type_args = s->d_type_args;
+  p.events = s->d_events; p.evcount = s->d_evcount; p.inwords = s->d_inwords; p.outwords = s->d_outwords;
+  p.ctrl = s->d_ctrl; p.trace = s->trace ? s->d_trace : nullptr; p.exec_count = s->trace ? s->d_exec : nullptr;
+  p.step_dev = nullptr; p.timeout_ns = s->timeout_ns; p.epoch = s->epoch; p.n_workers = (int32_t)s->h.n_workers;
+  p.step = s->step;
+}
+
+static int32_t launch_kernel(const etxb_params& p, int grid, cudaStream_t st) {
+  void* kargs[] = {(void*)&p};
+  CU(cudaLaunchCooperativeKernel((const void*)etxb::etxb_megakernel, dim3(grid), dim3(ETXB_THREADS), kargs, ETXB_SMEM_BYTES, st));
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
+  if (!s) return fail(ETXB_E_ARG, "null session");
+  CU(cudaSetDevice(s->device));
+  if (s->args_dirty) { int32_t rc = upload_type_args(s); if (rc) return rc; }
+  s->stream = cuda_stream ? (cudaStream_t)cuda_stream : s->own_stream;
+  if (s->trace && s->d_exec) CU(cudaMemsetAsync(s->d_exec, 0, (size_t)s->h.n_tasks * 4, s->stream));
+  ++s->epoch;
+  etxb_params p;
+  fill_params(s, p);
+  CU(cudaEventRecord(s->ev0, s->stream));
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream);
+  if (rc) return rc;
+  CU(cudaEventRecord(s->ev1, s->stream));
+  s->launched = true;
+  return ETXB_OK;
+}
+
+static int32_t read_ctrl(etxb_session* s) {
+  CU(cudaMemcpyAsync(s->h_ctrl, s->d_ctrl, 32, cudaMemcpyDeviceToHost, s->stream));
+  CU(cudaStreamSynchronize(s->stream));
+  return ETXB_OK;
+}
+
+// After a failed step the counters are inconsistent: bring every one to epoch * count and clear ctrl, so the next
+// step starts clean (the reference forces a full host reset after a failed step, host.h:388).
+static int32_t recover(etxb_session* s) {
+  std::vector<int32_t> ev((size_t)s->h.n_events * ETXB_EV_STRIDE, 0);
+  for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount[e]);
+  if (!ev.empty()) CU(cudaMemcpy(s->d_events, ev.data(), ev.size() * 4, cudaMemcpyHostToDevice));
+  CU(cudaMemset(s->d_ctrl, 0, 64));
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_wait(etxb_session* s, double timeout_s) {
+  if (!s) return fail(ETXB_E_ARG, "null session");
+  if (!s->launched) return ETXB_OK;
+  CU(cudaSetDevice(s->device));
+  const auto t0 = std::chrono::steady_clock::now();
+  bool aborted = false;
+  for (;;) {
+    cudaError_t q = cudaEventQuery(s->ev1);
+    if (q == cudaSuccess) break;
+    if (q != cudaErrorNotReady) return fail(ETXB_E_CUDA, std::string("kernel failed: ") + cudaGetErrorString(q));
+    const double el = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (!aborted && timeout_s > 0 && el > timeout_s) {             // host watchdog: ask the kernel to stop, keep waiting
+      const int32_t one = ETXB_CTRL_ABORT;
+      cudaStream_t side;
+      CU(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+      CU(cudaMemcpyAsync(s->d_ctrl, &one, 4, cudaMemcpyHostToDevice, side));
+      CU(cudaStreamSynchronize(side));
+      cudaStreamDestroy(side);
+      aborted = true;
+    }
+    if (el > 50e-6) std::this_thread::yield();
+  }
+  CU(cudaEventElapsedTime(&s->last_ms, s->ev0, s->ev1));
+  int32_t rc = read_ctrl(s);
+  if (rc) return rc;
+  s->launched = false;
+  const int32_t c = s->h_ctrl[0];
+  if (c == 0) return ETXB_OK;
+  char m[200];
+  snprintf(m, sizeof m, "step %u stopped: ctrl=%d task=%d event=%d value=%d target=%d", s->epoch, c, s->h_ctrl[1], s->h_ctrl[2], s->h_ctrl[3], s->h_ctrl[4]);
+  std::string msg = m;
+  recover(s);
+  if (c & ETXB_CTRL_BADTASK) return fail(ETXB_E_PLAN, msg);
+  if (c & ETXB_CTRL_TIMEOUT) return fail(ETXB_E_TIMEOUT, msg);
+  return fail(ETXB_E_ABORTED, msg);
+}
+
+extern "C" int32_t etxb_step(etxb_session* s, void* cuda_stream, double timeout_s) {
+  int32_t rc = etxb_launch(s, cuda_stream);
+  if (rc) return rc;
+  return etxb_wait(s, timeout_s);
+}
+
+extern "C" int32_t etxb_status(etxb_session* s, etxb_status_t* out) {
+  if (!s || !out) return fail(ETXB_E_ARG, "null argument");
+  out->ctrl = s->h_ctrl ? s->h_ctrl[0] : 0; out->stuck_task = s->h_ctrl && s->h_ctrl[0] ? s->h_ctrl[1] : -1;
+  out->stuck_event = s->h_ctrl[2]; out->stuck_value = s->h_ctrl[3]; out->stuck_target = s->h_ctrl[4];
+  out->tasks_run = 0; out->epoch = s->epoch; out->last_ms = s->last_ms;
+  if (s->trace && s->d_exec) {
+    std::vector<int32_t> ex(s->h.n_tasks);
+    CU(cudaSetDevice(s->device));
+    CU(cudaMemcpy(ex.data(), s->d_exec, ex.size() * 4, cudaMemcpyDeviceToHost));
+    for (int32_t v : ex) out->tasks_run += v;
+  }
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_trace(etxb_session* s, void* host_buf, size_t bytes) {
+  if (!s || !host_buf) return fail(ETXB_E_ARG, "null argument");
+  if (!s->d_trace) return fail(ETXB_E_ARG, "tracing is off (set option trace=1 before the step)");
+  if (bytes < (size_t)s->h.n_tasks * 32) return fail(ETXB_E_ARG, "trace buffer too small: 32 bytes per task");
+  CU(cudaSetDevice(s->device));
+  CU(cudaMemcpy(host_buf, s->d_trace, (size_t)s->h.n_tasks * 32, cudaMemcpyDeviceToHost));
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_exec_counts(etxb_session* s, int32_t* host_buf, size_t count) {
+  if (!s || !host_buf) return fail(ETXB_E_ARG, "null argument");
+  if (!s->d_exec) return fail(ETXB_E_ARG, "tracing is off (set option trace=1 before the step)");
+  if (count < s->h.n_tasks) return fail(ETXB_E_ARG, "buffer too small: one int32 per task");
+  CU(cudaSetDevice(s->device));
+  CU(cudaMemcpy(host_buf, s->d_exec, (size_t)s->h.n_tasks * 4, cudaMemcpyDeviceToHost));
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_decode_host(etxb_session* s, const int32_t* tokens_in, int32_t n_in, int32_t n_total, int32_t start_pos,
+                                    int32_t* tokens_out, float* step_ms) {
+  if (!s || !tokens_in || !tokens_out || n_in < 1 || n_total < 1) return fail(ETXB_E_ARG, "bad argument");
+  if (!s->step.token_in || !s->step.token_out) return fail(ETXB_E_ARG, "set_step must name token_in / token_out first");
+  CU(cudaSetDevice(s->device));
+  cudaStream_t st = s->own_stream;
+  int32_t next = tokens_in[0];
+  for (int t = 0; t < n_total; ++t) {
+    const int32_t tok = t < n_in ? tokens_in[t] : next;
+    s->h_tok[0] = tok;
+    // slot 0 of token_in / token_out is reused every step: the host owns the sequence
+    CU(cudaMemcpyAsync(s->step.token_in, s->h_tok, 4, cudaMemcpyHostToDevice, st));
+    s->step.tok = 0; s->step.pos = start_pos + t; s->step.write_next = 0;
+    int32_t rc = etxb_launch(s, st);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(s->h_tok + 8, s->step.token_out, 4, cudaMemcpyDeviceToHost, st));
+    rc = etxb_wait(s, 60.0);
+    if (rc) return rc;
+    CU(cudaStreamSynchronize(st));
+    next = s->h_tok[8];
+    tokens_out[t] = next;
+    if (step_ms) step_ms[t] = s->last_ms;
+  }
+  return ETXB_OK;
+}
+
+// ---- single-tile launches ---------------------------------------------------------------------------------------
+struct OpCtx {
+  etxb_task* d_tasks = nullptr; int cap_tasks = 0; int32_t* d_qbegin = nullptr; etxb_type* d_type = nullptr; void** d_targs = nullptr;
+  unsigned char* d_pool = nullptr; size_t cap_pool = 0; int32_t* d_ctrl = nullptr; int32_t* d_events = nullptr; int32_t* d_zero = nullptr;
+  int workers = 0;
+};
+static OpCtx g_op[64];
+
+extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock, size_t bytes, int32_t ntasks,
+                                  const etxb_step_params* step, void* cuda_stream) {
+  if (device < 0 || device >= 64 || body < 0 || body >= ETXB_BODY_COUNT || ntasks < 1) return fail(ETXB_E_ARG, "bad argument");
+  if (body >= ETXB_BODY_GEMV && (!argblock || bytes < 16)) return fail(ETXB_E_ARG, "this tile needs an argument block");
+  OpCtx& c = g_op[device];
+  int32_t rc = prepare_kernel(device, &c.workers);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  if (!c.d_type) {
+    CU(cudaMalloc((void**)&c.d_type, sizeof(etxb_type))); CU(cudaMalloc((void**)&c.d_targs, ETXB_MAX_ARGS * sizeof(void*)));
+    CU(cudaMalloc((void**)&c.d_qbegin, 4097 * 4)); CU(cudaMalloc((void**)&c.d_ctrl, 64)); CU(cudaMemset(c.d_ctrl, 0, 64));
+    CU(cudaMalloc((void**)&c.d_events, ETXB_EV_STRIDE * 4)); CU(cudaMemset(c.d_events, 0, ETXB_EV_STRIDE * 4));
+    CU(cudaMalloc((void**)&c.d_zero, 64)); CU(cudaMemset(c.d_zero, 0, 64));
+  }
+  if (ntasks > c.cap_tasks) {
+    if (c.d_tasks) { CU(cudaStreamSynchronize(st)); CU(cudaFree(c.d_tasks)); }
+    c.cap_tasks = ntasks + 1024;
+    CU(cudaMalloc((void**)&c.d_tasks, (size_t)c.cap_tasks * sizeof(etxb_task)));
+  }
+  const size_t need = bytes ? bytes : 16;
+  if (need > c.cap_pool) {
+    if (c.d_pool) { CU(cudaStreamSynchronize(st)); CU(cudaFree(c.d_pool)); }
+    c.cap_pool = need + 4096;
+    CU(cudaMalloc((void**)&c.d_pool, c.cap_pool));
+  }
+  const int W = c.workers;
+  std::vector<etxb_task> tasks(ntasks);
+  std::vector<int32_t> qb(W + 1, 0);
+  // worker w runs tasks w, w + W, ...: store grouped by worker
+  int n = 0;
+  for (int w = 0; w < W; ++w) {
+    qb[w] = n;
+    for (int t = w; t < ntasks; t += W) {
+      etxb_task& k = tasks[n++];
+      memset(&k, 0, sizeof k);
+      k.type = 0; k.coord[0] = t; k.id = t;
+    }
+  }
+  qb[W] = n;
+  etxb_type ty; memset(&ty, 0, sizeof ty);
+  ty.body = body; for (int k = 0; k < ETXB_MAX_ARGS; ++k) ty.args[k] = -1; ty.args[0] = 0;
+  void* targs[ETXB_MAX_ARGS] = {c.d_pool, nullptr, nullptr, nullptr};
+  CU(cudaMemcpyAsync(c.d_tasks, tasks.data(), tasks.size() * sizeof(etxb_task), cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c.d_qbegin, qb.data(), qb.size() * 4, cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c.d_type, &ty, sizeof ty, cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c.d_targs, targs, sizeof targs, cudaMemcpyHostToDevice, st));
+  if (bytes) CU(cudaMemcpyAsync(c.d_pool, argblock, bytes, cudaMemcpyHostToDevice, st));
+  etxb_params p; memset(&p, 0, sizeof p);
+  p.tasks = c.d_tasks; p.qbegin = c.d_qbegin; p.types = c.d_type; p.type_args = c.d_targs; p.events = c.d_events;
+  p.evcount = c.d_zero; p.inwords = c.d_zero; p.outwords = c.d_zero; p.ctrl = c.d_ctrl; p.timeout_ns = 2000000000ull; p.epoch = 1;
+  p.n_workers = W;
+  if (step) memcpy(&p.step, step, sizeof(p.step));
+  return launch_kernel(p, W, st);
+}

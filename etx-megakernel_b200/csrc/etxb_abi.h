@@ -1,0 +1,131 @@
+// Device/host shared layouts of the B200 decode megakernel: plan blob, task table, kernel parameters and the
+// argument blocks of the built-in tiles.
+//
+// The task descriptor {type, coord[4]} and the idea of per-worker static queues follow the reference runtime ABI
+// (etx/runtime/include/etx/abi.h:33-41, 77-80); the event protocol does not: counters here only ever count UP and a
+// consumer of step `epoch` waits for `epoch * arrivals_per_step`, so nothing is reset between steps (the reference
+// re-initialises every counter per step, etx/runtime/include/etx/host.h:264-325).
+#pragma once
+#include <stdint.h>
+
+#define ETXB_EV_STRIDE 32            // int32 words between event counters: one 128-byte line each (abi.h:7-12)
+#define ETXB_THREADS 512             // threads of one persistent CTA (16 warps)
+#define ETXB_NWARPS (ETXB_THREADS / 32)
+#define ETXB_MAX_ARGS 4              // tensor pointers a task type may name (Graph.call_device(args=[...]))
+#define ETXB_XS_FLOATS 40960         // staged activations: nb * K floats at most (160 KB)
+#define ETXB_SCRATCH_FLOATS 6144     // partial sums, top-k scratch, reductions (24 KB)
+#define ETXB_SMEM_BYTES ((ETXB_XS_FLOATS + ETXB_SCRATCH_FLOATS) * 4)
+#define ETXB_ATTN_PART 32            // KV positions per attention task
+#define ETXB_MAX_NB 8                // activation columns served by one weight read in the FMA GEMV
+
+// ---- plan blob ------------------------------------------------------------------------------------------------
+// header, then sections in this order, each starting on an 8-byte boundary:
+//   tensors   n_tensors x etxb_blob_tensor
+//   types     n_types   x etxb_type
+//   qbegin    (n_workers + 1) x int32       tasks are stored grouped by worker: worker w owns [qbegin[w], qbegin[w+1])
+//   tasks     n_tasks   x etxb_task
+//   evcount   n_events  x int32             arrivals one step delivers to each event counter
+//   inwords   n_in      x int32             event indices, referenced by etxb_task.in_off / in_n
+//   outwords  n_out     x int32
+//   pool      pool_bytes                    argument blocks (tensor 0, "impargs"), device pointers already inside
+#define ETXB_MAGIC 0x3030324258544555ull   // "UETXB200" little endian
+struct etxb_blob_header {
+  uint64_t magic;
+  uint32_t version, n_workers, n_tasks, n_types, n_events, n_in, n_out, n_tensors, pool_bytes, flags;
+  uint32_t reserved[4];
+};
+struct etxb_blob_tensor { char name[56]; uint64_t bytes; };
+
+struct etxb_type {
+  int32_t body;                 // ETXB_BODY_*
+  int32_t cst[4];               // TaskGrid.consts: cst[0] = byte offset of the grid's argument block in args[0]
+  int32_t args[ETXB_MAX_ARGS];  // plan tensor indices, -1 = unused
+  int32_t flags;                // bit0: prefetch hint allowed
+  int32_t pad[2];
+};
+
+struct etxb_task {
+  int32_t type;
+  int32_t coord[4];
+  int32_t in_off, in_n;         // events to wait for
+  int32_t out_off, out_n;       // events to arrive on
+  int32_t id;                   // index in program (graph) order, for traces and diagnostics
+};
+
+// ---- step parameters (the reference's VlParams, examples/vllm_llm/vl_tiles.hip:13-24) ---------------------------
+struct etxb_stepv {
+  int32_t tok, pos, write_next, H, V, nrep;
+  const void* embed; void* resid; int64_t* positions; int32_t* seq_lens; int64_t* slot_mapping;
+  const void* logits; int32_t* token_in; int32_t* token_out; uint64_t* token_time;
+};
+
+// ---- kernel parameters --------------------------------------------------------------------------------------
+struct etxb_params {
+  const etxb_task* tasks;
+  const int32_t* qbegin;
+  const etxb_type* types;
+  void* const* type_args;       // [n_types][ETXB_MAX_ARGS] device pointers
+  int32_t* events;              // counters, ETXB_EV_STRIDE words apart
+  const int32_t* evcount;
+  const int32_t* inwords;
+  const int32_t* outwords;
+  int32_t* ctrl;                // [0] status bits, [1] stuck task, [2] stuck event, [3] value, [4] target, [5] tasks run
+  uint64_t* trace;              // 4 x u64 per task (by task id) or null
+  int32_t* exec_count;          // per task id or null
+  const int32_t* step_dev;      // optional {tok, pos} pair in device memory overriding step.tok/pos (host decode loop)
+  unsigned long long timeout_ns;
+  uint32_t epoch;
+  int32_t n_workers;
+  etxb_stepv step;
+};
+
+// ctrl[0] bits
+#define ETXB_CTRL_ABORT 1
+#define ETXB_CTRL_TIMEOUT 2
+#define ETXB_CTRL_BADTASK 4
+
+// ---- argument blocks ----------------------------------------------------------------------------------------
+// GEMV family: byte for byte the reference's 160-byte block (etx/ops/gemv.py:80-94), grid words at 144.
+struct etxb_gemv_args {
+  const void* W; const void* x; void* out; const int32_t* ids; const float* wts; int64_t estride;   // 0..47
+  int32_t M, K, rpt, tpe;                                                                         // 48..63
+  const void* rows; const void* resid_in; void* resid_out; const void* ln;                        // 64..95
+  int32_t R; float eps; int32_t mode; int32_t E; const void* logits;                              // 96..119
+  int32_t nb, sx, sout, srows, srin, srout;                                                       // 120..143
+  uint32_t grid[3], nblocks;                                                                      // 144..159
+};
+// mode bits of the GEMV family.  0 plain; 1 norm fold (x = rmsnorm(bf16(resid_in + sum of R rows)), task 0 stores
+// resid_out and x); 2 / 3 top-k fold without / with renormalisation (etx/ops/gemv.py:75-79).  Extensions used by the
+// B200 builder: 0x100 bf16-round the routing weights (the oracle's numerics), 0x200 add a bf16 bias row taken from
+// `wts` (plain form only; the reference passes biases through its DSL_EXT block).
+#define ETXB_MODE_NORM 1
+#define ETXB_MODE_TOPK 2
+#define ETXB_MODE_TOPK_RENORM 3
+#define ETXB_MODE_BF16_WTS 0x100
+#define ETXB_MODE_BIAS 0x200
+
+// top-k: the reference's 64-byte block (etx/ops/topk.py:16-23), grid words at 48.
+struct etxb_topk_args {
+  const void* logits; float* wts; int32_t* ids; int32_t* tei; int32_t E, K, mode, nbsv;
+  uint32_t grid[3], nblocks;
+};
+
+// attention prep: the reference's 112-byte block (etx/ops/attnprep.py:11-15), grid words at 96.
+struct etxb_attnprep_args {
+  void* qkv; const void* qw; const void* kw; const void* cos_sin; const int64_t* positions; void* kc; void* vc;
+  const int64_t* slot_mapping; int32_t NH, NKV, HD; float eps; int32_t BS, X; int32_t pad[2];
+  uint32_t grid[3], nblocks;
+};
+
+// decode attention + reduce (the reference imports vLLM's kernels for these: importer/spec.py:243-244; this block is
+// this library's own): q rows are read from `q` with `q_stride` elements between heads.
+struct etxb_attn_args {
+  const void* q; const void* kc; const void* vc; const int32_t* block_tables; const int32_t* seq_lens;   // 0..39
+  float* exp_sums; float* max_logits; float* tmp_out; void* out;                                         // 40..71
+  float scale; int32_t NH, NKV, HD, BS, X, max_parts, max_blocks;                                        // 72..103
+  int32_t pad[2];                                                                                        // 104..111
+  uint32_t grid[3], nblocks;                                                                             // 112..127
+};
+
+// split-K demo (etx/operators/splitk_sum.py): parts[i][j] = sum of a chunk, out[i] = sum over j.
+struct etxb_splitk_args { const float* in; float* parts; float* out; int32_t rows, cols, chunks, pad; uint32_t grid[3], nblocks; };

@@ -1,0 +1,157 @@
+// The persistent kernel: one CTA per SM walks its static task queue; per task it waits for the task's events
+// (acquire, bounded), runs the tile body, drains its stores and arrives on the out events (release).
+//
+// Takes over the generated kernel of the reference: worker loop etx/codegen/kernel.py:517-572, the three-phase
+// etx_run_task kernel.py:341-468, and the native prologue / argmax tiles examples/vllm_llm/vl_tiles.hip:31-89.
+#pragma once
+#include "etxb_attn.cuh"
+#include "etxb_gemv.cuh"
+#include "etxb_prims.cuh"
+
+namespace etxb {
+
+// resid <- embedding row of token_in[t] (nrep copies), positions / seq_lens / slot_mapping <- pos (identity block table)
+__device__ __forceinline__ void tile_prologue(const etxb_stepv& S) {
+  const int t = S.tok;
+  if (tidx() == 0) {
+    if (S.token_time) S.token_time[2 * t] = globaltimer();
+    S.positions[0] = S.pos; S.seq_lens[0] = S.pos + 1; S.slot_mapping[0] = S.pos;
+  }
+  const int id = __ldcg(S.token_in + t);
+  const uint4* src = (const uint4*)((const __nv_bfloat16*)S.embed + (size_t)id * S.H);
+  uint4* dst = (uint4*)S.resid;
+  const int n8 = S.H / 8;
+  for (int i = tidx(); i < n8 * S.nrep; i += blockDim.x) dst[i] = __ldg(src + i % n8);
+}
+
+// greedy sampling: first maximum of the bf16 logits (ties -> lower index, like argmax over float32)
+__device__ __forceinline__ void tile_argmax(const etxb_stepv& S, const Smem& sm) {
+  float bv = -INFINITY; int bi = 0x7fffffff;
+  const uint4* lg4 = (const uint4*)S.logits;
+  const int n4 = S.V / 8;
+  auto scan = [&](const uint4 w, int base) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float lo = bf_lo(u[k]), hi = bf_hi(u[k]);
+      if (lo > bv) { bv = lo; bi = base + 2 * k; }
+      if (hi > bv) { bv = hi; bi = base + 2 * k + 1; }
+    }
+  };
+  int j = tidx();
+  const int B = blockDim.x;
+  for (; j + 3 * B < n4; j += 4 * B) {
+    const uint4 a0 = ld_act16(lg4 + j), a1 = ld_act16(lg4 + j + B), a2 = ld_act16(lg4 + j + 2 * B), a3 = ld_act16(lg4 + j + 3 * B);
+    scan(a0, 8 * j); scan(a1, 8 * (j + B)); scan(a2, 8 * (j + 2 * B)); scan(a3, 8 * (j + 3 * B));
+  }
+  for (; j < n4; j += B) scan(ld_act16(lg4 + j), 8 * j);
+  for (int i = 8 * n4 + tidx(); i < S.V; i += B) {
+    const float v = ld_bf(S.logits, i);
+    if (v > bv) { bv = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  float* sv = sm.scr; int* si = (int*)(sm.scr + 32);
+  if ((tidx() & 31) == 0) { sv[tidx() >> 5] = bv; si[tidx() >> 5] = bi; }
+  __syncthreads();
+  if (tidx() == 0) {
+    for (int w = 1; w < ETXB_NWARPS; ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    const int t = S.tok;
+    S.token_out[t] = bi;
+    if (S.write_next) S.token_in[t + 1] = bi;
+    if (S.token_time) S.token_time[2 * t + 1] = globaltimer();
+  }
+}
+
+// protocol demo (etx/operators/splitk_sum.py:10-33): parts[i][j] = sum of chunk j of row i; out[i] = sum_j parts[i][j]
+__device__ __forceinline__ void tile_splitk_part(const unsigned char* a, int i, int j, const Smem& sm) {
+  const etxb_splitk_args& d = *(const etxb_splitk_args*)a;
+  const int w = d.cols / d.chunks;
+  float s = 0.f;
+  for (int c = tidx(); c < w; c += blockDim.x) s += __ldcg(d.in + (size_t)i * d.cols + j * w + c);
+  s = block_sum(s, sm.scr);
+  if (tidx() == 0) d.parts[i * d.chunks + j] = s;
+}
+__device__ __forceinline__ void tile_splitk_sum(const unsigned char* a, int i) {
+  const etxb_splitk_args& d = *(const etxb_splitk_args*)a;
+  if (tidx() == 0) {
+    float s = 0.f;
+    for (int j = 0; j < d.chunks; ++j) s += __ldcg(d.parts + i * d.chunks + j);
+    d.out[i] = s;
+  }
+}
+
+// Run the body of task `cur`.  Everything it needs is re-read from the task table here, so that nothing but the
+// queue cursor stays live in registers across a tile (the tiles want the whole register file for their loads).
+__device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Smem& sm0) {
+  const Smem sm = sm0;
+  const etxb_task* t = p.tasks + cur;
+  const int type = t->type, c0 = t->coord[0], c1 = t->coord[1];
+  const etxb_type* ty = p.types + type;
+  const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)c1 * ty->cst[1];
+  switch (ty->body) {
+    case 0: break;
+    case 1: tile_prologue(p.step); break;
+    case 2: tile_argmax(p.step, sm); break;
+    case 3: tile_gemv(args, c0, sm); break;
+    case 4: tile_moe_up(args, c0, sm); break;
+    case 5: tile_moe_down(args, c0, sm); break;
+    case 6: tile_topk(args, c0, sm); break;
+    case 7: tile_attnprep(args, c0, sm); break;
+    case 8: tile_attn(args, c0, sm); break;
+    case 9: tile_attn_reduce(args, c0, sm); break;
+    case 10: tile_splitk_part(args, c0, c1, sm); break;
+    case 11: tile_splitk_sum(args, c0); break;
+    default:
+      if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);
+      break;
+  }
+}
+
+__global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_constant__ etxb_params p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int s_stop;
+  __shared__ unsigned long long s_deadline;
+  Smem sm;
+  sm.xs = (float*)smem_raw;
+  sm.scr = sm.xs + ETXB_XS_FLOATS;
+  if (threadIdx.x == 0) { s_stop = 0; s_deadline = globaltimer() + p.timeout_ns; }
+  __syncthreads();
+  if ((int)blockIdx.x >= p.n_workers) return;
+  const int q1 = p.qbegin[blockIdx.x + 1];
+  for (int cur = p.qbegin[blockIdx.x]; cur < q1; ++cur) {
+    if (threadIdx.x == 0) {
+      const etxb_task* t = p.tasks + cur;
+      const int in_off = t->in_off, in_n = t->in_n;
+      if (p.trace) p.trace[4 * (size_t)t->id] = globaltimer();
+      bool ok = ld_relaxed(p.ctrl) == 0;
+      for (int i = 0; ok && i < in_n; ++i) {
+        const int word = p.inwords[in_off + i];
+        ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)p.evcount[word]), cur, s_deadline);
+      }
+      if (!ok) s_stop = 1;
+      if (p.trace) p.trace[4 * (size_t)t->id + 1] = globaltimer();
+    }
+    __syncthreads();
+    if (s_stop) break;
+    run_body(p, cur, sm);
+    __syncthreads();                                               // every thread's stores are issued
+    if (threadIdx.x == 0) {
+      const etxb_task* t = p.tasks + cur;
+      const int out_off = t->out_off, out_n = t->out_n, id = t->id;
+      if (out_n > 0) {
+        __threadfence();                                           // ... and ordered before the arrivals at GPU scope
+        for (int i = 0; i < out_n; ++i) red_release_add(p.events + (size_t)p.outwords[out_off + i] * ETXB_EV_STRIDE, 1);
+      }
+      if (p.trace) { p.trace[4 * (size_t)id + 2] = globaltimer(); p.trace[4 * (size_t)id + 3] = blockIdx.x; }
+      if (p.exec_count) atomicAdd(p.exec_count + id, 1);
+    }
+  }
+}
+
+}  // namespace etxb

@@ -1,0 +1,172 @@
+"""Machine model: the data passes and model builders read (never the arch name).
+
+Same accessor surface as the reference's MachineModel (etx/machine/model.py:43-165: load_machine, effective_scope,
+vis, total_cus, cost accessors); the B200 entry adds what sizes the decode tiles: persistent CTA shape, the GEMV task
+split and the attention partition.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any
+
+import yaml
+
+from ..ir.types import Scope
+
+ARCH_DIR = Path(__file__).parent / "arch"
+
+
+@dataclass
+class ExecDomain:
+    name: str
+    count: int
+    cus: int
+    l2_mb: float = 0.0
+
+
+@dataclass
+class Visibility:
+    release: list
+    acquire: list
+    poll: str
+    arrive: str
+    memory: str = "any"
+    acquire_relaxed: list | None = None
+
+
+@dataclass
+class MachineModel:
+    name: str
+    family: str
+    vendor: str
+    wave_size: int
+    devices_per_package: int
+    exec_domains: list
+    shared_cache: dict
+    resources: dict
+    bandwidth: dict
+    visibility: dict
+    capabilities: dict
+    costs: dict
+    lowering: dict = field(default_factory=dict)
+    primitives: dict = field(default_factory=dict)
+    notes: list = field(default_factory=list)
+    extra: dict = field(default_factory=dict)
+
+    # ---- topology
+    @property
+    def leaf_domain(self) -> ExecDomain:
+        return self.exec_domains[-1]
+
+    @property
+    def num_domains(self) -> int:
+        n = 1
+        for d in self.exec_domains:
+            n *= d.count
+        return n
+
+    @property
+    def has_domain_level(self) -> bool:
+        return self.num_domains > 1
+
+    def cus_per_domain(self) -> int:
+        return self.leaf_domain.cus
+
+    def total_cus(self) -> int:
+        return self.num_domains * self.cus_per_domain()
+
+    # ---- scopes
+    def effective_scope(self, scope: Scope) -> Scope:
+        s = scope
+        if s == Scope.CLUSTER and not self.capabilities.get("cluster_launch", False):
+            s = Scope.DOMAIN
+        if s in (Scope.DOMAIN, Scope.WORKGROUP) and not self.has_domain_level:
+            s = Scope.DEVICE
+        elif s == Scope.WORKGROUP:
+            s = Scope.DOMAIN
+        return s
+
+    def vis(self, scope: Scope) -> Visibility:
+        s = self.effective_scope(scope)
+        if s not in self.visibility:
+            raise KeyError(f"{self.name}: no visibility entry for scope {s.name}")
+        return self.visibility[s]
+
+    def memory_for(self, scope: Scope) -> str:
+        m = self.vis(scope).memory
+        return "device" if m == "any" else m
+
+    # ---- costs (microseconds)
+    def t_sync_us(self, scope: Scope) -> float:
+        s = self.effective_scope(scope)
+        key = {Scope.DOMAIN: "t_local_ns", Scope.DEVICE: "t_cross_ns", Scope.SYSTEM: "t_dev_ns"}.get(s, "t_cross_ns")
+        if s == Scope.DEVICE and not self.has_domain_level:
+            key = "t_local_ns"
+        v = self.costs.get(key)
+        if v is None:
+            v = {"t_local_ns": 200, "t_cross_ns": 800, "t_dev_ns": 10000}[key]
+            self.notes.append(f"cost {key} uncalibrated on {self.name}; using {v} ns")
+            self.costs[key] = v
+        return float(v) / 1000.0
+
+    def t_pop_us(self) -> float:
+        return float(self.costs.get("t_pop_ns", 300)) / 1000.0
+
+    def t_push_us(self, cross_domain: bool) -> float:
+        return float(self.costs.get("t_push_ns", 300)) / 1000.0 + (self.t_sync_us(Scope.DEVICE) if cross_domain else 0.0)
+
+    def cache_bw_bytes_per_us(self) -> float:
+        return float(self.bandwidth.get("cache_bw_tbs", self.bandwidth["hbm_tbs"])) * 1e6
+
+    def hbm_bw_bytes_per_us(self) -> float:
+        return float(self.bandwidth["hbm_tbs"]) * 1e6
+
+    def supports(self, cap: str) -> Any:
+        return self.capabilities.get(cap, False)
+
+    # ---- tile sizing for the persistent decode kernel
+    def workers(self) -> int:
+        """Persistent CTAs: one per SM (the whole shared memory and register file of the SM belong to one CTA)."""
+        return self.total_cus()
+
+    def gemv_tasks(self, rows: int, waves: int = 1, min_rows: int = 1) -> tuple[int, int]:
+        """(tasks, rows per task) of a row-split GEMV: `waves` tasks per worker, rows spread as evenly as the
+        reference's blk * rpt mapping allows (etx/ops/gemv.py BODIES: r0 = blk * rpt)."""
+        want = max(1, self.workers() * waves)
+        rpt = max(min_rows, -(-rows // want))
+        return -(-rows // rpt), rpt
+
+    def attention_part(self) -> int:
+        """KV positions per attention task.  32 positions x 4 kv heads fills the SMs at a 1K context and keeps one
+        task's K and V (2 x 8 KB at head_dim 128) a single round trip."""
+        return 32
+
+
+def _visibility(raw: dict) -> dict:
+    return {Scope[k.upper()]: Visibility(release=list(v.get("release", [])), acquire=list(v.get("acquire", [])), poll=v["poll"],
+                                         arrive=v["arrive"], memory=v.get("memory", "any"),
+                                         acquire_relaxed=list(v["acquire_relaxed"]) if "acquire_relaxed" in v else None)
+            for k, v in raw.items()}
+
+
+def list_archs() -> list:
+    return sorted(p.stem for p in ARCH_DIR.glob("*.yaml"))
+
+
+def load_machine(name_or_path) -> MachineModel:
+    p = Path(name_or_path)
+    if not p.exists():
+        p = ARCH_DIR / f"{name_or_path}.yaml"
+    if not p.exists():
+        raise FileNotFoundError(f"no machine model {name_or_path!r}; known: {list_archs()}")
+    raw = yaml.safe_load(p.read_text(encoding="utf-8"))
+    known = {"name", "family", "vendor", "wave_size", "devices_per_package", "exec_domains", "shared_cache", "resources",
+             "bandwidth", "visibility", "capabilities", "costs", "lowering", "primitives", "notes"}
+    return MachineModel(name=raw["name"], family=raw["family"], vendor=raw["vendor"], wave_size=int(raw["wave_size"]),
+                        devices_per_package=int(raw.get("devices_per_package", 1)),
+                        exec_domains=[ExecDomain(**d) for d in raw["exec_domains"]], shared_cache=raw.get("shared_cache", {}),
+                        resources=raw["resources"], bandwidth=raw["bandwidth"], visibility=_visibility(raw["visibility"]),
+                        capabilities=raw.get("capabilities", {}), costs=dict(raw.get("costs", {})), lowering=raw.get("lowering", {}),
+                        primitives=dict(raw.get("primitives", {})), notes=list(raw.get("notes", [])),
+                        extra={k: v for k, v in raw.items() if k not in known})

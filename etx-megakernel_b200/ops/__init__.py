@@ -1,0 +1,9 @@
+"""Built-in tiles of the B200 megakernel as ETX ops (argument-block layouts + export tables)."""
+from . import attn, attnprep, gemv, topk
+
+
+def all_entries() -> dict:
+    out = {}
+    for m in (gemv, topk, attnprep, attn):
+        out.update(m.import_entries())
+    return out

@@ -1,0 +1,55 @@
+"""The streaming bf16 GEMV family as an ETX op: argument-block layout and export table.
+
+The layout is the reference's, byte for byte (etx/ops/gemv.py:80-94: 25 parameters, 160 bytes, grid words at 144, type
+string "pppppliiiippppifiipiiiiii"), so a host that fills blocks for the reference's dsl_gemv / dsl_moe_up / dsl_moe_down
+tiles fills them for the sm_100a tiles unchanged.  The tile bodies are CUDA (csrc/etxb_gemv.cuh), not generated text.
+
+Forms:
+  dsl_gemv[_fold]       out[r] = bf16(W[r,:] . x)  rows [blk*rpt, ...) of W [M, K]; fold: x = rmsnorm(bf16(resid + rows))
+  dsl_moe_up[_fold]     act[s, r] = bf16(bf16(silu(bf16 g)) * bf16 u), expert e = ids[s]; fold: top-k recomputed in-tile
+  dsl_moe_down[_fold]   out[s, r] = bf16(bf16(W_e[r,:] . act_s) * wts[s])
+mode: 0 plain, 1 norm fold, 2 / 3 top-k fold without / with renormalisation; | 0x100 bf16 routing weights (the numerics
+of the reference's CPU path), | 0x200 bf16 bias row passed in `wts` (plain form).
+"""
+from __future__ import annotations
+
+from ._layout import entry
+
+ARG_BYTES, GRID_OFF = 160, 144
+PARAMS = [("W", "ptr addrspace(1)", 0, 8), ("x", "ptr addrspace(1)", 8, 8), ("out", "ptr addrspace(1)", 16, 8),
+          ("ids", "ptr addrspace(1)", 24, 8), ("wts", "ptr addrspace(1)", 32, 8), ("estride", "i64", 40, 8),
+          ("M", "i32", 48, 4), ("K", "i32", 52, 4), ("rpt", "i32", 56, 4), ("tpe", "i32", 60, 4),
+          ("rows", "ptr addrspace(1)", 64, 8), ("resid_in", "ptr addrspace(1)", 72, 8), ("resid_out", "ptr addrspace(1)", 80, 8),
+          ("ln", "ptr addrspace(1)", 88, 8), ("R", "i32", 96, 4), ("eps", "float", 100, 4), ("mode", "i32", 104, 4),
+          ("E", "i32", 108, 4), ("logits", "ptr addrspace(1)", 112, 8),
+          ("nb", "i32", 120, 4), ("sx", "i32", 124, 4), ("sout", "i32", 128, 4), ("srows", "i32", 132, 4),
+          ("srin", "i32", 136, 4), ("srout", "i32", 140, 4)]
+FORMS = {"dsl_gemv": "plain", "dsl_moe_up": "silu_mul", "dsl_moe_down": "scale",
+         "dsl_gemv_fold": "plain", "dsl_moe_up_fold": "silu_mul", "dsl_moe_down_fold": "scale"}
+MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS = 1, 2, 3, 0x100, 0x200
+THREADS = 512
+XS_FLOATS = 40960          # staged activation floats per CTA: nb * K must fit
+MAX_ROWS_UP = 2560         # gate+up rows one moe_up task can hold in its scratch
+NB_ALLOWED = (1, 2, 4, 8)
+
+
+def type_string() -> str:
+    return "".join({"ptr addrspace(1)": "p", "i64": "l", "i32": "i", "float": "f"}[ty] for _, ty, _, _ in PARAMS)
+
+
+def import_entries(threads: int = THREADS) -> dict:
+    return {e: entry(e, form, PARAMS, ARG_BYTES, GRID_OFF, threads, f"ETX DSL GEMV ({form})") for e, form in FORMS.items()}
+
+
+def check_shape(export: str, *, M: int, K: int, rpt: int, nb: int = 1) -> None:
+    """Host-side guard of what the CUDA tiles support; raises before anything is packed."""
+    if K % 8:
+        raise ValueError(f"{export}: K={K} must be a multiple of 8 (16-byte weight vectors)")
+    if max(nb, 1) not in NB_ALLOWED:
+        raise ValueError(f"{export}: nb={nb} activation columns; supported {NB_ALLOWED}")
+    if max(nb, 1) * ((K + 7) // 8 * 8) > XS_FLOATS:
+        raise ValueError(f"{export}: nb*K={max(nb, 1) * K} exceeds the {XS_FLOATS}-float activation stage")
+    if FORMS[export] == "silu_mul" and rpt > MAX_ROWS_UP:
+        raise ValueError(f"{export}: rpt={rpt} rows per task exceeds {MAX_ROWS_UP}")
+    if rpt < 1 or M < 1:
+        raise ValueError(f"{export}: M and rpt must be positive")

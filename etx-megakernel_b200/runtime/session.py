@@ -1,0 +1,94 @@
+"""Session host: plan -> device session -> steps.  The Python face of the C ABI, shaped after the reference's
+etx_host lifecycle (etx/runtime/include/etx/host.h:518-531: setup once, then run = reset + launch + wait per step;
+here a step is launch + wait, nothing is reset).
+
+Buffers are torch tensors owned by the caller; only raw device pointers cross the boundary.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib as L
+
+
+class Session:
+    def __init__(self, plan, tensors: dict, pool: bytes, device: int = 0, pool_name: str = "impargs"):
+        """plan: passes.Plan.  tensors: name -> torch tensor (device memory) for every tensor the graph's grids name in
+        args=[...] except the argument pool, whose bytes are `pool` (uploaded by the library)."""
+        self.plan, self.device = plan, device
+        self.lib = L.load()
+        named = [(pool_name, len(pool))] + [(n, t.numel() * t.element_size()) for n, t in tensors.items()]
+        blob = plan.to_blob(named, pool)
+        self._h = C.c_void_p()
+        L.check(self.lib.etxb_create(blob, len(blob), device, C.byref(self._h)))
+        self._keep = dict(tensors)
+        for n, t in tensors.items():
+            L.check(self.lib.etxb_bind(self._h, n.encode(), C.c_void_p(t.data_ptr()), t.numel() * t.element_size()))
+        self.step_params = L.StepParams()
+
+    # -- lifecycle
+    def close(self):
+        if getattr(self, "_h", None):
+            self.lib.etxb_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_option(self, key: str, value: int):
+        L.check(self.lib.etxb_set_option(self._h, key.encode(), int(value)))
+
+    def set_step(self, **fields):
+        for k, v in fields.items():
+            if hasattr(v, "data_ptr"):
+                v = v.data_ptr()
+            setattr(self.step_params, k, v)
+        L.check(self.lib.etxb_set_step(self._h, C.byref(self.step_params)))
+
+    def launch(self, stream: int | None = None):
+        L.check(self.lib.etxb_launch(self._h, C.c_void_p(stream or 0)))
+
+    def wait(self, timeout_s: float = 60.0):
+        L.check(self.lib.etxb_wait(self._h, float(timeout_s)))
+
+    def run(self, timeout_s: float = 60.0, stream: int | None = None) -> bool:
+        """One step: launch + bounded wait.  Raises EtxbError on a failed step (the reference returns False and prints)."""
+        L.check(self.lib.etxb_step(self._h, C.c_void_p(stream or 0), float(timeout_s)))
+        return True
+
+    def status(self) -> L.Status:
+        st = L.Status()
+        L.check(self.lib.etxb_status(self._h, C.byref(st)))
+        return st
+
+    def trace(self) -> np.ndarray:
+        """[n_tasks][4] uint64: taken, deps ready, body done (globaltimer ns), worker; rows in program order."""
+        out = np.zeros((len(self.plan.tasks), 4), np.uint64)
+        L.check(self.lib.etxb_trace(self._h, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
+    def exec_counts(self) -> np.ndarray:
+        out = np.zeros(len(self.plan.tasks), np.int32)
+        L.check(self.lib.etxb_exec_counts(self._h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
+    def decode_host(self, tokens_in, n_total: int, start_pos: int = 0):
+        """Greedy decode through host buffers (tokens in and out of host memory every step).  Returns (tokens, ms per step)."""
+        tin = np.ascontiguousarray(tokens_in, np.int32)
+        out = np.zeros(n_total, np.int32)
+        ms = np.zeros(n_total, np.float32)
+        L.check(self.lib.etxb_decode_host(self._h, tin.ctypes.data_as(C.c_void_p), len(tin), n_total, start_pos,
+                                          out.ctypes.data_as(C.c_void_p), ms.ctypes.data_as(C.c_void_p)))
+        return out, ms
+
+
+def op_launch(body: str | int, argblock: bytes, ntasks: int, device: int = 0, step: L.StepParams | None = None, stream: int | None = None):
+    """Run `ntasks` tasks of one built-in tile on the persistent grid (asynchronous on `stream`)."""
+    b = L.BODY[body] if isinstance(body, str) else int(body)
+    L.check(L.load().etxb_op_launch(device, b, argblock, len(argblock), ntasks, C.byref(step) if step is not None else None,
+                                    C.c_void_p(stream or 0)))
