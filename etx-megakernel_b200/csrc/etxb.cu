@@ -15,6 +15,7 @@
 
 #include "../../include/etxb200.h"
 #include "etxb_kernel.cuh"
+#include "etxb_gemv_nb.cuh"
 
 static_assert(sizeof(etxb_gemv_args) == 160 && offsetof(etxb_gemv_args, grid) == 144, "GEMV block layout (etx/ops/gemv.py:80-94)");
 static_assert(sizeof(etxb_topk_args) == 64 && offsetof(etxb_topk_args, grid) == 48, "top-k block layout (etx/ops/topk.py:16-23)");
@@ -57,18 +58,22 @@ struct etxb_session {
 
 static int g_kernel_ready[64];
 
+static int g_sm_count[64];
+
 static int32_t prepare_kernel(int device, int* workers_out) {
   CU(cudaSetDevice(device));
-  cudaDeviceProp prop;
-  CU(cudaGetDeviceProperties(&prop, device));
-  if (device < 64 && !g_kernel_ready[device]) {
+  if (device < 0 || device >= 64) return fail(ETXB_E_ARG, "device index out of range");
+  if (!g_kernel_ready[device]) {                                   // once per device: attribute queries are slow
+    int sms = 0;
+    CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     CU(cudaFuncSetAttribute(etxb::etxb_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ETXB_SMEM_BYTES));
+    int per_sm = 0;
+    CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, etxb::etxb_megakernel, ETXB_THREADS, ETXB_SMEM_BYTES));
+    if (per_sm < 1) return fail(ETXB_E_RESIDENCY, "the persistent CTA does not fit one SM of this device");
+    g_sm_count[device] = sms;
     g_kernel_ready[device] = 1;
   }
-  int per_sm = 0;
-  CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, etxb::etxb_megakernel, ETXB_THREADS, ETXB_SMEM_BYTES));
-  if (per_sm < 1) return fail(ETXB_E_RESIDENCY, "the persistent CTA does not fit one SM of this device");
-  *workers_out = prop.multiProcessorCount;
+  *workers_out = g_sm_count[device];
   return ETXB_OK;
 }
 
@@ -422,6 +427,29 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   int32_t rc = prepare_kernel(device, &c.workers);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)cuda_stream;
+  if (body == ETXB_BODY_GEMV && bytes >= sizeof(etxb_gemv_args) && ((const etxb_gemv_args*)argblock)->nb > 1) {
+    // column-batched GEMV (the sweep with M = 2, 4, 8 tokens): its own kernel, one CTA per task
+    etxb_gemv_args d;
+    memcpy(&d, argblock, sizeof d);
+    if ((d.mode & 0xff) != 0) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: plain form only");
+    if ((int64_t)d.nb * ((d.K + 7) / 8 * 8) > ETXB_NB_XS_FLOATS) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: nb * K exceeds the activation stage");
+    const size_t smem = (ETXB_NB_XS_FLOATS + 256) * 4;
+    static int nb_ready[64];
+    if (!nb_ready[device]) {
+      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      nb_ready[device] = 1;
+    }
+    switch (d.nb) {
+      case 2: etxb::etxb_gemv_nb_kernel<2><<<ntasks, 512, smem, st>>>(d); break;
+      case 4: etxb::etxb_gemv_nb_kernel<4><<<ntasks, 512, smem, st>>>(d); break;
+      case 8: etxb::etxb_gemv_nb_kernel<8><<<ntasks, 512, smem, st>>>(d); break;
+      default: return fail(ETXB_E_UNSUPPORTED, "batched GEMV: nb must be 2, 4 or 8");
+    }
+    CU(cudaGetLastError());
+    return ETXB_OK;
+  }
   if (!c.d_type) {
     CU(cudaMalloc((void**)&c.d_type, sizeof(etxb_type))); CU(cudaMalloc((void**)&c.d_targs, ETXB_MAX_ARGS * sizeof(void*)));
     CU(cudaMalloc((void**)&c.d_qbegin, 4097 * 4)); CU(cudaMalloc((void**)&c.d_ctrl, 64)); CU(cudaMemset(c.d_ctrl, 0, 64));
@@ -455,6 +483,7 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   qb[W] = n;
   etxb_type ty; memset(&ty, 0, sizeof ty);
   ty.body = body; for (int k = 0; k < ETXB_MAX_ARGS; ++k) ty.args[k] = -1; ty.args[0] = 0;
+  ty.stream_word = -1;                                             // everything the weight addresses depend on precedes the launch
   void* targs[ETXB_MAX_ARGS] = {c.d_pool, nullptr, nullptr, nullptr};
   CU(cudaMemcpyAsync(c.d_tasks, tasks.data(), tasks.size() * sizeof(etxb_task), cudaMemcpyHostToDevice, st));
   CU(cudaMemcpyAsync(c.d_qbegin, qb.data(), qb.size() * 4, cudaMemcpyHostToDevice, st));

@@ -9,14 +9,26 @@
 #include <stdint.h>
 
 #define ETXB_EV_STRIDE 32            // int32 words between event counters: one 128-byte line each (abi.h:7-12)
-#define ETXB_THREADS 512             // threads of one persistent CTA (16 warps)
-#define ETXB_NWARPS (ETXB_THREADS / 32)
+#define ETXB_CONSUMER_WARPS 16       // warps that run tile bodies
+#define ETXB_CONSUMERS (ETXB_CONSUMER_WARPS * 32)
+#define ETXB_THREADS (ETXB_CONSUMERS + 32)   // + one producer warp that streams weights with bulk async copies
+#define ETXB_NWARPS ETXB_CONSUMER_WARPS
 #define ETXB_MAX_ARGS 4              // tensor pointers a task type may name (Graph.call_device(args=[...]))
-#define ETXB_XS_FLOATS 40960         // staged activations: nb * K floats at most (160 KB)
-#define ETXB_SCRATCH_FLOATS 6144     // partial sums, top-k scratch, reductions (24 KB)
-#define ETXB_SMEM_BYTES ((ETXB_XS_FLOATS + ETXB_SCRATCH_FLOATS) * 4)
+// shared memory of the persistent CTA
+#define ETXB_STAGE_BYTES 32768       // one ring stage: whole weight rows, so a row is at most 32 KB (K <= 16384)
+#define ETXB_NSTAGE 5                // 160 KB of weights in flight per SM
+#define ETXB_RING_BYTES (ETXB_STAGE_BYTES * ETXB_NSTAGE)
+#define ETXB_GEN_BYTES 65536         // activations: fp32 scratch [0,32K), bf16 x [32K,56K), row results [56K,64K); attention tiles use all of it
+#define ETXB_XF_FLOATS 8192          // norm fold works on K <= 8192 floats
+#define ETXB_XB_OFF 32768
+#define ETXB_XB_ELEMS 12288          // streamed GEMV rows are at most 12288 elements long
+#define ETXB_G_OFF 57344
+#define ETXB_G_FLOATS 2048
+#define ETXB_SCR_FLOATS 512
+#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512)
 #define ETXB_ATTN_PART 32            // KV positions per attention task
-#define ETXB_MAX_NB 8                // activation columns served by one weight read in the FMA GEMV
+#define ETXB_MAX_NB 8                // activation columns of the stand-alone batched GEMV kernel
+#define ETXB_NB_XS_FLOATS 40960      // its staged activations: nb * K floats
 
 // ---- plan blob ------------------------------------------------------------------------------------------------
 // header, then sections in this order, each starting on an 8-byte boundary:
@@ -40,8 +52,10 @@ struct etxb_type {
   int32_t body;                 // ETXB_BODY_*
   int32_t cst[4];               // TaskGrid.consts: cst[0] = byte offset of the grid's argument block in args[0]
   int32_t args[ETXB_MAX_ARGS];  // plan tensor indices, -1 = unused
-  int32_t flags;                // bit0: prefetch hint allowed
-  int32_t pad[2];
+  int32_t flags;                // bit0: the tile streams weights through the ring
+  int32_t stream_word;          // event the producer warp waits for before it reads the weight addresses of a task:
+                                // -1 none (static weights: stream ahead freely), -2 the task's own in-events, >= 0 that event
+  int32_t pad;
 };
 
 struct etxb_task {

@@ -104,10 +104,10 @@ __device__ __forceinline__ void tile_attn(const unsigned char* a, int blk, const
   float* st = sc + 16 * P;                                        // per head: max, sum
   // q rows
   const __nv_bfloat16* q = (const __nv_bfloat16*)d.q;
-  for (int i = tidx(); i < G * HD; i += blockDim.x) qs[i] = ld_bf(q, (size_t)h * G * HD + i);
+  for (int i = tidx(); i < G * HD; i += ETXB_CONSUMERS) qs[i] = ld_bf(q, (size_t)h * G * HD + i);
   // K and V blocks: HD * BS bf16 each, contiguous per (block, head)
   const int vec_per_blk = HD * BS / 8;
-  for (int i = tidx(); i < nblk * vec_per_blk; i += blockDim.x) {
+  for (int i = tidx(); i < nblk * vec_per_blk; i += ETXB_CONSUMERS) {
     const int b = i / vec_per_blk, r = i - b * vec_per_blk;
     const int lb = t0 / BS + b;
     if (lb * BS < seq) {
@@ -117,11 +117,11 @@ __device__ __forceinline__ void tile_attn(const unsigned char* a, int blk, const
       *(uint4*)(vs + (size_t)b * HD * BS + 8 * r) = ld_act16((const __nv_bfloat16*)d.vc + base + 8 * r);
     }
   }
-  __syncthreads();
+  csync();
   // scores: idx -> (g, half, t); the two halves of the head dimension are added left to right, then scaled
   const int hx = HD / X;                                          // 8-element groups per head
   float* ph = st + 64;                                            // [2][16 * P] half dot products
-  for (int idx = tidx(); idx < G * 2 * P; idx += blockDim.x) {
+  for (int idx = tidx(); idx < G * 2 * P; idx += ETXB_CONSUMERS) {
     const int t = idx % P, hf = (idx / P) & 1, g = idx / (2 * P);
     float acc = 0.f;
     if (t < ntok) {
@@ -138,10 +138,10 @@ __device__ __forceinline__ void tile_attn(const unsigned char* a, int blk, const
     }
     ph[hf * 16 * P + g * P + t] = acc;
   }
-  __syncthreads();
-  for (int i = tidx(); i < G * P; i += blockDim.x)
+  csync();
+  for (int i = tidx(); i < G * P; i += ETXB_CONSUMERS)
     sc[i] = (i % P) < ntok ? __fmul_rn(__fadd_rn(ph[i], ph[16 * P + i]), d.scale) : -INFINITY;
-  __syncthreads();
+  csync();
   // softmax statistics per q head (one warp per head, P == 32 lanes)
   for (int g = tidx() >> 5; g < G; g += ETXB_NWARPS) {
     const int lane = tidx() & 31;
@@ -152,9 +152,9 @@ __device__ __forceinline__ void tile_attn(const unsigned char* a, int blk, const
     sc[g * P + lane] = p;
     if (lane == 0) { st[2 * g] = m; st[2 * g + 1] = l; }
   }
-  __syncthreads();
+  csync();
   // output: idx -> (g, dd); o = sum_t p[t] * V[t][dd], positions in ascending order
-  for (int idx = tidx(); idx < G * HD; idx += blockDim.x) {
+  for (int idx = tidx(); idx < G * HD; idx += ETXB_CONSUMERS) {
     const int dd = idx % HD, g = idx / HD;
     float acc = 0.f;
     for (int b = 0; b < nblk; ++b) {
@@ -184,35 +184,35 @@ __device__ __forceinline__ void tile_attn_reduce(const unsigned char* a, int blk
   float* acc4 = sm.xs + 8192;                                     // [groups][HD]
   float* red = sm.scr;
   const int lane = tidx() & 31;
-  for (int p = tidx(); p < np; p += blockDim.x) {
+  for (int p = tidx(); p < np; p += ETXB_CONSUMERS) {
     wp[p] = __ldcg(d.max_logits + (size_t)hq * d.max_parts + p);
     es[p] = __ldcg(d.exp_sums + (size_t)hq * d.max_parts + p);
   }
-  __syncthreads();
+  csync();
   if (tidx() < 32) {
     float m = -INFINITY;
     for (int p = lane; p < np; p += 32) m = fmaxf(m, wp[p]);
     m = warp_max(m);
     if (lane == 0) red[41] = m;
   }
-  __syncthreads();
+  csync();
   const float m = red[41];
-  for (int p = tidx(); p < np; p += blockDim.x) wp[p] = expf(__fsub_rn(wp[p], m));
-  __syncthreads();
+  for (int p = tidx(); p < np; p += ETXB_CONSUMERS) wp[p] = expf(__fsub_rn(wp[p], m));
+  csync();
   if (tidx() < 32) {
     float L = 0.f;
     for (int p = lane; p < np; p += 32) L = __fmaf_rn(wp[p], es[p], L);
     L = warp_sum(L);
     if (lane == 0) red[40] = L;
   }
-  const int groups = (int)blockDim.x / HD > 0 ? (int)blockDim.x / HD : 1;
+  const int groups = ETXB_CONSUMERS / HD > 0 ? ETXB_CONSUMERS / HD : 1;
   const int dd = tidx() % HD, pg = tidx() / HD;
   if (pg < groups) {
     float o = 0.f;
     for (int p = pg; p < np; p += groups) o = __fmaf_rn(wp[p], __ldcg(d.tmp_out + ((size_t)hq * d.max_parts + p) * HD + dd), o);
     acc4[pg * HD + dd] = o;
   }
-  __syncthreads();
+  csync();
   if (tidx() < HD) {
     float o = 0.f;
     for (int g2 = 0; g2 < groups; ++g2) o = __fadd_rn(o, acc4[g2 * HD + tidx()]);

@@ -10,235 +10,66 @@
 // materialised vector is rounded to bf16, RMSNorm rounds twice, SiLU is rounded before the product, the routing
 // weight is a bf16 value, expert outputs are accumulated in bf16 in ascending expert id.
 //
-// Streaming: one warp owns a row (or a K segment of a row when a task has fewer rows than warps: split-K),
-// every lane keeps up to 8 independent 16-byte non-temporal weight loads in flight (64 KB per SM), fp32 FMA on
-// unpacked bf16, xor-butterfly across lanes, K segments added left to right: the summation order is fixed.
+// Weight streaming.  The weight rows of a task are one or two contiguous byte ranges.  The CTA's producer warp walks
+// the task queue AHEAD of the consumer warps and copies those ranges, whole rows at a time, into a ring of
+// ETXB_NSTAGE x 32 KB shared-memory stages with bulk asynchronous copies (cp.async.bulk, the TMA engine; completion
+// on an mbarrier per stage).  Weights depend on no event (expert weights: only on the routing), so the stream keeps
+// running while the consumers wait for their activations: HBM stays busy across phase boundaries.  The consumer
+// warps take the stages in order; warp w owns the rows q with q % 16 == w, reads 16-byte weight and activation
+// vectors from shared memory, accumulates in fp32 in a fixed order (lane-strided, then xor butterfly), and hands the
+// row result to the tile's epilogue.
 #pragma once
 #include "etxb_prims.cuh"
 
 namespace etxb {
 
 struct Smem {
-  float* xs;       // ETXB_XS_FLOATS staged activations (nb columns, KS floats apart)
-  float* scr;      // ETXB_SCRATCH_FLOATS
+  float* xs;                 // general region (ETXB_GEN_BYTES): fp32 scratch, bf16 activations, row results
+  float* scr;                // ETXB_SCR_FLOATS of reduction / routing scratch
+  unsigned char* ring;       // ETXB_NSTAGE stages
+  uint64_t* full;            // [ETXB_NSTAGE] stage filled (transaction bytes landed)
+  uint64_t* empty;           // [ETXB_NSTAGE] stage drained by all consumer warps
+  int32_t* prod;             // producer-warp scratch: 16 ids + 16 weights
+  const unsigned long long* deadline;
+  int32_t* ctrl;
+};
+__device__ __forceinline__ __nv_bfloat16* smem_xb(const Smem& sm) { return (__nv_bfloat16*)((unsigned char*)sm.xs + ETXB_XB_OFF); }
+__device__ __forceinline__ float* smem_g(const Smem& sm) { return (float*)((unsigned char*)sm.xs + ETXB_G_OFF); }
+
+// Bounded mbarrier wait: true when the phase completed; false when the step is being abandoned (another thread gave
+// up, the host aborted, or the deadline passed -- then this thread records it).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const Smem& sm, int where) {
+  uint32_t n = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++n & 255u) == 0) {
+      if (ld_relaxed(sm.ctrl) != 0) return false;
+      if ((n & 4095u) == 0 && globaltimer() > *sm.deadline) {
+        if (atomicOr(sm.ctrl, ETXB_CTRL_TIMEOUT) == 0) { sm.ctrl[1] = where; sm.ctrl[2] = -1; sm.ctrl[3] = (int32_t)parity; sm.ctrl[4] = -1; }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------------------------- what a task streams
+struct StreamDesc {
+  const unsigned char* base0;   // rows 0 .. n0-1
+  const unsigned char* base1;   // rows n0 .. n0+n1-1
+  int n0, n1, row_bytes;
 };
 
-// ---------------------------------------------------------------------------------------------- staging
-// nb columns of K bf16 values -> floats in shared memory; column b at xs + b * KS.  K % 8 == 0.
-__device__ __forceinline__ void stage_x(const void* x, int K, int sx, int nb, int KS, float* xs) {
-  const int nv = K >> 3;
-  for (int b = 0; b < nb; ++b) {
-    const __nv_bfloat16* xb = (const __nv_bfloat16*)x + (size_t)b * sx;
-    float* dst = xs + (size_t)b * KS;
-    for (int i = tidx(); i < nv; i += blockDim.x) {
-      const uint4 v = ld_act16(xb + 8 * i);
-      *(float4*)(dst + 8 * i) = make_float4(bf_lo(v.x), bf_hi(v.x), bf_lo(v.y), bf_hi(v.y));
-      *(float4*)(dst + 8 * i + 4) = make_float4(bf_lo(v.z), bf_hi(v.z), bf_lo(v.w), bf_hi(v.w));
-    }
-  }
-  __syncthreads();
-}
-
-// Norm fold of one column: z = bf16(resid_in + acc), acc = the R rows added one by one in bf16 in ascending id order
-// (R == 1: the row itself; rows == null: z = resid_in), then x = bf16(ln * bf16(z * r)), r = 1 / sqrt(mean(z^2) + eps)
-// with the mean summed in numpy's order.  `store`: this task also writes resid_out (z) and xout (x).
-__device__ __forceinline__ void stage_norm_col(const void* rows, const void* rin, void* rout, void* xout, const void* ln,
-                                               const int32_t* ids, int R, int K, float eps, float* xs, float* scr, bool store) {
-  int* order = (int*)(scr + 64);
-  if (R > 1) {
-    if (tidx() < R) {
-      int rank = tidx();
-      if (ids) {
-        const int mine = __ldcg(ids + tidx());
-        rank = 0;
-        for (int j = 0; j < R; ++j) {
-          const int o = __ldcg(ids + j);
-          rank += (o < mine) || (o == mine && j < tidx());
-        }
-      }
-      order[rank] = tidx();
-    }
-    __syncthreads();
-  }
-  const int nv = K >> 3;
-  for (int i = tidx(); i < nv; i += blockDim.x) {
-    float z[8];
-    const uint4 ri = ld_act16((const __nv_bfloat16*)rin + 8 * i);
-    const float rf[8] = {bf_lo(ri.x), bf_hi(ri.x), bf_lo(ri.y), bf_hi(ri.y), bf_lo(ri.z), bf_hi(ri.z), bf_lo(ri.w), bf_hi(ri.w)};
-    if (rows == nullptr || R == 0) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) z[j] = rf[j];
-    } else {
-      float acc[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int s0 = 0; s0 < R; s0 += 8) {                       // up to 8 rows in flight, added in order
-        uint4 rv[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (s0 + u < R) {
-            const int row = R > 1 ? order[s0 + u] : 0;
-            rv[u] = ld_act16((const __nv_bfloat16*)rows + (size_t)row * K + 8 * i);
-          }
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (s0 + u < R) {
-            const float v[8] = {bf_lo(rv[u].x), bf_hi(rv[u].x), bf_lo(rv[u].y), bf_hi(rv[u].y),
-                                bf_lo(rv[u].z), bf_hi(rv[u].z), bf_lo(rv[u].w), bf_hi(rv[u].w)};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = bfr(__fadd_rn(acc[j], v[j]));
-          }
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) z[j] = bfr(__fadd_rn(rf[j], acc[j]));
-    }
-    *(float4*)(xs + 8 * i) = make_float4(z[0], z[1], z[2], z[3]);
-    *(float4*)(xs + 8 * i + 4) = make_float4(z[4], z[5], z[6], z[7]);
-    if (store && rout != nullptr)
-      *(uint4*)((__nv_bfloat16*)rout + 8 * i) = make_uint4(pack_bf(z[0], z[1]), pack_bf(z[2], z[3]), pack_bf(z[4], z[5]), pack_bf(z[6], z[7]));
-  }
-  __syncthreads();
-  const float ss = sumsq_numpy_order(xs, K, scr);
-  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
-  __syncthreads();
-  for (int i = tidx(); i < nv; i += blockDim.x) {
-    const uint4 w = __ldg((const uint4*)((const __nv_bfloat16*)ln + 8 * i));
-    const float wf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = bfr(__fmul_rn(wf[j], bfr(__fmul_rn(xs[8 * i + j], r))));
-    *(float4*)(xs + 8 * i) = make_float4(v[0], v[1], v[2], v[3]);
-    *(float4*)(xs + 8 * i + 4) = make_float4(v[4], v[5], v[6], v[7]);
-    if (store && xout != nullptr)
-      *(uint4*)((__nv_bfloat16*)xout + 8 * i) = make_uint4(pack_bf(v[0], v[1]), pack_bf(v[2], v[3]), pack_bf(v[4], v[5]), pack_bf(v[6], v[7]));
-  }
-  __syncthreads();
-}
-
-// ---------------------------------------------------------------------------------------------- the stream
-template <int NB>
-__device__ __forceinline__ void fma8(const uint4 w, const float* xp, int KS, float* acc) {
-  const float wf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
-#pragma unroll
-  for (int b = 0; b < NB; ++b) {
-    const float4 xa = *(const float4*)(xp + (size_t)b * KS), xb = *(const float4*)(xp + (size_t)b * KS + 4);
-    float a = acc[b];
-    a = __fmaf_rn(wf[0], xa.x, a); a = __fmaf_rn(wf[1], xa.y, a); a = __fmaf_rn(wf[2], xa.z, a); a = __fmaf_rn(wf[3], xa.w, a);
-    a = __fmaf_rn(wf[4], xb.x, a); a = __fmaf_rn(wf[5], xb.y, a); a = __fmaf_rn(wf[6], xb.z, a); a = __fmaf_rn(wf[7], xb.w, a);
-    acc[b] = a;
-  }
-}
-
-// rows q = 0 .. nrows-1 of bf16 weights, row q at rowptr(q), K elements each (K % 8 == 0); activations xs (NB columns,
-// KS floats apart).  epi(q, v) is called once per row with the NB dot products by one thread.  part: scratch of at
-// least ETXB_NWARPS * NB floats.  All threads of the CTA call; contains __syncthreads().
-template <int NB, typename RowPtr, typename Epi>
-__device__ __forceinline__ void gemv_rows(int nrows, int K, RowPtr rowptr, const float* xs, int KS, float* part, Epi epi) {
-  const int lane = tidx() & 31, warp = tidx() >> 5;
-  const int nvec = K >> 3;
-  int ks = 1;                                                    // split-K factor: power of two, >= 32 vectors per segment
-  while (nrows * ks * 2 <= ETXB_NWARPS && (nvec / (ks * 2)) >= 32) ks *= 2;
-  const int segn = (((nvec + ks - 1) / ks) + 31) & ~31;           // vectors per segment, whole lanes-rounds
-  const int vpl = segn >> 5;                                      // vectors per lane per segment
-  const int units = nrows * ks;
-  constexpr int U = NB >= 4 ? 4 : 8;                              // independent 16-byte loads in flight per lane
-
-  if (ks == 1) {
-    if (vpl > 4) {
-      for (int q = warp; q < nrows; q += ETXB_NWARPS) {
-        const __nv_bfloat16* wr = rowptr(q);
-        float acc[NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) acc[b] = 0.f;
-        for (int v0 = 0; v0 < vpl; v0 += U) {
-          uint4 w[U];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int v = (v0 + u) * 32 + lane;
-            if (v0 + u < vpl && v < nvec) w[u] = ld_stream(wr + 8 * v);
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const int v = (v0 + u) * 32 + lane;
-            if (v0 + u < vpl && v < nvec) fma8<NB>(w[u], xs + 8 * v, KS, acc);
-          }
-        }
-        float out[NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) out[b] = warp_sum(acc[b]);
-        if (lane == 0) epi(q, out);
-      }
-    } else {                                                       // short rows: two rows per warp trip, <= 4 vectors each
-      for (int q0 = warp * 2; q0 < nrows; q0 += ETXB_NWARPS * 2) {
-        const bool two = q0 + 1 < nrows;
-        const __nv_bfloat16* wa = rowptr(q0);
-        const __nv_bfloat16* wb = two ? rowptr(q0 + 1) : wa;
-        uint4 w[2][4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int v = u * 32 + lane;
-          if (u < vpl && v < nvec) { w[0][u] = ld_stream(wa + 8 * v); if (two) w[1][u] = ld_stream(wb + 8 * v); }
-        }
-        float acc[2][NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) { acc[0][b] = 0.f; acc[1][b] = 0.f; }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int v = u * 32 + lane;
-          if (u < vpl && v < nvec) { fma8<NB>(w[0][u], xs + 8 * v, KS, acc[0]); if (two) fma8<NB>(w[1][u], xs + 8 * v, KS, acc[1]); }
-        }
-        float o0[NB], o1[NB];
-#pragma unroll
-        for (int b = 0; b < NB; ++b) { o0[b] = warp_sum(acc[0][b]); o1[b] = warp_sum(acc[1][b]); }
-        if (lane == 0) { epi(q0, o0); if (two) epi(q0 + 1, o1); }
-      }
-    }
-    return;
-  }
-  // split-K: unit u = (row, segment); partials to shared memory, summed left to right
-  __syncthreads();
-  for (int u = warp; u < units; u += ETXB_NWARPS) {
-    const int q = u / ks, seg = u - q * ks;
-    const __nv_bfloat16* wr = rowptr(q);
-    float acc[NB];
-#pragma unroll
-    for (int b = 0; b < NB; ++b) acc[b] = 0.f;
-    for (int v0 = 0; v0 < vpl; v0 += U) {
-      uint4 w[U];
-#pragma unroll
-      for (int t = 0; t < U; ++t) {
-        const int v = seg * segn + (v0 + t) * 32 + lane;
-        if (v0 + t < vpl && v < nvec) w[t] = ld_stream(wr + 8 * v);
-      }
-#pragma unroll
-      for (int t = 0; t < U; ++t) {
-        const int v = seg * segn + (v0 + t) * 32 + lane;
-        if (v0 + t < vpl && v < nvec) fma8<NB>(w[t], xs + 8 * v, KS, acc);
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      const float s = warp_sum(acc[b]);
-      if (lane == 0) part[u * NB + b] = s;
-    }
-  }
-  __syncthreads();
-  if (tidx() < nrows) {
-    float out[NB];
-#pragma unroll
-    for (int b = 0; b < NB; ++b) {
-      float s = 0.f;
-      for (int seg = 0; seg < ks; ++seg) s = __fadd_rn(s, part[(tidx() * ks + seg) * NB + b]);
-      out[b] = s;
-    }
-    epi(tidx(), out);
-  }
+__device__ __forceinline__ int stream_chunks(const StreamDesc& s) {
+  const int total = s.n0 + s.n1;
+  if (total <= 0) return 0;
+  const int rps = ETXB_STAGE_BYTES / s.row_bytes;
+  return (total + rps - 1) / rps;
 }
 
 // ---------------------------------------------------------------------------------------------- top-k
 // softmax over E bf16 logits (fp32), K rounds of argmax with the lower index winning ties, optional renormalisation
 // over the selected weights (numpy's summation order for <= 16 values), optional bf16 rounding of the weights.
-// One warp; E <= 256.  ids / wts / tei may point to shared or global memory; lane t stores result t.
+// One warp (all 32 lanes call); E <= 256, K <= 16.  ids / wts / tei may point to shared or global memory.
 __device__ __forceinline__ void warp_topk(const void* logits, int E, int K, bool renorm, bool bf16w,
                                           int32_t* ids, float* wts, int32_t* tei) {
   const int lane = tidx() & 31;
@@ -275,14 +106,25 @@ __device__ __forceinline__ void warp_topk(const void* logits, int E, int K, bool
     if (lane == t) { myw = bv; myid = bi; }
   }
   if (renorm) {
-    float sel[16];
-    const int n = K < 16 ? K : 16;
-    for (int t = 0; t < n; ++t) sel[t] = __shfl_sync(0xffffffffu, myw, t);
-    const float tot = sum_small_numpy_order(sel, n);
+    // numpy's order for the sum of the K selected weights: K < 8 left to right, else 8 accumulators + tree + tail
+    float tot;
+    if (K < 8) {
+      tot = 0.f;
+      for (int t = 0; t < K; ++t) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, myw, t));
+    } else {
+      float r = lane < 8 ? myw : 0.f;                              // accumulator j = lane j
+      const float second = __shfl_sync(0xffffffffu, myw, (lane & 7) + 8);
+      if (K >= 16 && lane < 8) r = __fadd_rn(r, second);
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, o));
+      tot = __shfl_sync(0xffffffffu, r, 0);
+      for (int t = (K >= 16 ? 16 : 8); t < K; ++t) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, myw, t));
+    }
     myw = __fdiv_rn(myw, tot);
   }
   if (bf16w) myw = bfr(myw);
   if (lane < K) { ids[lane] = myid; wts[lane] = myw; if (tei) tei[lane] = lane; }
+  __syncwarp();
 }
 
 __device__ __forceinline__ void tile_topk(const unsigned char* a, int blk, const Smem& sm) {
@@ -295,108 +137,257 @@ __device__ __forceinline__ void tile_topk(const unsigned char* a, int blk, const
             d.ids + (size_t)w * sv, d.wts + (size_t)w * sv, d.tei ? d.tei + (size_t)w * sv : nullptr);
 }
 
-// ---------------------------------------------------------------------------------------------- plain / folded GEMV
-template <int NB>
-__device__ __forceinline__ void gemv_plain_nb(const etxb_gemv_args& d, int blk, const Smem& sm) {
-  const int r0 = blk * d.rpt, r1 = min(d.M, r0 + d.rpt);
-  if (r0 >= r1) return;
-  const int KS = (d.K + 7) & ~7;
-  if ((d.mode & 0xff) == ETXB_MODE_NORM) {
-#pragma unroll 1
-    for (int b = 0; b < NB; ++b)
-      stage_norm_col(d.rows ? (const __nv_bfloat16*)d.rows + (size_t)b * d.srows : nullptr,
-                     (const __nv_bfloat16*)d.resid_in + (size_t)b * d.srin,
-                     d.resid_out ? (__nv_bfloat16*)d.resid_out + (size_t)b * d.srout : nullptr,
-                     d.x ? (__nv_bfloat16*)d.x + (size_t)b * d.sx : nullptr, d.ln,
-                     d.ids ? d.ids + (size_t)b * d.R : nullptr, d.R, d.K, d.eps, sm.xs + (size_t)b * KS, sm.scr, blk == 0);
-  } else {
-    stage_x(d.x, d.K, d.sx, NB, KS, sm.xs);
+// The weight rows task `blk` of a GEMV-family tile streams.  Called by the producer warp (scratch = its own ids /
+// weights area) and by the consumer side (its area): both compute the same descriptor, so the stage sequence agrees.
+// All 32 lanes of the calling warp must call (the top-k fold is a warp computation).
+__device__ __forceinline__ StreamDesc gemv_stream_desc(int body, const unsigned char* a, int blk, int32_t* lids, float* lwts) {
+  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
+  StreamDesc s;
+  s.base0 = s.base1 = nullptr; s.n0 = s.n1 = 0; s.row_bytes = d.K * 2;
+  if (blk >= (int)d.nblocks) return s;
+  if (body == 3) {
+    const int r0 = blk * d.rpt, r1 = min(d.M, r0 + d.rpt);
+    if (r0 >= r1) return s;
+    s.base0 = (const unsigned char*)d.W + (size_t)r0 * d.K * 2; s.n0 = r1 - r0;
+    return s;
   }
-  const __nv_bfloat16* W = (const __nv_bfloat16*)d.W;
-  const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
-  __nv_bfloat16* out = (__nv_bfloat16*)d.out;
-  const int K = d.K, sout = d.sout;
-  gemv_rows<NB>(r1 - r0, K, [&](int q) { return W + (size_t)(r0 + q) * K; }, sm.xs, KS, sm.scr + 128,
-                [&](int q, const float* v) {
-                  const float bv = bias ? __bfloat162float(bias[r0 + q]) : 0.f;
-#pragma unroll
-                  for (int b = 0; b < NB; ++b) out[(size_t)b * sout + r0 + q] = __float2bfloat16_rn(bias ? __fadd_rn(v[b], bv) : v[b]);
-                });
+  const int sl = blk / d.tpe, j = blk - sl * d.tpe;
+  const int r0 = j * d.rpt, r1 = min(d.M, r0 + d.rpt);
+  if (r0 >= r1) return s;
+  const int fold = d.mode & 0xff;
+  int e = 0;
+  if (fold >= 2) {
+    warp_topk(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
+    e = lids[sl];
+  } else if (d.ids) {
+    e = __ldcg(d.ids + sl);
+  }
+  const unsigned char* We = (const unsigned char*)d.W + (size_t)e * d.estride * 2;
+  s.base0 = We + (size_t)r0 * d.K * 2; s.n0 = r1 - r0;
+  if (body == 4) { s.base1 = We + (size_t)(d.M + r0) * d.K * 2; s.n1 = r1 - r0; }   // gate rows, then up rows
+  return s;
 }
 
-__device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const Smem& sm) {
-  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  if (blk >= (int)d.nblocks) return;
-  switch (d.nb <= 1 ? 1 : d.nb) {
-    case 1: gemv_plain_nb<1>(d, blk, sm); break;
-    case 2: gemv_plain_nb<2>(d, blk, sm); break;
-    case 4: gemv_plain_nb<4>(d, blk, sm); break;
-    case 8: gemv_plain_nb<8>(d, blk, sm); break;
-    default: break;                                                // rejected on the host
+// ---------------------------------------------------------------------------------------------- producer side
+// Issue the bulk copies of one task.  One warp; lane 0 issues.  n = running stage counter of this CTA.
+__device__ __forceinline__ bool produce_task(const StreamDesc& s, uint32_t& n, const Smem& sm, int where) {
+  const int total = s.n0 + s.n1;
+  if (total <= 0) return true;
+  const int rps = ETXB_STAGE_BYTES / s.row_bytes;
+  bool ok = true;
+  if ((tidx() & 31) == 0) {
+    for (int q0 = 0; q0 < total && ok; q0 += rps) {
+      const uint32_t st = n % ETXB_NSTAGE, par = (n / ETXB_NSTAGE) & 1;
+      ok = mbar_wait(sm.empty + st, par ^ 1, sm, where);           // a fresh barrier passes the first round
+      if (!ok) break;
+      const int nr = min(rps, total - q0);
+      unsigned char* dst = sm.ring + (size_t)st * ETXB_STAGE_BYTES;
+      mbar_expect_tx(sm.full + st, (uint32_t)(nr * s.row_bytes));
+      const int a0 = min(max(s.n0 - q0, 0), nr);                   // rows of this stage that come from the first range
+      if (a0 > 0) bulk_g2s(dst, s.base0 + (size_t)q0 * s.row_bytes, (uint32_t)(a0 * s.row_bytes), sm.full + st);
+      if (nr > a0) bulk_g2s(dst + (size_t)a0 * s.row_bytes, s.base1 + (size_t)(q0 + a0 - s.n0) * s.row_bytes,
+                            (uint32_t)((nr - a0) * s.row_bytes), sm.full + st);
+      ++n;
+    }
   }
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  n = __shfl_sync(0xffffffffu, n, 0);
+  return ok;
+}
+
+// ---------------------------------------------------------------------------------------------- consumer side
+__device__ __forceinline__ float dot8(const uint4 w, const uint4 x, float a) {
+  a = __fmaf_rn(bf_lo(w.x), bf_lo(x.x), a); a = __fmaf_rn(bf_hi(w.x), bf_hi(x.x), a);
+  a = __fmaf_rn(bf_lo(w.y), bf_lo(x.y), a); a = __fmaf_rn(bf_hi(w.y), bf_hi(x.y), a);
+  a = __fmaf_rn(bf_lo(w.z), bf_lo(x.z), a); a = __fmaf_rn(bf_hi(w.z), bf_hi(x.z), a);
+  a = __fmaf_rn(bf_lo(w.w), bf_lo(x.w), a); a = __fmaf_rn(bf_hi(w.w), bf_hi(x.w), a);
+  return a;
+}
+
+// Consume the stages of one task: row q (0 .. total-1) . xb -> epi(q, value), called by lane 0 of the owning warp.
+// Every consumer warp walks every stage (so the stage counter stays in step) and arrives on its `empty` barrier.
+template <typename Epi>
+__device__ __forceinline__ void consume_task(int total, int row_bytes, uint32_t& n, const Smem& sm, const __nv_bfloat16* xb, int where, Epi epi) {
+  if (total <= 0) return;
+  const int lane = tidx() & 31, cw = tidx() >> 5;
+  const int rps = ETXB_STAGE_BYTES / row_bytes, nvec = row_bytes >> 4;
+  const uint4* xv = (const uint4*)xb;
+  bool alive = true;
+  for (int q0 = 0; q0 < total; q0 += rps) {
+    const uint32_t st = n % ETXB_NSTAGE, par = (n / ETXB_NSTAGE) & 1;
+    ++n;
+    if (alive) alive = mbar_wait(sm.full + st, par, sm, where);
+    if (!alive) continue;                                          // step abandoned: keep counting, touch nothing
+    const int nr = min(rps, total - q0);
+    const unsigned char* stage = sm.ring + (size_t)st * ETXB_STAGE_BYTES;
+    for (int j = (cw - q0) & (ETXB_CONSUMER_WARPS - 1); j < nr; j += ETXB_CONSUMER_WARPS) {
+      const uint4* wv = (const uint4*)(stage + (size_t)j * row_bytes);
+      float acc = 0.f;
+#pragma unroll 4
+      for (int v = lane; v < nvec; v += 32) acc = dot8(wv[v], xv[v], acc);
+      acc = warp_sum(acc);
+      if (lane == 0) epi(q0 + j, acc);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.empty + st);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- activation staging
+// K bf16 values (written by other CTAs) -> shared memory, K % 8 == 0.
+__device__ __forceinline__ void stage_xb(const void* x, int K, __nv_bfloat16* xb) {
+  const int nv = K >> 3;
+  for (int i = tidx(); i < nv; i += ETXB_CONSUMERS) ((uint4*)xb)[i] = ld_act16((const __nv_bfloat16*)x + 8 * i);
+  csync();
+}
+
+// Norm fold: z = bf16(resid_in + acc), acc = the R rows added one by one in bf16 in ascending id order (R == 1: the row
+// itself; rows == null: z = resid_in), then x = bf16(ln * bf16(z * r)), r = 1 / sqrt(mean(z^2) + eps) with the mean summed
+// in numpy's order.  x goes to shared memory (xb); `store`: this task also writes resid_out (z) and xout (x).  K <= 8192.
+__device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, void* rout, void* xout, const void* ln,
+                                            const int32_t* ids, int R, int K, float eps, float* xf, __nv_bfloat16* xb, float* scr, bool store) {
+  int* order = (int*)(scr + 64);
+  if (R > 1) {
+    if (tidx() < R) {
+      int rank = tidx();
+      if (ids) {
+        const int mine = __ldcg(ids + tidx());
+        rank = 0;
+        for (int j = 0; j < R; ++j) {
+          const int o = __ldcg(ids + j);
+          rank += (o < mine) || (o == mine && j < tidx());
+        }
+      }
+      order[rank] = tidx();
+    }
+    csync();
+  }
+  const int nv = K >> 3;
+  for (int i = tidx(); i < nv; i += ETXB_CONSUMERS) {
+    float z[8];
+    const uint4 ri = ld_act16((const __nv_bfloat16*)rin + 8 * i);
+    const float rf[8] = {bf_lo(ri.x), bf_hi(ri.x), bf_lo(ri.y), bf_hi(ri.y), bf_lo(ri.z), bf_hi(ri.z), bf_lo(ri.w), bf_hi(ri.w)};
+    if (rows == nullptr || R == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) z[j] = rf[j];
+    } else {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s0 = 0; s0 < R; s0 += 8) {                       // up to 8 rows in flight, added in order
+        uint4 rv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (s0 + u < R) {
+            const int row = R > 1 ? order[s0 + u] : 0;
+            rv[u] = ld_act16((const __nv_bfloat16*)rows + (size_t)row * K + 8 * i);
+          }
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (s0 + u < R) {
+            const float v[8] = {bf_lo(rv[u].x), bf_hi(rv[u].x), bf_lo(rv[u].y), bf_hi(rv[u].y),
+                                bf_lo(rv[u].z), bf_hi(rv[u].z), bf_lo(rv[u].w), bf_hi(rv[u].w)};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = bfr(__fadd_rn(acc[j], v[j]));
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) z[j] = bfr(__fadd_rn(rf[j], acc[j]));
+    }
+    *(float4*)(xf + 8 * i) = make_float4(z[0], z[1], z[2], z[3]);
+    *(float4*)(xf + 8 * i + 4) = make_float4(z[4], z[5], z[6], z[7]);
+    if (store && rout != nullptr)
+      *(uint4*)((__nv_bfloat16*)rout + 8 * i) = make_uint4(pack_bf(z[0], z[1]), pack_bf(z[2], z[3]), pack_bf(z[4], z[5]), pack_bf(z[6], z[7]));
+  }
+  csync();
+  const float ss = sumsq_numpy_order(xf, K, scr);
+  const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
+  for (int i = tidx(); i < nv; i += ETXB_CONSUMERS) {
+    const uint4 w = __ldg((const uint4*)((const __nv_bfloat16*)ln + 8 * i));
+    const float wf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = bfr(__fmul_rn(wf[j], bfr(__fmul_rn(xf[8 * i + j], r))));
+    const uint4 o = make_uint4(pack_bf(v[0], v[1]), pack_bf(v[2], v[3]), pack_bf(v[4], v[5]), pack_bf(v[6], v[7]));
+    ((uint4*)xb)[i] = o;
+    if (store && xout != nullptr) *(uint4*)((__nv_bfloat16*)xout + 8 * i) = o;
+  }
+  csync();
+}
+
+// ---------------------------------------------------------------------------------------------- plain / folded GEMV
+__device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
+  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
+  const StreamDesc s = gemv_stream_desc(3, a, blk, nullptr, nullptr);
+  if (s.n0 <= 0) return;
+  const int r0 = blk * d.rpt;
+  __nv_bfloat16* xb = smem_xb(sm);
+  if ((d.mode & 0xff) == ETXB_MODE_NORM)
+    stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
+  else
+    stage_xb(d.x, d.K, xb);
+  const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
+  __nv_bfloat16* out = (__nv_bfloat16*)d.out;
+  consume_task(s.n0, s.row_bytes, n, sm, xb, where, [&](int q, float v) {
+    out[r0 + q] = __float2bfloat16_rn(bias ? __fadd_rn(v, __bfloat162float(bias[r0 + q])) : v);
+  });
 }
 
 // ---------------------------------------------------------------------------------------------- MoE gate+up
 // task blk: slot s = blk / tpe, row chunk j = blk % tpe; expert e = ids[s] (ids == null and no fold: expert 0, the
 // dense SwiGLU MLP); act[s][r] = bf16(bf16(silu(bf16 g)) * bf16 u), g = W_e[r,:].x, u = W_e[M + r,:].x.
-__device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, const Smem& sm) {
+__device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  if (blk >= (int)d.nblocks) return;
-  const int s = blk / d.tpe, j = blk - s * d.tpe;
-  const int r0 = j * d.rpt, r1 = min(d.M, r0 + d.rpt);
-  if (r0 >= r1) return;
-  const int n = r1 - r0;
-  int* lids = (int*)(sm.scr + 96); float* lwts = sm.scr + 112;
-  const int fold = d.mode & 0xff;
-  if (fold >= 2) {
-    if (tidx() < 32) warp_topk(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
-    __syncthreads();
-    if (j == 0 && tidx() == 0) {                              // the slot's first chunk publishes the routing
-      if (d.ids) ((int32_t*)d.ids)[s] = lids[s];
-      if (d.wts) ((float*)d.wts)[s] = lwts[s];
-    }
+  int32_t* lids = (int32_t*)(sm.scr + 96); float* lwts = sm.scr + 112;
+  StreamDesc s;
+  if (tidx() < 32) {                                               // the descriptor (and the folded top-k) is one warp's work
+    s = gemv_stream_desc(4, a, blk, lids, lwts);
+    if (tidx() == 0) ((int*)sm.scr)[128] = s.n0;
   }
-  const int e = fold >= 2 ? lids[s] : (d.ids ? __ldcg(d.ids + s) : 0);
-  const __nv_bfloat16* We = (const __nv_bfloat16*)d.W + (size_t)e * d.estride;
-  const int K = d.K, M = d.M, KS = (K + 7) & ~7;
+  csync();
+  const int rows = ((int*)sm.scr)[128];
+  if (rows <= 0) return;
+  const int sl = blk / d.tpe, j = blk - sl * d.tpe, r0 = j * d.rpt;
+  const int fold = d.mode & 0xff;
+  if (fold >= 2 && j == 0 && tidx() == 0) {                         // the slot's first chunk publishes the routing
+    if (d.ids) ((int32_t*)d.ids)[sl] = lids[sl];
+    if (d.wts) ((float*)d.wts)[sl] = lwts[sl];
+  }
+  __nv_bfloat16* xb = smem_xb(sm);
   if (fold == ETXB_MODE_NORM)                                      // dense MLP: the post-attention norm folded in
-    stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, K, d.eps, sm.xs, sm.scr, blk == 0);
+    stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
   else
-    stage_x(d.x, K, 0, 1, KS, sm.xs);
-  float* g = sm.scr + 1024;                                        // 2 * n floats (n <= 2048)
-  gemv_rows<1>(2 * n, K, [&](int q) { return We + (size_t)(q < n ? r0 + q : M + r0 + q - n) * K; }, sm.xs, KS, sm.scr + 128,
-               [&](int q, const float* v) { g[q] = bfr(v[0]); });
-  __syncthreads();
-  __nv_bfloat16* act = (__nv_bfloat16*)d.out + (size_t)s * M;
-  for (int r = tidx(); r < n; r += blockDim.x) act[r0 + r] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(g[r])), g[n + r]));
+    stage_xb(d.x, d.K, xb);
+  float* g = smem_g(sm);                                           // gate results, then up results
+  consume_task(2 * rows, d.K * 2, n, sm, xb, where, [&](int q, float v) { g[q] = bfr(v); });
+  csync();
+  __nv_bfloat16* act = (__nv_bfloat16*)d.out + (size_t)sl * d.M;
+  for (int r = tidx(); r < rows; r += ETXB_CONSUMERS) act[r0 + r] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(g[r])), g[rows + r]));
 }
 
 // ---------------------------------------------------------------------------------------------- MoE down
-// out[s][r] = bf16(bf16(W_e[r,:] . act_s) * wts[s]); wts == null (dense MLP): out[s][r] = bf16(W_e[r,:] . act_s).
-__device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, const Smem& sm) {
+// out[s][r] = bf16(bf16(W_e[r,:] . act_s) * wts[s]); no weights (dense MLP): out[s][r] = bf16(W_e[r,:] . act_s).
+__device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  if (blk >= (int)d.nblocks) return;
-  const int s = blk / d.tpe, j = blk - s * d.tpe;
-  const int r0 = j * d.rpt, r1 = min(d.M, r0 + d.rpt);
-  if (r0 >= r1) return;
-  int* lids = (int*)(sm.scr + 96); float* lwts = sm.scr + 112;
-  const int fold = d.mode & 0xff;
-  if (fold >= 2) {
-    if (tidx() < 32) warp_topk(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
-    __syncthreads();
+  int32_t* lids = (int32_t*)(sm.scr + 96); float* lwts = sm.scr + 112;
+  if (tidx() < 32) {
+    const StreamDesc s = gemv_stream_desc(5, a, blk, lids, lwts);
+    if (tidx() == 0) ((int*)sm.scr)[128] = s.n0;
   }
-  const int e = fold >= 2 ? lids[s] : (d.ids ? __ldcg(d.ids + s) : 0);
+  csync();
+  const int rows = ((int*)sm.scr)[128];
+  if (rows <= 0) return;
+  const int sl = blk / d.tpe, j = blk - sl * d.tpe, r0 = j * d.rpt;
+  const int fold = d.mode & 0xff;
   const bool scaled = fold >= 2 || d.wts != nullptr;
-  const float ws = fold >= 2 ? lwts[s] : (d.wts ? __ldcg(d.wts + s) : 1.f);
-  const __nv_bfloat16* We = (const __nv_bfloat16*)d.W + (size_t)e * d.estride;
-  const int K = d.K, KS = (K + 7) & ~7;
-  stage_x((const __nv_bfloat16*)d.x + (size_t)s * K, K, 0, 1, KS, sm.xs);
-  __nv_bfloat16* out = (__nv_bfloat16*)d.out + (size_t)s * d.M;
-  gemv_rows<1>(r1 - r0, K, [&](int q) { return We + (size_t)(r0 + q) * K; }, sm.xs, KS, sm.scr + 128,
-               [&](int q, const float* v) {
-                 const float y = bfr(v[0]);
-                 out[r0 + q] = __float2bfloat16_rn(scaled ? __fmul_rn(y, ws) : y);
-               });
+  const float ws = fold >= 2 ? lwts[sl] : (d.wts ? __ldcg(d.wts + sl) : 1.f);
+  __nv_bfloat16* xb = smem_xb(sm);
+  stage_xb((const __nv_bfloat16*)d.x + (size_t)sl * d.K, d.K, xb);
+  __nv_bfloat16* out = (__nv_bfloat16*)d.out + (size_t)sl * d.M;
+  consume_task(rows, d.K * 2, n, sm, xb, where, [&](int q, float v) {
+    const float y = bfr(v);
+    out[r0 + q] = __float2bfloat16_rn(scaled ? __fmul_rn(y, ws) : y);
+  });
 }
 
 }  // namespace etxb

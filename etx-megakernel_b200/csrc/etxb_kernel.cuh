@@ -21,7 +21,7 @@ __device__ __forceinline__ void tile_prologue(const etxb_stepv& S) {
   const uint4* src = (const uint4*)((const __nv_bfloat16*)S.embed + (size_t)id * S.H);
   uint4* dst = (uint4*)S.resid;
   const int n8 = S.H / 8;
-  for (int i = tidx(); i < n8 * S.nrep; i += blockDim.x) dst[i] = __ldg(src + i % n8);
+  for (int i = tidx(); i < n8 * S.nrep; i += ETXB_CONSUMERS) dst[i] = __ldg(src + i % n8);
 }
 
 // greedy sampling: first maximum of the bf16 logits (ties -> lower index, like argmax over float32)
@@ -39,7 +39,7 @@ __device__ __forceinline__ void tile_argmax(const etxb_stepv& S, const Smem& sm)
     }
   };
   int j = tidx();
-  const int B = blockDim.x;
+  const int B = ETXB_CONSUMERS;
   for (; j + 3 * B < n4; j += 4 * B) {
     const uint4 a0 = ld_act16(lg4 + j), a1 = ld_act16(lg4 + j + B), a2 = ld_act16(lg4 + j + 2 * B), a3 = ld_act16(lg4 + j + 3 * B);
     scan(a0, 8 * j); scan(a1, 8 * (j + B)); scan(a2, 8 * (j + 2 * B)); scan(a3, 8 * (j + 3 * B));
@@ -57,7 +57,7 @@ __device__ __forceinline__ void tile_argmax(const etxb_stepv& S, const Smem& sm)
   }
   float* sv = sm.scr; int* si = (int*)(sm.scr + 32);
   if ((tidx() & 31) == 0) { sv[tidx() >> 5] = bv; si[tidx() >> 5] = bi; }
-  __syncthreads();
+  csync();
   if (tidx() == 0) {
     for (int w = 1; w < ETXB_NWARPS; ++w)
       if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
@@ -73,7 +73,7 @@ __device__ __forceinline__ void tile_splitk_part(const unsigned char* a, int i, 
   const etxb_splitk_args& d = *(const etxb_splitk_args*)a;
   const int w = d.cols / d.chunks;
   float s = 0.f;
-  for (int c = tidx(); c < w; c += blockDim.x) s += __ldcg(d.in + (size_t)i * d.cols + j * w + c);
+  for (int c = tidx(); c < w; c += ETXB_CONSUMERS) s += __ldcg(d.in + (size_t)i * d.cols + j * w + c);
   s = block_sum(s, sm.scr);
   if (tidx() == 0) d.parts[i * d.chunks + j] = s;
 }
@@ -86,10 +86,9 @@ __device__ __forceinline__ void tile_splitk_sum(const unsigned char* a, int i) {
   }
 }
 
-// Run the body of task `cur`.  Everything it needs is re-read from the task table here, so that nothing but the
-// queue cursor stays live in registers across a tile (the tiles want the whole register file for their loads).
-__device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Smem& sm0) {
-  const Smem sm = sm0;
+// Run the body of task `cur` on the consumer warps.  Everything it needs is re-read from the task table here, so that
+// nothing but the queue cursor and the stage counter stay live across a tile.
+__device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Smem& sm, uint32_t& n) {
   const etxb_task* t = p.tasks + cur;
   const int type = t->type, c0 = t->coord[0], c1 = t->coord[1];
   const etxb_type* ty = p.types + type;
@@ -98,9 +97,9 @@ __device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Sm
     case 0: break;
     case 1: tile_prologue(p.step); break;
     case 2: tile_argmax(p.step, sm); break;
-    case 3: tile_gemv(args, c0, sm); break;
-    case 4: tile_moe_up(args, c0, sm); break;
-    case 5: tile_moe_down(args, c0, sm); break;
+    case 3: tile_gemv(args, c0, sm, n, cur); break;
+    case 4: tile_moe_up(args, c0, sm, n, cur); break;
+    case 5: tile_moe_down(args, c0, sm, n, cur); break;
     case 6: tile_topk(args, c0, sm); break;
     case 7: tile_attnprep(args, c0, sm); break;
     case 8: tile_attn(args, c0, sm); break;
@@ -113,18 +112,78 @@ __device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Sm
   }
 }
 
+// The producer warp: walks the same queue ahead of the consumers and streams the weight rows of every GEMV-family
+// task into the ring.  It waits only for what the weight ADDRESSES depend on (nothing for static weights, the router's
+// event for expert weights), never for the task's activations.
+__device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& sm, int q0, int q1) {
+  uint32_t n = 0;
+  const int lane = tidx() & 31;
+  bool ok = true;
+  for (int cur = q0; cur < q1 && ok; ++cur) {
+    const etxb_task* t = p.tasks + cur;
+    const int type = t->type;
+    const etxb_type* ty = p.types + type;
+    const int body = ty->body;
+    if (body < 3 || body > 5) continue;
+    const int sw = ty->stream_word;
+    if (sw != -1) {
+      int good = 1;
+      if (lane == 0) {
+        if (sw >= 0) good = wait_event(p, sw, (int32_t)(p.epoch * (uint32_t)p.evcount[sw]), cur, *sm.deadline) ? 1 : 0;
+        else
+          for (int i = 0; good && i < t->in_n; ++i) {
+            const int word = p.inwords[t->in_off + i];
+            good = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)p.evcount[word]), cur, *sm.deadline) ? 1 : 0;
+          }
+      }
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) break;
+    } else if (ld_relaxed(p.ctrl) != 0) {
+      break;
+    }
+    const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
+    const StreamDesc s = gemv_stream_desc(body, args, t->coord[0], sm.prod, (float*)(sm.prod + 16));
+    ok = produce_task(s, n, sm, cur);
+  }
+  // Nothing is left in flight on a normal exit (the consumers waited for every stage).  When the step was abandoned,
+  // wait (bounded) for the copies already issued before the CTA's shared memory goes away.
+  if (ld_relaxed(p.ctrl) != 0 && lane == 0) {
+    const uint32_t issued = n < ETXB_NSTAGE ? n : ETXB_NSTAGE;
+    for (uint32_t k = 0; k < issued; ++k) {
+      const uint32_t m = n - 1 - k, st = m % ETXB_NSTAGE, par = (m / ETXB_NSTAGE) & 1;
+      for (int spin = 0; spin < 2000000 && !mbar_try_wait(sm.full + st, par); ++spin) {}
+    }
+  }
+}
+
 __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_constant__ etxb_params p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int s_stop;
   __shared__ unsigned long long s_deadline;
   Smem sm;
-  sm.xs = (float*)smem_raw;
-  sm.scr = sm.xs + ETXB_XS_FLOATS;
-  if (threadIdx.x == 0) { s_stop = 0; s_deadline = globaltimer() + p.timeout_ns; }
+  sm.ring = smem_raw;
+  sm.xs = (float*)(smem_raw + ETXB_RING_BYTES);
+  sm.scr = (float*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES);
+  sm.full = (uint64_t*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4);
+  sm.empty = sm.full + ETXB_NSTAGE;
+  sm.prod = (int32_t*)(sm.empty + ETXB_NSTAGE);
+  sm.deadline = &s_deadline;
+  sm.ctrl = p.ctrl;
+  if (threadIdx.x == 0) {
+    s_stop = 0;
+    s_deadline = globaltimer() + p.timeout_ns;
+    for (int i = 0; i < ETXB_NSTAGE; ++i) { mbar_init(sm.full + i, 1); mbar_init(sm.empty + i, ETXB_CONSUMER_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
   __syncthreads();
   if ((int)blockIdx.x >= p.n_workers) return;
-  const int q1 = p.qbegin[blockIdx.x + 1];
-  for (int cur = p.qbegin[blockIdx.x]; cur < q1; ++cur) {
+  const int q0 = p.qbegin[blockIdx.x], q1 = p.qbegin[blockIdx.x + 1];
+  if (threadIdx.x >= ETXB_CONSUMERS) {
+    producer_loop(p, sm, q0, q1);
+    return;
+  }
+  uint32_t n = 0;                                                  // stages consumed so far (same count the producer keeps)
+  for (int cur = q0; cur < q1; ++cur) {
     if (threadIdx.x == 0) {
       const etxb_task* t = p.tasks + cur;
       const int in_off = t->in_off, in_n = t->in_n;
@@ -137,14 +196,15 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
       if (!ok) s_stop = 1;
       if (p.trace) p.trace[4 * (size_t)t->id + 1] = globaltimer();
     }
-    __syncthreads();
+    csync();
     if (s_stop) break;
-    run_body(p, cur, sm);
-    __syncthreads();                                               // every thread's stores are issued
+    run_body(p, cur, sm, n);
+    csync();                                                       // every consumer thread's stores are issued
     if (threadIdx.x == 0) {
       const etxb_task* t = p.tasks + cur;
       const int out_off = t->out_off, out_n = t->out_n, id = t->id;
-      if (out_n > 0) {
+      if (ld_relaxed(p.ctrl) != 0) s_stop = 1;                     // a stage wait gave up inside the body: no arrivals
+      else if (out_n > 0) {
         __threadfence();                                           // ... and ordered before the arrivals at GPU scope
         for (int i = 0; i < out_n; ++i) red_release_add(p.events + (size_t)p.outwords[out_off + i] * ETXB_EV_STRIDE, 1);
       }

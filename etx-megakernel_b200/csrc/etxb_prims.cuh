@@ -20,6 +20,32 @@ __device__ __forceinline__ int tidx() {
   return t;
 }
 
+// Barrier of the consumer warps only (named barrier 1): the producer warp never joins it.
+__device__ __forceinline__ void csync() { asm volatile("bar.sync 1, %0;" ::"n"(ETXB_CONSUMERS) : "memory"); }
+
+// ---------------------------------------------------------------------------------------------- mbarrier + bulk async copy
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// global -> shared bulk copy (TMA engine, untiled): 16-byte aligned addresses, size a multiple of 16; completes on `bar`
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------- memory ordering
 __device__ __forceinline__ int32_t ld_acquire(const int32_t* p) {
   int32_t v;
@@ -105,9 +131,9 @@ __device__ __forceinline__ float warp_max(float v) {
 // block sum in a fixed order: lanes by butterfly, warps left to right.  red: >= 32 floats.  All threads call.
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
-  __syncthreads();
+  csync();
   if ((tidx() & 31) == 0) red[tidx() >> 5] = v;
-  __syncthreads();
+  csync();
   float s = 0.f;
 #pragma unroll
   for (int w = 0; w < ETXB_NWARPS; ++w) s += red[w];
@@ -119,10 +145,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // blocks combined by a balanced binary tree.  Exact for n = 128 * 2^j, 128 <= n <= 16 * blockDim; other n fall back
 // to block_sum (same value up to fp32 rounding).  x in shared memory; red >= 32 floats; all threads call.
 __device__ __forceinline__ float sumsq_numpy_order(const float* x, int n, float* red) {
-  const bool pow2 = n >= 128 && (n & (n - 1)) == 0 && n <= 16 * (int)blockDim.x;
+  const bool pow2 = n >= 128 && (n & (n - 1)) == 0 && n <= 16 * ETXB_CONSUMERS;
   if (!pow2) {
     float s = 0.f;
-    for (int i = tidx(); i < n; i += blockDim.x) s = __fmaf_rn(x[i], x[i], s);
+    for (int i = tidx(); i < n; i += ETXB_CONSUMERS) s = __fmaf_rn(x[i], x[i], s);
     return block_sum(s, red);
   }
   const int nacc = n >> 4;                                         // 8 accumulators per 128-element block
@@ -136,9 +162,9 @@ __device__ __forceinline__ float sumsq_numpy_order(const float* x, int n, float*
   }
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, o));   // accumulators, then 4 blocks
-  __syncthreads();
+  csync();
   if ((t & 31) == 0) red[t >> 5] = r;
-  __syncthreads();
+  csync();
   const int nw = (nacc + 31) >> 5;                                 // power of two (or 1)
   float v = (t & 31) < nw ? red[t & 31] : 0.f;
   for (int o = 1; o < nw; o <<= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));

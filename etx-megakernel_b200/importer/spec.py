@@ -30,7 +30,7 @@ class Operator:
     dtypes: str = "bf16 tensors, fp32 reductions, int32 indices, int64 positions"
     checks: tuple = ()               # (parameter index, name, expression over p<i>, gx, gy, gz)
     arguments: dict = field(default_factory=dict)
-    block_rule: tuple = (("512", "512"), ("1", "1"), ("1", "1"))
+    block_rule: tuple = (("544", "544"), ("1", "1"), ("1", "1"))
 
     def grid(self, **context):
         return tuple(int(eval(v, {"__builtins__": {}}, context)) for v in self.grid_rule)
@@ -76,20 +76,20 @@ _GEMV_CHECKS = ((_I["K"], "K % 8", "p%d - p%d %% 8" % (_I["K"], _I["K"])),)
 
 
 def _gemv_op(name, form, grid, shape, reads, writes, roles):
-    return Operator(name, f"etxb::tile_{form}", grid, shape, dict(THREADS=_gemv.THREADS, XS_FLOATS=_gemv.XS_FLOATS, NB=_gemv.NB_ALLOWED),
+    return Operator(name, f"etxb::tile_{form}", grid, shape, dict(THREADS=_gemv.THREADS, MAX_K=_gemv.MAX_K, NB=_gemv.NB_ALLOWED),
                     reads, writes, layouts="W row-major [M][K] (MoE: [E][...]), activations contiguous",
                     checks=_GEMV_CHECKS, arguments={r: ARGUMENTS[r] for r in roles})
 
 
 OPERATORS = {
-    "dsl_gemv": _gemv_op("dsl_gemv", "gemv", ("CU", "1", "1"), "nb in (1,2,4,8), K % 8 == 0, nb*K <= 40960", ("weights", "input", "bias"),
+    "dsl_gemv": _gemv_op("dsl_gemv", "gemv", ("CU", "1", "1"), "K % 8 == 0, K <= 12288; stand-alone nb in (2,4,8) with nb*K <= 40960", ("weights", "input", "bias"),
                          ("output",), ("o_proj",)),
     "dsl_gemv_fold": _gemv_op("dsl_gemv_fold", "gemv", ("CU", "1", "1"), "as dsl_gemv; norm fold over R <= 16 rows", ("weights", "rows", "residual", "norm_weight", "expert_ids"),
                               ("output", "residual_out", "normed"), ("qkv", "router", "lm_head")),
-    "dsl_moe_up": _gemv_op("dsl_moe_up", "moe_up", ("TOPK*tpe", "1", "1"), "K <= 40960, rpt <= 2560", ("weights", "input", "expert_ids"), ("activation",), ("gate_up",)),
+    "dsl_moe_up": _gemv_op("dsl_moe_up", "moe_up", ("TOPK*tpe", "1", "1"), "K <= 12288, rpt <= 1024", ("weights", "input", "expert_ids"), ("activation",), ("gate_up",)),
     "dsl_moe_up_fold": _gemv_op("dsl_moe_up_fold", "moe_up", ("TOPK*tpe", "1", "1"), "as dsl_moe_up; E <= 256, TOPK <= 16", ("weights", "input", "logits"),
                                 ("activation", "expert_ids", "routing_weights"), ("moe_up",)),
-    "dsl_moe_down": _gemv_op("dsl_moe_down", "moe_down", ("TOPK*tpe", "1", "1"), "K <= 40960", ("weights", "activation", "expert_ids", "routing_weights"), ("expert_output",), ("moe_down", "down")),
+    "dsl_moe_down": _gemv_op("dsl_moe_down", "moe_down", ("TOPK*tpe", "1", "1"), "K <= 12288", ("weights", "activation", "expert_ids", "routing_weights"), ("expert_output",), ("moe_down", "down")),
     "dsl_moe_down_fold": _gemv_op("dsl_moe_down_fold", "moe_down", ("TOPK*tpe", "1", "1"), "as dsl_moe_down", ("weights", "activation", "logits"), ("expert_output",), ("moe_down",)),
     "dsl_topk": Operator("dsl_topk", "etxb::tile_topk", ("1", "1", "1"), "E <= 256, K <= 16, batch columns <= 16", dict(MAX_E=_topk.MAX_E, MAX_K=_topk.MAX_K),
                          ("logits",), ("routing_weights", "expert_ids", "token_expert_indices"),
@@ -128,7 +128,7 @@ def validate_values(export, values, grid):
             raise ValueError(f"{spec.name}: {label} conflicts: expected {expected}, got {values[index]}")
     if name in _gemv.FORMS:
         v = dict(zip((n for n, *_ in _gemv.PARAMS), values))
-        _gemv.check_shape(name, M=v["M"], K=v["K"], rpt=v["rpt"], nb=v["nb"])
+        _gemv.check_shape(name, M=v["M"], K=v["K"], rpt=v["rpt"], nb=v["nb"], mode=v["mode"])
         need = -(-v["M"] // v["rpt"]) * (1 if _gemv.FORMS[name] == "plain" else 1)
         if _gemv.FORMS[name] == "plain" and gx * gy * gz < need:
             raise ValueError(f"{spec.name}: grid of {gx * gy * gz} tasks leaves rows unwritten (needs {need})")

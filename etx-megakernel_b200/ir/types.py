@@ -82,6 +82,9 @@ class TileBody:
     coherence: str = "imported"
     arg_bytes: int = 0
     coherence_caps: tuple = ()
+    stream_after: str | None = None    # B200 backend: what the tile's WEIGHT ADDRESSES depend on -- "" nothing (static weights:
+                                       # the producer warp streams them ahead of the task's events), an event name (a
+                                       # single-counter event, e.g. the router's for expert weights), None = the task's in-events
 
 
 @dataclass

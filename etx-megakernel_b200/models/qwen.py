@@ -294,14 +294,14 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
     scale = float(np.float32(1.0 / np.sqrt(d.HD)))
     hf_mode = op_gemv.MODE_BF16_WTS
 
-    def tile(symbol):
-        return cuda_link(SRC, symbol)
+    def tile(symbol, stream_after=None):
+        return cuda_link(SRC, symbol, stream_after=stream_after)
 
-    def add(name, export, role, layer, blob, tasks, grid, in_ev, in_map, out_ev, out_map, out_shape, out_count, M=0, K=0):
+    def add(name, export, role, layer, blob, tasks, grid, in_ev, in_map, out_ev, out_map, out_shape, out_count, M=0, K=0, after=None):
         off = pool.add(blob)
         pool.rows.append((name, export, role, layer, off, tasks, M, K))
         g.etensor(out_ev, out_shape, wait_count=out_count)
-        g.call_device(name, grid, tile("etx_tile_" + export), resource=res, args=["impargs"], consts=(off,),
+        g.call_device(name, grid, tile("etx_tile_" + export, after), resource=res, args=["impargs"], consts=(off,),
                       in_edges={in_ev: in_map}, out_edges={out_ev: out_map}, duration_us=2.0)
         return out_ev
 
@@ -321,7 +321,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                           resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else slots, eps=d.eps,
                           ids=0 if (first or not d.moe) else ptr("ti"), wts=W("bqkv") if d.bias else 0,
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0), nb=1)
-        prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H)
+        prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
         # ---- attention prep per kv head
         blob = argblock.pack_named(ent["dsl_attnprep"], (d.NKV, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,
                                    kw=W("kn") if d.qk_norm else 0, cos_sin=ptr("cos_sin"), positions=ptr("positions"),
@@ -340,13 +340,13 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         # ---- o_proj
         t, rpt = sz.o
         blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1)
-        prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD)
+        prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD, after="")
         if d.moe:
             # ---- router with the post-attention norm fold: task 0 stores resid2 and the normed vector
             t, rpt = sz.router
             blob = gemv_block("dsl_gemv_fold", t, W=W("wr"), x=ptr("o_norm"), out=ptr("rlog"), M=d.E, K=d.H, rpt=rpt, tpe=1, rows=ptr("o"),
                               resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=1, eps=d.eps, mode=op_gemv.MODE_NORM, nb=1)
-            prev = add(f"router_{L}", "dsl_gemv_fold", "router", L, blob, t, (t,), prev, "i->(0)", f"E_rt_{L}", "i->(0)", (1,), t, d.E, d.H)
+            prev = add(f"router_{L}", "dsl_gemv_fold", "router", L, blob, t, (t,), prev, "i->(0)", f"E_rt_{L}", "i->(0)", (1,), t, d.E, d.H, after="")
             topk_mode = (op_gemv.MODE_TOPK_RENORM if d.norm_topk else op_gemv.MODE_TOPK) | hf_mode
             if not fold_topk:
                 from ..ops import topk as op_topk2
@@ -362,10 +362,13 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                        prev, "i->(0)", f"E_up_{L}", f"i->(i/{tpe})", (slots,), tpe, d.MI, d.H)
             up_tpe = tpe
             tpe, rpt = sz.down
-            blob = gemv_block("dsl_moe_down", slots * tpe, W=W("w2"), x=ptr("mc2"), out=ptr("mc3"), ids=ptr("ti"), wts=ptr("tw"),
-                              estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, eps=d.eps, nb=1)
-            prev = add(f"moe_down_{L}", "dsl_moe_down", "moe_down", L, blob, slots * tpe, (slots * tpe,), prev, f"i->(i/{tpe})",
-                       f"E_dn_{L}", "i->(0)", (1,), slots * tpe, d.H, d.MI)
+            dn_export = "dsl_moe_down_fold" if fold_topk else "dsl_moe_down"
+            blob = gemv_block(dn_export, slots * tpe, W=W("w2"), x=ptr("mc2"), out=ptr("mc3"), ids=ptr("ti"), wts=ptr("tw"),
+                              estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps, mode=topk_mode if fold_topk else 0,
+                              E=d.E, logits=ptr("rlog"), nb=1)
+            # expert weights depend on the routing only: with the top-k folded in, the stream may start once the router is done
+            prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, slots * tpe, (slots * tpe,), prev, f"i->(i/{tpe})",
+                       f"E_dn_{L}", "i->(0)", (1,), slots * tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None)
             del up_tpe
         else:
             # ---- dense SwiGLU: gate+up with the post-attention norm fold, then down
@@ -373,17 +376,17 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
             blob = gemv_block("dsl_moe_up", tpe, W=W("wgu"), x=ptr("o_norm"), out=ptr("mc2"), estride=0, M=d.INTER, K=d.H, rpt=rpt, tpe=tpe,
                               rows=ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=1, eps=d.eps,
                               mode=op_gemv.MODE_NORM, nb=1)
-            prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H)
+            prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H, after="")
             tpe, rpt = sz.down
             blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("mc3"), estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
                               eps=d.eps, nb=1)
-            prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER)
+            prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="")
     # ---- lm_head with the final-norm fold, then greedy sampling
     t, rpt = sz.lm
     blob = gemv_block("dsl_gemv_fold", t, W=ptr("embed") if d.tie else ptr("lm_head"), x=ptr("hn"), out=ptr("logits"), M=d.V, K=d.H, rpt=rpt,
                       tpe=1, rows=ptr("mc3"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=slots, eps=d.eps,
                       ids=ptr("ti") if d.moe else 0, mode=op_gemv.MODE_NORM, nb=1)
-    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H)
+    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},
                   out_edges={"E_argmax": "i->i"}, duration_us=3.0)

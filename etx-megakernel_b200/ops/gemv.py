@@ -27,10 +27,12 @@ PARAMS = [("W", "ptr addrspace(1)", 0, 8), ("x", "ptr addrspace(1)", 8, 8), ("ou
 FORMS = {"dsl_gemv": "plain", "dsl_moe_up": "silu_mul", "dsl_moe_down": "scale",
          "dsl_gemv_fold": "plain", "dsl_moe_up_fold": "silu_mul", "dsl_moe_down_fold": "scale"}
 MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS = 1, 2, 3, 0x100, 0x200
-THREADS = 512
-XS_FLOATS = 40960          # staged activation floats per CTA: nb * K must fit
-MAX_ROWS_UP = 2560         # gate+up rows one moe_up task can hold in its scratch
+THREADS = 544              # 16 consumer warps + the producer warp of the persistent CTA
+MAX_K = 12288              # a streamed row (and its bf16 activation vector in shared memory)
+MAX_K_NORM = 8192          # the norm fold works on fp32 in shared memory
+MAX_ROWS_UP = 1024         # gate+up results one moe_up task holds in shared memory
 NB_ALLOWED = (1, 2, 4, 8)
+NB_XS_FLOATS = 40960       # stand-alone batched GEMV (nb > 1): nb * K floats of staged activations
 
 
 def type_string() -> str:
@@ -41,14 +43,22 @@ def import_entries(threads: int = THREADS) -> dict:
     return {e: entry(e, form, PARAMS, ARG_BYTES, GRID_OFF, threads, f"ETX DSL GEMV ({form})") for e, form in FORMS.items()}
 
 
-def check_shape(export: str, *, M: int, K: int, rpt: int, nb: int = 1) -> None:
+def check_shape(export: str, *, M: int, K: int, rpt: int, nb: int = 1, mode: int = 0) -> None:
     """Host-side guard of what the CUDA tiles support; raises before anything is packed."""
+    nb = max(nb, 1)
     if K % 8:
         raise ValueError(f"{export}: K={K} must be a multiple of 8 (16-byte weight vectors)")
-    if max(nb, 1) not in NB_ALLOWED:
+    if nb not in NB_ALLOWED:
         raise ValueError(f"{export}: nb={nb} activation columns; supported {NB_ALLOWED}")
-    if max(nb, 1) * ((K + 7) // 8 * 8) > XS_FLOATS:
-        raise ValueError(f"{export}: nb*K={max(nb, 1) * K} exceeds the {XS_FLOATS}-float activation stage")
+    if nb > 1:
+        if FORMS[export] != "plain" or (mode & 0xff):
+            raise ValueError(f"{export}: nb > 1 is built for the plain stand-alone GEMV only")
+        if nb * K > NB_XS_FLOATS:
+            raise ValueError(f"{export}: nb*K={nb * K} exceeds the {NB_XS_FLOATS}-float activation stage")
+    elif K > MAX_K:
+        raise ValueError(f"{export}: K={K} exceeds {MAX_K} (one row must fit a 32 KB ring stage)")
+    if (mode & 0xff) == MODE_NORM and K > MAX_K_NORM:
+        raise ValueError(f"{export}: norm fold over K={K} > {MAX_K_NORM}")
     if FORMS[export] == "silu_mul" and rpt > MAX_ROWS_UP:
         raise ValueError(f"{export}: rpt={rpt} rows per task exceeds {MAX_ROWS_UP}")
     if rpt < 1 or M < 1:

@@ -152,7 +152,19 @@ class Plan:
                 if a not in names:
                     raise ValueError(f"grid {gname!r} names tensor {a!r} which the session does not bind")
             idx = [names.index(a) for a in argn] + [-1] * (MAX_ARGS - len(argn))
-            types += struct.pack("<i4i4ii2i", TILE_SYMBOLS[g.body.symbol], *cst, *idx, 1 if g.body.prefetch else 0, 0, 0)
+            body = TILE_SYMBOLS[g.body.symbol]
+            after = g.body.stream_after
+            if after is None:
+                sword = -2
+            elif after == "":
+                sword = -1
+            else:
+                if after not in self.events or self.events[after].numel != 1:
+                    raise ValueError(f"grid {gname!r}: stream_after={after!r} must name an event with a single counter")
+                if not any(after in self.graph.grid(p.grid).out_edges for p in self.tasks if p.id < self.task_index[(gname, self.inst.tasks[gname][0])]):
+                    raise ValueError(f"grid {gname!r}: stream_after={after!r} is not produced before it")
+                sword = self.events[after].offset
+            types += struct.pack("<i4i4iiii", body, *cst, *idx, 1 if 3 <= body <= 5 else 0, sword, 0)
         W = self.workers_per_device()
         qbegin, rows, inw, outw = [0], [], [], []
         for w in range(W):

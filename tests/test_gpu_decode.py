@@ -103,13 +103,16 @@ def check_greedy(od, W, prompt, n_gen, ctx, must_be_identical=False):
     return got == want
 
 
-@pytest.mark.parametrize("seed,identical", [(0, False), (1, True)])
-def test_thirty_two_greedy_tokens_moe(seed, identical):
-    """32 greedy tokens against the oracle on a 3-layer MoE model with the Qwen3 head geometry."""
+def test_thirty_two_greedy_tokens_moe():
+    """32 greedy tokens against the oracle on a 3-layer MoE model with the Qwen3 head geometry, four seeds: every
+    difference must be a near-tie of the oracle's own logits, and most seeds must match token for token."""
     od = O.Dims(name="m", H=1024, NH=16, NKV=4, HD=128, INTER=0, L=3, V=4096, qk_norm=True, moe=True, E=32, TOPK=8, MI=256, norm_topk=True)
-    W = O.SyntheticWeights(od, seed=seed, gamma="ones")
-    prompt = np.random.default_rng(seed).integers(0, od.V, 40)
-    check_greedy(od, W, prompt, 32, 96, must_be_identical=identical)
+    identical = 0
+    for seed in range(4):
+        W = O.SyntheticWeights(od, seed=seed, gamma="ones")
+        prompt = np.random.default_rng(seed).integers(0, od.V, 40)
+        identical += check_greedy(od, W, prompt, 32, 96)
+    assert identical >= 2, f"only {identical} of 4 seeds gave 32 identical tokens"
 
 
 def test_thirty_two_greedy_tokens_dense_with_bias():
