@@ -20,7 +20,9 @@
 static_assert(sizeof(etxb_gemv_args) == 160 && offsetof(etxb_gemv_args, grid) == 144, "GEMV block layout (etx/ops/gemv.py:80-94)");
 static_assert(sizeof(etxb_topk_args) == 64 && offsetof(etxb_topk_args, grid) == 48, "top-k block layout (etx/ops/topk.py:16-23)");
 static_assert(sizeof(etxb_attnprep_args) == 112 && offsetof(etxb_attnprep_args, grid) == 96, "attnprep block layout (etx/ops/attnprep.py:11-15)");
+static_assert(sizeof(etxb_attnf_args) == 176 && offsetof(etxb_attnf_args, grid) == 160, "fused attention block layout");
 static_assert(sizeof(etxb_attn_args) == 128 && offsetof(etxb_attn_args, grid) == 112, "attention block layout");
+static_assert(ETXB_SMEM_BYTES + 1024 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may opt into");
 static_assert(sizeof(etxb_task) == 40 && sizeof(etxb_type) == 48, "plan table layouts");
 static_assert(sizeof(etxb_stepv) == sizeof(etxb_step_params), "step parameter layouts must agree");
 
@@ -154,6 +156,7 @@ static int32_t parse_plan(etxb_session* s, const unsigned char* b, size_t n) {
     if (ty.body >= ETXB_BODY_GEMV && ty.args[0] < 0) return fail(ETXB_E_PLAN, "plan blob: tile without an argument tensor");
   }
   if (pool.size() != s->tensors[0].bytes) return fail(ETXB_E_PLAN, "plan blob: tensor 0 must be the argument pool");
+  if (h.pool_bytes < 192) pool.resize(192, 0);
   // upload
   CU(cudaSetDevice(s->device));
   auto up = [&](void** d, const void* src, size_t bytes) -> cudaError_t {
@@ -167,6 +170,7 @@ static int32_t parse_plan(etxb_session* s, const unsigned char* b, size_t n) {
   CU(up((void**)&s->d_evcount, s->evcount.data(), h.n_events * 4));
   CU(up((void**)&s->d_inwords, s->inwords.data(), h.n_in * 4));
   CU(up((void**)&s->d_outwords, s->outwords.data(), h.n_out * 4));
+  pool.resize(pool.size() + 256, 0);                               // the context prefetch reads 192 bytes from a block start
   CU(up((void**)&s->d_pool, pool.data(), pool.size()));
   CU(cudaMalloc((void**)&s->d_type_args, (size_t)h.n_types * ETXB_MAX_ARGS * sizeof(void*)));
   const size_t evbytes = (size_t)(h.n_events ? h.n_events : 1) * ETXB_EV_STRIDE * 4;

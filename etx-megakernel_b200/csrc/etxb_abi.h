@@ -24,8 +24,9 @@
 #define ETXB_XB_ELEMS 12288          // streamed GEMV rows are at most 12288 elements long
 #define ETXB_G_OFF 57344
 #define ETXB_G_FLOATS 2048
-#define ETXB_SCR_FLOATS 512
-#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512)
+#define ETXB_SCR_FLOATS 256
+#define ETXB_CTX_BYTES 384           // one prefetched task context: header + argument block copy
+#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 256 + 2 * ETXB_CTX_BYTES)
 #define ETXB_ATTN_PART 32            // KV positions per attention task
 #define ETXB_MAX_NB 8                // activation columns of the stand-alone batched GEMV kernel
 #define ETXB_NB_XS_FLOATS 40960      // its staged activations: nb * K floats
@@ -139,6 +140,18 @@ struct etxb_attn_args {
   float scale; int32_t NH, NKV, HD, BS, X, max_parts, max_blocks;                                        // 72..103
   int32_t pad[2];                                                                                        // 104..111
   uint32_t grid[3], nblocks;                                                                             // 112..127
+};
+
+// fused attention phase (this library's own): q/k norm + rope + cache write of the new position, split-KV attention over
+// 32 positions, and the merge of the partitions by the last task of each kv head to finish (counters: one monotonic
+// int32 per kv head, never reset).  Task blk = part * NKV + h.
+struct etxb_attnf_args {
+  void* qkv; const void* qw; const void* kw; const void* cos_sin; void* kc; void* vc;                            // 0..47
+  const int32_t* block_tables; const int32_t* seq_lens; const int64_t* positions; const int64_t* slot_mapping;  // 48..79
+  float* exp_sums; float* max_logits; float* tmp_out; void* out; int32_t* counters;                             // 80..119
+  float scale, eps; int32_t NH, NKV, HD, BS, X, max_parts;                                                      // 120..151
+  int32_t pad[2];                                                                                               // 152..159
+  uint32_t grid[3], nblocks;                                                                                    // 160..175
 };
 
 // split-K demo (etx/operators/splitk_sum.py): parts[i][j] = sum of a chunk, out[i] = sum over j.

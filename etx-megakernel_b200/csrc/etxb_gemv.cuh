@@ -263,8 +263,10 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
     csync();
   }
   const int nv = K >> 3;
-  for (int i = tidx(); i < nv; i += ETXB_CONSUMERS) {
+  uint4 lw[2];                                                     // norm weights of this thread's (at most two) vectors, fetched with the rows
+  for (int i = tidx(), it = 0; i < nv; i += ETXB_CONSUMERS, ++it) {
     float z[8];
+    if (it < 2) lw[it] = __ldg((const uint4*)((const __nv_bfloat16*)ln + 8 * i));
     const uint4 ri = ld_act16((const __nv_bfloat16*)rin + 8 * i);
     const float rf[8] = {bf_lo(ri.x), bf_hi(ri.x), bf_lo(ri.y), bf_hi(ri.y), bf_lo(ri.z), bf_hi(ri.z), bf_lo(ri.w), bf_hi(ri.w)};
     if (rows == nullptr || R == 0) {
@@ -302,8 +304,8 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
   csync();
   const float ss = sumsq_numpy_order(xf, K, scr);
   const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
-  for (int i = tidx(); i < nv; i += ETXB_CONSUMERS) {
-    const uint4 w = __ldg((const uint4*)((const __nv_bfloat16*)ln + 8 * i));
+  for (int i = tidx(), it = 0; i < nv; i += ETXB_CONSUMERS, ++it) {
+    const uint4 w = it == 0 ? lw[0] : lw[1];
     const float wf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
     float v[8];
 #pragma unroll

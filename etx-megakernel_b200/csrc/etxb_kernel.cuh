@@ -86,14 +86,40 @@ __device__ __forceinline__ void tile_splitk_sum(const unsigned char* a, int i) {
   }
 }
 
-// Run the body of task `cur` on the consumer warps.  Everything it needs is re-read from the task table here, so that
-// nothing but the queue cursor and the stage counter stay live across a tile.
-__device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Smem& sm, uint32_t& n) {
+// A task's context, fetched into shared memory one task ahead (by the last consumer warp, at the start of the previous
+// body), so that the chain task table -> type table -> argument pointer -> argument block -> data loses four dependent
+// global round trips: the tiles read their argument block from shared memory and thread 0 finds its event words here.
+struct TaskCtx {
+  int32_t body, c0, c1, id, in_n, out_n, in_off, out_off;
+  int32_t in_word[4], in_cnt[4], out_word[4];
+  int32_t pad[4];
+  unsigned char args[ETXB_CTX_BYTES - 96];
+};
+static_assert(sizeof(TaskCtx) == ETXB_CTX_BYTES, "context slot size");
+
+// one warp; all 32 lanes call
+__device__ __forceinline__ void load_ctx(const etxb_params& p, int cur, TaskCtx* c) {
+  const int lane = tidx() & 31;
   const etxb_task* t = p.tasks + cur;
-  const int type = t->type, c0 = t->coord[0], c1 = t->coord[1];
+  const int type = t->type;
   const etxb_type* ty = p.types + type;
-  const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)c1 * ty->cst[1];
-  switch (ty->body) {
+  const int body = ty->body;
+  const unsigned char* base = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
+  if (body >= 3 && lane < 24) *(uint64_t*)(c->args + 8 * lane) = __ldg((const uint64_t*)(base + 8 * lane));   // 192 bytes: every block is <= 160
+  if (lane == 0) {
+    c->body = body; c->c0 = t->coord[0]; c->c1 = t->coord[1]; c->id = t->id;
+    c->in_n = t->in_n; c->out_n = t->out_n; c->in_off = t->in_off; c->out_off = t->out_off;
+  }
+  if (lane < 4 && lane < t->in_n) { const int w = p.inwords[t->in_off + lane]; c->in_word[lane] = w; c->in_cnt[lane] = p.evcount[w]; }
+  if (lane >= 4 && lane < 8 && lane - 4 < t->out_n) c->out_word[lane - 4] = p.outwords[t->out_off + lane - 4];
+  __syncwarp();
+}
+
+// Run the body of the task whose context is `c` on the consumer warps.
+__device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c, int cur, const Smem& sm, uint32_t& n) {
+  const unsigned char* args = c->args;
+  const int c0 = c->c0, c1 = c->c1;
+  switch (c->body) {
     case 0: break;
     case 1: tile_prologue(p.step); break;
     case 2: tile_argmax(p.step, sm); break;
@@ -101,11 +127,12 @@ __device__ __forceinline__ void run_body(const etxb_params& p, int cur, const Sm
     case 4: tile_moe_up(args, c0, sm, n, cur); break;
     case 5: tile_moe_down(args, c0, sm, n, cur); break;
     case 6: tile_topk(args, c0, sm); break;
-    case 7: tile_attnprep(args, c0, sm); break;
-    case 8: tile_attn(args, c0, sm); break;
-    case 9: tile_attn_reduce(args, c0, sm); break;
+    case 7: tile_attnprep(args, c0, sm, p.step); break;
+    case 8: tile_attn(args, c0, sm, p.step); break;
+    case 9: tile_attn_reduce(args, c0, sm, p.step); break;
     case 10: tile_splitk_part(args, c0, c1, sm); break;
     case 11: tile_splitk_sum(args, c0); break;
+    case 12: tile_attn_fused(args, c0, sm, p.step); break;
     default:
       if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);
       break;
@@ -182,32 +209,38 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     producer_loop(p, sm, q0, q1);
     return;
   }
+  TaskCtx* ctx = (TaskCtx*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 256);
+  if (q0 < q1 && threadIdx.x >= ETXB_CONSUMERS - 32) load_ctx(p, q0, ctx);
+  csync();
   uint32_t n = 0;                                                  // stages consumed so far (same count the producer keeps)
   for (int cur = q0; cur < q1; ++cur) {
+    const TaskCtx* c = ctx + ((cur - q0) & 1);
     if (threadIdx.x == 0) {
-      const etxb_task* t = p.tasks + cur;
-      const int in_off = t->in_off, in_n = t->in_n;
-      if (p.trace) p.trace[4 * (size_t)t->id] = globaltimer();
+      const int in_n = c->in_n;
+      if (p.trace) p.trace[4 * (size_t)c->id] = globaltimer();
       bool ok = ld_relaxed(p.ctrl) == 0;
       for (int i = 0; ok && i < in_n; ++i) {
-        const int word = p.inwords[in_off + i];
-        ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)p.evcount[word]), cur, s_deadline);
+        int word, cnt;
+        if (i < 4) { word = c->in_word[i]; cnt = c->in_cnt[i]; }
+        else { word = p.inwords[c->in_off + i]; cnt = p.evcount[word]; }
+        ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
       }
       if (!ok) s_stop = 1;
-      if (p.trace) p.trace[4 * (size_t)t->id + 1] = globaltimer();
+      if (p.trace) p.trace[4 * (size_t)c->id + 1] = globaltimer();
     }
     csync();
     if (s_stop) break;
-    run_body(p, cur, sm, n);
+    if (threadIdx.x >= ETXB_CONSUMERS - 32 && cur + 1 < q1) load_ctx(p, cur + 1, ctx + ((cur + 1 - q0) & 1));   // next task's context
+    run_body(p, c, cur, sm, n);
     csync();                                                       // every consumer thread's stores are issued
     if (threadIdx.x == 0) {
-      const etxb_task* t = p.tasks + cur;
-      const int out_off = t->out_off, out_n = t->out_n, id = t->id;
+      const int out_n = c->out_n, id = c->id;
       if (ld_relaxed(p.ctrl) != 0) s_stop = 1;                     // a stage wait gave up inside the body: no arrivals
-      else if (out_n > 0) {
-        __threadfence();                                           // ... and ordered before the arrivals at GPU scope
-        for (int i = 0; i < out_n; ++i) red_release_add(p.events + (size_t)p.outwords[out_off + i] * ETXB_EV_STRIDE, 1);
-      }
+      else
+        for (int i = 0; i < out_n; ++i) {                          // release: orders the CTA's stores (seen through the barrier) before the count
+          const int word = i < 4 ? c->out_word[i] : p.outwords[c->out_off + i];
+          red_release_add(p.events + (size_t)word * ETXB_EV_STRIDE, 1);
+        }
       if (p.trace) { p.trace[4 * (size_t)id + 2] = globaltimer(); p.trace[4 * (size_t)id + 3] = blockIdx.x; }
       if (p.exec_count) atomicAdd(p.exec_count + id, 1);
     }

@@ -70,6 +70,10 @@ ARGUMENTS = {
              ("i32", "BS"), ("i32", "X"), ("i32", "parts"), ("i32", "MAXBLK")],
 }
 ARGUMENTS["reduce"] = ARGUMENTS["attn"]
+ARGUMENTS["attn_fused"] = [("ptr", "qkv"), ("ptr", 'W(pl + "qn")'), ("ptr", 'W(pl + "kn")'), ("ptr", 'W("cos_sin")'), ("ptr", "kc[layer]"),
+                           ("ptr", "vc[layer]"), ("ptr", "block_tables"), ("ptr", "seq_lens"), ("ptr", "positions"), ("ptr", "slot_mapping"),
+                           ("ptr", "exp_sums"), ("ptr", "max_logits"), ("ptr", "tmp_out"), ("ptr", "attn_out"), ("ptr", "attn_counters + layer * NKV"),
+                           ("f32", "scale"), ("f32", "eps"), ("i32", "NH"), ("i32", "NKV"), ("i32", "HD"), ("i32", "BS"), ("i32", "X"), ("i32", "parts")]
 
 _I = {n: i for i, (n, *_rest) in enumerate(_gemv.PARAMS)}
 _GEMV_CHECKS = ((_I["K"], "K % 8", "p%d - p%d %% 8" % (_I["K"], _I["K"])),)
@@ -102,6 +106,11 @@ OPERATORS = {
                             ("query", "key_cache", "value_cache", "block_tables", "seq_lens"), ("exp_sums", "max_logits", "tmp_out"),
                             layouts="query row-major, key cache [block, head, HD/8, BS, 8], value cache [block, head, HD, BS]",
                             checks=((14, "X", "8"),), arguments={"attn": ARGUMENTS["attn"]}),
+    "attn_fused": Operator("attn_fused", "etxb::tile_attn_fused", ("parts*NKV", "1", "1"), "G + 2 <= 16, G * HD <= 2048, G * parts <= 8192, PART = 32",
+                           dict(PART=_attn.PART, X=8), ("qkv", "q_weight", "k_weight", "cos_sin", "key_cache", "value_cache", "block_tables", "seq_lens",
+                                                       "positions", "slot_mapping"), ("key_cache", "value_cache", "exp_sums", "max_logits", "tmp_out", "output", "counters"),
+                           layouts="key cache [block, head, HD/8, BS, 8], value cache [block, head, HD, BS]",
+                           checks=((21, "X", "8"),), arguments={"attn_fused": ARGUMENTS["attn_fused"]}),
     "attn_reduce": Operator("attn_reduce", "etxb::tile_attn_reduce", ("NH", "1", "1"), "max_parts <= 4096", dict(PART=_attn.PART),
                             ("exp_sums", "max_logits", "tmp_out", "seq_lens"), ("output",), arguments={"reduce": ARGUMENTS["reduce"]}),
 }
@@ -142,5 +151,9 @@ def validate_values(export, values, grid):
         _prep.check_shape(values[8], values[9], values[10], values[12], values[13])
         if gx * gy * gz != values[9]:
             raise ValueError(f"{spec.name}: grid must be one task per kv head")
+    elif name == "attn_fused":
+        _attn.check_fused(values[17], values[18], values[19], values[20], values[21], values[22])
+        if gx * gy * gz != values[22] * values[18]:
+            raise ValueError(f"{spec.name}: grid must be max_parts * NKV tasks (the merge counts them)")
     elif name in ("attn_decode", "attn_reduce"):
         _attn.check_shape(values[10], values[11], values[12], values[13], values[14], values[15])

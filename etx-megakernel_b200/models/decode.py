@@ -44,7 +44,7 @@ def to_device_weights(packed: dict, device) -> dict:
 
 class DecodeProgram:
     def __init__(self, dims: Q.Dims, weights: dict, device: int = 0, maxlen: int = 1072, steps: int | None = None, machine="b200",
-                 fold_topk: bool = True, workers: int | None = None):
+                 fold_topk: bool = True, fused_attn: bool = True, workers: int | None = None):
         self.d, self.maxlen = dims, maxlen
         self.dev = torch.device("cuda", device)
         self.machine = load_machine(machine) if isinstance(machine, str) else machine
@@ -64,7 +64,7 @@ class DecodeProgram:
             if t is None:
                 t = self.w[name]
             return t.data_ptr()
-        self.graph, self.pool, self.sizing = Q.build_graph(dims, ptr, maxlen, self.machine, fold_topk=fold_topk)
+        self.graph, self.pool, self.sizing = Q.build_graph(dims, ptr, maxlen, self.machine, fold_topk=fold_topk, fused_attn=fused_attn)
         pool = self.pool.bytes()
         self.plan = compile_graph(self.graph, self.machine, {"POOL": len(pool)}, options=PassOptions(workers=workers))
         self.session = Session(self.plan, {"vl": self.vl}, pool, device)

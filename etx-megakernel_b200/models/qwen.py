@@ -160,7 +160,8 @@ def buffer_shapes(d: Dims, maxlen: int, steps: int, parts: int) -> dict:
          "block_tables": ((nblk,), "i32"), "token_in": ((steps + 2,), "i32"), "token_out": ((steps + 1,), "i32"),
          "token_time": ((2 * (steps + 1),), "i64"),
          "exp_sums": ((d.NH, parts), "f32"), "max_logits": ((d.NH, parts), "f32"), "tmp_out": ((d.NH, parts, d.HD), "f32"),
-         "kc": ((d.L, nblk, d.NKV, d.HD // X, BS, X), "bf16"), "vc": ((d.L, nblk, d.NKV, d.HD, BS), "bf16")}
+         "kc": ((d.L, nblk, d.NKV, d.HD // X, BS, X), "bf16"), "vc": ((d.L, nblk, d.NKV, d.HD, BS), "bf16"),
+         "attn_counters": ((d.L, d.NKV), "i32")}
     if d.moe:
         s.update({"rlog": ((d.E,), "bf16"), "tw": ((d.TOPK,), "f32"), "ti": ((d.TOPK,), "i32"), "tei": ((d.TOPK,), "i32"),
                   "mc2": ((d.TOPK, d.MI), "bf16"), "mc3": ((d.TOPK, d.H), "bf16")})
@@ -269,7 +270,7 @@ class ArgPool:
         return bytes(self.buf + b"\0" * (-len(self.buf) % 16))
 
 
-def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = "b200", *, fold_topk: bool = True):
+def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = "b200", *, fold_topk: bool = True, fused_attn: bool = True):
     """The decode step of `d` as a Graph plus its argument pool.
 
     ptr(name) -> device address (int) of a buffer (buffer_shapes) or packed weight (weight_shapes); "kc" / "vc" are the
@@ -322,21 +323,34 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                           ids=0 if (first or not d.moe) else ptr("ti"), wts=W("bqkv") if d.bias else 0,
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0), nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
-        # ---- attention prep per kv head
-        blob = argblock.pack_named(ent["dsl_attnprep"], (d.NKV, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,
-                                   kw=W("kn") if d.qk_norm else 0, cos_sin=ptr("cos_sin"), positions=ptr("positions"),
-                                   kc=ptr("kc") + L * kv_layer_bytes, vc=ptr("vc") + L * kv_layer_bytes, slot_mapping=ptr("slot_mapping"),
-                                   NH=d.NH, NKV=d.NKV, HD=d.HD, eps=d.eps, BS=BS, X=X)
-        prev = add(f"prep_{L}", "dsl_attnprep", "prep", L, blob, d.NKV, (d.NKV,), prev, "i->(0)", f"E_prep_{L}", "i->i", (d.NKV,), 1)
-        # ---- attention partitions and their merge
-        ablob = argblock.pack_named(ent["attn_decode"], (sz.parts * d.NKV, 1, 1), q=ptr("qkv"), kc=ptr("kc") + L * kv_layer_bytes,
-                                    vc=ptr("vc") + L * kv_layer_bytes, block_tables=ptr("block_tables"), seq_lens=ptr("seq_lens"),
-                                    exp_sums=ptr("exp_sums"), max_logits=ptr("max_logits"), tmp_out=ptr("tmp_out"), out=ptr("attn_out"),
-                                    scale=scale, NH=d.NH, NKV=d.NKV, HD=d.HD, BS=BS, X=X, max_parts=sz.parts, max_blocks=nblk)
-        prev = add(f"attn_{L}", "attn_decode", "attn", L, ablob, sz.parts * d.NKV, (sz.parts * d.NKV,), prev, f"i->(i%{d.NKV})",
-                   f"E_attn_{L}", f"i->(i%{d.NKV})", (d.NKV,), sz.parts)
-        rblob = ablob[:op_attn.GRID_OFF] + np.asarray([d.NH, 1, 1, d.NH], "<u4").tobytes()
-        prev = add(f"reduce_{L}", "attn_reduce", "reduce", L, rblob, d.NH, (d.NH,), prev, f"i->(i/{d.G})", f"E_red_{L}", "i->(0)", (1,), d.NH)
+        if fused_attn:
+            # ---- the attention phase as one grid: prep + 32-position partitions + merge by the last task of each kv head
+            blob = argblock.pack_named(ent["attn_fused"], (sz.parts * d.NKV, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,
+                                       kw=W("kn") if d.qk_norm else 0, cos_sin=ptr("cos_sin"), kc=ptr("kc") + L * kv_layer_bytes,
+                                       vc=ptr("vc") + L * kv_layer_bytes, block_tables=ptr("block_tables"), seq_lens=ptr("seq_lens"),
+                                       positions=ptr("positions"), slot_mapping=ptr("slot_mapping"), exp_sums=ptr("exp_sums"),
+                                       max_logits=ptr("max_logits"), tmp_out=ptr("tmp_out"), out=ptr("attn_out"),
+                                       counters=ptr("attn_counters") + 4 * L * d.NKV, scale=scale, eps=d.eps, NH=d.NH, NKV=d.NKV, HD=d.HD,
+                                       BS=BS, X=X, max_parts=sz.parts)
+            prev = add(f"attn_{L}", "attn_fused", "attn_fused", L, blob, sz.parts * d.NKV, (sz.parts * d.NKV,), prev, "i->(0)",
+                       f"E_red_{L}", "i->(0)", (1,), sz.parts * d.NKV)
+        else:
+            # ---- attention prep per kv head
+            blob = argblock.pack_named(ent["dsl_attnprep"], (d.NKV, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,
+                                       kw=W("kn") if d.qk_norm else 0, cos_sin=ptr("cos_sin"), positions=ptr("positions"),
+                                       kc=ptr("kc") + L * kv_layer_bytes, vc=ptr("vc") + L * kv_layer_bytes, slot_mapping=ptr("slot_mapping"),
+                                       NH=d.NH, NKV=d.NKV, HD=d.HD, eps=d.eps, BS=BS, X=X)
+            prev = add(f"prep_{L}", "dsl_attnprep", "prep", L, blob, d.NKV, (d.NKV,), prev, "i->(0)", f"E_prep_{L}", "i->i", (d.NKV,), 1)
+            # ---- attention partitions and their merge
+            ablob = argblock.pack_named(ent["attn_decode"], (sz.parts * d.NKV, 1, 1), q=ptr("qkv"), kc=ptr("kc") + L * kv_layer_bytes,
+                                        vc=ptr("vc") + L * kv_layer_bytes, block_tables=ptr("block_tables"), seq_lens=ptr("seq_lens"),
+                                        exp_sums=ptr("exp_sums"), max_logits=ptr("max_logits"), tmp_out=ptr("tmp_out"), out=ptr("attn_out"),
+                                        scale=scale, NH=d.NH, NKV=d.NKV, HD=d.HD, BS=BS, X=X, max_parts=sz.parts, max_blocks=nblk)
+            prev = add(f"attn_{L}", "attn_decode", "attn", L, ablob, sz.parts * d.NKV, (sz.parts * d.NKV,), prev, f"i->(i%{d.NKV})",
+                       f"E_attn_{L}", f"i->(i%{d.NKV})", (d.NKV,), sz.parts)
+            rblob = ablob[:op_attn.GRID_OFF] + np.asarray([d.NH, 1, 1, d.NH], "<u4").tobytes()
+            prev = add(f"reduce_{L}", "attn_reduce", "reduce", L, rblob, d.NH, (d.NH,), prev, f"i->(i/{d.G})", f"E_red_{L}", "i->(0)", (1,), d.NH)
+
         # ---- o_proj
         t, rpt = sz.o
         blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1)

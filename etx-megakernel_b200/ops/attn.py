@@ -17,10 +17,34 @@ PARAMS = [("q", "ptr addrspace(1)", 0, 8), ("kc", "ptr addrspace(1)", 8, 8), ("v
           ("HD", "i32", 84, 4), ("BS", "i32", 88, 4), ("X", "i32", 92, 4), ("max_parts", "i32", 96, 4), ("max_blocks", "i32", 100, 4)]
 
 
-def import_entries(threads: int = 512) -> dict:
-    return {e: entry(e, e, PARAMS, ARG_BYTES, GRID_OFF, threads, spec)
-            for e, spec in (("attn_decode", "paged GQA decode attention, 32 positions x one kv head per task"),
-                            ("attn_reduce", "merge of the attention partitions of one q head"))}
+# the fused phase (export attn_fused): q/k norm + rope + cache write of the new position, attention over the partition,
+# and the merge by the last task of each kv head (counters: one int32 per kv head, monotonic, never reset)
+F_ARG_BYTES, F_GRID_OFF = 176, 160
+F_PARAMS = [("qkv", "ptr addrspace(1)", 0, 8), ("qw", "ptr addrspace(1)", 8, 8), ("kw", "ptr addrspace(1)", 16, 8),
+            ("cos_sin", "ptr addrspace(1)", 24, 8), ("kc", "ptr addrspace(1)", 32, 8), ("vc", "ptr addrspace(1)", 40, 8),
+            ("block_tables", "ptr addrspace(1)", 48, 8), ("seq_lens", "ptr addrspace(1)", 56, 8), ("positions", "ptr addrspace(1)", 64, 8),
+            ("slot_mapping", "ptr addrspace(1)", 72, 8), ("exp_sums", "ptr addrspace(1)", 80, 8), ("max_logits", "ptr addrspace(1)", 88, 8),
+            ("tmp_out", "ptr addrspace(1)", 96, 8), ("out", "ptr addrspace(1)", 104, 8), ("counters", "ptr addrspace(1)", 112, 8),
+            ("scale", "float", 120, 4), ("eps", "float", 124, 4), ("NH", "i32", 128, 4), ("NKV", "i32", 132, 4), ("HD", "i32", 136, 4),
+            ("BS", "i32", 140, 4), ("X", "i32", 144, 4), ("max_parts", "i32", 148, 4)]
+
+
+def import_entries(threads: int = 544) -> dict:
+    out = {e: entry(e, e, PARAMS, ARG_BYTES, GRID_OFF, threads, spec)
+           for e, spec in (("attn_decode", "paged GQA decode attention, 32 positions x one kv head per task"),
+                           ("attn_reduce", "merge of the attention partitions of one q head"))}
+    out["attn_fused"] = entry("attn_fused", "attn_fused", F_PARAMS, F_ARG_BYTES, F_GRID_OFF, threads,
+                              "q/k norm + rope + cache write + paged GQA decode attention + merge, one phase")
+    return out
+
+
+def check_fused(NH: int, NKV: int, HD: int, BS: int, X: int, max_parts: int) -> None:
+    check_shape(NH, NKV, HD, BS, X, max_parts)
+    G = NH // NKV
+    if G + 2 > 16 or G * HD > 2048 or HD % 32:
+        raise ValueError(f"attn_fused: needs G + 2 <= 16 warps, G * HD <= 2048 and HD % 32 == 0 (G={G}, HD={HD})")
+    if G * max_parts > 8192:
+        raise ValueError(f"attn_fused: G * max_parts = {G * max_parts} exceeds 8192 (context too long for the in-tile merge)")
 
 
 def check_shape(NH: int, NKV: int, HD: int, BS: int, X: int, max_parts: int) -> None:

@@ -33,7 +33,7 @@ TILE_SYMBOLS = {
     "etx_tile_dsl_moe_up": 4, "etx_tile_dsl_moe_up_fold": 4,
     "etx_tile_dsl_moe_down": 5, "etx_tile_dsl_moe_down_fold": 5,
     "etx_tile_dsl_topk": 6, "etx_tile_dsl_attnprep": 7,
-    "etx_tile_attn_decode": 8, "etx_tile_attn_reduce": 9,
+    "etx_tile_attn_decode": 8, "etx_tile_attn_reduce": 9, "etx_tile_attn_fused": 12,
     "etx_tile_partial_sum": 10, "etx_tile_final_sum": 11,
 }
 

@@ -23,6 +23,7 @@ def qdims(od: O.Dims) -> Q.Dims:
 
 
 def make_program(od, W, maxlen, **kw):
+    kw.setdefault("fused_attn", True)
     d = qdims(od)
     return D.DecodeProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, maxlen), "cuda:0"), device=0, maxlen=maxlen, **kw)
 
@@ -113,6 +114,21 @@ def test_thirty_two_greedy_tokens_moe():
         prompt = np.random.default_rng(seed).integers(0, od.V, 40)
         identical += check_greedy(od, W, prompt, 32, 96)
     assert identical >= 2, f"only {identical} of 4 seeds gave 32 identical tokens"
+
+
+def test_unfused_attention_phases_and_separate_topk_give_the_same_tokens():
+    """The graph with the reference's phase structure (prep -> attn -> reduce, stand-alone top-k) and the fused one
+    produce identical tokens and identical final buffers: the fusions change the schedule, not the arithmetic."""
+    od = SMALL_MOE
+    W = O.SyntheticWeights(od, seed=3, gamma="ones")
+    prompt = np.random.default_rng(4).integers(0, od.V, 10)
+    a = make_program(od, W, 64)
+    ta = a.generate(prompt, 12); la = a.read("logits"); ka, va = a.read_kv(1, 21)
+    a.close()
+    b = make_program(od, W, 64, fused_attn=False, fold_topk=False)
+    tb = b.generate(prompt, 12); lb = b.read("logits"); kb, vb = b.read_kv(1, 21)
+    b.close()
+    assert ta.tolist() == tb.tolist() and np.array_equal(la, lb) and np.array_equal(ka, kb) and np.array_equal(va, vb)
 
 
 def test_thirty_two_greedy_tokens_dense_with_bias():

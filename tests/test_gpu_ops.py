@@ -220,6 +220,59 @@ def test_paged_attention(NH, NKV, HD, seq):
     assert_bf16_close(host(out), want, f"attention seq={seq}", min_exact=0.9)
 
 
+@pytest.mark.parametrize("NH,NKV,HD,qk_norm,seq", [(32, 4, 128, True, 1025), (32, 4, 128, True, 1024), (8, 2, 128, True, 1), (8, 2, 128, True, 33),
+                                                    (4, 2, 64, False, 100), (32, 8, 128, True, 640), (16, 2, 128, True, 97)])
+def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq):
+    """The one-phase attention tile (norm + rope + cache write of the new position, split-KV attention, merge by the last
+    task of each kv head) against the oracle: new cache slot bit-exact, output within bf16 tolerance; run twice with the
+    same never-reset counters to cover the modulo arithmetic of the merge election."""
+    rng = np.random.default_rng(seq + NH)
+    G = NH // NKV
+    pos = seq - 1
+    maxlen = ((seq + 31) // 32) * 32 + 32
+    nblk, parts = maxlen // 16, maxlen // 32
+    K = O.bfr(rng.standard_normal((seq, NKV, HD), dtype=np.float32) * np.float32(0.5))
+    V = O.bfr(rng.standard_normal((seq, NKV, HD), dtype=np.float32))
+    qkv = O.bfr(rng.standard_normal((NH + 2 * NKV, HD), dtype=np.float32))
+    qn = O.bfr(1 + 0.1 * rng.standard_normal(HD, dtype=np.float32)); kn = O.bfr(1 + 0.1 * rng.standard_normal(HD, dtype=np.float32))
+    cos, sin = O.rope_tables(1e6, HD, maxlen)
+    q, k, v = qkv[:NH], qkv[NH:NH + NKV], qkv[NH + NKV:]
+    if qk_norm:
+        q = np.stack([O.rmsnorm(h, qn, 1e-6) for h in q]); k = np.stack([O.rmsnorm(h, kn, 1e-6) for h in k])
+    q = np.stack([O.apply_rope(h, cos[pos], sin[pos]) for h in q]); k = np.stack([O.apply_rope(h, cos[pos], sin[pos]) for h in k])
+    K[pos], V[pos] = k, v
+    scale = np.float32(1.0 / np.sqrt(HD))
+    want = np.zeros((NH, HD), np.float32)
+    for h in range(NH):
+        s = (K[:, h // G] @ q[h]) * scale
+        s = s - s.max(); pr = np.exp(s); pr = pr / pr.sum()
+        want[h] = O.bfr(pr @ V[:, h // G])
+    Kold, Vold = K.copy(), V.copy()
+    Kold[pos], Vold[pos] = 9.0, 9.0                                       # stale slot contents the tile must overwrite
+    kc0, vc0 = O.paged_from_contig(Kold, Vold, nblk)
+    kc_ref, vc_ref = O.paged_from_contig(K, V, nblk)
+    d_kc, d_vc, d_qkv = dev_bf16(kc0), dev_bf16(vc0), dev_bf16(qkv)
+    d_qn, d_kn = dev_bf16(qn), dev_bf16(kn)
+    cs = torch.from_numpy(Q.rope_table(1e6, HD, maxlen).view(np.int16)).to(DEV).view(torch.bfloat16)
+    bt = torch.arange(nblk, dtype=torch.int32, device=DEV); sl = torch.tensor([seq], dtype=torch.int32, device=DEV)
+    p64 = torch.tensor([pos], dtype=torch.int64, device=DEV)
+    es = torch.zeros((NH, parts), dtype=torch.float32, device=DEV); ml = torch.zeros_like(es)
+    tmp = torch.zeros((NH, parts, HD), dtype=torch.float32, device=DEV); out = torch.zeros((NH, HD), dtype=torch.bfloat16, device=DEV)
+    cnt = torch.zeros(NKV, dtype=torch.int32, device=DEV)
+    blob = argblock.pack_named(ENT["attn_fused"], (parts * NKV, 1, 1), qkv=d_qkv.data_ptr(), qw=d_qn.data_ptr() if qk_norm else 0,
+                               kw=d_kn.data_ptr() if qk_norm else 0, cos_sin=cs.data_ptr(), kc=d_kc.data_ptr(), vc=d_vc.data_ptr(),
+                               block_tables=bt.data_ptr(), seq_lens=sl.data_ptr(), positions=p64.data_ptr(), slot_mapping=p64.data_ptr(),
+                               exp_sums=es.data_ptr(), max_logits=ml.data_ptr(), tmp_out=tmp.data_ptr(), out=out.data_ptr(),
+                               counters=cnt.data_ptr(), scale=float(scale), eps=1e-6, NH=NH, NKV=NKV, HD=HD, BS=16, X=8, max_parts=parts)
+    for rerun in range(2):
+        out.zero_()
+        op_launch("attn_fused", blob, parts * NKV)
+        assert np.array_equal(host(d_kc), kc_ref) and np.array_equal(host(d_vc), vc_ref)
+        assert_bf16_close(host(out), want, f"fused attention seq={seq} run {rerun}", min_exact=0.9)
+        assert host(cnt).tolist() == [parts * (rerun + 1)] * NKV
+        assert np.array_equal(host(d_qkv), qkv)                          # the fused tile leaves qkv as the GEMV wrote it
+
+
 @pytest.mark.parametrize("E,TOPK,MI,H,fold", [(16, 4, 128, 512, True), (128, 8, 768, 2048, True), (128, 8, 768, 2048, False), (8, 2, 256, 256, True)])
 def test_moe_block(E, TOPK, MI, H, fold):
     """router logits -> top-k -> gate/up with SiLU*mul -> down scaled by the bf16 routing weight, against the oracle's
