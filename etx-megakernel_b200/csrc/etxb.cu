@@ -22,7 +22,7 @@ static_assert(sizeof(etxb_topk_args) == 64 && offsetof(etxb_topk_args, grid) == 
 static_assert(sizeof(etxb_attnprep_args) == 112 && offsetof(etxb_attnprep_args, grid) == 96, "attnprep block layout (etx/ops/attnprep.py:11-15)");
 static_assert(sizeof(etxb_attnf_args) == 176 && offsetof(etxb_attnf_args, grid) == 160, "fused attention block layout");
 static_assert(sizeof(etxb_attn_args) == 128 && offsetof(etxb_attn_args, grid) == 112, "attention block layout");
-static_assert(ETXB_SMEM_BYTES + 1024 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may opt into");
+static_assert(ETXB_SMEM_BYTES + 256 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may opt into");
 static_assert(sizeof(etxb_task) == 40 && sizeof(etxb_type) == 48, "plan table layouts");
 static_assert(sizeof(etxb_stepv) == sizeof(etxb_step_params), "step parameter layouts must agree");
 
@@ -245,7 +245,8 @@ extern "C" int32_t etxb_set_option(etxb_session* s, const char* key, int64_t val
     CU(cudaSetDevice(s->device));
     s->trace = value != 0;
     if (s->trace && !s->d_trace) {
-      CU(cudaMalloc((void**)&s->d_trace, (size_t)s->h.n_tasks * 32 + 32));
+      CU(cudaMalloc((void**)&s->d_trace, (size_t)s->h.n_tasks * 64 + 64));
+      CU(cudaMemset(s->d_trace, 0, (size_t)s->h.n_tasks * 64 + 64));
       CU(cudaMalloc((void**)&s->d_exec, (size_t)s->h.n_tasks * 4 + 4));
     }
     return ETXB_OK;
@@ -374,9 +375,9 @@ extern "C" int32_t etxb_status(etxb_session* s, etxb_status_t* out) {
 extern "C" int32_t etxb_trace(etxb_session* s, void* host_buf, size_t bytes) {
   if (!s || !host_buf) return fail(ETXB_E_ARG, "null argument");
   if (!s->d_trace) return fail(ETXB_E_ARG, "tracing is off (set option trace=1 before the step)");
-  if (bytes < (size_t)s->h.n_tasks * 32) return fail(ETXB_E_ARG, "trace buffer too small: 32 bytes per task");
+  if (bytes < (size_t)s->h.n_tasks * 64) return fail(ETXB_E_ARG, "trace buffer too small: 64 bytes per task");
   CU(cudaSetDevice(s->device));
-  CU(cudaMemcpy(host_buf, s->d_trace, (size_t)s->h.n_tasks * 32, cudaMemcpyDeviceToHost));
+  CU(cudaMemcpy(host_buf, s->d_trace, (size_t)s->h.n_tasks * 64, cudaMemcpyDeviceToHost));
   return ETXB_OK;
 }
 

@@ -26,7 +26,7 @@
 #define ETXB_G_FLOATS 2048
 #define ETXB_SCR_FLOATS 256
 #define ETXB_CTX_BYTES 384           // one prefetched task context: header + argument block copy
-#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 256 + 2 * ETXB_CTX_BYTES)
+#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512 + 2 * ETXB_CTX_BYTES)
 #define ETXB_ATTN_PART 32            // KV positions per attention task
 #define ETXB_MAX_NB 8                // activation columns of the stand-alone batched GEMV kernel
 #define ETXB_NB_XS_FLOATS 40960      // its staged activations: nb * K floats
@@ -118,6 +118,8 @@ struct etxb_gemv_args {
 #define ETXB_MODE_TOPK_RENORM 3
 #define ETXB_MODE_BF16_WTS 0x100
 #define ETXB_MODE_BIAS 0x200
+#define ETXB_MODE_SUM_SLOTS 0x400     // MoE down: the task covers every slot and writes their bf16 sum in ascending expert id
+// bits 16..23 of mode: expert slots per task of the MoE forms (0 = 1)
 
 // top-k: the reference's 64-byte block (etx/ops/topk.py:16-23), grid words at 48.
 struct etxb_topk_args {

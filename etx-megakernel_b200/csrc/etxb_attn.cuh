@@ -237,6 +237,7 @@ __device__ __forceinline__ void tile_attn_fused(const unsigned char* a, int blk,
         *(uint4*)(vs + (size_t)b * HD * BS + 8 * r) = ld_act16((const __nv_bfloat16*)d.vc + base + 8 * r);
       }
     }
+    mark(sm, 0);
     // raw q heads of the group (+ the new k and v rows for the owner)
     for (int i = tidx(); i < G * HD; i += ETXB_CONSUMERS) raw[i] = ld_bf(qkv, (size_t)h * G * HD + i);
     if (owner)
@@ -273,6 +274,7 @@ __device__ __forceinline__ void tile_attn_fused(const unsigned char* a, int blk,
       }
     }
     csync();
+    mark(sm, 1);
     // scores: idx -> (g, half, t); the two halves of the head dimension are added left to right, then scaled
     const int hx = HD / X;
     for (int idx = tidx(); idx < G * 2 * P; idx += ETXB_CONSUMERS) {
@@ -324,6 +326,7 @@ __device__ __forceinline__ void tile_attn_fused(const unsigned char* a, int blk,
   }
   // the last task of this kv head to get here merges the partitions of its G q heads
   csync();
+  mark(sm, 2);
   if (tidx() == 0) {
     __threadfence();
     const int old = atomicAdd(d.counters + h, 1);
@@ -331,6 +334,7 @@ __device__ __forceinline__ void tile_attn_fused(const unsigned char* a, int blk,
     if (*flag) __threadfence();
   }
   csync();
+  mark(sm, 3);
   if (!*flag) return;
   float* wl = sm.xs;                                              // [G][np] max logits, then weights
   float* es = sm.xs + 8192;                                       // [G][np] exp sums (G * np <= 8192)

@@ -32,7 +32,10 @@ struct Smem {
   int32_t* prod;             // producer-warp scratch: 16 ids + 16 weights
   const unsigned long long* deadline;
   int32_t* ctrl;
+  uint64_t* tr;              // 8 stamps of the running task when tracing, else null (slots 4..7 are in-body marks)
 };
+// in-body time stamp k (0..3) of the running task; thread 0 only, no-op unless tracing
+__device__ __forceinline__ void mark(const Smem& sm, int k) { if (sm.tr != nullptr && tidx() == 0) sm.tr[4 + k] = globaltimer(); }
 __device__ __forceinline__ __nv_bfloat16* smem_xb(const Smem& sm) { return (__nv_bfloat16*)((unsigned char*)sm.xs + ETXB_XB_OFF); }
 __device__ __forceinline__ float* smem_g(const Smem& sm) { return (float*)((unsigned char*)sm.xs + ETXB_G_OFF); }
 
@@ -53,19 +56,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 }
 
 // ---------------------------------------------------------------------------------------------- what a task streams
-struct StreamDesc {
-  const unsigned char* base0;   // rows 0 .. n0-1
-  const unsigned char* base1;   // rows n0 .. n0+n1-1
-  int n0, n1, row_bytes;
+// The weight rows of a task: `nranges` contiguous ranges of `n` rows each (row_bytes per row), taken range by range.
+//   plain GEMV   one range: rows [r0, r0 + n) of W
+//   MoE gate+up  per expert slot of the task: the gate rows, then the up rows (2 * spt ranges)
+//   MoE down     per expert slot of the task: rows [r0, r0 + n) of that expert's W2 (spt ranges)
+struct GemvTask {
+  int nranges, n, row_bytes, r0, group, spt;
 };
-
-__device__ __forceinline__ int stream_chunks(const StreamDesc& s) {
-  const int total = s.n0 + s.n1;
-  if (total <= 0) return 0;
-  const int rps = ETXB_STAGE_BYTES / s.row_bytes;
-  return (total + rps - 1) / rps;
-}
-
 // ---------------------------------------------------------------------------------------------- top-k
 // softmax over E bf16 logits (fp32), K rounds of argmax with the lower index winning ties, optional renormalisation
 // over the selected weights (numpy's summation order for <= 16 values), optional bf16 rounding of the weights.
@@ -137,43 +134,54 @@ __device__ __forceinline__ void tile_topk(const unsigned char* a, int blk, const
             d.ids + (size_t)w * sv, d.wts + (size_t)w * sv, d.tei ? d.tei + (size_t)w * sv : nullptr);
 }
 
-// The weight rows task `blk` of a GEMV-family tile streams.  Called by the producer warp (scratch = its own ids /
-// weights area) and by the consumer side (its area): both compute the same descriptor, so the stage sequence agrees.
-// All 32 lanes of the calling warp must call (the top-k fold is a warp computation).
-__device__ __forceinline__ StreamDesc gemv_stream_desc(int body, const unsigned char* a, int blk, int32_t* lids, float* lwts) {
-  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  StreamDesc s;
-  s.base0 = s.base1 = nullptr; s.n0 = s.n1 = 0; s.row_bytes = d.K * 2;
-  if (blk >= (int)d.nblocks) return s;
+// Decode task `blk` of a GEMV-family tile (pure arithmetic on the argument block).  Slots per task: mode bits 16..23
+// (0 = 1): task blk covers slots [group * spt, (group + 1) * spt), group = blk / tpe, row chunk j = blk % tpe.
+__device__ __forceinline__ GemvTask gemv_task(int body, const etxb_gemv_args& d, int blk) {
+  GemvTask t;
+  t.nranges = 0; t.n = 0; t.row_bytes = d.K * 2; t.r0 = 0; t.group = 0; t.spt = 1;
+  if (blk >= (int)d.nblocks) return t;
   if (body == 3) {
     const int r0 = blk * d.rpt, r1 = min(d.M, r0 + d.rpt);
-    if (r0 >= r1) return s;
-    s.base0 = (const unsigned char*)d.W + (size_t)r0 * d.K * 2; s.n0 = r1 - r0;
-    return s;
+    if (r0 < r1) { t.nranges = 1; t.n = r1 - r0; t.r0 = r0; }
+    return t;
   }
-  const int sl = blk / d.tpe, j = blk - sl * d.tpe;
+  const int spt = ((d.mode >> 16) & 0xff) ? ((d.mode >> 16) & 0xff) : 1;
+  const int group = blk / d.tpe, j = blk - group * d.tpe;
   const int r0 = j * d.rpt, r1 = min(d.M, r0 + d.rpt);
-  if (r0 >= r1) return s;
-  const int fold = d.mode & 0xff;
-  int e = 0;
+  if (r0 < r1) { t.nranges = (body == 4 ? 2 : 1) * spt; t.n = r1 - r0; t.r0 = r0; t.group = group; t.spt = spt; }
+  return t;
+}
+
+// Expert ids (and routing weights) of the task's slots into `lids` / `lwts` (indexed by global slot).  One warp, all
+// lanes call.  Top-k fold: recomputed from the logits; else read from the ids / wts buffers; no ids: expert 0.
+__device__ __forceinline__ void gemv_routing(const etxb_gemv_args& d, int32_t* lids, float* lwts) {
+  const int fold = d.mode & 0xff, lane = tidx() & 31;
   if (fold >= 2) {
     warp_topk(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
-    e = lids[sl];
-  } else if (d.ids) {
-    e = __ldcg(d.ids + sl);
+  } else {
+    if (lane < 16) {
+      lids[lane] = (d.ids && lane < d.R) ? __ldcg(d.ids + lane) : 0;
+      lwts[lane] = (d.wts && lane < d.R) ? __ldcg(d.wts + lane) : 1.f;
+    }
+    __syncwarp();
   }
-  const unsigned char* We = (const unsigned char*)d.W + (size_t)e * d.estride * 2;
-  s.base0 = We + (size_t)r0 * d.K * 2; s.n0 = r1 - r0;
-  if (body == 4) { s.base1 = We + (size_t)(d.M + r0) * d.K * 2; s.n1 = r1 - r0; }   // gate rows, then up rows
-  return s;
+}
+
+__device__ __forceinline__ const unsigned char* gemv_range_base(int body, const etxb_gemv_args& d, const GemvTask& t, int i, const int32_t* lids) {
+  if (body == 3) return (const unsigned char*)d.W + (size_t)t.r0 * t.row_bytes;
+  const int slot = t.group * t.spt + (body == 4 ? i >> 1 : i);
+  const unsigned char* We = (const unsigned char*)d.W + (size_t)lids[slot] * d.estride * 2;
+  const int row = t.r0 + ((body == 4 && (i & 1)) ? d.M : 0);        // up rows follow the M gate rows
+  return We + (size_t)row * t.row_bytes;
 }
 
 // ---------------------------------------------------------------------------------------------- producer side
 // Issue the bulk copies of one task.  One warp; lane 0 issues.  n = running stage counter of this CTA.
-__device__ __forceinline__ bool produce_task(const StreamDesc& s, uint32_t& n, const Smem& sm, int where) {
-  const int total = s.n0 + s.n1;
+__device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, const GemvTask& t, const int32_t* lids, uint32_t& n,
+                                             const Smem& sm, int where) {
+  const int total = t.nranges * t.n;
   if (total <= 0) return true;
-  const int rps = ETXB_STAGE_BYTES / s.row_bytes;
+  const int rps = ETXB_STAGE_BYTES / t.row_bytes;
   bool ok = true;
   if ((tidx() & 31) == 0) {
     for (int q0 = 0; q0 < total && ok; q0 += rps) {
@@ -182,11 +190,15 @@ __device__ __forceinline__ bool produce_task(const StreamDesc& s, uint32_t& n, c
       if (!ok) break;
       const int nr = min(rps, total - q0);
       unsigned char* dst = sm.ring + (size_t)st * ETXB_STAGE_BYTES;
-      mbar_expect_tx(sm.full + st, (uint32_t)(nr * s.row_bytes));
-      const int a0 = min(max(s.n0 - q0, 0), nr);                   // rows of this stage that come from the first range
-      if (a0 > 0) bulk_g2s(dst, s.base0 + (size_t)q0 * s.row_bytes, (uint32_t)(a0 * s.row_bytes), sm.full + st);
-      if (nr > a0) bulk_g2s(dst + (size_t)a0 * s.row_bytes, s.base1 + (size_t)(q0 + a0 - s.n0) * s.row_bytes,
-                            (uint32_t)((nr - a0) * s.row_bytes), sm.full + st);
+      mbar_expect_tx(sm.full + st, (uint32_t)(nr * t.row_bytes));
+      int q = q0;
+      while (q < q0 + nr) {                                        // one copy per piece of a range that falls into this stage
+        const int rg = q / t.n, r = q - rg * t.n;
+        const int cnt = min(t.n - r, q0 + nr - q);
+        bulk_g2s(dst + (size_t)(q - q0) * t.row_bytes, gemv_range_base(body, d, t, rg, lids) + (size_t)r * t.row_bytes,
+                 (uint32_t)(cnt * t.row_bytes), sm.full + st);
+        q += cnt;
+      }
       ++n;
     }
   }
@@ -204,24 +216,27 @@ __device__ __forceinline__ float dot8(const uint4 w, const uint4 x, float a) {
   return a;
 }
 
-// Consume the stages of one task: row q (0 .. total-1) . xb -> epi(q, value), called by lane 0 of the owning warp.
+// Consume the stages of one task: row q (0 .. total-1, range q / rows_per_range) . its activation vector -> epi(q, value),
+// called by lane 0 of the owning warp.  Range i uses the vector at xb + i * xstride (xstride = 0: one vector for all).
 // Every consumer warp walks every stage (so the stage counter stays in step) and arrives on its `empty` barrier.
 template <typename Epi>
-__device__ __forceinline__ void consume_task(int total, int row_bytes, uint32_t& n, const Smem& sm, const __nv_bfloat16* xb, int where, Epi epi) {
+__device__ __forceinline__ void consume_task(int total, int rows_per_range, int row_bytes, uint32_t& n, const Smem& sm, const __nv_bfloat16* xb,
+                                             int xstride, int where, Epi epi) {
   if (total <= 0) return;
   const int lane = tidx() & 31, cw = tidx() >> 5;
   const int rps = ETXB_STAGE_BYTES / row_bytes, nvec = row_bytes >> 4;
-  const uint4* xv = (const uint4*)xb;
   bool alive = true;
   for (int q0 = 0; q0 < total; q0 += rps) {
     const uint32_t st = n % ETXB_NSTAGE, par = (n / ETXB_NSTAGE) & 1;
     ++n;
     if (alive) alive = mbar_wait(sm.full + st, par, sm, where);
     if (!alive) continue;                                          // step abandoned: keep counting, touch nothing
+    if (q0 == 0) mark(sm, 1);
     const int nr = min(rps, total - q0);
     const unsigned char* stage = sm.ring + (size_t)st * ETXB_STAGE_BYTES;
     for (int j = (cw - q0) & (ETXB_CONSUMER_WARPS - 1); j < nr; j += ETXB_CONSUMER_WARPS) {
       const uint4* wv = (const uint4*)(stage + (size_t)j * row_bytes);
+      const uint4* xv = (const uint4*)(xb + (size_t)((q0 + j) / rows_per_range) * xstride);
       float acc = 0.f;
 #pragma unroll 4
       for (int v = lane; v < nvec; v += 32) acc = dot8(wv[v], xv[v], acc);
@@ -320,9 +335,9 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
 // ---------------------------------------------------------------------------------------------- plain / folded GEMV
 __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  const StreamDesc s = gemv_stream_desc(3, a, blk, nullptr, nullptr);
-  if (s.n0 <= 0) return;
-  const int r0 = blk * d.rpt;
+  const GemvTask t = gemv_task(3, d, blk);
+  if (t.n <= 0) return;
+  const int r0 = t.r0;
   __nv_bfloat16* xb = smem_xb(sm);
   if ((d.mode & 0xff) == ETXB_MODE_NORM)
     stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
@@ -330,66 +345,99 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
     stage_xb(d.x, d.K, xb);
   const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
   __nv_bfloat16* out = (__nv_bfloat16*)d.out;
-  consume_task(s.n0, s.row_bytes, n, sm, xb, where, [&](int q, float v) {
+  mark(sm, 0);
+  consume_task(t.n, t.n, t.row_bytes, n, sm, xb, 0, where, [&](int q, float v) {
     out[r0 + q] = __float2bfloat16_rn(bias ? __fadd_rn(v, __bfloat162float(bias[r0 + q])) : v);
   });
 }
 
 // ---------------------------------------------------------------------------------------------- MoE gate+up
-// task blk: slot s = blk / tpe, row chunk j = blk % tpe; expert e = ids[s] (ids == null and no fold: expert 0, the
-// dense SwiGLU MLP); act[s][r] = bf16(bf16(silu(bf16 g)) * bf16 u), g = W_e[r,:].x, u = W_e[M + r,:].x.
+// task blk: expert slots [group * spt, ...), row chunk j = blk % tpe; expert e = ids[slot] (no ids and no fold: expert
+// 0, the dense SwiGLU MLP); act[slot][r] = bf16(bf16(silu(bf16 g)) * bf16 u), g = W_e[r,:].x, u = W_e[M + r,:].x.
 __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
+  const GemvTask t = gemv_task(4, d, blk);
+  if (t.n <= 0) return;
   int32_t* lids = (int32_t*)(sm.scr + 96); float* lwts = sm.scr + 112;
-  StreamDesc s;
-  if (tidx() < 32) {                                               // the descriptor (and the folded top-k) is one warp's work
-    s = gemv_stream_desc(4, a, blk, lids, lwts);
-    if (tidx() == 0) ((int*)sm.scr)[128] = s.n0;
-  }
-  csync();
-  const int rows = ((int*)sm.scr)[128];
-  if (rows <= 0) return;
-  const int sl = blk / d.tpe, j = blk - sl * d.tpe, r0 = j * d.rpt;
   const int fold = d.mode & 0xff;
-  if (fold >= 2 && j == 0 && tidx() == 0) {                         // the slot's first chunk publishes the routing
-    if (d.ids) ((int32_t*)d.ids)[sl] = lids[sl];
-    if (d.wts) ((float*)d.wts)[sl] = lwts[sl];
+  if (tidx() < 32) {
+    if (fold >= 2) {
+      gemv_routing(d, lids, lwts);
+      if (blk - t.group * d.tpe == 0 && tidx() < t.spt) {           // the group's first chunk publishes its slots' routing
+        const int sl = t.group * t.spt + tidx();
+        if (d.ids) ((int32_t*)d.ids)[sl] = lids[sl];
+        if (d.wts) ((float*)d.wts)[sl] = lwts[sl];
+      }
+    }
   }
   __nv_bfloat16* xb = smem_xb(sm);
   if (fold == ETXB_MODE_NORM)                                      // dense MLP: the post-attention norm folded in
     stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
   else
     stage_xb(d.x, d.K, xb);
-  float* g = smem_g(sm);                                           // gate results, then up results
-  consume_task(2 * rows, d.K * 2, n, sm, xb, where, [&](int q, float v) { g[q] = bfr(v); });
+  float* g = smem_g(sm);                                           // per slot: n gate results, then n up results
+  const int rows = t.n;
+  mark(sm, 0);
+  consume_task(t.nranges * rows, rows, t.row_bytes, n, sm, xb, 0, where, [&](int q, float v) { g[q] = bfr(v); });
   csync();
-  __nv_bfloat16* act = (__nv_bfloat16*)d.out + (size_t)sl * d.M;
-  for (int r = tidx(); r < rows; r += ETXB_CONSUMERS) act[r0 + r] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(g[r])), g[rows + r]));
+  mark(sm, 2);
+  for (int i = tidx(); i < t.spt * rows; i += ETXB_CONSUMERS) {
+    const int s = i / rows, r = i - s * rows;
+    __nv_bfloat16* act = (__nv_bfloat16*)d.out + (size_t)(t.group * t.spt + s) * d.M;
+    act[t.r0 + r] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(g[2 * s * rows + r])), g[(2 * s + 1) * rows + r]));
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- MoE down
-// out[s][r] = bf16(bf16(W_e[r,:] . act_s) * wts[s]); no weights (dense MLP): out[s][r] = bf16(W_e[r,:] . act_s).
+// y[slot][r] = bf16(bf16(W_e[r,:] . act_slot) * wts[slot]) (no weights, the dense MLP: bf16(W_e[r,:] . act)).
+// Plain form: out[slot][r] = y.  Summed form (mode bit ETXB_MODE_SUM_SLOTS, the task covers every slot): out[r] = the
+// y of all slots added one by one in bf16 in ascending expert id -- the expert combine of the CPU path
+// (examples/llm/ref_numpy.py:142-148), which the reference leaves to the next layer's norm fold.
 __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
+  const GemvTask t = gemv_task(5, d, blk);
+  if (t.n <= 0) return;
   int32_t* lids = (int32_t*)(sm.scr + 96); float* lwts = sm.scr + 112;
-  if (tidx() < 32) {
-    const StreamDesc s = gemv_stream_desc(5, a, blk, lids, lwts);
-    if (tidx() == 0) ((int*)sm.scr)[128] = s.n0;
-  }
-  csync();
-  const int rows = ((int*)sm.scr)[128];
-  if (rows <= 0) return;
-  const int sl = blk / d.tpe, j = blk - sl * d.tpe, r0 = j * d.rpt;
   const int fold = d.mode & 0xff;
   const bool scaled = fold >= 2 || d.wts != nullptr;
-  const float ws = fold >= 2 ? lwts[sl] : (d.wts ? __ldcg(d.wts + sl) : 1.f);
+  if (tidx() < 32) gemv_routing(d, lids, lwts);
   __nv_bfloat16* xb = smem_xb(sm);
-  stage_xb((const __nv_bfloat16*)d.x + (size_t)sl * d.K, d.K, xb);
-  __nv_bfloat16* out = (__nv_bfloat16*)d.out + (size_t)sl * d.M;
-  consume_task(rows, d.K * 2, n, sm, xb, where, [&](int q, float v) {
+  const int K = d.K, rows = t.n;
+  for (int i = tidx(); i < t.spt * (K >> 3); i += ETXB_CONSUMERS) {          // the task's slots' activation vectors
+    const int s = i / (K >> 3), v = i - s * (K >> 3);
+    ((uint4*)xb)[i] = ld_act16((const __nv_bfloat16*)d.x + (size_t)(t.group * t.spt + s) * K + 8 * v);
+  }
+  csync();
+  float* g = smem_g(sm);
+  const bool sum = (d.mode & ETXB_MODE_SUM_SLOTS) != 0;
+  __nv_bfloat16* out = (__nv_bfloat16*)d.out;
+  mark(sm, 0);
+  consume_task(t.nranges * rows, rows, t.row_bytes, n, sm, xb, K, where, [&](int q, float v) {
+    const int s = q / rows, r = q - s * rows, sl = t.group * t.spt + s;
     const float y = bfr(v);
-    out[r0 + q] = __float2bfloat16_rn(scaled ? __fmul_rn(y, ws) : y);
+    const float ys = scaled ? bfr(__fmul_rn(y, lwts[sl])) : y;
+    if (sum) g[q] = ys;
+    else out[(size_t)sl * d.M + t.r0 + r] = __float2bfloat16_rn(ys);
   });
+  if (!sum) return;
+  csync();
+  mark(sm, 2);
+  int* order = (int*)(sm.scr + 64);                                // slots in ascending expert id
+  if (tidx() < t.spt) {
+    const int mine = lids[t.group * t.spt + tidx()];
+    int rank = 0;
+    for (int j = 0; j < t.spt; ++j) {
+      const int o = lids[t.group * t.spt + j];
+      rank += (o < mine) || (o == mine && j < tidx());
+    }
+    order[rank] = tidx();
+  }
+  csync();
+  for (int r = tidx(); r < rows; r += ETXB_CONSUMERS) {
+    float acc = 0.f;
+    for (int k = 0; k < t.spt; ++k) acc = bfr(__fadd_rn(acc, g[order[k] * rows + r]));
+    out[t.r0 + r] = __float2bfloat16_rn(acc);
+  }
 }
 
 }  // namespace etxb

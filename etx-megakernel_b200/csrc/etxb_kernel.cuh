@@ -169,8 +169,13 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
       break;
     }
     const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
-    const StreamDesc s = gemv_stream_desc(body, args, t->coord[0], sm.prod, (float*)(sm.prod + 16));
-    ok = produce_task(s, n, sm, cur);
+    // the argument block through shared memory (one 160-byte read instead of a dependent global load per field)
+    etxb_gemv_args* pa = (etxb_gemv_args*)(sm.prod + 32);
+    if (lane < 20) ((uint64_t*)pa)[lane] = __ldg((const uint64_t*)args + lane);
+    __syncwarp();
+    const GemvTask gt = gemv_task(body, *pa, t->coord[0]);
+    if (gt.n > 0 && body != 3) gemv_routing(*pa, sm.prod, (float*)(sm.prod + 16));
+    ok = produce_task(body, *pa, gt, sm.prod, n, sm, cur);
   }
   // Nothing is left in flight on a normal exit (the consumers waited for every stage).  When the step was abandoned,
   // wait (bounded) for the copies already issued before the CTA's shared memory goes away.
@@ -196,6 +201,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   sm.prod = (int32_t*)(sm.empty + ETXB_NSTAGE);
   sm.deadline = &s_deadline;
   sm.ctrl = p.ctrl;
+  sm.tr = nullptr;
   if (threadIdx.x == 0) {
     s_stop = 0;
     s_deadline = globaltimer() + p.timeout_ns;
@@ -209,7 +215,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     producer_loop(p, sm, q0, q1);
     return;
   }
-  TaskCtx* ctx = (TaskCtx*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 256);
+  TaskCtx* ctx = (TaskCtx*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512);
   if (q0 < q1 && threadIdx.x >= ETXB_CONSUMERS - 32) load_ctx(p, q0, ctx);
   csync();
   uint32_t n = 0;                                                  // stages consumed so far (same count the producer keeps)
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     const TaskCtx* c = ctx + ((cur - q0) & 1);
     if (threadIdx.x == 0) {
       const int in_n = c->in_n;
-      if (p.trace) p.trace[4 * (size_t)c->id] = globaltimer();
+      if (p.trace) p.trace[8 * (size_t)c->id] = globaltimer();
       bool ok = ld_relaxed(p.ctrl) == 0;
       for (int i = 0; ok && i < in_n; ++i) {
         int word, cnt;
@@ -226,11 +232,12 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
         ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
       }
       if (!ok) s_stop = 1;
-      if (p.trace) p.trace[4 * (size_t)c->id + 1] = globaltimer();
+      if (p.trace) p.trace[8 * (size_t)c->id + 1] = globaltimer();
     }
     csync();
     if (s_stop) break;
     if (threadIdx.x >= ETXB_CONSUMERS - 32 && cur + 1 < q1) load_ctx(p, cur + 1, ctx + ((cur + 1 - q0) & 1));   // next task's context
+    sm.tr = p.trace ? p.trace + 8 * (size_t)c->id : nullptr;
     run_body(p, c, cur, sm, n);
     csync();                                                       // every consumer thread's stores are issued
     if (threadIdx.x == 0) {
@@ -241,7 +248,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
           const int word = i < 4 ? c->out_word[i] : p.outwords[c->out_off + i];
           red_release_add(p.events + (size_t)word * ETXB_EV_STRIDE, 1);
         }
-      if (p.trace) { p.trace[4 * (size_t)id + 2] = globaltimer(); p.trace[4 * (size_t)id + 3] = blockIdx.x; }
+      if (p.trace) { p.trace[8 * (size_t)id + 2] = globaltimer(); p.trace[8 * (size_t)id + 3] = blockIdx.x; }
       if (p.exec_count) atomicAdd(p.exec_count + id, 1);
     }
   }

@@ -141,8 +141,15 @@ def validate_values(export, values, grid):
         need = -(-v["M"] // v["rpt"]) * (1 if _gemv.FORMS[name] == "plain" else 1)
         if _gemv.FORMS[name] == "plain" and gx * gy * gz < need:
             raise ValueError(f"{spec.name}: grid of {gx * gy * gz} tasks leaves rows unwritten (needs {need})")
-        if _gemv.FORMS[name] != "plain" and (v["tpe"] < 1 or v["tpe"] * v["rpt"] < v["M"]):
-            raise ValueError(f"{spec.name}: tpe * rpt = {v['tpe'] * v['rpt']} does not cover M = {v['M']}")
+        if _gemv.FORMS[name] != "plain":
+            if v["tpe"] < 1 or v["tpe"] * v["rpt"] < v["M"]:
+                raise ValueError(f"{spec.name}: tpe * rpt = {v['tpe'] * v['rpt']} does not cover M = {v['M']}")
+            spt = ((v["mode"] >> 16) & 0xff) or 1
+            slots = max(v["R"], 1) if (v["mode"] & 0xff) >= 2 or v["ids"] else 1
+            if slots % spt or gx * gy * gz != (slots // spt) * v["tpe"]:
+                raise ValueError(f"{spec.name}: grid {gx * gy * gz} != (slots {slots} / {spt} per task) * tpe {v['tpe']}")
+            if (v["mode"] & _gemv.MODE_SUM_SLOTS) and (name.startswith("dsl_moe_up") or spt != slots):
+                raise ValueError(f"{spec.name}: the summed form is for moe_down with every slot in one task")
         if (v["mode"] & 0xff) >= 2:
             _topk.check_shape(v["E"], v["R"])
     elif name == "dsl_topk":

@@ -130,24 +130,37 @@ class Sizing:
     qkv: tuple          # (tasks, rows per task)
     o: tuple
     router: tuple
-    up: tuple           # (tasks per expert slot, rows per task)
-    down: tuple
+    up: tuple           # (expert slots per task, row chunks per slot group, rows per chunk)
+    down: tuple         # (tasks, rows per task): every task covers all slots and sums them
     lm: tuple
     parts: int          # attention partitions (of 32 positions) covering maxlen
 
 
 def size_for(d: Dims, m: MachineModel, maxlen: int) -> Sizing:
     W = m.workers()
-
-    def per_slot(rows, slots, waves):
-        tpe = max(1, (W * waves) // max(slots, 1))
-        rpt = -(-rows // tpe)
-        return -(-rows // rpt), rpt
     slots = d.TOPK if d.moe else 1
     mi = d.MI if d.moe else d.INTER
+
+    def up_split():
+        """(slots per task, chunks per slot group, rows per chunk): the divisor of the slot count that loads the SMs most
+        evenly with ONE task per SM (a task then streams 2 * spt * rpt rows without a restart)."""
+        best = None
+        for spt in [s for s in range(1, slots + 1) if slots % s == 0]:
+            groups = slots // spt
+            tpe = max(1, W // groups)
+            rpt = -(-mi // tpe)
+            tpe = -(-mi // rpt)
+            if 2 * spt * rpt > op_gemv.MAX_RESULTS or groups * tpe > W:
+                continue
+            eff = (slots * mi) / (W * spt * rpt)
+            if best is None or eff > best[0] + 1e-9 or (abs(eff - best[0]) < 1e-9 and spt > best[1]):
+                best = (eff, spt, tpe, rpt)
+        if best is None:
+            raise ValueError("no expert task split fits the tile limits")
+        return best[1:]
+    dt, drpt = m.gemv_tasks(d.H)
     return Sizing(workers=W, qkv=m.gemv_tasks(d.NQKV), o=m.gemv_tasks(d.H), router=m.gemv_tasks(d.E) if d.moe else (0, 0),
-                  up=per_slot(mi, slots, 2 if d.moe else 1), down=per_slot(d.H, slots, 2 if d.moe else 1),
-                  lm=m.gemv_tasks(d.V, waves=4), parts=-(-maxlen // m.attention_part()))
+                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.V, waves=4), parts=-(-maxlen // m.attention_part()))
 
 
 # ------------------------------------------------------------------------------------------------ buffers
@@ -161,7 +174,7 @@ def buffer_shapes(d: Dims, maxlen: int, steps: int, parts: int) -> dict:
          "token_time": ((2 * (steps + 1),), "i64"),
          "exp_sums": ((d.NH, parts), "f32"), "max_logits": ((d.NH, parts), "f32"), "tmp_out": ((d.NH, parts, d.HD), "f32"),
          "kc": ((d.L, nblk, d.NKV, d.HD // X, BS, X), "bf16"), "vc": ((d.L, nblk, d.NKV, d.HD, BS), "bf16"),
-         "attn_counters": ((d.L, d.NKV), "i32")}
+         "attn_counters": ((d.L, d.NKV), "i32"), "moe_out": ((d.H,), "bf16")}
     if d.moe:
         s.update({"rlog": ((d.E,), "bf16"), "tw": ((d.TOPK,), "f32"), "ti": ((d.TOPK,), "i32"), "tei": ((d.TOPK,), "i32"),
                   "mc2": ((d.TOPK, d.MI), "bf16"), "mc3": ((d.TOPK, d.H), "bf16")})
@@ -318,9 +331,9 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         t, rpt = sz.qkv
         first = L == 0
         blob = gemv_block("dsl_gemv_fold", t, W=W("wqkv"), x=ptr("hn"), out=ptr("qkv"), M=d.NQKV, K=d.H, rpt=rpt, tpe=1,
-                          rows=0 if first else ptr("mc3"), resid_in=ptr("resid") if first else ptr("resid2"),
-                          resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else slots, eps=d.eps,
-                          ids=0 if (first or not d.moe) else ptr("ti"), wts=W("bqkv") if d.bias else 0,
+                          rows=0 if first else ptr("moe_out"), resid_in=ptr("resid") if first else ptr("resid2"),
+                          resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else 1, eps=d.eps,
+                          ids=0, wts=W("bqkv") if d.bias else 0,
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0), nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
         if fused_attn:
@@ -367,39 +380,40 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                 blob = argblock.pack_named(op_topk2.import_entries()["dsl_topk"], (1, 1, 1), logits=ptr("rlog"), wts=ptr("tw"), ids=ptr("ti"),
                                            tei=ptr("tei"), E=d.E, K=d.TOPK, mode=(1 if d.norm_topk else 0) | hf_mode, nbsv=0)
                 prev = add(f"topk_{L}", "dsl_topk", "topk", L, blob, 1, (1,), prev, "i->(0)", f"E_topk_{L}", "i->(0)", (1,), 1)
-            # ---- experts
-            tpe, rpt = sz.up
-            blob = gemv_block("dsl_moe_up_fold" if fold_topk else "dsl_moe_up", slots * tpe, W=W("w13"), x=ptr("o_norm"), out=ptr("mc2"),
+            # ---- experts: one gate+up task per SM (spt slots x one row chunk), then one down task per SM that covers every
+            #      slot of its output rows and adds them in bf16 in ascending expert id (the expert combine)
+            spt, tpe, rpt = sz.up
+            groups = slots // spt
+            up_export = "dsl_moe_up_fold" if fold_topk else "dsl_moe_up"
+            blob = gemv_block(up_export, groups * tpe, W=W("w13"), x=ptr("o_norm"), out=ptr("mc2"),
                               ids=ptr("ti"), wts=ptr("tw"), estride=2 * d.MI * d.H, M=d.MI, K=d.H, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps,
-                              mode=topk_mode if fold_topk else 0, E=d.E, logits=ptr("rlog"), nb=1)
-            prev = add(f"moe_up_{L}", "dsl_moe_up_fold" if fold_topk else "dsl_moe_up", "moe_up", L, blob, slots * tpe, (slots * tpe,),
-                       prev, "i->(0)", f"E_up_{L}", f"i->(i/{tpe})", (slots,), tpe, d.MI, d.H)
-            up_tpe = tpe
+                              mode=(topk_mode if fold_topk else 0) | op_gemv.mode_spt(spt), E=d.E, logits=ptr("rlog"), nb=1)
+            prev = add(f"moe_up_{L}", up_export, "moe_up", L, blob, groups * tpe, (groups * tpe,),
+                       prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), groups * tpe, d.MI, d.H)
             tpe, rpt = sz.down
             dn_export = "dsl_moe_down_fold" if fold_topk else "dsl_moe_down"
-            blob = gemv_block(dn_export, slots * tpe, W=W("w2"), x=ptr("mc2"), out=ptr("mc3"), ids=ptr("ti"), wts=ptr("tw"),
-                              estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps, mode=topk_mode if fold_topk else 0,
-                              E=d.E, logits=ptr("rlog"), nb=1)
+            blob = gemv_block(dn_export, tpe, W=W("w2"), x=ptr("mc2"), out=ptr("moe_out"), ids=ptr("ti"), wts=ptr("tw"),
+                              estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps,
+                              mode=(topk_mode if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS, E=d.E, logits=ptr("rlog"), nb=1)
             # expert weights depend on the routing only: with the top-k folded in, the stream may start once the router is done
-            prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, slots * tpe, (slots * tpe,), prev, f"i->(i/{tpe})",
-                       f"E_dn_{L}", "i->(0)", (1,), slots * tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None)
-            del up_tpe
+            prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, tpe, (tpe,), prev, "i->(0)",
+                       f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None)
         else:
             # ---- dense SwiGLU: gate+up with the post-attention norm fold, then down
-            tpe, rpt = sz.up
+            spt, tpe, rpt = sz.up
             blob = gemv_block("dsl_moe_up", tpe, W=W("wgu"), x=ptr("o_norm"), out=ptr("mc2"), estride=0, M=d.INTER, K=d.H, rpt=rpt, tpe=tpe,
                               rows=ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=1, eps=d.eps,
                               mode=op_gemv.MODE_NORM, nb=1)
             prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H, after="")
             tpe, rpt = sz.down
-            blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("mc3"), estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
+            blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("moe_out"), estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
                               eps=d.eps, nb=1)
             prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="")
     # ---- lm_head with the final-norm fold, then greedy sampling
     t, rpt = sz.lm
     blob = gemv_block("dsl_gemv_fold", t, W=ptr("embed") if d.tie else ptr("lm_head"), x=ptr("hn"), out=ptr("logits"), M=d.V, K=d.H, rpt=rpt,
-                      tpe=1, rows=ptr("mc3"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=slots, eps=d.eps,
-                      ids=ptr("ti") if d.moe else 0, mode=op_gemv.MODE_NORM, nb=1)
+                      tpe=1, rows=ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=1, eps=d.eps,
+                      ids=0, mode=op_gemv.MODE_NORM, nb=1)
     prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},

@@ -9,7 +9,9 @@ Forms:
   dsl_moe_up[_fold]     act[s, r] = bf16(bf16(silu(bf16 g)) * bf16 u), expert e = ids[s]; fold: top-k recomputed in-tile
   dsl_moe_down[_fold]   out[s, r] = bf16(bf16(W_e[r,:] . act_s) * wts[s])
 mode: 0 plain, 1 norm fold, 2 / 3 top-k fold without / with renormalisation; | 0x100 bf16 routing weights (the numerics
-of the reference's CPU path), | 0x200 bf16 bias row passed in `wts` (plain form).
+of the reference's CPU path), | 0x200 bf16 bias row passed in `wts` (plain form), | 0x400 MoE down: the task covers
+every slot and writes out[r] = the slots' results added in bf16 in ascending expert id (the expert combine), bits
+16..23 expert slots per task (task blk -> slots [blk / tpe * spt, ...), row chunk blk % tpe).
 """
 from __future__ import annotations
 
@@ -26,11 +28,16 @@ PARAMS = [("W", "ptr addrspace(1)", 0, 8), ("x", "ptr addrspace(1)", 8, 8), ("ou
           ("srin", "i32", 136, 4), ("srout", "i32", 140, 4)]
 FORMS = {"dsl_gemv": "plain", "dsl_moe_up": "silu_mul", "dsl_moe_down": "scale",
          "dsl_gemv_fold": "plain", "dsl_moe_up_fold": "silu_mul", "dsl_moe_down_fold": "scale"}
-MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS = 1, 2, 3, 0x100, 0x200
+MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS, MODE_SUM_SLOTS = 1, 2, 3, 0x100, 0x200, 0x400
+
+
+def mode_spt(spt: int) -> int:
+    """Expert slots per task of the MoE forms, carried in mode bits 16..23 (0 and 1 both mean one slot per task)."""
+    return (spt & 0xff) << 16
 THREADS = 544              # 16 consumer warps + the producer warp of the persistent CTA
 MAX_K = 12288              # a streamed row (and its bf16 activation vector in shared memory)
 MAX_K_NORM = 8192          # the norm fold works on fp32 in shared memory
-MAX_ROWS_UP = 1024         # gate+up results one moe_up task holds in shared memory
+MAX_RESULTS = 2048         # row results one MoE task holds in shared memory (ranges x rows per range)
 NB_ALLOWED = (1, 2, 4, 8)
 NB_XS_FLOATS = 40960       # stand-alone batched GEMV (nb > 1): nb * K floats of staged activations
 
@@ -59,7 +66,12 @@ def check_shape(export: str, *, M: int, K: int, rpt: int, nb: int = 1, mode: int
         raise ValueError(f"{export}: K={K} exceeds {MAX_K} (one row must fit a 32 KB ring stage)")
     if (mode & 0xff) == MODE_NORM and K > MAX_K_NORM:
         raise ValueError(f"{export}: norm fold over K={K} > {MAX_K_NORM}")
-    if FORMS[export] == "silu_mul" and rpt > MAX_ROWS_UP:
-        raise ValueError(f"{export}: rpt={rpt} rows per task exceeds {MAX_ROWS_UP}")
+    spt = ((mode >> 16) & 0xff) or 1
+    if FORMS[export] == "silu_mul" and 2 * spt * rpt > MAX_RESULTS:
+        raise ValueError(f"{export}: 2 * {spt} slots * rpt={rpt} row results exceed {MAX_RESULTS}")
+    if FORMS[export] == "scale" and (spt * rpt > MAX_RESULTS or spt * K > MAX_K):
+        raise ValueError(f"{export}: {spt} slots per task: results {spt * rpt} > {MAX_RESULTS} or activations {spt * K} > {MAX_K}")
+    if FORMS[export] == "plain" and (mode & (MODE_SUM_SLOTS | 0xff0000)):
+        raise ValueError(f"{export}: slot bits are for the MoE forms only")
     if rpt < 1 or M < 1:
         raise ValueError(f"{export}: M and rpt must be positive")

@@ -67,8 +67,9 @@ class Session:
         return st
 
     def trace(self) -> np.ndarray:
-        """[n_tasks][4] uint64: taken, deps ready, body done (globaltimer ns), worker; rows in program order."""
-        out = np.zeros((len(self.plan.tasks), 4), np.uint64)
+        """[n_tasks][8] uint64: taken, deps ready, body done (globaltimer ns), worker, then four in-body marks (0 when a
+        tile did not set one); rows in program order."""
+        out = np.zeros((len(self.plan.tasks), 8), np.uint64)
         L.check(self.lib.etxb_trace(self._h, out.ctypes.data_as(C.c_void_p), out.nbytes))
         return out
 

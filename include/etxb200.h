@@ -114,7 +114,8 @@ int32_t etxb_launch(etxb_session* s, void* cuda_stream);
 int32_t etxb_wait(etxb_session* s, double timeout_s);
 int32_t etxb_step(etxb_session* s, void* cuda_stream, double timeout_s);
 int32_t etxb_status(etxb_session* s, etxb_status_t* out);
-/* Copies 4 x uint64 per task {taken, deps ready, body done, worker} (globaltimer ns) of the last traced step. */
+/* Copies 8 x uint64 per task of the last traced step: {taken, deps ready, body done, worker, 4 in-body marks}
+ * (globaltimer ns; a mark a tile did not set is 0). */
 int32_t etxb_trace(etxb_session* s, void* host_buf, size_t bytes);
 int32_t etxb_exec_counts(etxb_session* s, int32_t* host_buf, size_t count);
 int32_t etxb_destroy(etxb_session* s);

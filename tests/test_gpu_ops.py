@@ -28,14 +28,15 @@ def host(t):
     return (t.float() if t.dtype == torch.bfloat16 else t).cpu().numpy()
 
 
-def assert_bf16_close(got, want, what, min_exact=0.98):
+def assert_bf16_close(got, want, what, min_exact=0.98, per_element=True):
     """max |got - want| <= BF16_REL * max|want| (the reference's own check uses 2 bf16 ulps with a floor of scale/4096,
     examples/vllm_llm/host.hip:954-1141), and nearly every element identical: only fp32 summation order differs."""
     scale = float(np.max(np.abs(want))) or 1.0
     err = float(np.max(np.abs(got - want)))
     assert err <= BF16_REL * scale, f"{what}: max abs err {err} vs scale {scale}"
     ulp = np.maximum(np.abs(want) * 2.0 ** -7, scale / 4096)
-    assert np.all(np.abs(got - want) <= 2 * ulp + 1e-30), f"{what}: an element is off by more than 2 bf16 ulps"
+    if per_element:
+        assert np.all(np.abs(got - want) <= 2 * ulp + 1e-30), f"{what}: an element is off by more than 2 bf16 ulps"
     exact = float(np.mean(got == want))
     assert exact >= min_exact, f"{what}: only {exact:.4f} of the elements are bit-identical"
 
@@ -302,12 +303,54 @@ def test_moe_block(E, TOPK, MI, H, fold):
     op_launch("moe_up", up, TOPK * tpe)
     rpt2 = -(-H // tpe)
     dn = argblock.pack_named(ENT["dsl_moe_down"], (TOPK * tpe, 1, 1), W=d_w2.data_ptr(), x=act.data_ptr(), out=y.data_ptr(), ids=ti.data_ptr(),
-                             wts=tw.data_ptr(), estride=H * MI, M=H, K=MI, rpt=rpt2, tpe=tpe, nb=1)
+                             wts=tw.data_ptr(), estride=H * MI, M=H, K=MI, rpt=rpt2, tpe=tpe, R=TOPK, nb=1)
     op_launch("moe_down", dn, TOPK * tpe)
     assert host(ti).tolist() == ids.tolist()
     assert np.all(np.abs(host(tw) - wts) <= np.abs(wts) * 2.0 ** -7)
     assert_bf16_close(host(act), act_ref, "moe_up act", min_exact=0.97)
     assert_bf16_close(host(y), y_ref, "moe_down y", min_exact=0.95)
+
+
+@pytest.mark.parametrize("E,TOPK,MI,H,spt", [(128, 8, 768, 2048, 2), (16, 4, 128, 512, 4), (128, 8, 768, 2048, 8), (64, 6, 1408, 2048, 3)])
+def test_moe_block_grouped_slots_and_summed_down(E, TOPK, MI, H, spt):
+    """Several expert slots per gate+up task, and the down form that covers every slot and writes the expert combine
+    (bf16 adds in ascending expert id, examples/llm/ref_numpy.py:142-148) instead of one row per slot."""
+    rng = np.random.default_rng(E * 7 + spt)
+    xs = O.bfr(rng.standard_normal(H, dtype=np.float32))
+    logits = O.bfr(rng.standard_normal(E, dtype=np.float32))
+    w13 = O.bfr(rng.standard_normal((E, 2 * MI, H), dtype=np.float32) * np.float32(0.02))
+    w2 = O.bfr(rng.standard_normal((E, H, MI), dtype=np.float32) * np.float32(0.02))
+    ids, wts = O.softmax_topk(logits, TOPK, True)
+    act_ref = np.zeros((TOPK, MI), np.float32)
+    acc = np.float32(0)
+    ys = {}
+    for s, (e, we) in enumerate(zip(ids.tolist(), wts.tolist())):
+        g = O.bfr(w13[e, :MI] @ xs); u = O.bfr(w13[e, MI:] @ xs)
+        act_ref[s] = O.bfr(O.bfr(O.silu(g)) * u)
+        ys[e] = O.bfr(O.bfr(w2[e] @ act_ref[s]) * np.float32(we))
+    for e in sorted(ys):
+        acc = O.bfr(acc + ys[e])
+    d_x, d_lg, d_w13, d_w2 = dev_bf16(xs), dev_bf16(logits), dev_bf16(w13), dev_bf16(w2)
+    ti = torch.zeros(TOPK, dtype=torch.int32, device=DEV); tw = torch.zeros(TOPK, dtype=torch.float32, device=DEV)
+    act = torch.zeros((TOPK, MI), dtype=torch.bfloat16, device=DEV); out = torch.zeros(H, dtype=torch.bfloat16, device=DEV)
+    tpe = 7
+    rpt = -(-MI // tpe); tpe = -(-MI // rpt)
+    groups = TOPK // spt
+    mode = (3 | 0x100) | (spt << 16)
+    up = argblock.pack_named(ENT["dsl_moe_up_fold"], (groups * tpe, 1, 1), W=d_w13.data_ptr(), x=d_x.data_ptr(), out=act.data_ptr(), ids=ti.data_ptr(),
+                             wts=tw.data_ptr(), estride=2 * MI * H, M=MI, K=H, rpt=rpt, tpe=tpe, R=TOPK, mode=mode, E=E, logits=d_lg.data_ptr(), nb=1)
+    op_launch("moe_up", up, groups * tpe)
+    tpe2 = 9
+    rpt2 = -(-H // tpe2); tpe2 = -(-H // rpt2)
+    dn = argblock.pack_named(ENT["dsl_moe_down_fold"], (tpe2, 1, 1), W=d_w2.data_ptr(), x=act.data_ptr(), out=out.data_ptr(), ids=ti.data_ptr(),
+                             wts=tw.data_ptr(), estride=H * MI, M=H, K=MI, rpt=rpt2, tpe=tpe2, R=TOPK, mode=(3 | 0x100) | (TOPK << 16) | 0x400,
+                             E=E, logits=d_lg.data_ptr(), nb=1)
+    op_launch("moe_down", dn, tpe2)
+    assert host(ti).tolist() == ids.tolist()
+    assert_bf16_close(host(act), act_ref, "grouped moe_up act", min_exact=0.97)
+    # a sum of eight rounded terms can cancel: the 2-ulp bound is relative to the terms, not to the (smaller) sum
+    assert_bf16_close(host(out), acc, "summed moe_down", min_exact=0.9, per_element=False)
+    assert np.all(np.abs(host(out) - acc) <= 4 * 2.0 ** -8 * max(np.abs(y).max() for y in ys.values()))
 
 
 def test_argument_block_rejected_before_launch():
