@@ -36,7 +36,7 @@ __device__ __forceinline__ float head_sumsq(const float* x, int n) {
 
 // task h = kv head: warps 0..G-1 do the q heads h*G + w, warp G the k head (both in place on qkv; k also into the
 // cache), warp G+1 copies the v row into the cache.  G + 2 <= 16, HD a multiple of 32 and <= 256.
-__device__ __forceinline__ void tile_attnprep(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
+__device__ __noinline__ void tile_attnprep(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
   const etxb_attnprep_args& d = *(const etxb_attnprep_args*)a;
   if (blk >= (int)d.nblocks) return;
   const int h = blk, NH = d.NH, NKV = d.NKV, HD = d.HD, G = NH / NKV, BS = d.BS, X = d.X;
@@ -88,7 +88,7 @@ __device__ __forceinline__ void tile_attnprep(const unsigned char* a, int blk, c
 // task blk = part * NKV + h: positions [part*32, part*32 + 32) of kv head h against its G q heads.
 // Writes, per q head, the partition's max logit, exp sum and unnormalised output (fp32).  HD <= 256, HD % 8 == 0,
 // BS 16 or 32, X 8.
-__device__ __forceinline__ void tile_attn(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
+__device__ __noinline__ void tile_attn(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
   const etxb_attn_args& d = *(const etxb_attn_args*)a;
   if (blk >= (int)d.nblocks) return;
   const int NKV = d.NKV, HD = d.HD, G = d.NH / NKV, BS = d.BS, X = d.X, P = ETXB_ATTN_PART;
@@ -173,204 +173,8 @@ __device__ __forceinline__ void tile_attn(const unsigned char* a, int blk, const
   }
 }
 
-// One head row (HD values in shared memory, d = lane * epl + j held by lane): optional RMSNorm with weight nw, then
-// neox rotary with the bf16 cos | sin row cs.  o[j] receives the bf16-rounded results.  One warp.
-__device__ __forceinline__ void head_norm_rope(const float* xh, const __nv_bfloat16* nw, const __nv_bfloat16* cs, int HD, float eps, float* o) {
-  const int lane = tidx() & 31, half = HD >> 1, epl = HD >> 5;
-  float v[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] = j < epl ? xh[lane * epl + j] : 0.f;
-  if (nw != nullptr) {
-    const float ss = head_sumsq(xh, HD);
-    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)HD), eps)));
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (j < epl) v[j] = bfr(__fmul_rn(__bfloat162float(nw[lane * epl + j]), bfr(__fmul_rn(v[j], r))));
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);    // element d +- HD/2 lives 16 lanes away
-    if (j < epl) {
-      const int dd = lane * epl + j;
-      const float rot = dd < half ? -other : other;
-      const float c = __bfloat162float(cs[dd % half]), sn = __bfloat162float(cs[half + dd % half]);
-      o[j] = bfr(__fadd_rn(bfr(__fmul_rn(v[j], c)), bfr(__fmul_rn(rot, sn))));
-    }
-  }
-}
-
-// The whole attention phase of one (partition, kv head): see etxb_attnf_args.  Numerics as the three separate tiles.
-__device__ __forceinline__ void tile_attn_fused(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
-  const etxb_attnf_args& d = *(const etxb_attnf_args*)a;
-  if (blk >= (int)d.nblocks) return;
-  const int NH = d.NH, NKV = d.NKV, HD = d.HD, G = NH / NKV, BS = d.BS, X = d.X, P = ETXB_ATTN_PART;
-  const int part = blk / NKV, h = blk - part * NKV;
-  const int lane = tidx() & 31, warp = tidx() >> 5;
-  const long long pos = (const void*)d.positions == (const void*)S.positions ? (long long)S.pos : __ldcg((const long long*)d.positions);
-  const long long slot = (const void*)d.slot_mapping == (const void*)S.slot_mapping ? (long long)S.pos : __ldcg((const long long*)d.slot_mapping);
-  const int seq = (const void*)d.seq_lens == (const void*)S.seq_lens ? S.pos + 1 : __ldcg(d.seq_lens);
-  const int t0 = part * P;
-  const int np = (seq + P - 1) / P;
-  // shared layout (G * HD <= 2048, HD <= 256: at most 57.6 KB of the 64 KB region)
-  float* qs = sm.xs;                                              // [G][HD] floats (normed + roped q)
-  __nv_bfloat16* ks = (__nv_bfloat16*)(qs + G * HD);              // [nblk][HD/X][BS][X]
-  __nv_bfloat16* vs = ks + P * HD;                                // [nblk][HD][BS]
-  float* sc = (float*)(vs + P * HD);                              // [G][P]
-  float* st = sc + 16 * P;                                        // per head: max, sum
-  float* ph = st + 64;                                            // [2][16 * P] half dot products
-  float* raw = ph + 2 * 16 * P;                                   // [G + 2][HD] raw q rows, k row, v row
-  int* flag = (int*)(sm.scr + 130);
-  if (t0 < seq) {
-    const int ntok = min(P, seq - t0);
-    const int nblk = P / BS;
-    const bool owner = pos >= t0 && pos < t0 + P;                 // this partition holds the position being written
-    const __nv_bfloat16* qkv = (const __nv_bfloat16*)d.qkv;
-    // cached K and V blocks of this partition (the new position's slot is overwritten in shared memory below)
-    const int vec_per_blk = HD * BS / 8;
-    for (int i = tidx(); i < nblk * vec_per_blk; i += ETXB_CONSUMERS) {
-      const int b = i / vec_per_blk, r = i - b * vec_per_blk;
-      const int lb = t0 / BS + b;
-      if (lb * BS < seq) {
-        const long long pb = __ldg(d.block_tables + lb);
-        const size_t base = ((size_t)pb * NKV + h) * HD * BS;
-        *(uint4*)(ks + (size_t)b * HD * BS + 8 * r) = ld_act16((const __nv_bfloat16*)d.kc + base + 8 * r);
-        *(uint4*)(vs + (size_t)b * HD * BS + 8 * r) = ld_act16((const __nv_bfloat16*)d.vc + base + 8 * r);
-      }
-    }
-    mark(sm, 0);
-    // raw q heads of the group (+ the new k and v rows for the owner)
-    for (int i = tidx(); i < G * HD; i += ETXB_CONSUMERS) raw[i] = ld_bf(qkv, (size_t)h * G * HD + i);
-    if (owner)
-      for (int i = tidx(); i < 2 * HD; i += ETXB_CONSUMERS)
-        raw[G * HD + i] = ld_bf(qkv, (size_t)(i < HD ? NH + h : NH + NKV + h) * HD + (i < HD ? i : i - HD));
-    csync();
-    const __nv_bfloat16* cs = (const __nv_bfloat16*)d.cos_sin + (size_t)pos * HD;
-    const int epl = HD >> 5;
-    const long long cb = slot / BS; const int off = (int)(slot % BS);
-    const int lb_new = (int)(pos / BS) - t0 / BS, lo_new = (int)(pos % BS);       // where the new row sits in the shared tiles
-    if (warp < G) {
-      float o[8];
-      head_norm_rope(raw + warp * HD, (const __nv_bfloat16*)d.qw, cs, HD, d.eps, o);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) if (j < epl) qs[warp * HD + lane * epl + j] = o[j];
-    } else if (warp == G && owner) {
-      float o[8];
-      head_norm_rope(raw + G * HD, (const __nv_bfloat16*)d.kw, cs, HD, d.eps, o);
-      __nv_bfloat16* kc = (__nv_bfloat16*)d.kc;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (j < epl) {
-          const int dd = lane * epl + j;
-          const __nv_bfloat16 kb = __float2bfloat16_rn(o[j]);
-          kc[(((size_t)cb * NKV + h) * (HD / X) + dd / X) * BS * X + (size_t)off * X + dd % X] = kb;
-          ks[(size_t)lb_new * HD * BS + ((size_t)(dd / X) * BS + lo_new) * X + dd % X] = kb;
-        }
-    } else if (warp == G + 1 && owner) {
-      __nv_bfloat16* vc = (__nv_bfloat16*)d.vc;
-      for (int dd = lane; dd < HD; dd += 32) {
-        const __nv_bfloat16 vb = __float2bfloat16_rn(raw[(G + 1) * HD + dd]);
-        vc[(((size_t)cb * NKV + h) * HD + dd) * BS + off] = vb;
-        vs[(size_t)lb_new * HD * BS + (size_t)dd * BS + lo_new] = vb;
-      }
-    }
-    csync();
-    mark(sm, 1);
-    // scores: idx -> (g, half, t); the two halves of the head dimension are added left to right, then scaled
-    const int hx = HD / X;
-    for (int idx = tidx(); idx < G * 2 * P; idx += ETXB_CONSUMERS) {
-      const int t = idx % P, hf = (idx / P) & 1, g = idx / (2 * P);
-      float acc = 0.f;
-      if (t < ntok) {
-        const int b = t / BS, o = t % BS;
-        const __nv_bfloat16* kb = ks + (size_t)b * HD * BS;
-        for (int dg = hf * (hx / 2); dg < (hf + 1) * (hx / 2); ++dg) {
-          const uint4 kv = *(const uint4*)(kb + ((size_t)dg * BS + o) * X);
-          const float* qq = qs + g * HD + dg * X;
-          acc = __fmaf_rn(bf_lo(kv.x), qq[0], acc); acc = __fmaf_rn(bf_hi(kv.x), qq[1], acc);
-          acc = __fmaf_rn(bf_lo(kv.y), qq[2], acc); acc = __fmaf_rn(bf_hi(kv.y), qq[3], acc);
-          acc = __fmaf_rn(bf_lo(kv.z), qq[4], acc); acc = __fmaf_rn(bf_hi(kv.z), qq[5], acc);
-          acc = __fmaf_rn(bf_lo(kv.w), qq[6], acc); acc = __fmaf_rn(bf_hi(kv.w), qq[7], acc);
-        }
-      }
-      ph[hf * 16 * P + g * P + t] = acc;
-    }
-    csync();
-    for (int i = tidx(); i < G * P; i += ETXB_CONSUMERS)
-      sc[i] = (i % P) < ntok ? __fmul_rn(__fadd_rn(ph[i], ph[16 * P + i]), d.scale) : -INFINITY;
-    csync();
-    for (int g = warp; g < G; g += ETXB_NWARPS) {
-      const float s = sc[g * P + lane];
-      const float m = warp_max(s);
-      const float pr = lane < ntok ? expf(__fsub_rn(s, m)) : 0.f;
-      const float l = warp_sum(pr);
-      sc[g * P + lane] = pr;
-      if (lane == 0) { st[2 * g] = m; st[2 * g + 1] = l; }
-    }
-    csync();
-    for (int idx = tidx(); idx < G * HD; idx += ETXB_CONSUMERS) {
-      const int dd = idx % HD, g = idx / HD;
-      float acc = 0.f;
-      for (int b = 0; b < nblk; ++b) {
-        if (b * BS >= ntok) break;
-        const __nv_bfloat16* vb = vs + ((size_t)b * HD + dd) * BS;
-        const int lim = min(BS, ntok - b * BS);
-        for (int o = 0; o < lim; ++o) acc = __fmaf_rn(sc[g * P + b * BS + o], __bfloat162float(vb[o]), acc);
-      }
-      const int hq = h * G + g;
-      d.tmp_out[((size_t)hq * d.max_parts + part) * HD + dd] = acc;
-      if (dd == 0) {
-        d.max_logits[(size_t)hq * d.max_parts + part] = st[2 * g];
-        d.exp_sums[(size_t)hq * d.max_parts + part] = st[2 * g + 1];
-      }
-    }
-  }
-  // the last task of this kv head to get here merges the partitions of its G q heads
-  csync();
-  mark(sm, 2);
-  if (tidx() == 0) {
-    __threadfence();
-    const int old = atomicAdd(d.counters + h, 1);
-    *flag = ((old + 1) % d.max_parts) == 0;
-    if (*flag) __threadfence();
-  }
-  csync();
-  mark(sm, 3);
-  if (!*flag) return;
-  float* wl = sm.xs;                                              // [G][np] max logits, then weights
-  float* es = sm.xs + 8192;                                       // [G][np] exp sums (G * np <= 8192)
-  float* red = sm.scr;                                            // [G] 1 / denominators at red + 200
-  for (int i = tidx(); i < G * np; i += ETXB_CONSUMERS) {
-    const int g = i / np, pp = i - g * np;
-    wl[i] = __ldcg(d.max_logits + (size_t)(h * G + g) * d.max_parts + pp);
-    es[i] = __ldcg(d.exp_sums + (size_t)(h * G + g) * d.max_parts + pp);
-  }
-  csync();
-  for (int g = warp; g < G; g += ETXB_NWARPS) {
-    float m = -INFINITY;
-    for (int pp = lane; pp < np; pp += 32) m = fmaxf(m, wl[g * np + pp]);
-    m = warp_max(m);
-    float L = 0.f;
-    for (int pp = lane; pp < np; pp += 32) {
-      const float w = expf(__fsub_rn(wl[g * np + pp], m));
-      wl[g * np + pp] = w;
-      L = __fmaf_rn(w, es[g * np + pp], L);
-    }
-    L = warp_sum(L);
-    if (lane == 0) red[200 + g] = L;
-  }
-  csync();
-  for (int idx = tidx(); idx < G * HD; idx += ETXB_CONSUMERS) {
-    const int dd = idx % HD, g = idx / HD;
-    const float* tp = d.tmp_out + (size_t)(h * G + g) * d.max_parts * HD + dd;
-    float o = 0.f;
-#pragma unroll 4
-    for (int pp = 0; pp < np; ++pp) o = __fmaf_rn(wl[g * np + pp], __ldcg(tp + (size_t)pp * HD), o);
-    ((__nv_bfloat16*)d.out)[(size_t)(h * G + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[200 + g]));
-  }
-}
-
 // task blk = q head: out[hq][:] = bf16(sum_p w_p * tmp[p][:] / sum_p w_p * l_p), w_p = exp(m_p - max m).
-__device__ __forceinline__ void tile_attn_reduce(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
+__device__ __noinline__ void tile_attn_reduce(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
   const etxb_attn_args& d = *(const etxb_attn_args*)a;
   if (blk >= (int)d.nblocks) return;
   const int HD = d.HD, hq = blk, P = ETXB_ATTN_PART;

@@ -67,40 +67,40 @@ struct GemvTask {
 // softmax over E bf16 logits (fp32), K rounds of argmax with the lower index winning ties, optional renormalisation
 // over the selected weights (numpy's summation order for <= 16 values), optional bf16 rounding of the weights.
 // One warp (all 32 lanes call); E <= 256, K <= 16.  ids / wts / tei may point to shared or global memory.
-__device__ __forceinline__ void warp_topk(const void* logits, int E, int K, bool renorm, bool bf16w,
-                                          int32_t* ids, float* wts, int32_t* tei) {
+__device__ __noinline__ void warp_topk(const void* logits, int E, int K, bool renorm, bool bf16w,
+                                       int32_t* ids, float* wts, int32_t* tei) {
   const int lane = tidx() & 31;
-  float p[8]; bool taken[8];
+  float p[8];
   float m = -INFINITY;
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const int e = lane + 32 * k;
     p[k] = e < E ? ld_bf(logits, e) : -INFINITY;
-    taken[k] = e >= E;
     m = fmaxf(m, p[k]);
   }
   m = warp_max(m);
   float s = 0.f;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) { p[k] = taken[k] ? 0.f : expf(__fsub_rn(p[k], m)); s = __fadd_rn(s, p[k]); }
+  for (int k = 0; k < 8; ++k) { p[k] = (lane + 32 * k < E) ? expf(__fsub_rn(p[k], m)) : 0.f; s = __fadd_rn(s, p[k]); }
   s = warp_sum(s);
+  // Selection keys: a probability is a non-negative float, so its bit pattern orders like the value; + 1 keeps a valid
+  // zero probability above "no candidate" (0).  Each round is two warp reductions (redux.sync): the maximum key, then
+  // the lowest expert index holding it (the lower index wins ties).  NaN logits are not supported.
+  uint32_t key[8];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) p[k] = __fdiv_rn(p[k], s);
+  for (int k = 0; k < 8; ++k) { p[k] = __fdiv_rn(p[k], s); key[k] = (lane + 32 * k < E) ? __float_as_uint(p[k]) + 1u : 0u; }
   float myw = 0.f; int myid = 0x7fffffff;
   for (int t = 0; t < K; ++t) {
-    float bv = -1.f; int bi = 0x7fffffff;
+    uint32_t bk = 0; int bi = 0x7fffffff;
 #pragma unroll
     for (int k = 0; k < 8; ++k)
-      if (!taken[k] && p[k] > bv) { bv = p[k]; bi = lane + 32 * k; }
+      if (key[k] > bk) { bk = key[k]; bi = lane + 32 * k; }
+    const uint32_t top = __reduce_max_sync(0xffffffffu, bk);
+    const int win = (int)__reduce_min_sync(0xffffffffu, (uint32_t)(bk == top && top != 0u ? bi : 0x7fffffff));
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-#pragma unroll
-    for (int k = 0; k < 8; ++k) taken[k] = taken[k] || (lane + 32 * k == bi);
-    if (lane == t) { myw = bv; myid = bi; }
+    for (int k = 0; k < 8; ++k)
+      if (lane + 32 * k == win) key[k] = 0u;
+    if (lane == t) { myw = top != 0u ? __uint_as_float(top - 1u) : -1.f; myid = win; }
   }
   if (renorm) {
     // numpy's order for the sum of the K selected weights: K < 8 left to right, else 8 accumulators + tree + tail

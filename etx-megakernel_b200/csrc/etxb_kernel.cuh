@@ -5,6 +5,7 @@
 // etx_run_task kernel.py:341-468, and the native prologue / argmax tiles examples/vllm_llm/vl_tiles.hip:31-89.
 #pragma once
 #include "etxb_attn.cuh"
+#include "etxb_attn_fused.cuh"
 #include "etxb_gemv.cuh"
 #include "etxb_prims.cuh"
 
