@@ -208,6 +208,7 @@ __device__ __noinline__ void attn_fused_merge(const etxb_attnf_args& d, const Sm
     es[i] = __ldcg(d.exp_sums + (size_t)(h * G + g) * d.max_parts + pp);
   }
   csync();
+  mark(sm, 0);
   for (int g = warp; g < G; g += ETXB_NWARPS) {
     float m = -INFINITY;
     for (int pp = lane; pp < np; pp += 32) m = fmaxf(m, wl[g * np + pp]);
@@ -222,13 +223,40 @@ __device__ __noinline__ void attn_fused_merge(const etxb_attnf_args& d, const Sm
     if (lane == 0) red[g] = L;
   }
   csync();
-  for (int idx = tidx(); idx < G * HD; idx += ETXB_CONSUMERS) {
-    const int dd = idx % HD, g = idx / HD;
+  mark(sm, 1);
+  // weighted sum of the partials: a thread owns four consecutive output values (16-byte loads) and every groups-th
+  // partition; the groups' sums are then added left to right.  A fixed order, so the result is reproducible.
+  const int quads = G * HD / 4, groups = ETXB_CONSUMERS / quads > 0 ? ETXB_CONSUMERS / quads : 1;
+  float* part = sm.xs + 12288;                                    // [groups][G * HD] = 2048 floats, over the exp sums (dead by now)
+  for (int item = tidx(); item < quads * groups; item += ETXB_CONSUMERS) {
+    const int qd = item % quads, grp = item / quads;
+    const int g = (4 * qd) / HD, dd = 4 * qd - g * HD;
     const float* tp = d.tmp_out + (size_t)(h * G + g) * d.max_parts * HD + dd;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p0 = grp; p0 < np; p0 += 4 * groups) {
+      float4 v[4]; float w[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int pp = p0 + u * groups;
+        const int pc = pp < np ? pp : np - 1;                      // clamped: the weight of a padded load is zero
+        v[u] = __ldcg((const float4*)(tp + (size_t)pc * HD));
+        w[u] = pp < np ? wl[g * np + pp] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        o.x = __fmaf_rn(w[u], v[u].x, o.x); o.y = __fmaf_rn(w[u], v[u].y, o.y);
+        o.z = __fmaf_rn(w[u], v[u].z, o.z); o.w = __fmaf_rn(w[u], v[u].w, o.w);
+      }
+    }
+    *(float4*)(part + (size_t)grp * G * HD + 4 * qd) = o;
+  }
+  csync();
+  mark(sm, 2);
+  for (int idx = tidx(); idx < G * HD; idx += ETXB_CONSUMERS) {
+    const int g = idx / HD;
     float o = 0.f;
-#pragma unroll 4
-    for (int pp = 0; pp < np; ++pp) o = __fmaf_rn(wl[g * np + pp], __ldcg(tp + (size_t)pp * HD), o);
-    ((__nv_bfloat16*)d.out)[(size_t)(h * G + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
+    for (int grp = 0; grp < groups; ++grp) o = __fadd_rn(o, part[(size_t)grp * G * HD + idx]);
+    ((__nv_bfloat16*)d.out)[(size_t)h * G * HD + idx] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
   }
 }
 

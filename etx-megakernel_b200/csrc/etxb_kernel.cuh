@@ -153,6 +153,11 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
     const etxb_type* ty = p.types + type;
     const int body = ty->body;
     if (body < 3 || body > 5) continue;
+    // the argument block through shared memory, fetched BEFORE the wait below (it depends on no event)
+    const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
+    etxb_gemv_args* pa = (etxb_gemv_args*)(sm.prod + 32);
+    if (lane < 20) ((uint64_t*)pa)[lane] = __ldg((const uint64_t*)args + lane);
+    __syncwarp();
     const int sw = ty->stream_word;
     if (sw != -1) {
       int good = 1;
@@ -169,11 +174,6 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
     } else if (ld_relaxed(p.ctrl) != 0) {
       break;
     }
-    const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
-    // the argument block through shared memory (one 160-byte read instead of a dependent global load per field)
-    etxb_gemv_args* pa = (etxb_gemv_args*)(sm.prod + 32);
-    if (lane < 20) ((uint64_t*)pa)[lane] = __ldg((const uint64_t*)args + lane);
-    __syncwarp();
     const GemvTask gt = gemv_task(body, *pa, t->coord[0]);
     if (gt.n > 0 && body != 3) gemv_routing(*pa, sm.prod, (float*)(sm.prod + 16));
     ok = produce_task(body, *pa, gt, sm.prod, n, sm, cur);
