@@ -502,3 +502,75 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   if (step) memcpy(&p.step, step, sizeof(p.step));
   return launch_kernel(p, W, st);
 }
+
+// ---- attention phase without any allocation ---------------------------------------------------------------------
+// Some callers cannot allocate device memory at the point where they need attention: code running inside a region
+// that forbids cudaMalloc (a real-time serving loop that pre-sized its pools, a plug-in that only receives the
+// host's input and output buffers, a caller that already handed all free memory to its KV cache).  The fused
+// attention tile needs scratch for the per-partition partial results; here that scratch is a file-scope device array
+// of fixed size that every GPU loading this library holds until the process exits.
+#define ETXB_STATIC_MAX_NH 64        // q heads
+#define ETXB_STATIC_MAX_PARTS 64     // partitions of 32 positions: context <= 2048
+#define ETXB_STATIC_MAX_HD 128
+struct etxb_static_scratch {
+  float tmp_out[ETXB_STATIC_MAX_NH * ETXB_STATIC_MAX_PARTS * ETXB_STATIC_MAX_HD];   // 2 MiB
+  float exp_sums[ETXB_STATIC_MAX_NH * ETXB_STATIC_MAX_PARTS];
+  float max_logits[ETXB_STATIC_MAX_NH * ETXB_STATIC_MAX_PARTS];
+  int32_t counters[ETXB_STATIC_MAX_NH];
+};
+static __device__ __align__(256) unsigned char g_attn_scratch[sizeof(etxb_static_scratch)];
+static etxb_static_scratch* g_attn_scratch_dev[64];   // device address of the array on each device, set once per device
+
+namespace etxb {
+__global__ void __launch_bounds__(ETXB_CONSUMERS, 1) etxb_attn_static_kernel(const etxb_attnf_args d, const etxb_stepv S) {
+  extern __shared__ __align__(128) unsigned char st_smem[];
+  Smem sm;
+  sm.xs = (float*)st_smem;
+  sm.scr = (float*)(st_smem + ETXB_GEN_BYTES);
+  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.tr = nullptr;
+  tile_attn_fused((const unsigned char*)&d, (int)blockIdx.x, sm, S);
+}
+}  // namespace etxb
+
+// The fused attention phase (see etxb_attnf_args) with its partial-result scratch in the static array above.
+// `argblock` is an etxb_attnf_args block as for the attn_fused tile; its exp_sums, max_logits, tmp_out and counters
+// pointers are ignored.  Limits: NH <= 64, max_parts <= 64 (context <= 2048), HD <= 128; larger sizes are refused
+// with ETXB_E_UNSUPPORTED.  Calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on a
+// device looks the array's device address up (cudaGetSymbolAddress) and raises the kernel's shared-memory limit: make
+// that first call before any stream capture.  Every call shares the one array: it keeps the previous call's
+// partials, the election counters are cleared at the start of each call, and two calls that overlap on the GPU
+// (different streams) race on it.  Asynchronous on `cuda_stream`.
+extern "C" int32_t etxb_attn_fused_static(int device, const void* argblock, size_t bytes, void* cuda_stream) {
+  if (!argblock || bytes < sizeof(etxb_attnf_args)) return fail(ETXB_E_ARG, "attn_fused_static: needs a 176-byte attn_fused argument block");
+  if (device < 0 || device >= 64) return fail(ETXB_E_ARG, "device index out of range");
+  etxb_attnf_args d;
+  memcpy(&d, argblock, sizeof d);
+  if (d.NKV < 1 || d.NH < d.NKV || d.NH % d.NKV) return fail(ETXB_E_ARG, "attn_fused_static: NH must be a multiple of NKV");
+  const int G = d.NH / d.NKV;
+  if (d.NH > ETXB_STATIC_MAX_NH || d.max_parts > ETXB_STATIC_MAX_PARTS || d.HD > ETXB_STATIC_MAX_HD || d.max_parts < 1) {
+    char m[200];
+    snprintf(m, sizeof m, "attn_fused_static: NH=%d, max_parts=%d, HD=%d exceed the static scratch (NH <= %d, max_parts <= %d, HD <= %d)",
+             d.NH, d.max_parts, d.HD, ETXB_STATIC_MAX_NH, ETXB_STATIC_MAX_PARTS, ETXB_STATIC_MAX_HD);
+    return fail(ETXB_E_UNSUPPORTED, m);
+  }
+  if (G + 2 > ETXB_CONSUMER_WARPS || G * d.HD > 2048 || d.HD % 32 || d.X != 8 || (d.BS != 16 && d.BS != 32) || G * d.max_parts > 8192)
+    return fail(ETXB_E_UNSUPPORTED, "attn_fused_static: shape outside the fused attention tile (G + 2 <= 16, G * HD <= 2048, HD % 32 == 0, X = 8, BS 16 or 32)");
+  if (d.nblocks != (uint32_t)(d.max_parts * d.NKV)) return fail(ETXB_E_ARG, "attn_fused_static: the grid must be max_parts * NKV tasks");
+  CU(cudaSetDevice(device));
+  const int smem = ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4;
+  if (!g_attn_scratch_dev[device]) {                              // set-up, once per device, with that device current
+    void* p = nullptr;
+    CU(cudaGetSymbolAddress(&p, g_attn_scratch));
+    CU(cudaFuncSetAttribute(etxb::etxb_attn_static_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    g_attn_scratch_dev[device] = (etxb_static_scratch*)p;
+  }
+  etxb_static_scratch* sc = g_attn_scratch_dev[device];
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  CU(cudaMemsetAsync(sc->counters, 0, sizeof(sc->counters), st));  // the merge election counts arrivals from zero
+  d.tmp_out = sc->tmp_out; d.exp_sums = sc->exp_sums; d.max_logits = sc->max_logits; d.counters = sc->counters;
+  etxb_stepv S;
+  memset(&S, 0, sizeof S);                                        // no step buffers: position / slot / length come from the block's pointers
+  etxb::etxb_attn_static_kernel<<<d.nblocks, ETXB_CONSUMERS, smem, st>>>(d, S);
+  CU(cudaGetLastError());
+  return ETXB_OK;
+}

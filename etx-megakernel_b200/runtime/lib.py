@@ -26,7 +26,7 @@ BODY = {"nop": 0, "prologue": 1, "argmax": 2, "gemv": 3, "moe_up": 4, "moe_down"
 # every symbol include/etxb200.h declares
 SYMBOLS = ["etxb_version", "etxb_last_error", "etxb_device_info", "etxb_create", "etxb_bind", "etxb_set_step", "etxb_set_option",
            "etxb_launch", "etxb_wait", "etxb_step", "etxb_status", "etxb_trace", "etxb_exec_counts", "etxb_destroy",
-           "etxb_decode_host", "etxb_op_launch"]
+           "etxb_decode_host", "etxb_op_launch", "etxb_attn_fused_static"]
 
 
 class EtxbError(RuntimeError):
@@ -97,6 +97,7 @@ def load():
         "etxb_launch": [vp, vp], "etxb_wait": [vp, C.c_double], "etxb_step": [vp, vp, C.c_double], "etxb_status": [vp, C.POINTER(Status)],
         "etxb_trace": [vp, vp, sz], "etxb_exec_counts": [vp, vp, sz], "etxb_destroy": [vp],
         "etxb_decode_host": [vp, vp, i32, i32, i32, vp, vp], "etxb_op_launch": [C.c_int, i32, vp, sz, i32, C.POINTER(StepParams), vp],
+        "etxb_attn_fused_static": [C.c_int, vp, sz, vp],
     }
     for name, args in proto.items():
         fn = getattr(lib, name)

@@ -93,3 +93,9 @@ def op_launch(body: str | int, argblock: bytes, ntasks: int, device: int = 0, st
     b = L.BODY[body] if isinstance(body, str) else int(body)
     L.check(L.load().etxb_op_launch(device, b, argblock, len(argblock), ntasks, C.byref(step) if step is not None else None,
                                     C.c_void_p(stream or 0)))
+
+
+def attn_fused_static(argblock: bytes, device: int = 0, stream: int | None = None):
+    """The fused attention phase through the entry point that allocates nothing (scratch in a static device array of the
+    library: NH <= 64, max_parts <= 64, HD <= 128).  `argblock`: an attn_fused block; its scratch pointers are ignored."""
+    L.check(L.load().etxb_attn_fused_static(device, argblock, len(argblock), C.c_void_p(stream or 0)))

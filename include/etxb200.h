@@ -133,6 +133,16 @@ int32_t etxb_decode_host(etxb_session* s, const int32_t* tokens_in, int32_t n_in
 int32_t etxb_op_launch(int device, int32_t body, const void* argblock, size_t bytes, int32_t ntasks,
                        const etxb_step_params* step /* may be null */, void* cuda_stream);
 
+/* The fused attention phase with NO device allocation: its partial-result scratch lives in a fixed-size static
+ * device array inside the library (about 2.1 MiB, held by every GPU that loads the library until the process exits).
+ * No counterpart in the reference.  For callers that cannot allocate when they need attention (a plug-in that only
+ * gets the host's buffers, a serving loop that pre-sized its pools, a caller whose free memory all went to the KV
+ * cache).  `argblock`: an attn_fused block (etx-megakernel_b200/csrc/etxb_abi.h: etxb_attnf_args); its four scratch
+ * pointers are ignored.  Limits: NH <= 64, max_parts <= 64 (context <= 2048), HD <= 128, else ETXB_E_UNSUPPORTED.
+ * The first call on a device does the one-time set-up (symbol address, shared-memory limit): make it before any
+ * stream capture.  All calls share the array; calls that overlap on the GPU race on it.  Asynchronous on the stream. */
+int32_t etxb_attn_fused_static(int device, const void* argblock, size_t bytes, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
