@@ -43,7 +43,7 @@ struct etxb_session {
   std::vector<etxb_task> tasks;
   std::vector<void*> tensor_ptr;       // device address of every plan tensor (index 0 = argument pool)
   // device copies
-  etxb_task* d_tasks = nullptr; int32_t* d_qbegin = nullptr; etxb_type* d_types = nullptr; void** d_type_args = nullptr;
+  etxb_task* d_tasks = nullptr; etxb_rec* d_recs = nullptr; int32_t* d_qbegin = nullptr; etxb_type* d_types = nullptr; void** d_type_args = nullptr;
   int32_t* d_events = nullptr; int32_t* d_evcount = nullptr; int32_t* d_inwords = nullptr; int32_t* d_outwords = nullptr;
   int32_t* d_ctrl = nullptr; uint64_t* d_trace = nullptr; int32_t* d_exec = nullptr; unsigned char* d_pool = nullptr;
   int32_t* h_ctrl = nullptr;           // pinned mirror
@@ -208,7 +208,7 @@ extern "C" int32_t etxb_destroy(etxb_session* s) {
   if (!s) return ETXB_OK;
   cudaSetDevice(s->device);
   if (s->launched) cudaDeviceSynchronize();
-  void* ptrs[] = {s->d_tasks, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
+  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
                   s->d_ctrl, s->d_trace, s->d_exec, s->d_pool};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (s->h_ctrl) cudaFreeHost(s->h_ctrl);
@@ -264,12 +264,31 @@ static int32_t upload_type_args(etxb_session* s) {
       ta[t * ETXB_MAX_ARGS + k] = s->tensor_ptr[idx];
     }
   CU(cudaMemcpy(s->d_type_args, ta.data(), ta.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  // per-task records in queue order (the consumer loop prefetches them)
+  std::vector<etxb_rec> recs(s->tasks.size());
+  for (size_t i = 0; i < s->tasks.size(); ++i) {
+    const etxb_task& t = s->tasks[i];
+    const etxb_type& ty = s->types[t.type];
+    etxb_rec& r = recs[i];
+    memset(&r, 0, sizeof r);
+    r.body = ty.body; r.c0 = t.coord[0]; r.c1 = t.coord[1]; r.id = t.id;
+    r.in_n = t.in_n; r.out_n = t.out_n; r.in_off = t.in_off; r.out_off = t.out_off;
+    for (int k = 0; k < 4 && k < t.in_n; ++k) { r.in_word[k] = s->inwords[t.in_off + k]; r.in_cnt[k] = s->evcount[r.in_word[k]]; }
+    for (int k = 0; k < 4 && k < t.out_n; ++k) r.out_word[k] = s->outwords[t.out_off + k];
+    // tiles below the GEMV family take no argument block: point them at the pool so the 192-byte prefetch stays in bounds
+    const bool has_block = ty.body >= ETXB_BODY_GEMV && ty.args[0] >= 0;
+    r.args = has_block ? (uint64_t)(uintptr_t)ta[(size_t)t.type * ETXB_MAX_ARGS] + (uint64_t)ty.cst[0] + (uint64_t)t.coord[1] * (uint64_t)ty.cst[1]
+                       : (uint64_t)(uintptr_t)s->d_pool;
+    r.stream_word = ty.stream_word;
+  }
+  if (!s->d_recs) CU(cudaMalloc((void**)&s->d_recs, recs.size() * sizeof(etxb_rec) + 96));
+  CU(cudaMemcpy(s->d_recs, recs.data(), recs.size() * sizeof(etxb_rec), cudaMemcpyHostToDevice));
   s->args_dirty = false;
   return ETXB_OK;
 }
 
 static void fill_params(etxb_session* s, etxb_params& p) {
-  p.tasks = s->d_tasks; p.qbegin = s->d_qbegin; p.types = s->d_types; p.type_args = s->d_type_args;
+  p.tasks = s->d_tasks; p.recs = s->d_recs; p.qbegin = s->d_qbegin; p.types = s->d_types; p.type_args = s->d_type_args;
   p.events = s->d_events; p.evcount = s->d_evcount; p.inwords = s->d_inwords; p.outwords = s->d_outwords;
   p.ctrl = s->d_ctrl; p.trace = s->trace ? s->d_trace : nullptr; p.exec_count = s->trace ? s->d_exec : nullptr;
   p.step_dev = nullptr; p.timeout_ns = s->timeout_ns; p.epoch = s->epoch; p.n_workers = (int32_t)s->h.n_workers;
@@ -418,7 +437,7 @@ extern "C" int32_t etxb_decode_host(etxb_session* s, const int32_t* tokens_in, i
 
 // ---- single-tile launches ---------------------------------------------------------------------------------------
 struct OpCtx {
-  etxb_task* d_tasks = nullptr; int cap_tasks = 0; int32_t* d_qbegin = nullptr; etxb_type* d_type = nullptr; void** d_targs = nullptr;
+  etxb_task* d_tasks = nullptr; etxb_rec* d_recs = nullptr; int cap_tasks = 0; int32_t* d_qbegin = nullptr; etxb_type* d_type = nullptr; void** d_targs = nullptr;
   unsigned char* d_pool = nullptr; size_t cap_pool = 0; int32_t* d_ctrl = nullptr; int32_t* d_events = nullptr; int32_t* d_zero = nullptr;
   int workers = 0;
 };
@@ -462,9 +481,10 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
     CU(cudaMalloc((void**)&c.d_zero, 64)); CU(cudaMemset(c.d_zero, 0, 64));
   }
   if (ntasks > c.cap_tasks) {
-    if (c.d_tasks) { CU(cudaStreamSynchronize(st)); CU(cudaFree(c.d_tasks)); }
+    if (c.d_tasks) { CU(cudaStreamSynchronize(st)); CU(cudaFree(c.d_tasks)); CU(cudaFree(c.d_recs)); }
     c.cap_tasks = ntasks + 1024;
     CU(cudaMalloc((void**)&c.d_tasks, (size_t)c.cap_tasks * sizeof(etxb_task)));
+    CU(cudaMalloc((void**)&c.d_recs, (size_t)c.cap_tasks * sizeof(etxb_rec)));
   }
   const size_t need = bytes ? bytes : 16;
   if (need > c.cap_pool) {
@@ -474,6 +494,7 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   }
   const int W = c.workers;
   std::vector<etxb_task> tasks(ntasks);
+  std::vector<etxb_rec> recs(ntasks);
   std::vector<int32_t> qb(W + 1, 0);
   // worker w runs tasks w, w + W, ...: store grouped by worker
   int n = 0;
@@ -483,6 +504,9 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
       etxb_task& k = tasks[n++];
       memset(&k, 0, sizeof k);
       k.type = 0; k.coord[0] = t; k.id = t;
+      etxb_rec& r = recs[n - 1];
+      memset(&r, 0, sizeof r);
+      r.body = body; r.c0 = t; r.id = t; r.args = (uint64_t)(uintptr_t)c.d_pool; r.stream_word = -1;
     }
   }
   qb[W] = n;
@@ -491,12 +515,13 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   ty.stream_word = -1;                                             // everything the weight addresses depend on precedes the launch
   void* targs[ETXB_MAX_ARGS] = {c.d_pool, nullptr, nullptr, nullptr};
   CU(cudaMemcpyAsync(c.d_tasks, tasks.data(), tasks.size() * sizeof(etxb_task), cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c.d_recs, recs.data(), recs.size() * sizeof(etxb_rec), cudaMemcpyHostToDevice, st));
   CU(cudaMemcpyAsync(c.d_qbegin, qb.data(), qb.size() * 4, cudaMemcpyHostToDevice, st));
   CU(cudaMemcpyAsync(c.d_type, &ty, sizeof ty, cudaMemcpyHostToDevice, st));
   CU(cudaMemcpyAsync(c.d_targs, targs, sizeof targs, cudaMemcpyHostToDevice, st));
   if (bytes) CU(cudaMemcpyAsync(c.d_pool, argblock, bytes, cudaMemcpyHostToDevice, st));
   etxb_params p; memset(&p, 0, sizeof p);
-  p.tasks = c.d_tasks; p.qbegin = c.d_qbegin; p.types = c.d_type; p.type_args = c.d_targs; p.events = c.d_events;
+  p.tasks = c.d_tasks; p.recs = c.d_recs; p.qbegin = c.d_qbegin; p.types = c.d_type; p.type_args = c.d_targs; p.events = c.d_events;
   p.evcount = c.d_zero; p.inwords = c.d_zero; p.outwords = c.d_zero; p.ctrl = c.d_ctrl; p.timeout_ns = 2000000000ull; p.epoch = 1;
   p.n_workers = W;
   if (step) memcpy(&p.step, step, sizeof(p.step));

@@ -25,8 +25,9 @@
 #define ETXB_G_OFF 57344
 #define ETXB_G_FLOATS 2048
 #define ETXB_SCR_FLOATS 256
-#define ETXB_CTX_BYTES 384           // one prefetched task context: header + argument block copy
-#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512 + 2 * ETXB_CTX_BYTES)
+#define ETXB_CTX_BYTES 288           // one prefetched task context: 96-byte record + 192 bytes of argument block
+#define ETXB_CTX_SLOTS 4
+#define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512 + ETXB_CTX_SLOTS * ETXB_CTX_BYTES)
 #define ETXB_ATTN_PART 32            // KV positions per attention task
 #define ETXB_MAX_NB 8                // activation columns of the stand-alone batched GEMV kernel
 #define ETXB_NB_XS_FLOATS 40960      // its staged activations: nb * K floats
@@ -67,6 +68,15 @@ struct etxb_task {
   int32_t id;                   // index in program (graph) order, for traces and diagnostics
 };
 
+// Per-task record, in queue order, built by the host when the tensors are bound: everything the consumer loop needs of
+// a task in one 96-byte read (the task table -> type table -> argument pointer chain resolved ahead of time).
+struct etxb_rec {
+  int32_t body, c0, c1, id, in_n, out_n, in_off, out_off;
+  int32_t in_word[4], in_cnt[4], out_word[4];      // the first four of each list; longer lists continue in inwords / outwords
+  uint64_t args;                                   // device address of the task's argument block
+  int32_t stream_word, pad;
+};
+
 // ---- step parameters (the reference's VlParams, examples/vllm_llm/vl_tiles.hip:13-24) ---------------------------
 struct etxb_stepv {
   int32_t tok, pos, write_next, H, V, nrep;
@@ -79,6 +89,7 @@ struct etxb_params {
   const etxb_task* tasks;
   const int32_t* qbegin;
   const etxb_type* types;
+  const etxb_rec* recs;         // [n_tasks] in queue order
   void* const* type_args;       // [n_types][ETXB_MAX_ARGS] device pointers
   int32_t* events;              // counters, ETXB_EV_STRIDE words apart
   const int32_t* evcount;

@@ -87,40 +87,38 @@ __device__ __forceinline__ void tile_splitk_sum(const unsigned char* a, int i) {
   }
 }
 
-// A task's context, fetched into shared memory one task ahead (by the last consumer warp, at the start of the previous
-// body), so that the chain task table -> type table -> argument pointer -> argument block -> data loses four dependent
-// global round trips: the tiles read their argument block from shared memory and thread 0 finds its event words here.
+// A task's context in shared memory: its record and a copy of its argument block.  The last consumer warp fetches them
+// with asynchronous copies (cp.async) while earlier bodies run -- the record two tasks ahead, the argument block one
+// task ahead (its address is in the record) -- and only waits for them at the end of a body, so the chain task ->
+// arguments -> data costs the tiles no dependent global round trip and the fetch itself is off the critical path.
 struct TaskCtx {
-  int32_t body, c0, c1, id, in_n, out_n, in_off, out_off;
-  int32_t in_word[4], in_cnt[4], out_word[4];
-  int32_t pad[4];
+  etxb_rec r;
   unsigned char args[ETXB_CTX_BYTES - 96];
 };
-static_assert(sizeof(TaskCtx) == ETXB_CTX_BYTES, "context slot size");
+static_assert(sizeof(etxb_rec) == 96 && sizeof(TaskCtx) == ETXB_CTX_BYTES, "context slot layout");
 
-// one warp; all 32 lanes call
-__device__ __forceinline__ void load_ctx(const etxb_params& p, int cur, TaskCtx* c) {
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// one warp: lanes 0..5 fetch the record of task `rec_task`, lanes 8..19 the argument block of task `arg_task` (whose
+// record must already be in its slot); -1 skips either.  Asynchronous: cp_async_wait_all() completes them.
+__device__ __forceinline__ void fetch_ctx(const etxb_params& p, TaskCtx* ctx, int q0, int rec_task, int arg_task) {
   const int lane = tidx() & 31;
-  const etxb_task* t = p.tasks + cur;
-  const int type = t->type;
-  const etxb_type* ty = p.types + type;
-  const int body = ty->body;
-  const unsigned char* base = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
-  if (body >= 3 && lane < 24) *(uint64_t*)(c->args + 8 * lane) = __ldg((const uint64_t*)(base + 8 * lane));   // 192 bytes: every block is <= 160
-  if (lane == 0) {
-    c->body = body; c->c0 = t->coord[0]; c->c1 = t->coord[1]; c->id = t->id;
-    c->in_n = t->in_n; c->out_n = t->out_n; c->in_off = t->in_off; c->out_off = t->out_off;
+  if (rec_task >= 0 && lane < 6) cp_async16((unsigned char*)&ctx[(rec_task - q0) & (ETXB_CTX_SLOTS - 1)].r + 16 * lane,
+                                            (const unsigned char*)(p.recs + rec_task) + 16 * lane);
+  if (arg_task >= 0 && lane >= 8 && lane < 20) {
+    TaskCtx* c = ctx + ((arg_task - q0) & (ETXB_CTX_SLOTS - 1));
+    cp_async16(c->args + 16 * (lane - 8), (const unsigned char*)c->r.args + 16 * (lane - 8));
   }
-  if (lane < 4 && lane < t->in_n) { const int w = p.inwords[t->in_off + lane]; c->in_word[lane] = w; c->in_cnt[lane] = p.evcount[w]; }
-  if (lane >= 4 && lane < 8 && lane - 4 < t->out_n) c->out_word[lane - 4] = p.outwords[t->out_off + lane - 4];
-  __syncwarp();
 }
 
 // Run the body of the task whose context is `c` on the consumer warps.
 __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c, int cur, const Smem& sm, uint32_t& n) {
   const unsigned char* args = c->args;
-  const int c0 = c->c0, c1 = c->c1;
-  switch (c->body) {
+  const int c0 = c->r.c0, c1 = c->r.c1;
+  switch (c->r.body) {
     case 0: break;
     case 1: tile_prologue(p.step); break;
     case 2: tile_argmax(p.step, sm); break;
@@ -148,24 +146,21 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
   const int lane = tidx() & 31;
   bool ok = true;
   for (int cur = q0; cur < q1 && ok; ++cur) {
-    const etxb_task* t = p.tasks + cur;
-    const int type = t->type;
-    const etxb_type* ty = p.types + type;
-    const int body = ty->body;
+    const etxb_rec* t = p.recs + cur;
+    const int body = t->body;
     if (body < 3 || body > 5) continue;
     // the argument block through shared memory, fetched BEFORE the wait below (it depends on no event)
-    const unsigned char* args = (const unsigned char*)p.type_args[type * ETXB_MAX_ARGS] + ty->cst[0] + (size_t)t->coord[1] * ty->cst[1];
     etxb_gemv_args* pa = (etxb_gemv_args*)(sm.prod + 32);
-    if (lane < 20) ((uint64_t*)pa)[lane] = __ldg((const uint64_t*)args + lane);
+    if (lane < 20) ((uint64_t*)pa)[lane] = __ldg((const uint64_t*)t->args + lane);
     __syncwarp();
-    const int sw = ty->stream_word;
+    const int sw = t->stream_word;
     if (sw != -1) {
       int good = 1;
       if (lane == 0) {
         if (sw >= 0) good = wait_event(p, sw, (int32_t)(p.epoch * (uint32_t)p.evcount[sw]), cur, *sm.deadline) ? 1 : 0;
         else
           for (int i = 0; good && i < t->in_n; ++i) {
-            const int word = p.inwords[t->in_off + i];
+            const int word = i < 4 ? t->in_word[i] : p.inwords[t->in_off + i];
             good = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)p.evcount[word]), cur, *sm.deadline) ? 1 : 0;
           }
       }
@@ -174,7 +169,7 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
     } else if (ld_relaxed(p.ctrl) != 0) {
       break;
     }
-    const GemvTask gt = gemv_task(body, *pa, t->coord[0]);
+    const GemvTask gt = gemv_task(body, *pa, t->c0);
     if (gt.n > 0 && body != 3) gemv_routing(*pa, sm.prod, (float*)(sm.prod + 16));
     ok = produce_task(body, *pa, gt, sm.prod, n, sm, cur);
   }
@@ -217,36 +212,45 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     return;
   }
   TaskCtx* ctx = (TaskCtx*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512);
-  if (q0 < q1 && threadIdx.x >= ETXB_CONSUMERS - 32) load_ctx(p, q0, ctx);
+  const bool fetcher = threadIdx.x >= ETXB_CONSUMERS - 32;          // the last consumer warp keeps the contexts coming
+  if (fetcher && q0 < q1) {
+    fetch_ctx(p, ctx, q0, q0, -1);
+    fetch_ctx(p, ctx, q0, q0 + 1 < q1 ? q0 + 1 : -1, -1);
+    cp_async_wait_all();
+    __syncwarp();
+    fetch_ctx(p, ctx, q0, -1, q0);
+    cp_async_wait_all();
+  }
   csync();
   uint32_t n = 0;                                                  // stages consumed so far (same count the producer keeps)
   for (int cur = q0; cur < q1; ++cur) {
-    const TaskCtx* c = ctx + ((cur - q0) & 1);
+    const TaskCtx* c = ctx + ((cur - q0) & (ETXB_CTX_SLOTS - 1));
     if (threadIdx.x == 0) {
-      const int in_n = c->in_n;
-      if (p.trace) p.trace[8 * (size_t)c->id] = globaltimer();
+      const int in_n = c->r.in_n;
+      if (p.trace) p.trace[8 * (size_t)c->r.id] = globaltimer();
       bool ok = ld_relaxed(p.ctrl) == 0;
       for (int i = 0; ok && i < in_n; ++i) {
         int word, cnt;
-        if (i < 4) { word = c->in_word[i]; cnt = c->in_cnt[i]; }
-        else { word = p.inwords[c->in_off + i]; cnt = p.evcount[word]; }
+        if (i < 4) { word = c->r.in_word[i]; cnt = c->r.in_cnt[i]; }
+        else { word = p.inwords[c->r.in_off + i]; cnt = p.evcount[word]; }
         ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
       }
       if (!ok) s_stop = 1;
-      if (p.trace) p.trace[8 * (size_t)c->id + 1] = globaltimer();
+      if (p.trace) p.trace[8 * (size_t)c->r.id + 1] = globaltimer();
     }
     csync();
     if (s_stop) break;
-    if (threadIdx.x >= ETXB_CONSUMERS - 32 && cur + 1 < q1) load_ctx(p, cur + 1, ctx + ((cur + 1 - q0) & 1));   // next task's context
-    sm.tr = p.trace ? p.trace + 8 * (size_t)c->id : nullptr;
+    if (fetcher) fetch_ctx(p, ctx, q0, cur + 2 < q1 ? cur + 2 : -1, cur + 1 < q1 ? cur + 1 : -1);   // asynchronous
+    sm.tr = p.trace ? p.trace + 8 * (size_t)c->r.id : nullptr;
     run_body(p, c, cur, sm, n);
-    csync();                                                       // every consumer thread's stores are issued
+    if (fetcher) cp_async_wait_all();
+    csync();                                                       // every consumer thread's stores are issued, the next contexts landed
     if (threadIdx.x == 0) {
-      const int out_n = c->out_n, id = c->id;
+      const int out_n = c->r.out_n, id = c->r.id;
       if (ld_relaxed(p.ctrl) != 0) s_stop = 1;                     // a stage wait gave up inside the body: no arrivals
       else
         for (int i = 0; i < out_n; ++i) {                          // release: orders the CTA's stores (seen through the barrier) before the count
-          const int word = i < 4 ? c->out_word[i] : p.outwords[c->out_off + i];
+          const int word = i < 4 ? c->r.out_word[i] : p.outwords[c->r.out_off + i];
           red_release_add(p.events + (size_t)word * ETXB_EV_STRIDE, 1);
         }
       if (p.trace) { p.trace[8 * (size_t)id + 2] = globaltimer(); p.trace[8 * (size_t)id + 3] = blockIdx.x; }
