@@ -32,6 +32,7 @@ struct Smem {
   int32_t* prod;             // producer-warp scratch: 16 ids + 16 weights
   const unsigned long long* deadline;
   int32_t* ctrl;
+  int* stop;                 // CTA-local: a wait inside a body gave up (the body's results are not to be announced)
   uint64_t* tr;              // 8 stamps of the running task when tracing, else null (slots 4..7 are in-body marks)
 };
 // in-body time stamp k (0..3) of the running task; thread 0 only, no-op unless tracing
@@ -45,9 +46,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   uint32_t n = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++n & 255u) == 0) {
-      if (ld_relaxed(sm.ctrl) != 0) return false;
+      if (ld_relaxed(sm.ctrl) != 0) { *(volatile int*)sm.stop = 1; return false; }
       if ((n & 4095u) == 0 && globaltimer() > *sm.deadline) {
         if (atomicOr(sm.ctrl, ETXB_CTRL_TIMEOUT) == 0) { sm.ctrl[1] = where; sm.ctrl[2] = -1; sm.ctrl[3] = (int32_t)parity; sm.ctrl[4] = -1; }
+        *(volatile int*)sm.stop = 1;
         return false;
       }
     }
@@ -67,13 +69,14 @@ struct GemvTask {
 // softmax over E bf16 logits (fp32), K rounds of argmax with the lower index winning ties, optional renormalisation
 // over the selected weights (numpy's summation order for <= 16 values), optional bf16 rounding of the weights.
 // One warp (all 32 lanes call); E <= 256, K <= 16.  ids / wts / tei may point to shared or global memory.
-__device__ __noinline__ void warp_topk(const void* logits, int E, int K, bool renorm, bool bf16w,
-                                       int32_t* ids, float* wts, int32_t* tei) {
+template <int NK>
+__device__ __forceinline__ void warp_topk_n(const void* logits, int E, int K, bool renorm, bool bf16w,
+                                            int32_t* ids, float* wts, int32_t* tei) {
   const int lane = tidx() & 31;
-  float p[8];
+  float p[NK];
   float m = -INFINITY;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
+  for (int k = 0; k < NK; ++k) {
     const int e = lane + 32 * k;
     p[k] = e < E ? ld_bf(logits, e) : -INFINITY;
     m = fmaxf(m, p[k]);
@@ -81,26 +84,39 @@ __device__ __noinline__ void warp_topk(const void* logits, int E, int K, bool re
   m = warp_max(m);
   float s = 0.f;
 #pragma unroll
-  for (int k = 0; k < 8; ++k) { p[k] = (lane + 32 * k < E) ? expf(__fsub_rn(p[k], m)) : 0.f; s = __fadd_rn(s, p[k]); }
+  for (int k = 0; k < NK; ++k) { p[k] = (lane + 32 * k < E) ? expf(__fsub_rn(p[k], m)) : 0.f; s = __fadd_rn(s, p[k]); }
   s = warp_sum(s);
   // Selection keys: a probability is a non-negative float, so its bit pattern orders like the value; + 1 keeps a valid
-  // zero probability above "no candidate" (0).  Each round is two warp reductions (redux.sync): the maximum key, then
-  // the lowest expert index holding it (the lower index wins ties).  NaN logits are not supported.
-  uint32_t key[8];
+  // zero probability above "no candidate" (0).  A candidate is the 64-bit pair (key, ~expert): the larger pair is the
+  // larger probability or, on a tie, the lower expert.  Each lane sorts its NK candidates once (descending), so a
+  // round only looks at the lane's head: two warp reductions (redux.sync) find the winner, whose lane pops its head.
+  // NaN logits are not supported.
+  unsigned long long c[NK];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) { p[k] = __fdiv_rn(p[k], s); key[k] = (lane + 32 * k < E) ? __float_as_uint(p[k]) + 1u : 0u; }
+  for (int k = 0; k < NK; ++k) {
+    const int e = lane + 32 * k;
+    const uint32_t key = e < E ? __float_as_uint(__fdiv_rn(p[k], s)) + 1u : 0u;
+    c[k] = ((unsigned long long)key << 32) | (uint32_t)(0xffffffffu - (uint32_t)e);
+  }
+#pragma unroll
+  for (int i = 1; i < NK; ++i)                                      // insertion network: c[0] >= c[1] >= ...
+#pragma unroll
+    for (int j = i; j > 0; --j) {
+      const unsigned long long hi = c[j - 1] > c[j] ? c[j - 1] : c[j], lo = c[j - 1] > c[j] ? c[j] : c[j - 1];
+      c[j - 1] = hi; c[j] = lo;
+    }
   float myw = 0.f; int myid = 0x7fffffff;
   for (int t = 0; t < K; ++t) {
-    uint32_t bk = 0; int bi = 0x7fffffff;
+    const uint32_t hk = (uint32_t)(c[0] >> 32), hi_ = (uint32_t)c[0];
+    const uint32_t top = __reduce_max_sync(0xffffffffu, hk);
+    const uint32_t wl = __reduce_max_sync(0xffffffffu, hk == top ? hi_ : 0u);
+    const bool any = top != 0u;
+    if (any && hk == top && hi_ == wl) {                            // the winner's lane pops its head
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (key[k] > bk) { bk = key[k]; bi = lane + 32 * k; }
-    const uint32_t top = __reduce_max_sync(0xffffffffu, bk);
-    const int win = (int)__reduce_min_sync(0xffffffffu, (uint32_t)(bk == top && top != 0u ? bi : 0x7fffffff));
-#pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (lane + 32 * k == win) key[k] = 0u;
-    if (lane == t) { myw = top != 0u ? __uint_as_float(top - 1u) : -1.f; myid = win; }
+      for (int k = 0; k + 1 < NK; ++k) c[k] = c[k + 1];
+      c[NK - 1] = 0ull;
+    }
+    if (lane == t) { myw = any ? __uint_as_float(top - 1u) : -1.f; myid = any ? (int)(0xffffffffu - wl) : 0x7fffffff; }
   }
   if (renorm) {
     // numpy's order for the sum of the K selected weights: K < 8 left to right, else 8 accumulators + tree + tail
@@ -122,6 +138,12 @@ __device__ __noinline__ void warp_topk(const void* logits, int E, int K, bool re
   if (bf16w) myw = bfr(myw);
   if (lane < K) { ids[lane] = myid; wts[lane] = myw; if (tei) tei[lane] = lane; }
   __syncwarp();
+}
+
+__device__ __noinline__ void warp_topk(const void* logits, int E, int K, bool renorm, bool bf16w,
+                                       int32_t* ids, float* wts, int32_t* tei) {
+  if (E <= 128) warp_topk_n<4>(logits, E, K, renorm, bf16w, ids, wts, tei);
+  else warp_topk_n<8>(logits, E, K, renorm, bf16w, ids, wts, tei);
 }
 
 __device__ __forceinline__ void tile_topk(const unsigned char* a, int blk, const Smem& sm) {

@@ -197,6 +197,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   sm.prod = (int32_t*)(sm.empty + ETXB_NSTAGE);
   sm.deadline = &s_deadline;
   sm.ctrl = p.ctrl;
+  sm.stop = &s_stop;
   sm.tr = nullptr;
   if (threadIdx.x == 0) {
     s_stop = 0;
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     if (threadIdx.x == 0) {
       const int in_n = c->r.in_n;
       if (p.trace) p.trace[8 * (size_t)c->r.id] = globaltimer();
-      bool ok = ld_relaxed(p.ctrl) == 0;
+      bool ok = true;                                              // wait_event polls the abort word itself
       for (int i = 0; ok && i < in_n; ++i) {
         int word, cnt;
         if (i < 4) { word = c->r.in_word[i]; cnt = c->r.in_cnt[i]; }
@@ -247,8 +248,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     csync();                                                       // every consumer thread's stores are issued, the next contexts landed
     if (threadIdx.x == 0) {
       const int out_n = c->r.out_n, id = c->r.id;
-      if (ld_relaxed(p.ctrl) != 0) s_stop = 1;                     // a stage wait gave up inside the body: no arrivals
-      else
+      if (s_stop == 0)                                             // (set when a stage wait gave up inside the body: no arrivals then)
         for (int i = 0; i < out_n; ++i) {                          // release: orders the CTA's stores (seen through the barrier) before the count
           const int word = i < 4 ? c->r.out_word[i] : p.outwords[c->r.out_off + i];
           red_release_add(p.events + (size_t)word * ETXB_EV_STRIDE, 1);
