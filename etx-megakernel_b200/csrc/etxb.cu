@@ -580,6 +580,7 @@ extern "C" int32_t etxb_attn_fused_static(int device, const void* argblock, size
   }
   if (G + 2 > ETXB_CONSUMER_WARPS || G * d.HD > 2048 || d.HD % 32 || d.X != 8 || (d.BS != 16 && d.BS != 32) || G * d.max_parts > 8192)
     return fail(ETXB_E_UNSUPPORTED, "attn_fused_static: shape outside the fused attention tile (G + 2 <= 16, G * HD <= 2048, HD % 32 == 0, X = 8, BS 16 or 32)");
+  if (d.gq != 0) return fail(ETXB_E_UNSUPPORTED, "attn_fused_static: the general form only (gq = 0)");
   if (d.nblocks != (uint32_t)(d.max_parts * d.NKV)) return fail(ETXB_E_ARG, "attn_fused_static: the grid must be max_parts * NKV tasks");
   CU(cudaSetDevice(device));
   const int smem = ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4;

@@ -163,7 +163,7 @@ struct etxb_attnf_args {
   const int32_t* block_tables; const int32_t* seq_lens; const int64_t* positions; const int64_t* slot_mapping;  // 48..79
   float* exp_sums; float* max_logits; float* tmp_out; void* out; int32_t* counters;                             // 80..119
   float scale, eps; int32_t NH, NKV, HD, BS, X, max_parts;                                                      // 120..151
-  int32_t pad[2];                                                                                               // 152..159
+  int32_t gq, part_len;   // 152..159: gq > 0 selects the grouped form (gq q heads x part_len = 128 positions per task, task = part * (NH / gq) + group; counters: one per group)
   uint32_t grid[3], nblocks;                                                                                    // 160..175
 };
 

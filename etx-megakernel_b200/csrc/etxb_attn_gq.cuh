@@ -1,0 +1,298 @@
+// The attention phase of a decode step, the form tuned for head_dim 128 and 16-position cache blocks: one task per
+// (128-position partition, group of GQ q heads that share a kv head).  Same work as the general fused tile
+// (etxb_attn_fused.cuh: q/k RMSNorm + neox rotary, the new position's k / v rows into the paged cache, split-KV
+// attention, merge by the last task to finish) with two differences that shorten its critical path:
+//   * the partition's K and V go from the cache straight into registers (each thread keeps the 64 + 64 bytes it will
+//     multiply), no shared-memory staging;
+//   * a task covers few q heads and many positions, so the merge that the last task runs reads GQ * parts partial
+//     rows (2 * 9 at a 1K context) instead of G * parts of 32 positions (8 * 34): one round of loads.
+// The groups of one kv head read the same K / V (through L2); the first group of the kv head writes the cache slot.
+// The new position never comes from the cache: its k / v rows are taken from shared memory as one extra position.
+//
+// It stands where the reference runs dsl_attnprep (etx/ops/attnprep.py:86-211), vLLM's paged attention and its reduce
+// kernel (etx/importer/spec.py:243-244; grids examples/vllm_llm/model.py:78-84, 358-362); numerics follow
+// examples/llm/ref_numpy.py:113-129 (fp32 scores and sums over bf16 q, k, v; bf16 output).
+#pragma once
+#include "etxb_attn_fused.cuh"
+
+namespace etxb {
+
+#define ETXB_GQ_PART 128   // positions per task
+
+template <int GQ>
+struct GqSmem {
+  static constexpr int HD = 128, PL = ETXB_GQ_PART;
+  float* raw;   // [GQ + 2][HD] raw q rows, new k row, new v row
+  float* cw;    // [3][HD] cos | sin row, q norm weight, k norm weight
+  float* qs;    // [GQ][HD] normed + roped q
+  float* knew;  // [HD] normed + roped new k (bf16 values)
+  float* vnew;  // [HD] new v (bf16 values)
+  float* ph;    // [4][GQ][PL] quarter dot products
+  float* sc;    // [GQ][PL] probabilities
+  float* st;    // [GQ] max, [GQ] sum, [GQ] probability of the new position
+  float* po;    // [4][GQ][HD] partial outputs
+  __device__ explicit GqSmem(float* b) {
+    raw = b; cw = raw + (GQ + 2) * HD; qs = cw + 3 * HD; knew = qs + GQ * HD; vnew = knew + HD;
+    ph = vnew + HD; sc = ph + 4 * GQ * PL; st = sc + GQ * PL; po = st + 32;
+  }
+};
+static_assert(((8 + 2) + 3 + 8 + 2 + 32 + 8 + 32) * 128 * 4 + 128 <= ETXB_GEN_BYTES, "GQ = 8 layout fits the general region");
+
+// out[hq][:] = bf16(sum_p w_p * tmp[p][:] / sum_p w_p * l_p), w_p = exp(m_p - max m), for q heads hq0 .. hq0 + GQ - 1.
+// Run by the last task of the q group; reads the partials the other CTAs wrote (L2).  GQ * np <= 4096.
+template <int GQ>
+__device__ __forceinline__ void attn_gq_merge(const etxb_attnf_args& d, const Smem& sm, int hq0, int np) {
+  constexpr int HD = 128;
+  const int lane = tidx() & 31, warp = tidx() >> 5;
+  float* wl = sm.xs;                                              // [GQ][np] max logits, then weights
+  float* es = sm.xs + 4096;                                       // [GQ][np] exp sums
+  float* red = sm.scr + 200;                                      // [GQ] denominators
+  for (int i = tidx(); i < GQ * np; i += ETXB_CONSUMERS) {
+    const int g = i / np, pp = i - g * np;
+    wl[i] = __ldcg(d.max_logits + (size_t)(hq0 + g) * d.max_parts + pp);
+    es[i] = __ldcg(d.exp_sums + (size_t)(hq0 + g) * d.max_parts + pp);
+  }
+  csync();
+  mark(sm, 0);
+  if (warp < GQ) {
+    const int g = warp;
+    float m = -INFINITY;
+    for (int pp = lane; pp < np; pp += 32) m = fmaxf(m, wl[g * np + pp]);
+    m = warp_max(m);
+    float L = 0.f;
+    for (int pp = lane; pp < np; pp += 32) {
+      const float w = expf(__fsub_rn(wl[g * np + pp], m));
+      wl[g * np + pp] = w;
+      L = __fmaf_rn(w, es[g * np + pp], L);
+    }
+    L = warp_sum(L);
+    if (lane == 0) red[g] = L;
+  }
+  csync();
+  mark(sm, 1);
+  for (int idx = tidx(); idx < GQ * HD; idx += ETXB_CONSUMERS) {    // one output value per thread, partitions in ascending order
+    const int g = idx >> 7, dd = idx & (HD - 1);
+    const float* tp = d.tmp_out + (size_t)(hq0 + g) * d.max_parts * HD + dd;
+    const float* wg = wl + g * np;
+    float o = 0.f;
+    for (int p0 = 0; p0 < np; p0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(tp + (size_t)min(p0 + u, np - 1) * HD);   // clamped: a padded load gets weight 0
+#pragma unroll
+      for (int u = 0; u < 8; ++u) o = __fmaf_rn(p0 + u < np ? wg[p0 + u] : 0.f, v[u], o);
+    }
+    ((__nv_bfloat16*)d.out)[(size_t)(hq0 + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
+  }
+  mark(sm, 2);
+}
+
+template <int GQ>
+__device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, const Smem& sm, const etxb_stepv& S) {
+  constexpr int HD = 128, BS = 16, X = 8, PL = ETXB_GQ_PART, HV = HD / 8;
+  const int NKV = d.NKV, G = d.NH / NKV, NQG = d.NH / GQ;
+  const int part = blk / NQG, qg = blk - part * NQG;
+  const int hq0 = qg * GQ, h = hq0 / G;                           // first q head of the group, its kv head
+  const bool writer = hq0 - h * G == 0;                           // the kv head's first group stores the new k / v rows
+  // the step's own buffers hold what the prologue wrote from the step parameters: take the values from there
+  const long long pos = (const void*)d.positions == (const void*)S.positions ? (long long)S.pos : __ldcg((const long long*)d.positions);
+  const long long slot = (const void*)d.slot_mapping == (const void*)S.slot_mapping ? (long long)S.pos : __ldcg((const long long*)d.slot_mapping);
+  const int seq = (const void*)d.seq_lens == (const void*)S.seq_lens ? S.pos + 1 : __ldcg(d.seq_lens);
+  const int t0 = part * PL;
+  const int tid = tidx(), lane = tid & 31, warp = tid >> 5;
+  int* flag = (int*)(sm.scr + 130);
+  if (t0 < seq) {
+    const GqSmem<GQ> s(sm.xs);
+    const bool owner = pos >= t0 && pos < t0 + PL;                // this partition holds the position being written
+    const int tpos = owner ? (int)(pos - t0) : -1;
+    const int ntok = min(PL, seq - t0);
+    // positions taken from the cache: all of the partition's but the new one (its slot is stale until this step's write)
+    auto cached = [&](int tt) { return tt < ntok && tt != tpos; };
+    const int t = tid & (PL - 1), qr = tid >> 7;                  // K: position t, dims [32 qr, 32 qr + 32);  V: dim t, blocks 2 qr, 2 qr + 1
+    // ---- K and V of the partition: cache -> registers (nothing here depends on this step's q)
+    uint4 kreg[4], vreg[4];
+    {
+      const int lb = t0 / BS + (t >> 4);
+      const bool live = lb * BS < seq;
+      const long long pb = live ? __ldg(d.block_tables + lb) : 0;
+      const __nv_bfloat16* kp = (const __nv_bfloat16*)d.kc + ((((size_t)pb * NKV + h) * HV + qr * 4) * BS + (t & 15)) * X;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kreg[j] = live ? ld_act16(kp + (size_t)j * BS * X) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int lv = t0 / BS + 2 * qr + u;
+        const bool lv_live = lv * BS < seq;
+        const long long pv = lv_live ? __ldg(d.block_tables + lv) : 0;
+        const __nv_bfloat16* vp = (const __nv_bfloat16*)d.vc + (((size_t)pv * NKV + h) * HD + t) * BS;
+        vreg[2 * u] = lv_live ? ld_act16(vp) : make_uint4(0u, 0u, 0u, 0u);
+        vreg[2 * u + 1] = lv_live ? ld_act16(vp + 8) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    // ---- this step's rows: raw q heads, (owner) new k and v rows; rotary row and norm weights
+    {
+      const __nv_bfloat16* qkv = (const __nv_bfloat16*)d.qkv;
+      const int nq = GQ * HV, nrow = nq + (owner ? 2 * HV : 0);
+      for (int i = tid; i < nrow + 3 * HV; i += ETXB_CONSUMERS) {
+        if (i < nrow) {
+          const __nv_bfloat16* src = i < nq ? qkv + (size_t)hq0 * HD + 8 * i
+                                            : (i < nq + HV ? qkv + (size_t)(d.NH + h) * HD + 8 * (i - nq)
+                                                           : qkv + (size_t)(d.NH + NKV + h) * HD + 8 * (i - nq - HV));
+          unpack8(ld_act16(src), s.raw + (i < nq ? 8 * i : GQ * HD + 8 * (i - nq)));
+        } else {
+          const int c = i - nrow, which = c / HV, v = c - which * HV;
+          const __nv_bfloat16* src = which == 0 ? (const __nv_bfloat16*)d.cos_sin + (size_t)pos * HD
+                                                : (const __nv_bfloat16*)(which == 1 ? d.qw : d.kw);
+          if (src != nullptr) unpack8(__ldg((const uint4*)src + v), s.cw + which * HD + 8 * v);
+        }
+      }
+    }
+    csync();
+    mark(sm, 0);
+    // ---- norm + rope of the q heads (warps 0..GQ-1), of the new k row (warp GQ); the new v row (warp GQ + 1)
+    if (warp < GQ) {
+      float o[8];
+      head_norm_rope_s(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s.qs[warp * HD + lane * 4 + j] = o[j];
+    } else if (warp == GQ && owner) {
+      float o[8];
+      head_norm_rope_s(s.raw + GQ * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
+      const long long cb = slot / BS; const int off = (int)(slot % BS);
+      __nv_bfloat16* kc = (__nv_bfloat16*)d.kc;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int dd = lane * 4 + j;
+        s.knew[dd] = o[j];
+        if (writer) kc[((((size_t)cb * NKV + h) * HV + dd / X) * BS + off) * X + dd % X] = __float2bfloat16_rn(o[j]);
+      }
+    } else if (warp == GQ + 1 && owner) {
+      const long long cb = slot / BS; const int off = (int)(slot % BS);
+      __nv_bfloat16* vc = (__nv_bfloat16*)d.vc;
+      for (int dd = lane; dd < HD; dd += 32) {
+        const float v = s.raw[(GQ + 1) * HD + dd];
+        s.vnew[dd] = v;
+        if (writer) vc[(((size_t)cb * NKV + h) * HD + dd) * BS + off] = __float2bfloat16_rn(v);
+      }
+    }
+    csync();
+    mark(sm, 1);
+    // ---- scores: thread (qr, t) holds 32 dims of position t; quarter sums to shared memory
+    {
+      float acc[GQ];
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) acc[g] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float kf[8];
+        unpack8(kreg[j], kf);
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float4 qa = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8), qb = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8 + 4);
+          acc[g] = __fmaf_rn(kf[0], qa.x, acc[g]); acc[g] = __fmaf_rn(kf[1], qa.y, acc[g]);
+          acc[g] = __fmaf_rn(kf[2], qa.z, acc[g]); acc[g] = __fmaf_rn(kf[3], qa.w, acc[g]);
+          acc[g] = __fmaf_rn(kf[4], qb.x, acc[g]); acc[g] = __fmaf_rn(kf[5], qb.y, acc[g]);
+          acc[g] = __fmaf_rn(kf[6], qb.z, acc[g]); acc[g] = __fmaf_rn(kf[7], qb.w, acc[g]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) s.ph[(qr * GQ + g) * PL + t] = acc[g];
+    }
+    csync();
+    // ---- softmax statistics: one warp per q head, lane holds positions lane + 32 k
+    if (warp < GQ) {
+      const int g = warp;
+      float sv[4], m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int tt = lane + 32 * k;
+        const float dot = __fadd_rn(__fadd_rn(__fadd_rn(s.ph[g * PL + tt], s.ph[(GQ + g) * PL + tt]), s.ph[(2 * GQ + g) * PL + tt]), s.ph[(3 * GQ + g) * PL + tt]);
+        sv[k] = cached(tt) ? __fmul_rn(dot, d.scale) : -INFINITY;
+        m = fmaxf(m, sv[k]);
+      }
+      float snew = -INFINITY;
+      if (owner) {                                                 // the new position: q . k_new from shared memory
+        float a = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a = __fmaf_rn(s.qs[g * HD + lane * 4 + j], s.knew[lane * 4 + j], a);
+        snew = __fmul_rn(warp_sum(a), d.scale);
+      }
+      m = fmaxf(warp_max(m), snew);
+      float l = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float pr = cached(lane + 32 * k) ? expf(__fsub_rn(sv[k], m)) : 0.f;
+        s.sc[g * PL + lane + 32 * k] = pr;
+        l = __fadd_rn(l, pr);
+      }
+      l = warp_sum(l);
+      const float pn = owner ? expf(__fsub_rn(snew, m)) : 0.f;
+      if (lane == 0) { s.st[g] = m; s.st[GQ + g] = __fadd_rn(l, pn); s.st[2 * GQ + g] = pn; }
+    }
+    csync();
+    mark(sm, 2);
+    // ---- output: thread (qr, dd = t) multiplies its two blocks of 16 positions; quarter sums to shared memory
+    {
+      float acc[GQ];
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) acc[g] = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int tb = (2 * qr + u) * BS;
+        if (tb < ntok) {
+          float f[16];
+          unpack8(vreg[2 * u], f); unpack8(vreg[2 * u + 1], f + 8);
+#pragma unroll
+          for (int o = 0; o < 16; ++o) f[o] = cached(tb + o) ? f[o] : 0.f;   // stale slots may hold anything: never multiply them
+#pragma unroll
+          for (int g = 0; g < GQ; ++g) {
+#pragma unroll
+            for (int o4 = 0; o4 < 4; ++o4) {
+              const float4 pr = *(const float4*)(s.sc + g * PL + tb + 4 * o4);
+              acc[g] = __fmaf_rn(pr.x, f[4 * o4], acc[g]); acc[g] = __fmaf_rn(pr.y, f[4 * o4 + 1], acc[g]);
+              acc[g] = __fmaf_rn(pr.z, f[4 * o4 + 2], acc[g]); acc[g] = __fmaf_rn(pr.w, f[4 * o4 + 3], acc[g]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) s.po[(qr * GQ + g) * HD + t] = acc[g];
+    }
+    csync();
+    for (int idx = tid; idx < GQ * HD; idx += ETXB_CONSUMERS) {
+      const int g = idx >> 7, dd = idx & (HD - 1);
+      float o = __fadd_rn(__fadd_rn(__fadd_rn(s.po[g * HD + dd], s.po[(GQ + g) * HD + dd]), s.po[(2 * GQ + g) * HD + dd]), s.po[(3 * GQ + g) * HD + dd]);
+      if (owner) o = __fmaf_rn(s.st[2 * GQ + g], s.vnew[dd], o);
+      d.tmp_out[((size_t)(hq0 + g) * d.max_parts + part) * HD + dd] = o;
+      if (dd == 0) {
+        d.max_logits[(size_t)(hq0 + g) * d.max_parts + part] = s.st[g];
+        d.exp_sums[(size_t)(hq0 + g) * d.max_parts + part] = s.st[GQ + g];
+      }
+    }
+  }
+  csync();                                                         // the partials of this task are issued
+  if (tid == 0) {
+    __threadfence();
+    const int old = atomicAdd(d.counters + qg, 1);                 // monotonic: max_parts arrivals per step and q group
+    *flag = ((old + 1) % d.max_parts) == 0;
+    if (*flag) __threadfence();
+  }
+  csync();
+  mark(sm, 3);
+  if (*flag) attn_gq_merge<GQ>(d, sm, hq0, (seq + PL - 1) / PL);
+}
+
+// Fused attention, either form: gq > 0 in the argument block selects the grouped form above (head_dim 128, cache
+// blocks of 16, partitions of 128 positions), else the general tile.
+__device__ __forceinline__ void tile_attn_any(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
+  const etxb_attnf_args& d = *(const etxb_attnf_args*)a;
+  if (d.gq == 0) { tile_attn_fused(a, blk, sm, S); return; }
+  if (blk >= (int)d.nblocks) return;
+  switch (d.gq) {
+    case 1: attn_gq_impl<1>(d, blk, sm, S); break;
+    case 2: attn_gq_impl<2>(d, blk, sm, S); break;
+    case 4: attn_gq_impl<4>(d, blk, sm, S); break;
+    default: attn_gq_impl<8>(d, blk, sm, S); break;
+  }
+}
+
+}  // namespace etxb

@@ -5,7 +5,7 @@
 // etx_run_task kernel.py:341-468, and the native prologue / argmax tiles examples/vllm_llm/vl_tiles.hip:31-89.
 #pragma once
 #include "etxb_attn.cuh"
-#include "etxb_attn_fused.cuh"
+#include "etxb_attn_gq.cuh"
 #include "etxb_gemv.cuh"
 #include "etxb_prims.cuh"
 
@@ -131,7 +131,7 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
     case 9: tile_attn_reduce(args, c0, sm, p.step); break;
     case 10: tile_splitk_part(args, c0, c1, sm); break;
     case 11: tile_splitk_sum(args, c0); break;
-    case 12: tile_attn_fused(args, c0, sm, p.step); break;
+    case 12: tile_attn_any(args, c0, sm, p.step); break;
     default:
       if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);
       break;

@@ -159,8 +159,9 @@ def validate_values(export, values, grid):
         if gx * gy * gz != values[9]:
             raise ValueError(f"{spec.name}: grid must be one task per kv head")
     elif name == "attn_fused":
-        _attn.check_fused(values[17], values[18], values[19], values[20], values[21], values[22])
-        if gx * gy * gz != values[22] * values[18]:
-            raise ValueError(f"{spec.name}: grid must be max_parts * NKV tasks (the merge counts them)")
+        _attn.check_fused(*values[17:25])
+        want = values[22] * (values[17] // values[23] if values[23] else values[18])
+        if gx * gy * gz != want:
+            raise ValueError(f"{spec.name}: grid must be max_parts * NKV tasks (grouped form: max_parts * NH / gq); the merge counts them")
     elif name in ("attn_decode", "attn_reduce"):
         _attn.check_shape(values[10], values[11], values[12], values[13], values[14], values[15])

@@ -142,6 +142,17 @@ class MachineModel:
         task's K and V (2 x 8 KB at head_dim 128) a single round trip."""
         return 32
 
+    def attention_groups(self, NH: int, NKV: int, HD: int, BS: int, maxlen: int) -> tuple:
+        """(q heads per task, positions per task, partitions) of the grouped attention tile, or (0, 0, 0) when the
+        shape needs the general tile.  The fewest q heads per task that still gives every task its own SM: the merge
+        a group's last task runs reads gq * partitions partial rows, and the groups of a kv head share its K / V in L2."""
+        G = NH // NKV
+        if HD != 128 or BS != 16 or G not in (1, 2, 4, 8):
+            return (0, 0, 0)
+        parts = -(-maxlen // 128)
+        fits = [gq for gq in (1, 2, 4, 8) if G % gq == 0 and (NH // gq) * parts <= self.workers()]
+        return (fits[0] if fits else G, 128, parts)
+
 
 def _visibility(raw: dict) -> dict:
     return {Scope[k.upper()]: Visibility(release=list(v.get("release", [])), acquire=list(v.get("acquire", [])), poll=v["poll"],

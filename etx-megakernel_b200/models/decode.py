@@ -44,7 +44,7 @@ def to_device_weights(packed: dict, device) -> dict:
 
 class DecodeProgram:
     def __init__(self, dims: Q.Dims, weights: dict, device: int = 0, maxlen: int = 1072, steps: int | None = None, machine="b200",
-                 fold_topk: bool = True, fused_attn: bool = True, workers: int | None = None):
+                 fold_topk: bool = True, fused_attn: bool | str = True, workers: int | None = None):
         self.d, self.maxlen = dims, maxlen
         self.dev = torch.device("cuda", device)
         self.machine = load_machine(machine) if isinstance(machine, str) else machine

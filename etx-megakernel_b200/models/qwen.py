@@ -134,6 +134,7 @@ class Sizing:
     down: tuple         # (tasks, rows per task): every task covers all slots and sums them
     lm: tuple
     parts: int          # attention partitions (of 32 positions) covering maxlen
+    attn: tuple = (0, 0, 0)   # grouped attention tile: (q heads per task, positions per task, partitions); (0, 0, 0): general tile
 
 
 def size_for(d: Dims, m: MachineModel, maxlen: int) -> Sizing:
@@ -160,7 +161,8 @@ def size_for(d: Dims, m: MachineModel, maxlen: int) -> Sizing:
         return best[1:]
     dt, drpt = m.gemv_tasks(d.H)
     return Sizing(workers=W, qkv=m.gemv_tasks(d.NQKV), o=m.gemv_tasks(d.H), router=m.gemv_tasks(d.E) if d.moe else (0, 0),
-                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.V, waves=4), parts=-(-maxlen // m.attention_part()))
+                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.V, waves=4), parts=-(-maxlen // m.attention_part()),
+                  attn=m.attention_groups(d.NH, d.NKV, d.HD, BS, maxlen))
 
 
 # ------------------------------------------------------------------------------------------------ buffers
@@ -174,7 +176,7 @@ def buffer_shapes(d: Dims, maxlen: int, steps: int, parts: int) -> dict:
          "token_time": ((2 * (steps + 1),), "i64"),
          "exp_sums": ((d.NH, parts), "f32"), "max_logits": ((d.NH, parts), "f32"), "tmp_out": ((d.NH, parts, d.HD), "f32"),
          "kc": ((d.L, nblk, d.NKV, d.HD // X, BS, X), "bf16"), "vc": ((d.L, nblk, d.NKV, d.HD, BS), "bf16"),
-         "attn_counters": ((d.L, d.NKV), "i32"), "moe_out": ((d.H,), "bf16")}
+         "attn_counters": ((d.L, d.NH), "i32"), "moe_out": ((d.H,), "bf16")}
     if d.moe:
         s.update({"rlog": ((d.E,), "bf16"), "tw": ((d.TOPK,), "f32"), "ti": ((d.TOPK,), "i32"), "tei": ((d.TOPK,), "i32"),
                   "mc2": ((d.TOPK, d.MI), "bf16"), "mc3": ((d.TOPK, d.H), "bf16")})
@@ -283,7 +285,8 @@ class ArgPool:
         return bytes(self.buf + b"\0" * (-len(self.buf) % 16))
 
 
-def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = "b200", *, fold_topk: bool = True, fused_attn: bool = True):
+def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = "b200", *, fold_topk: bool = True,
+                fused_attn: bool | str = True):
     """The decode step of `d` as a Graph plus its argument pool.
 
     ptr(name) -> device address (int) of a buffer (buffer_shapes) or packed weight (weight_shapes); "kc" / "vc" are the
@@ -337,16 +340,19 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0), nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
         if fused_attn:
-            # ---- the attention phase as one grid: prep + 32-position partitions + merge by the last task of each kv head
-            blob = argblock.pack_named(ent["attn_fused"], (sz.parts * d.NKV, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,
+            # ---- the attention phase as one grid: prep + split-KV partitions + merge by the last task to finish
+            gq, plen, gparts = (0, 0, 0) if fused_attn == "general" else sz.attn
+            nparts, ntask = (gparts, gparts * (d.NH // gq)) if gq else (sz.parts, sz.parts * d.NKV)
+            op_attn.check_fused(d.NH, d.NKV, d.HD, BS, X, nparts, gq, plen)
+            blob = argblock.pack_named(ent["attn_fused"], (ntask, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,
                                        kw=W("kn") if d.qk_norm else 0, cos_sin=ptr("cos_sin"), kc=ptr("kc") + L * kv_layer_bytes,
                                        vc=ptr("vc") + L * kv_layer_bytes, block_tables=ptr("block_tables"), seq_lens=ptr("seq_lens"),
                                        positions=ptr("positions"), slot_mapping=ptr("slot_mapping"), exp_sums=ptr("exp_sums"),
                                        max_logits=ptr("max_logits"), tmp_out=ptr("tmp_out"), out=ptr("attn_out"),
-                                       counters=ptr("attn_counters") + 4 * L * d.NKV, scale=scale, eps=d.eps, NH=d.NH, NKV=d.NKV, HD=d.HD,
-                                       BS=BS, X=X, max_parts=sz.parts)
-            prev = add(f"attn_{L}", "attn_fused", "attn_fused", L, blob, sz.parts * d.NKV, (sz.parts * d.NKV,), prev, "i->(0)",
-                       f"E_red_{L}", "i->(0)", (1,), sz.parts * d.NKV)
+                                       counters=ptr("attn_counters") + 4 * L * d.NH, scale=scale, eps=d.eps, NH=d.NH, NKV=d.NKV, HD=d.HD,
+                                       BS=BS, X=X, max_parts=nparts, gq=gq, part_len=plen)
+            prev = add(f"attn_{L}", "attn_fused", "attn_fused", L, blob, ntask, (ntask,), prev, "i->(0)",
+                       f"E_red_{L}", "i->(0)", (1,), ntask)
         else:
             # ---- attention prep per kv head
             blob = argblock.pack_named(ent["dsl_attnprep"], (d.NKV, 1, 1), qkv=ptr("qkv"), qw=W("qn") if d.qk_norm else 0,

@@ -26,7 +26,11 @@ F_PARAMS = [("qkv", "ptr addrspace(1)", 0, 8), ("qw", "ptr addrspace(1)", 8, 8),
             ("slot_mapping", "ptr addrspace(1)", 72, 8), ("exp_sums", "ptr addrspace(1)", 80, 8), ("max_logits", "ptr addrspace(1)", 88, 8),
             ("tmp_out", "ptr addrspace(1)", 96, 8), ("out", "ptr addrspace(1)", 104, 8), ("counters", "ptr addrspace(1)", 112, 8),
             ("scale", "float", 120, 4), ("eps", "float", 124, 4), ("NH", "i32", 128, 4), ("NKV", "i32", 132, 4), ("HD", "i32", 136, 4),
-            ("BS", "i32", 140, 4), ("X", "i32", 144, 4), ("max_parts", "i32", 148, 4)]
+            ("BS", "i32", 140, 4), ("X", "i32", 144, 4), ("max_parts", "i32", 148, 4),
+            # gq > 0: the grouped form -- a task is gq q heads of one kv head x part_len (128) positions, task index
+            # part * (NH / gq) + group, one counter per group; gq = 0: the general form (32 positions x one kv head)
+            ("gq", "i32", 152, 4), ("part_len", "i32", 156, 4)]
+GQ_PART = 128
 
 
 def import_entries(threads: int = 544) -> dict:
@@ -38,9 +42,16 @@ def import_entries(threads: int = 544) -> dict:
     return out
 
 
-def check_fused(NH: int, NKV: int, HD: int, BS: int, X: int, max_parts: int) -> None:
+def check_fused(NH: int, NKV: int, HD: int, BS: int, X: int, max_parts: int, gq: int = 0, part_len: int = 0) -> None:
     check_shape(NH, NKV, HD, BS, X, max_parts)
     G = NH // NKV
+    if gq:
+        if gq not in (1, 2, 4, 8) or G % gq or HD != 128 or BS != 16 or part_len != GQ_PART:
+            raise ValueError(f"attn_fused grouped form: needs gq in (1, 2, 4, 8) dividing G={G}, head_dim 128, block size 16 and "
+                             f"part_len {GQ_PART} (gq={gq}, HD={HD}, BS={BS}, part_len={part_len})")
+        if gq * max_parts > 4096:
+            raise ValueError(f"attn_fused grouped form: gq * max_parts = {gq * max_parts} exceeds 4096")
+        return
     if G + 2 > 16 or G * HD > 2048 or HD % 32:
         raise ValueError(f"attn_fused: needs G + 2 <= 16 warps, G * HD <= 2048 and HD % 32 == 0 (G={G}, HD={HD})")
     if G * max_parts > 8192:

@@ -221,17 +221,23 @@ def test_paged_attention(NH, NKV, HD, seq):
     assert_bf16_close(host(out), want, f"attention seq={seq}", min_exact=0.9)
 
 
-@pytest.mark.parametrize("NH,NKV,HD,qk_norm,seq", [(32, 4, 128, True, 1025), (32, 4, 128, True, 1024), (8, 2, 128, True, 1), (8, 2, 128, True, 33),
-                                                    (4, 2, 64, False, 100), (32, 8, 128, True, 640), (16, 2, 128, True, 97)])
-def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq):
+@pytest.mark.parametrize("NH,NKV,HD,qk_norm,seq,gq", [
+    (32, 4, 128, True, 1025, 0), (32, 4, 128, True, 1024, 0), (8, 2, 128, True, 1, 0), (8, 2, 128, True, 33, 0), (4, 2, 64, False, 100, 0),
+    (32, 8, 128, True, 640, 0), (16, 2, 128, True, 97, 0),
+    # the grouped form: gq q heads x 128 positions per task
+    (32, 4, 128, True, 1025, 2), (32, 4, 128, True, 1024, 2), (32, 4, 128, True, 1041, 8), (8, 2, 128, True, 1, 1), (8, 2, 128, True, 129, 4),
+    (32, 8, 128, False, 640, 2), (32, 8, 128, True, 128, 4), (16, 2, 128, True, 257, 8), (4, 4, 128, True, 77, 1)])
+def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq, gq):
     """The one-phase attention tile (norm + rope + cache write of the new position, split-KV attention, merge by the last
-    task of each kv head) against the oracle: new cache slot bit-exact, output within bf16 tolerance; run twice with the
-    same never-reset counters to cover the modulo arithmetic of the merge election."""
+    task to finish) against the oracle, in its general and its grouped form: new cache slot bit-exact, output within bf16
+    tolerance; run twice with the same never-reset counters to cover the modulo arithmetic of the merge election."""
     rng = np.random.default_rng(seq + NH)
     G = NH // NKV
     pos = seq - 1
-    maxlen = ((seq + 31) // 32) * 32 + 32
-    nblk, parts = maxlen // 16, maxlen // 32
+    plen = 128 if gq else 32
+    maxlen = ((seq + plen - 1) // plen) * plen + plen
+    nblk, parts = maxlen // 16, maxlen // plen
+    ntask, ncnt = (parts * (NH // gq), NH // gq) if gq else (parts * NKV, NKV)
     K = O.bfr(rng.standard_normal((seq, NKV, HD), dtype=np.float32) * np.float32(0.5))
     V = O.bfr(rng.standard_normal((seq, NKV, HD), dtype=np.float32))
     qkv = O.bfr(rng.standard_normal((NH + 2 * NKV, HD), dtype=np.float32))
@@ -259,18 +265,19 @@ def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq):
     p64 = torch.tensor([pos], dtype=torch.int64, device=DEV)
     es = torch.zeros((NH, parts), dtype=torch.float32, device=DEV); ml = torch.zeros_like(es)
     tmp = torch.zeros((NH, parts, HD), dtype=torch.float32, device=DEV); out = torch.zeros((NH, HD), dtype=torch.bfloat16, device=DEV)
-    cnt = torch.zeros(NKV, dtype=torch.int32, device=DEV)
-    blob = argblock.pack_named(ENT["attn_fused"], (parts * NKV, 1, 1), qkv=d_qkv.data_ptr(), qw=d_qn.data_ptr() if qk_norm else 0,
+    cnt = torch.zeros(ncnt, dtype=torch.int32, device=DEV)
+    blob = argblock.pack_named(ENT["attn_fused"], (ntask, 1, 1), qkv=d_qkv.data_ptr(), qw=d_qn.data_ptr() if qk_norm else 0,
                                kw=d_kn.data_ptr() if qk_norm else 0, cos_sin=cs.data_ptr(), kc=d_kc.data_ptr(), vc=d_vc.data_ptr(),
                                block_tables=bt.data_ptr(), seq_lens=sl.data_ptr(), positions=p64.data_ptr(), slot_mapping=p64.data_ptr(),
                                exp_sums=es.data_ptr(), max_logits=ml.data_ptr(), tmp_out=tmp.data_ptr(), out=out.data_ptr(),
-                               counters=cnt.data_ptr(), scale=float(scale), eps=1e-6, NH=NH, NKV=NKV, HD=HD, BS=16, X=8, max_parts=parts)
+                               counters=cnt.data_ptr(), scale=float(scale), eps=1e-6, NH=NH, NKV=NKV, HD=HD, BS=16, X=8, max_parts=parts,
+                               gq=gq, part_len=plen if gq else 0)
     for rerun in range(2):
         out.zero_()
-        op_launch("attn_fused", blob, parts * NKV)
+        op_launch("attn_fused", blob, ntask)
         assert np.array_equal(host(d_kc), kc_ref) and np.array_equal(host(d_vc), vc_ref)
         assert_bf16_close(host(out), want, f"fused attention seq={seq} run {rerun}", min_exact=0.9)
-        assert host(cnt).tolist() == [parts * (rerun + 1)] * NKV
+        assert host(cnt).tolist() == [parts * (rerun + 1)] * ncnt
         assert np.array_equal(host(d_qkv), qkv)                          # the fused tile leaves qkv as the GEMV wrote it
 
 

@@ -32,10 +32,10 @@ def test_qwen3_moe_graph_phases_and_counts():
                      "qkv_1", "attn_1", "o_proj_1", "router_1", "moe_up_1", "moe_down_1", "lm_head", "argmax"]
     plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
     shape = {n: plan.inst.grid_shapes[n] for n in names}
-    assert shape["qkv_0"] == (147,) and shape["attn_0"] == (34 * 4,) and shape["o_proj_0"] == (147,) and shape["router_0"] == (128,)
+    assert shape["qkv_0"] == (147,) and shape["attn_0"] == (9 * 16,) and shape["o_proj_0"] == (147,) and shape["router_0"] == (128,)
     assert shape["moe_up_0"] == (148,) and shape["moe_down_0"] == (147,) and shape["lm_head"] == (592,)
     assert all(m == "static" for m in plan.modes.values())
-    assert plan.events["E_up_0"].counts == [148] and plan.events["E_red_0"].counts == [136]
+    assert plan.events["E_up_0"].counts == [148] and plan.events["E_red_0"].counts == [144] and sz.attn == (2, 128, 9)
     assert verify_plan(plan) == []
     assert sz.up == (2, 37, 21)                            # two expert slots per task, 37 row chunks of 21 rows: 148 tasks
     # the unfused structure keeps the reference's phases
