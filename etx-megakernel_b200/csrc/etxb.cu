@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(ETXB_CONSUMERS, 1) etxb_attn_static_kernel(con
   Smem sm;
   sm.xs = (float*)st_smem;
   sm.scr = (float*)(st_smem + ETXB_GEN_BYTES);
-  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.stop = nullptr; sm.tr = nullptr;
+  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.stop = nullptr; sm.tr = nullptr; sm.events = nullptr; sm.evcount = nullptr; sm.inwords = nullptr; sm.epoch = 0; sm.rec = nullptr; sm.cur = 0;
   tile_attn_fused((const unsigned char*)&d, (int)blockIdx.x, sm, S);
 }
 }  // namespace etxb

@@ -34,11 +34,38 @@ struct Smem {
   int32_t* ctrl;
   int* stop;                 // CTA-local: a wait inside a body gave up (the body's results are not to be announced)
   uint64_t* tr;              // 8 stamps of the running task when tracing, else null (slots 4..7 are in-body marks)
+  // what wait_inputs() needs, by value (reading the kernel parameters through a pointer is a global-memory access):
+  int32_t* events;           // null outside the persistent kernel: nothing to wait for
+  const int32_t* evcount;
+  const int32_t* inwords;
+  uint32_t epoch;
+  const etxb_rec* rec;       // the running task's record
+  int cur;                   // the running task's index in the queue order (reported when a wait gives up)
 };
 // in-body time stamp k (0..3) of the running task; thread 0 only, no-op unless tracing
 __device__ __forceinline__ void mark(const Smem& sm, int k) { if (sm.tr != nullptr && tidx() == 0) sm.tr[4 + k] = globaltimer(); }
 __device__ __forceinline__ __nv_bfloat16* smem_xb(const Smem& sm) { return (__nv_bfloat16*)((unsigned char*)sm.xs + ETXB_XB_OFF); }
 __device__ __forceinline__ float* smem_g(const Smem& sm) { return (float*)((unsigned char*)sm.xs + ETXB_G_OFF); }
+
+// Wait for the running task's in-events.  ONE thread calls; the others meet it at the next barrier and then read
+// *sm.stop.  Normally the kernel's task loop calls this before the body; a tile that can start loads which do not
+// depend on its inputs (the attention tile's K / V) is entered without the wait and calls it itself once those loads
+// are issued.  False: the step is being abandoned (sm.stop is set).
+__device__ __forceinline__ bool wait_inputs(const Smem& sm) {
+  bool ok = true;
+  if (sm.events != nullptr) {
+    const etxb_rec& r = *sm.rec;
+    for (int i = 0; ok && i < r.in_n; ++i) {
+      int word, cnt;
+      if (i < 4) { word = r.in_word[i]; cnt = r.in_cnt[i]; }
+      else { word = sm.inwords[r.in_off + i]; cnt = sm.evcount[word]; }
+      ok = wait_event(sm.events, sm.ctrl, word, (int32_t)(sm.epoch * (uint32_t)cnt), sm.cur, *sm.deadline);
+    }
+    if (!ok) *(volatile int*)sm.stop = 1;
+    if (sm.tr != nullptr) sm.tr[1] = globaltimer();
+  }
+  return ok;
+}
 
 // Bounded mbarrier wait: true when the phase completed; false when the step is being abandoned (another thread gave
 // up, the host aborted, or the deadline passed -- then this thread records it).
@@ -206,6 +233,7 @@ __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, 
   const int rps = ETXB_STAGE_BYTES / t.row_bytes;
   bool ok = true;
   if ((tidx() & 31) == 0) {
+    const uint64_t pol = l2_policy_evict_first();
     for (int q0 = 0; q0 < total && ok; q0 += rps) {
       const uint32_t st = n % ETXB_NSTAGE, par = (n / ETXB_NSTAGE) & 1;
       ok = mbar_wait(sm.empty + st, par ^ 1, sm, where);           // a fresh barrier passes the first round
@@ -217,8 +245,8 @@ __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, 
       while (q < q0 + nr) {                                        // one copy per piece of a range that falls into this stage
         const int rg = q / t.n, r = q - rg * t.n;
         const int cnt = min(t.n - r, q0 + nr - q);
-        bulk_g2s(dst + (size_t)(q - q0) * t.row_bytes, gemv_range_base(body, d, t, rg, lids) + (size_t)r * t.row_bytes,
-                 (uint32_t)(cnt * t.row_bytes), sm.full + st);
+        bulk_g2s_hint(dst + (size_t)(q - q0) * t.row_bytes, gemv_range_base(body, d, t, rg, lids) + (size_t)r * t.row_bytes,
+                      (uint32_t)(cnt * t.row_bytes), sm.full + st, pol);
         q += cnt;
       }
       ++n;

@@ -45,6 +45,17 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// The same with an L2 eviction policy.  Weights are read once per step: streamed "evict first", the gigabytes that pass
+// through L2 every step leave the small things everybody re-reads (activations, KV cache, tables, argument blocks) in it.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
 
 // ---------------------------------------------------------------------------------------------- memory ordering
 __device__ __forceinline__ int32_t ld_acquire(const int32_t* p) {
@@ -68,25 +79,29 @@ __device__ __forceinline__ unsigned long long globaltimer() {
 
 // Wait until counter >= target (wrap-safe).  Bounded: gives up when the host sets the abort bit or when the
 // deadline passes, records where, and returns false; the kernel then drains and returns (no trap, no endless spin).
-__device__ __forceinline__ bool wait_event(const etxb_params& p, int word, int32_t target, int task_id,
+__device__ __forceinline__ bool wait_event(const int32_t* events, int32_t* ctrl, int word, int32_t target, int task_id,
                                            unsigned long long deadline) {
-  const int32_t* e = p.events + (size_t)word * ETXB_EV_STRIDE;
+  const int32_t* e = events + (size_t)word * ETXB_EV_STRIDE;
   uint32_t n = 0;
   for (;;) {
     const int32_t v = ld_acquire(e);
     if ((int32_t)(v - target) >= 0) return true;
     if ((++n & 63u) == 0) {
-      const int32_t c = ld_relaxed(p.ctrl);
+      const int32_t c = ld_relaxed(ctrl);
       if (c != 0) return false;                                   // someone else gave up, or the host aborted
       if ((n & 1023u) == 0 && globaltimer() > deadline) {
-        if (atomicOr(p.ctrl, ETXB_CTRL_TIMEOUT) == 0) {           // first to give up records the place
-          p.ctrl[1] = task_id; p.ctrl[2] = word; p.ctrl[3] = v; p.ctrl[4] = target;
+        if (atomicOr(ctrl, ETXB_CTRL_TIMEOUT) == 0) {           // first to give up records the place
+          ctrl[1] = task_id; ctrl[2] = word; ctrl[3] = v; ctrl[4] = target;
         }
         return false;
       }
       __nanosleep(64);
     }
   }
+}
+
+__device__ __forceinline__ bool wait_event(const etxb_params& p, int word, int32_t target, int task_id, unsigned long long deadline) {
+  return wait_event(p.events, p.ctrl, word, target, task_id, deadline);
 }
 
 // ---------------------------------------------------------------------------------------------- bf16
