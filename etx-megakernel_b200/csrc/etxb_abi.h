@@ -130,6 +130,9 @@ struct etxb_gemv_args {
 #define ETXB_MODE_BF16_WTS 0x100
 #define ETXB_MODE_BIAS 0x200
 #define ETXB_MODE_SUM_SLOTS 0x400     // MoE down: the task covers every slot and writes their bf16 sum in ascending expert id
+#define ETXB_MODE_ROUTE_READY 0x800   // MoE down with the top-k fold: the gate/up tiles it waits for have published the routing in
+                                      // ids / wts, so the consumer warps read it there (one load) instead of redoing the top-k;
+                                      // the producer warp, which runs ahead of the gate/up phase, still derives it from the logits
 // bits 16..23 of mode: expert slots per task of the MoE forms (0 = 1)
 
 // top-k: the reference's 64-byte block (etx/ops/topk.py:16-23), grid words at 48.

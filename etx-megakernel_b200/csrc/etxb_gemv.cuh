@@ -450,7 +450,17 @@ __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, c
   int32_t* lids = (int32_t*)(sm.scr + 96); float* lwts = sm.scr + 112;
   const int fold = d.mode & 0xff;
   const bool scaled = fold >= 2 || d.wts != nullptr;
-  if (tidx() < 32) gemv_routing(d, lids, lwts);
+  if (tidx() < 32) {
+    if (fold >= 2 && (d.mode & ETXB_MODE_ROUTE_READY) && d.ids != nullptr && d.wts != nullptr) {
+      if (tidx() < 16) {
+        lids[tidx()] = tidx() < d.R ? __ldcg(d.ids + tidx()) : 0;
+        lwts[tidx()] = tidx() < d.R ? __ldcg(d.wts + tidx()) : 1.f;
+      }
+      __syncwarp();
+    } else {
+      gemv_routing(d, lids, lwts);
+    }
+  }
   __nv_bfloat16* xb = smem_xb(sm);
   const int K = d.K, rows = t.n;
   for (int i = tidx(); i < t.spt * (K >> 3); i += ETXB_CONSUMERS) {          // the task's slots' activation vectors

@@ -400,7 +400,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
             dn_export = "dsl_moe_down_fold" if fold_topk else "dsl_moe_down"
             blob = gemv_block(dn_export, tpe, W=W("w2"), x=ptr("mc2"), out=ptr("moe_out"), ids=ptr("ti"), wts=ptr("tw"),
                               estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps,
-                              mode=(topk_mode if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS, E=d.E, logits=ptr("rlog"), nb=1)
+                              mode=(topk_mode | op_gemv.MODE_ROUTE_READY if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS, E=d.E, logits=ptr("rlog"), nb=1)
             # expert weights depend on the routing only: with the top-k folded in, the stream may start once the router is done
             prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, tpe, (tpe,), prev, "i->(0)",
                        f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None)

@@ -28,7 +28,7 @@ PARAMS = [("W", "ptr addrspace(1)", 0, 8), ("x", "ptr addrspace(1)", 8, 8), ("ou
           ("srin", "i32", 136, 4), ("srout", "i32", 140, 4)]
 FORMS = {"dsl_gemv": "plain", "dsl_moe_up": "silu_mul", "dsl_moe_down": "scale",
          "dsl_gemv_fold": "plain", "dsl_moe_up_fold": "silu_mul", "dsl_moe_down_fold": "scale"}
-MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS, MODE_SUM_SLOTS = 1, 2, 3, 0x100, 0x200, 0x400
+MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS, MODE_SUM_SLOTS, MODE_ROUTE_READY = 1, 2, 3, 0x100, 0x200, 0x400, 0x800
 
 
 def mode_spt(spt: int) -> int:
