@@ -137,6 +137,17 @@ class MachineModel:
         rpt = max(min_rows, -(-rows // want))
         return -(-rows // rpt), rpt
 
+    # measured on B200 (per-task device stamps of the decode kernel): what one persistent CTA streams and multiplies
+    # per microsecond once its weights flow, and what a tile costs before / after that (event poll, activation
+    # staging with or without the norm fold, routing, release)
+    STREAM_BYTES_PER_US = 40e3
+    TILE_OVERHEAD_US = {"qkv": 3.4, "o_proj": 1.6, "router": 4.6, "moe_up": 5.5, "moe_down": 6.5, "lm_head": 3.0, "gate_up": 3.4,
+                        "down": 2.5, "attn_fused": 8.0, "prep": 3.0, "attn": 6.0, "reduce": 3.0, "topk": 3.0}
+
+    def tile_duration_us(self, role: str, task_bytes: float) -> float:
+        """Annotation for the schedule simulator: fixed cost of the tile kind + its weight bytes at the per-CTA stream rate."""
+        return self.TILE_OVERHEAD_US.get(role, 2.0) + task_bytes / self.STREAM_BYTES_PER_US
+
     def attention_part(self) -> int:
         """KV positions per attention task.  32 positions x 4 kv heads fills the SMs at a 1K context and keeps one
         task's K and V (2 x 8 KB at head_dim 128) a single round trip."""

@@ -318,15 +318,17 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         off = pool.add(blob)
         pool.rows.append((name, export, role, layer, off, tasks, M, K))
         g.etensor(out_ev, out_shape, wait_count=out_count)
+        slots = (d.TOPK if role in ("moe_up", "moe_down") else 1) * (2 if role in ("moe_up", "gate_up") else 1)
         g.call_device(name, grid, tile("etx_tile_" + export, after), resource=res, args=["impargs"], consts=(off,),
-                      in_edges={in_ev: in_map}, out_edges={out_ev: out_map}, duration_us=2.0)
+                      in_edges={in_ev: in_map}, out_edges={out_ev: out_map},
+                      duration_us=round(m.tile_duration_us(role, 2.0 * slots * M * K / max(1, tasks)), 2))
         return out_ev
 
     def gemv_block(export, tasks, **f):
         return argblock.pack_named(ent[export], (tasks, 1, 1), **f)
 
     g.etensor("E_pro", (1,), wait_count=1)
-    g.call_device("prologue", (1,), tile("vl_prologue"), resource=res, args=["vl"], consts=(0,), out_edges={"E_pro": "i->i"}, duration_us=2.0)
+    g.call_device("prologue", (1,), tile("vl_prologue"), resource=res, args=["vl"], consts=(0,), out_edges={"E_pro": "i->i"}, duration_us=3.8)
     prev = "E_pro"
     for L in range(d.L):
         W = lambda n, L=L: ptr(f"{L}.{n}")                                  # noqa: E731
@@ -423,7 +425,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
     prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},
-                  out_edges={"E_argmax": "i->i"}, duration_us=3.0)
+                  out_edges={"E_argmax": "i->i"}, duration_us=8.5)
     return g, pool, sz
 
 
