@@ -43,7 +43,9 @@ struct etxb_session {
   std::vector<etxb_task> tasks;
   std::vector<void*> tensor_ptr;       // device address of every plan tensor (index 0 = argument pool)
   // device copies
-  etxb_task* d_tasks = nullptr; etxb_rec* d_recs = nullptr; int32_t* d_qbegin = nullptr; etxb_type* d_types = nullptr; void** d_type_args = nullptr;
+  etxb_task* d_tasks = nullptr; etxb_rec* d_recs = nullptr; etxb_rec* d_urecs = nullptr; int32_t* d_uqbegin = nullptr;
+  bool grid_order_ok = true;
+  int32_t* d_qbegin = nullptr; etxb_type* d_types = nullptr; void** d_type_args = nullptr;
   int32_t* d_events = nullptr; int32_t* d_evcount = nullptr; int32_t* d_inwords = nullptr; int32_t* d_outwords = nullptr;
   int32_t* d_ctrl = nullptr; uint64_t* d_trace = nullptr; int32_t* d_exec = nullptr; unsigned char* d_pool = nullptr;
   int32_t* h_ctrl = nullptr;           // pinned mirror
@@ -208,7 +210,7 @@ extern "C" int32_t etxb_destroy(etxb_session* s) {
   if (!s) return ETXB_OK;
   cudaSetDevice(s->device);
   if (s->launched) cudaDeviceSynchronize();
-  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
+  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_urecs, s->d_uqbegin, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
                   s->d_ctrl, s->d_trace, s->d_exec, s->d_pool};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (s->h_ctrl) cudaFreeHost(s->h_ctrl);
@@ -283,6 +285,29 @@ static int32_t upload_type_args(etxb_session* s) {
   }
   if (!s->d_recs) CU(cudaMalloc((void**)&s->d_recs, recs.size() * sizeof(etxb_rec) + 96));
   CU(cudaMemcpy(s->d_recs, recs.data(), recs.size() * sizeof(etxb_rec), cudaMemcpyHostToDevice));
+  // the same records grouped by grid (type), worker by worker, for the one-launch-per-grid baseline
+  const uint32_t W = s->h.n_workers, NT = s->h.n_types;
+  std::vector<etxb_rec> ug; ug.reserve(recs.size());
+  std::vector<int32_t> uq((size_t)NT * (W + 1), 0);
+  for (uint32_t t = 0; t < NT; ++t) {
+    for (uint32_t w = 0; w < W; ++w) {
+      uq[(size_t)t * (W + 1) + w] = (int32_t)ug.size();
+      for (int32_t i = s->qbegin[w]; i < s->qbegin[w + 1]; ++i)
+        if ((uint32_t)s->tasks[i].type == t) ug.push_back(recs[i]);
+    }
+    uq[(size_t)t * (W + 1) + W] = (int32_t)ug.size();
+  }
+  // launching grid by grid in type order is only a valid order when every producer's grid precedes its consumers'
+  std::vector<int32_t> word_type(s->h.n_events, -1);
+  for (const etxb_task& t : s->tasks)
+    for (int k = 0; k < t.out_n; ++k) word_type[s->outwords[t.out_off + k]] = std::max(word_type[s->outwords[t.out_off + k]], t.type);
+  s->grid_order_ok = true;
+  for (const etxb_task& t : s->tasks)
+    for (int k = 0; k < t.in_n; ++k)
+      if (word_type[s->inwords[t.in_off + k]] >= t.type) s->grid_order_ok = false;
+  if (!s->d_urecs) { CU(cudaMalloc((void**)&s->d_urecs, ug.size() * sizeof(etxb_rec) + 96)); CU(cudaMalloc((void**)&s->d_uqbegin, uq.size() * 4)); }
+  CU(cudaMemcpy(s->d_urecs, ug.data(), ug.size() * sizeof(etxb_rec), cudaMemcpyHostToDevice));
+  CU(cudaMemcpy(s->d_uqbegin, uq.data(), uq.size() * 4, cudaMemcpyHostToDevice));
   s->args_dirty = false;
   return ETXB_OK;
 }
@@ -313,6 +338,32 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream);
   if (rc) return rc;
+  CU(cudaEventRecord(s->ev1, s->stream));
+  s->launched = true;
+  return ETXB_OK;
+}
+
+// The unfused baseline (the reference's etx/codegen/kernel.py:645-681 and host.h:440-457): the same tiles and the same
+// task records, but one kernel launch per grid, in grid order on one stream.  The in-events of a launch's tasks were
+// all counted up by earlier launches, so nothing waits inside a launch; what is lost is what the single launch is
+// for: weights streaming ahead across phase boundaries and the hand-off without a launch in between.
+extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
+  if (!s) return fail(ETXB_E_ARG, "null session");
+  CU(cudaSetDevice(s->device));
+  if (s->args_dirty) { int32_t rc = upload_type_args(s); if (rc) return rc; }
+  if (!s->grid_order_ok) return fail(ETXB_E_UNSUPPORTED, "a grid waits for a grid that comes later in the plan: no launch-per-grid order");
+  s->stream = cuda_stream ? (cudaStream_t)cuda_stream : s->own_stream;
+  if (s->trace && s->d_exec) CU(cudaMemsetAsync(s->d_exec, 0, (size_t)s->h.n_tasks * 4, s->stream));
+  ++s->epoch;
+  etxb_params p;
+  fill_params(s, p);
+  p.recs = s->d_urecs;
+  CU(cudaEventRecord(s->ev0, s->stream));
+  for (uint32_t t = 0; t < s->h.n_types; ++t) {
+    p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream);
+    if (rc) return rc;
+  }
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
   return ETXB_OK;

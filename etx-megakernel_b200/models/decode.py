@@ -100,14 +100,19 @@ class DecodeProgram:
         return (t.float() if t.dtype == torch.bfloat16 else t).cpu().numpy()
 
     # ---- stepping
-    def step(self, t: int, pos: int, write_next: bool, wait: bool = True):
+    def step(self, t: int, pos: int, write_next: bool, wait: bool = True, unfused: bool = False):
+        """One decode step; unfused=True runs it as one kernel launch per grid (the baseline the single launch is compared with)."""
         self.session.set_step(tok=t, pos=pos, write_next=int(write_next))
-        if wait:
+        if unfused:
+            self.session.launch_unfused()
+            if wait:
+                self.session.wait(60.0)
+        elif wait:
             self.session.run(60.0)
         else:
             self.session.launch()
 
-    def generate(self, prompt, n_gen: int, start_pos: int = 0, sync_every: int = 64):
+    def generate(self, prompt, n_gen: int, start_pos: int = 0, sync_every: int = 64, unfused: bool = False):
         """Feed `prompt` token by token (positions start_pos ...), then n_gen greedy tokens; the next token never leaves
         the device.  Returns the n_gen generated ids (the argmax after the last prompt token is the first)."""
         prompt = [int(x) for x in prompt]
@@ -119,7 +124,7 @@ class DecodeProgram:
         self.buf["token_in"].copy_(tin)
         torch.cuda.synchronize(self.dev)
         for t in range(n):
-            self.step(t, start_pos + t, write_next=t + 1 >= len(prompt), wait=(t % sync_every == sync_every - 1) or t == n - 1)
+            self.step(t, start_pos + t, write_next=t + 1 >= len(prompt), wait=(t % sync_every == sync_every - 1) or t == n - 1, unfused=unfused)
         return self.buf["token_out"][len(prompt) - 1:n].cpu().numpy()
 
     def generate_host(self, prompt, n_gen: int, start_pos: int = 0):

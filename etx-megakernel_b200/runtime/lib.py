@@ -25,7 +25,7 @@ BODY = {"nop": 0, "prologue": 1, "argmax": 2, "gemv": 3, "moe_up": 4, "moe_down"
 
 # every symbol include/etxb200.h declares
 SYMBOLS = ["etxb_version", "etxb_last_error", "etxb_device_info", "etxb_create", "etxb_bind", "etxb_set_step", "etxb_set_option",
-           "etxb_launch", "etxb_wait", "etxb_step", "etxb_status", "etxb_trace", "etxb_exec_counts", "etxb_destroy",
+           "etxb_launch", "etxb_launch_unfused", "etxb_wait", "etxb_step", "etxb_status", "etxb_trace", "etxb_exec_counts", "etxb_destroy",
            "etxb_decode_host", "etxb_op_launch", "etxb_attn_fused_static"]
 
 
@@ -94,7 +94,7 @@ def load():
     proto = {
         "etxb_device_info": [C.c_int, C.POINTER(DeviceInfo)], "etxb_create": [vp, sz, C.c_int, C.POINTER(vp)],
         "etxb_bind": [vp, C.c_char_p, vp, sz], "etxb_set_step": [vp, C.POINTER(StepParams)], "etxb_set_option": [vp, C.c_char_p, C.c_int64],
-        "etxb_launch": [vp, vp], "etxb_wait": [vp, C.c_double], "etxb_step": [vp, vp, C.c_double], "etxb_status": [vp, C.POINTER(Status)],
+        "etxb_launch": [vp, vp], "etxb_launch_unfused": [vp, vp], "etxb_wait": [vp, C.c_double], "etxb_step": [vp, vp, C.c_double], "etxb_status": [vp, C.POINTER(Status)],
         "etxb_trace": [vp, vp, sz], "etxb_exec_counts": [vp, vp, sz], "etxb_destroy": [vp],
         "etxb_decode_host": [vp, vp, i32, i32, i32, vp, vp], "etxb_op_launch": [C.c_int, i32, vp, sz, i32, C.POINTER(StepParams), vp],
         "etxb_attn_fused_static": [C.c_int, vp, sz, vp],

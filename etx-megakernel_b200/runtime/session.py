@@ -53,6 +53,10 @@ class Session:
     def launch(self, stream: int | None = None):
         L.check(self.lib.etxb_launch(self._h, C.c_void_p(stream or 0)))
 
+    def launch_unfused(self, stream: int | None = None):
+        """The same step as one launch per grid (the unfused baseline); wait() as after launch()."""
+        L.check(self.lib.etxb_launch_unfused(self._h, C.c_void_p(stream or 0)))
+
     def wait(self, timeout_s: float = 60.0):
         L.check(self.lib.etxb_wait(self._h, float(timeout_s)))
 

@@ -111,6 +111,10 @@ int32_t etxb_set_step(etxb_session* s, const etxb_step_params* p);
 /* Options: "timeout_ms" (device wait deadline), "trace" (0/1: per-task stamps + execution counts). */
 int32_t etxb_set_option(etxb_session* s, const char* key, int64_t value);
 int32_t etxb_launch(etxb_session* s, void* cuda_stream);
+/* The unfused baseline: the same step as one kernel launch PER GRID, in plan order on one stream (what the reference
+ * builds with kernel.py:645-681 and runs with host.h:440-457 to state the gain of the single launch).  Same results;
+ * refused (ETXB_E_UNSUPPORTED) when a grid waits for a grid that comes later in the plan. */
+int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream);
 int32_t etxb_wait(etxb_session* s, double timeout_s);
 int32_t etxb_step(etxb_session* s, void* cuda_stream, double timeout_s);
 int32_t etxb_status(etxb_session* s, etxb_status_t* out);

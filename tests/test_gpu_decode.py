@@ -139,6 +139,24 @@ def test_unfused_attention_phases_and_separate_topk_give_the_same_tokens():
     assert np.abs(kg - ka).max() <= 2e-2 * np.abs(ka).max() and np.abs(vg - va).max() <= 2e-2 * np.abs(va).max()
 
 
+def test_launch_per_grid_baseline_gives_the_same_tokens():
+    """The unfused baseline (one launch per grid) runs the same tiles in the same order: identical tokens, logits and cache."""
+    od = SMALL_MOE
+    W = O.SyntheticWeights(od, seed=5, gamma="ones")
+    prompt = np.random.default_rng(6).integers(0, od.V, 9)
+    res = []
+    for unfused in (False, True):
+        p = make_program(od, W, 64)
+        res.append((p.generate(prompt, 10, unfused=unfused), p.read("logits"), *p.read_kv(1, 18)))
+        if unfused:
+            p.session.set_option("trace", 1)
+            p.step(0, 20, False, unfused=True)
+            assert (p.session.exec_counts() == 1).all()             # every task ran exactly once across the launches
+        p.close()
+    (ta, la, ka, va), (tb, lb, kb, vb) = res
+    assert ta.tolist() == tb.tolist() and np.array_equal(la, lb) and np.array_equal(ka, kb) and np.array_equal(va, vb)
+
+
 def test_thirty_two_greedy_tokens_dense_with_bias():
     od = O.Dims(name="dn", H=512, NH=8, NKV=2, HD=64, INTER=1536, L=3, V=2048, theta=1e4, tie=True, bias=True, qk_norm=False, moe=False)
     W = O.SyntheticWeights(od, seed=2, gamma="ones", std=0.05)
