@@ -507,21 +507,16 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
     etxb_gemv_args d;
     memcpy(&d, argblock, sizeof d);
     if ((d.mode & 0xff) != 0) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: plain form only");
-    if ((int64_t)d.nb * ((d.K + 7) / 8 * 8) > ETXB_NB_XS_FLOATS) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: nb * K exceeds the activation stage");
-    const size_t smem = (ETXB_NB_XS_FLOATS + 256) * 4;
+    if (d.nb > 8 || d.K % 8) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: nb must be 2 .. 8 and K a multiple of 8");
+    const size_t smem = (size_t)d.nb * ((size_t)d.K * 2 + ETXB_NB_PAD) + (size_t)ETXB_NB_PART_FLOATS * 4;
+    if (smem > 200 * 1024) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: nb * K exceeds the activation stage (nb tokens x K bf16 in shared memory)");
+    if (d.rpt > 1024) return fail(ETXB_E_UNSUPPORTED, "batched GEMV: more than 1024 rows per task");
     static int nb_ready[64];
     if (!nb_ready[device]) {
-      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      CU(cudaFuncSetAttribute(etxb::etxb_gemv_nb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
       nb_ready[device] = 1;
     }
-    switch (d.nb) {
-      case 2: etxb::etxb_gemv_nb_kernel<2><<<ntasks, 512, smem, st>>>(d); break;
-      case 4: etxb::etxb_gemv_nb_kernel<4><<<ntasks, 512, smem, st>>>(d); break;
-      case 8: etxb::etxb_gemv_nb_kernel<8><<<ntasks, 512, smem, st>>>(d); break;
-      default: return fail(ETXB_E_UNSUPPORTED, "batched GEMV: nb must be 2, 4 or 8");
-    }
+    etxb::etxb_gemv_nb_kernel<<<ntasks, ETXB_NB_THREADS, smem, st>>>(d);
     CU(cudaGetLastError());
     return ETXB_OK;
   }

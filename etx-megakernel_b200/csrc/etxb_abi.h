@@ -30,7 +30,6 @@
 #define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512 + ETXB_CTX_SLOTS * ETXB_CTX_BYTES)
 #define ETXB_ATTN_PART 32            // KV positions per attention task
 #define ETXB_MAX_NB 8                // activation columns of the stand-alone batched GEMV kernel
-#define ETXB_NB_XS_FLOATS 40960      // its staged activations: nb * K floats
 
 // ---- plan blob ------------------------------------------------------------------------------------------------
 // header, then sections in this order, each starting on an 8-byte boundary:

@@ -39,7 +39,7 @@ MAX_K = 12288              # a streamed row (and its bf16 activation vector in s
 MAX_K_NORM = 8192          # the norm fold works on fp32 in shared memory
 MAX_RESULTS = 2048         # row results one MoE task holds in shared memory (ranges x rows per range)
 NB_ALLOWED = (1, 2, 4, 8)
-NB_XS_FLOATS = 40960       # stand-alone batched GEMV (nb > 1): nb * K floats of staged activations
+NB_STAGE_BYTES = 200 * 1024 - 32768   # stand-alone batched GEMV (nb > 1): nb token rows of K bf16 (+ 64 bytes each) staged in shared memory
 
 
 def type_string() -> str:
@@ -60,8 +60,9 @@ def check_shape(export: str, *, M: int, K: int, rpt: int, nb: int = 1, mode: int
     if nb > 1:
         if FORMS[export] != "plain" or (mode & 0xff):
             raise ValueError(f"{export}: nb > 1 is built for the plain stand-alone GEMV only")
-        if nb * K > NB_XS_FLOATS:
-            raise ValueError(f"{export}: nb*K={nb * K} exceeds the {NB_XS_FLOATS}-float activation stage")
+        if nb > 8 or nb * (2 * K + 64) > NB_STAGE_BYTES or rpt > 1024:
+            raise ValueError(f"{export}: batched form takes nb <= 8, nb * (2 K + 64) <= {NB_STAGE_BYTES} bytes of staged activations and "
+                             f"at most 1024 rows per task (nb={nb}, K={K}, rpt={rpt})")
     elif K > MAX_K:
         raise ValueError(f"{export}: K={K} exceeds {MAX_K} (one row must fit a 32 KB ring stage)")
     if (mode & 0xff) == MODE_NORM and K > MAX_K_NORM:
