@@ -158,8 +158,10 @@ struct etxb_attn_args {
 };
 
 // fused attention phase (this library's own): q/k norm + rope + cache write of the new position, split-KV attention over
-// 32 positions, and the merge of the partitions by the last task of each kv head to finish (counters: one monotonic
-// int32 per kv head, never reset).  Task blk = part * NKV + h.
+// a partition of the context, and the merge of the partitions by the last task to finish (counters: monotonic int32,
+// never reset).  General form (gq = 0): task blk = part * NKV + h covers 32 positions x the G q heads of kv head h, one
+// counter per kv head.  Grouped form (gq > 0, head_dim 128, cache blocks of 16): task blk = part * (NH / gq) + group
+// covers part_len = 128 positions x gq q heads, one counter per group.
 struct etxb_attnf_args {
   void* qkv; const void* qw; const void* kw; const void* cos_sin; void* kc; void* vc;                            // 0..47
   const int32_t* block_tables; const int32_t* seq_lens; const int64_t* positions; const int64_t* slot_mapping;  // 48..79

@@ -161,7 +161,7 @@ def size_for(d: Dims, m: MachineModel, maxlen: int) -> Sizing:
         return best[1:]
     dt, drpt = m.gemv_tasks(d.H)
     return Sizing(workers=W, qkv=m.gemv_tasks(d.NQKV), o=m.gemv_tasks(d.H), router=m.gemv_tasks(d.E) if d.moe else (0, 0),
-                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.V, waves=4), parts=-(-maxlen // m.attention_part()),
+                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.V, waves=1), parts=-(-maxlen // m.attention_part()),
                   attn=m.attention_groups(d.NH, d.NKV, d.HD, BS, maxlen))
 
 

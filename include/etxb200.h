@@ -57,7 +57,7 @@ enum {
   ETXB_BODY_ATTN_REDUCE = 9,  /* merge of the partitions of one q head */
   ETXB_BODY_SPLITK_PART = 10, /* demo: partial sums of a split-K reduction (etx/operators/splitk_sum.py) */
   ETXB_BODY_SPLITK_SUM = 11,
-  ETXB_BODY_ATTN_FUSED = 12,  /* prep + split-KV attention + merge by the last task of a kv head, one phase */
+  ETXB_BODY_ATTN_FUSED = 12,  /* prep + split-KV attention + merge by the last task to finish, one phase (general and grouped form) */
   ETXB_BODY_COUNT = 13
 };
 

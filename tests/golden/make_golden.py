@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures in this directory by running the REFERENCE's own CPU code.
 
-Run in a container that has the reference checkout (default /root/reference, or $ETX_REFERENCE):
+Run where the reference checkout is available ($ETX_REFERENCE, default: a directory `reference` beside this repository):
 
     python tests/golden/make_golden.py
 
@@ -23,7 +23,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
-REF = Path(os.environ.get("ETX_REFERENCE", "/root/reference"))
+REF = Path(os.environ.get("ETX_REFERENCE", str(ROOT.parent / "reference")))
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(REF))
 

@@ -10,7 +10,7 @@ from etx_megakernel_b200 import api
 def test_model_request_plans_and_simulates():
     req = api.PlanRequest(api.model("qwen3-30b-a3b", config={"layers": 2, "maxlen": 1072}))
     pw = api.plan(req)
-    assert pw.report["tasks"] == 2316 and pw.report["workers"] == 148 and pw.report["grids"]["moe_up_0"] == 148
+    assert pw.report["tasks"] == 1872 and pw.report["workers"] == 148 and pw.report["grids"]["moe_up_0"] == 148
     assert pw.report["verify"] == [] and pw.machine["name"] == "b200" and all(m == "static" for m in pw.report["modes"].values())
     again = api.PlannedWorkload.from_dict(json.loads(json.dumps(pw.to_dict())))
     assert again.identity == pw.identity and api.plan(req).identity == pw.identity          # detached, reproducible records

@@ -33,7 +33,7 @@ def test_qwen3_moe_graph_phases_and_counts():
     plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
     shape = {n: plan.inst.grid_shapes[n] for n in names}
     assert shape["qkv_0"] == (147,) and shape["attn_0"] == (9 * 16,) and shape["o_proj_0"] == (147,) and shape["router_0"] == (128,)
-    assert shape["moe_up_0"] == (148,) and shape["moe_down_0"] == (147,) and shape["lm_head"] == (592,)
+    assert shape["moe_up_0"] == (148,) and shape["moe_down_0"] == (147,) and shape["lm_head"] == (148,)
     assert all(m == "static" for m in plan.modes.values())
     assert plan.events["E_up_0"].counts == [148] and plan.events["E_red_0"].counts == [144] and sz.attn == (2, 128, 9)
     assert verify_plan(plan) == []

@@ -47,7 +47,7 @@ def test_timeline_tables_and_critical_path():
     tl = Timeline.from_sim(plan, r)
     assert abs(tl.span_us - r.makespan_us) < 1e-9
     rows = {x["grid"]: x for x in tl.by_grid()}
-    assert rows["moe_up_0"]["tasks"] == 148 and rows["lm_head"]["tasks"] == 592
+    assert rows["moe_up_0"]["tasks"] == 148 and rows["lm_head"]["tasks"] == 148
     assert rows["qkv_1"]["last_ready"] > rows["moe_down_0"]["last_done"]
     steps, totals = tl.critical_path()
     whole = sum(v["body"] + v["dependency"] + v["queue"] for v in totals.values()) + steps[-1].gap_us
