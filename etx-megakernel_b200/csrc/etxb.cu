@@ -45,6 +45,8 @@ struct etxb_session {
   // device copies
   etxb_task* d_tasks = nullptr; etxb_rec* d_recs = nullptr; etxb_rec* d_urecs = nullptr; int32_t* d_uqbegin = nullptr;
   bool grid_order_ok = true;
+  int variant = 0;                     // kernel variant picked from the plan (select_variant); force_full overrides it
+  bool force_full = false;
   int32_t* d_qbegin = nullptr; etxb_type* d_types = nullptr; void** d_type_args = nullptr;
   int32_t* d_events = nullptr; int32_t* d_evcount = nullptr; int32_t* d_inwords = nullptr; int32_t* d_outwords = nullptr;
   int32_t* d_ctrl = nullptr; uint64_t* d_trace = nullptr; int32_t* d_exec = nullptr; unsigned char* d_pool = nullptr;
@@ -64,15 +66,53 @@ static int g_kernel_ready[64];
 
 static int g_sm_count[64];
 
+// Which kernel can run this plan?  The lean decode kernels hold only the tiles of a fused decode step; a plan qualifies
+// when every grid is one of those tiles with its argument block in the pool (one block per grid) and the blocks stay
+// inside what the lean forms cover: norm folds of at most one row, top-k folds over at most 128 experts, grouped
+// attention (head_dim 128, cache blocks of 16, partitions of 128) with the same group size everywhere.
+static int select_variant(const etxb_session* s, const std::vector<unsigned char>& pool) {
+  int gq = 0;
+  bool any_attn = false;
+  for (const etxb_type& ty : s->types) {
+    const int b = ty.body;
+    if (b == ETXB_BODY_NOP || b == ETXB_BODY_PROLOGUE || b == ETXB_BODY_ARGMAX) continue;
+    if (!(b == ETXB_BODY_GEMV || b == ETXB_BODY_MOE_UP || b == ETXB_BODY_MOE_DOWN || b == ETXB_BODY_ATTN_FUSED)) return 0;
+    if (ty.args[0] != 0 || ty.cst[1] != 0 || ty.cst[0] < 0) return 0;
+    const size_t off = (size_t)ty.cst[0];
+    if (b == ETXB_BODY_ATTN_FUSED) {
+      if (off + sizeof(etxb_attnf_args) > pool.size()) return 0;
+      etxb_attnf_args a;
+      memcpy(&a, pool.data() + off, sizeof a);
+      if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || a.HD != 128 || a.BS != 16 || a.part_len != 128) return 0;
+      if (any_attn && a.gq != gq) return 0;
+      gq = a.gq; any_attn = true;
+    } else {
+      if (off + sizeof(etxb_gemv_args) > pool.size()) return 0;
+      etxb_gemv_args a;
+      memcpy(&a, pool.data() + off, sizeof a);
+      const int fold = a.mode & 0xff;
+      if (fold == ETXB_MODE_NORM && a.R > 1) return 0;
+      if (fold >= 2 && a.E > 128) return 0;
+    }
+  }
+  if (!any_attn) gq = 1;                                           // no attention grid: any lean kernel will do
+  return gq == 1 ? 1 : gq == 2 ? 2 : gq == 4 ? 3 : 4;
+}
+
+// The kernel variants: index 0 = the full kernel, 1..4 = the lean decode kernels for grouped attention with 1, 2, 4, 8
+// q heads per task (etxb_kernel.cuh, run_body).
+static const void* const g_kernels[5] = {(const void*)etxb::etxb_megakernel<0>, (const void*)etxb::etxb_megakernel<1>, (const void*)etxb::etxb_megakernel<2>,
+                                         (const void*)etxb::etxb_megakernel<4>, (const void*)etxb::etxb_megakernel<8>};
+
 static int32_t prepare_kernel(int device, int* workers_out) {
   CU(cudaSetDevice(device));
   if (device < 0 || device >= 64) return fail(ETXB_E_ARG, "device index out of range");
   if (!g_kernel_ready[device]) {                                   // once per device: attribute queries are slow
     int sms = 0;
     CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    CU(cudaFuncSetAttribute(etxb::etxb_megakernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ETXB_SMEM_BYTES));
+    for (const void* k : g_kernels) CU(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, ETXB_SMEM_BYTES));
     int per_sm = 0;
-    CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, etxb::etxb_megakernel, ETXB_THREADS, ETXB_SMEM_BYTES));
+    CU(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, etxb::etxb_megakernel<0>, ETXB_THREADS, ETXB_SMEM_BYTES));
     if (per_sm < 1) return fail(ETXB_E_RESIDENCY, "the persistent CTA does not fit one SM of this device");
     g_sm_count[device] = sms;
     g_kernel_ready[device] = 1;
@@ -172,6 +212,7 @@ static int32_t parse_plan(etxb_session* s, const unsigned char* b, size_t n) {
   CU(up((void**)&s->d_evcount, s->evcount.data(), h.n_events * 4));
   CU(up((void**)&s->d_inwords, s->inwords.data(), h.n_in * 4));
   CU(up((void**)&s->d_outwords, s->outwords.data(), h.n_out * 4));
+  s->variant = select_variant(s, pool);
   pool.resize(pool.size() + 256, 0);                               // the context prefetch reads 192 bytes from a block start
   CU(up((void**)&s->d_pool, pool.data(), pool.size()));
   CU(cudaMalloc((void**)&s->d_type_args, (size_t)h.n_types * ETXB_MAX_ARGS * sizeof(void*)));
@@ -253,6 +294,7 @@ extern "C" int32_t etxb_set_option(etxb_session* s, const char* key, int64_t val
     }
     return ETXB_OK;
   }
+  if (!strcmp(key, "full_kernel")) { s->force_full = value != 0; return ETXB_OK; }
   return fail(ETXB_E_ARG, std::string("unknown option ") + key);
 }
 
@@ -320,9 +362,9 @@ static void fill_params(etxb_session* s, etxb_params& p) {
   p.step = s->step;
 }
 
-static int32_t launch_kernel(const etxb_params& p, int grid, cudaStream_t st) {
+static int32_t launch_kernel(const etxb_params& p, int grid, cudaStream_t st, int variant = 0) {
   void* kargs[] = {(void*)&p};
-  CU(cudaLaunchCooperativeKernel((const void*)etxb::etxb_megakernel, dim3(grid), dim3(ETXB_THREADS), kargs, ETXB_SMEM_BYTES, st));
+  CU(cudaLaunchCooperativeKernel(g_kernels[variant], dim3(grid), dim3(ETXB_THREADS), kargs, ETXB_SMEM_BYTES, st));
   return ETXB_OK;
 }
 
@@ -336,7 +378,7 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   etxb_params p;
   fill_params(s, p);
   CU(cudaEventRecord(s->ev0, s->stream));
-  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream);
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
   if (rc) return rc;
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
@@ -361,7 +403,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   for (uint32_t t = 0; t < s->h.n_types; ++t) {
     p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
-    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream);
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
     if (rc) return rc;
   }
   CU(cudaEventRecord(s->ev1, s->stream));
@@ -433,6 +475,7 @@ extern "C" int32_t etxb_status(etxb_session* s, etxb_status_t* out) {
   out->ctrl = s->h_ctrl ? s->h_ctrl[0] : 0; out->stuck_task = s->h_ctrl && s->h_ctrl[0] ? s->h_ctrl[1] : -1;
   out->stuck_event = s->h_ctrl[2]; out->stuck_value = s->h_ctrl[3]; out->stuck_target = s->h_ctrl[4];
   out->tasks_run = 0; out->epoch = s->epoch; out->last_ms = s->last_ms;
+  out->kernel_variant = s->force_full ? 0 : s->variant;
   if (s->trace && s->d_exec) {
     std::vector<int32_t> ex(s->h.n_tasks);
     CU(cudaSetDevice(s->device));

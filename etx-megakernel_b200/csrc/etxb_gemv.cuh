@@ -167,9 +167,11 @@ __device__ __forceinline__ void warp_topk_n(const void* logits, int E, int K, bo
   __syncwarp();
 }
 
+// LEAN: the form the host picks when every top-k of the plan has E <= 128 (no code for more experts in that kernel).
+template <bool LEAN>
 __device__ __noinline__ void warp_topk(const void* logits, int E, int K, bool renorm, bool bf16w,
                                        int32_t* ids, float* wts, int32_t* tei) {
-  if (E <= 128) warp_topk_n<4>(logits, E, K, renorm, bf16w, ids, wts, tei);
+  if (LEAN || E <= 128) warp_topk_n<4>(logits, E, K, renorm, bf16w, ids, wts, tei);
   else warp_topk_n<8>(logits, E, K, renorm, bf16w, ids, wts, tei);
 }
 
@@ -179,7 +181,7 @@ __device__ __forceinline__ void tile_topk(const unsigned char* a, int blk, const
   const int nb = (d.nbsv & 0xff) ? (d.nbsv & 0xff) : 1, sv = d.nbsv >> 8;
   const int w = tidx() >> 5;
   if (w >= nb) return;
-  warp_topk((const __nv_bfloat16*)d.logits + (size_t)w * d.E, d.E, d.K, (d.mode & 0xff) == 1, (d.mode & ETXB_MODE_BF16_WTS) != 0,
+  warp_topk<false>((const __nv_bfloat16*)d.logits + (size_t)w * d.E, d.E, d.K, (d.mode & 0xff) == 1, (d.mode & ETXB_MODE_BF16_WTS) != 0,
             d.ids + (size_t)w * sv, d.wts + (size_t)w * sv, d.tei ? d.tei + (size_t)w * sv : nullptr);
 }
 
@@ -203,10 +205,11 @@ __device__ __forceinline__ GemvTask gemv_task(int body, const etxb_gemv_args& d,
 
 // Expert ids (and routing weights) of the task's slots into `lids` / `lwts` (indexed by global slot).  One warp, all
 // lanes call.  Top-k fold: recomputed from the logits; else read from the ids / wts buffers; no ids: expert 0.
+template <bool LEAN>
 __device__ __forceinline__ void gemv_routing(const etxb_gemv_args& d, int32_t* lids, float* lwts) {
   const int fold = d.mode & 0xff, lane = tidx() & 31;
   if (fold >= 2) {
-    warp_topk(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
+    warp_topk<LEAN>(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
   } else {
     if (lane < 16) {
       lids[lane] = (d.ids && lane < d.R) ? __ldcg(d.ids + lane) : 0;
@@ -309,10 +312,12 @@ __device__ __forceinline__ void stage_xb(const void* x, int K, __nv_bfloat16* xb
 // Norm fold: z = bf16(resid_in + acc), acc = the R rows added one by one in bf16 in ascending id order (R == 1: the row
 // itself; rows == null: z = resid_in), then x = bf16(ln * bf16(z * r)), r = 1 / sqrt(mean(z^2) + eps) with the mean summed
 // in numpy's order.  x goes to shared memory (xb); `store`: this task also writes resid_out (z) and xout (x).  K <= 8192.
+// LEAN: the form the host picks when every norm fold of the plan adds at most one row (R <= 1): no ordering, no row loop.
+template <bool LEAN>
 __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, void* rout, void* xout, const void* ln,
                                             const int32_t* ids, int R, int K, float eps, float* xf, __nv_bfloat16* xb, float* scr, bool store) {
   int* order = (int*)(scr + 64);
-  if (R > 1) {
+  if (!LEAN && R > 1) {
     if (tidx() < R) {
       int rank = tidx();
       if (ids) {
@@ -337,6 +342,11 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
     if (rows == nullptr || R == 0) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) z[j] = rf[j];
+    } else if (LEAN) {
+      const uint4 rv = ld_act16((const __nv_bfloat16*)rows + 8 * i);
+      const float v[8] = {bf_lo(rv.x), bf_hi(rv.x), bf_lo(rv.y), bf_hi(rv.y), bf_lo(rv.z), bf_hi(rv.z), bf_lo(rv.w), bf_hi(rv.w)};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) z[j] = bfr(__fadd_rn(rf[j], v[j]));      // bf16(0 + row) = row: the one-row case of the loop below
     } else {
       float acc[8];
 #pragma unroll
@@ -383,6 +393,7 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
 }
 
 // ---------------------------------------------------------------------------------------------- plain / folded GEMV
+template <bool LEAN>
 __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(3, d, blk);
@@ -390,7 +401,7 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
   const int r0 = t.r0;
   __nv_bfloat16* xb = smem_xb(sm);
   if ((d.mode & 0xff) == ETXB_MODE_NORM)
-    stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
+    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
   else
     stage_xb(d.x, d.K, xb);
   const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
@@ -404,6 +415,7 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
 // ---------------------------------------------------------------------------------------------- MoE gate+up
 // task blk: expert slots [group * spt, ...), row chunk j = blk % tpe; expert e = ids[slot] (no ids and no fold: expert
 // 0, the dense SwiGLU MLP); act[slot][r] = bf16(bf16(silu(bf16 g)) * bf16 u), g = W_e[r,:].x, u = W_e[M + r,:].x.
+template <bool LEAN>
 __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(4, d, blk);
@@ -412,7 +424,7 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
   const int fold = d.mode & 0xff;
   if (tidx() < 32) {
     if (fold >= 2) {
-      gemv_routing(d, lids, lwts);
+      gemv_routing<LEAN>(d, lids, lwts);
       if (blk - t.group * d.tpe == 0 && tidx() < t.spt) {           // the group's first chunk publishes its slots' routing
         const int sl = t.group * t.spt + tidx();
         if (d.ids) ((int32_t*)d.ids)[sl] = lids[sl];
@@ -422,7 +434,7 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
   }
   __nv_bfloat16* xb = smem_xb(sm);
   if (fold == ETXB_MODE_NORM)                                      // dense MLP: the post-attention norm folded in
-    stage_norm_col(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
+    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
   else
     stage_xb(d.x, d.K, xb);
   float* g = smem_g(sm);                                           // per slot: n gate results, then n up results
@@ -443,6 +455,7 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
 // Plain form: out[slot][r] = y.  Summed form (mode bit ETXB_MODE_SUM_SLOTS, the task covers every slot): out[r] = the
 // y of all slots added one by one in bf16 in ascending expert id -- the expert combine of the CPU path
 // (examples/llm/ref_numpy.py:142-148), which the reference leaves to the next layer's norm fold.
+template <bool LEAN>
 __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(5, d, blk);
@@ -458,7 +471,7 @@ __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, c
       }
       __syncwarp();
     } else {
-      gemv_routing(d, lids, lwts);
+      gemv_routing<LEAN>(d, lids, lwts);
     }
   }
   __nv_bfloat16* xb = smem_xb(sm);

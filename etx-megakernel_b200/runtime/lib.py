@@ -44,7 +44,7 @@ class StepParams(C.Structure):
 
 class Status(C.Structure):
     _fields_ = [("ctrl", C.c_int32), ("stuck_task", C.c_int32), ("stuck_event", C.c_int32), ("stuck_value", C.c_int32),
-                ("stuck_target", C.c_int32), ("tasks_run", C.c_int32), ("epoch", C.c_uint32), ("last_ms", C.c_float)]
+                ("stuck_target", C.c_int32), ("tasks_run", C.c_int32), ("epoch", C.c_uint32), ("last_ms", C.c_float), ("kernel_variant", C.c_int32)]
 
 
 class DeviceInfo(C.Structure):

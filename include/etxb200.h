@@ -86,6 +86,8 @@ typedef struct etxb_status_t {
   int32_t tasks_run;       /* tasks completed in the last step (only counted when tracing is on) */
   uint32_t epoch;          /* steps launched so far */
   float last_ms;           /* device time of the last etxb_step / etxb_wait, CUDA events */
+  int32_t kernel_variant;  /* 0: the full kernel; 1..4: the lean decode kernel (grouped attention with 1, 2, 4, 8 q heads per task)
+                              the library picked for this plan; option "full_kernel" = 1 forces 0 */
 } etxb_status_t;
 
 typedef struct etxb_device_info_t {
@@ -108,7 +110,8 @@ int32_t etxb_create(const void* plan_blob, size_t bytes, int device, etxb_sessio
 /* Give a named plan tensor its device address.  The caller keeps ownership and must keep it alive. */
 int32_t etxb_bind(etxb_session* s, const char* name, void* dev_ptr, size_t bytes);
 int32_t etxb_set_step(etxb_session* s, const etxb_step_params* p);
-/* Options: "timeout_ms" (device wait deadline), "trace" (0/1: per-task stamps + execution counts). */
+/* Options: "timeout_ms" (device wait deadline), "trace" (0/1: per-task stamps + execution counts), "full_kernel" (0/1: run
+ * the kernel that holds every tile even when the plan qualifies for the lean decode kernel; see etxb_status_t.kernel_variant). */
 int32_t etxb_set_option(etxb_session* s, const char* key, int64_t value);
 int32_t etxb_launch(etxb_session* s, void* cuda_stream);
 /* The unfused baseline: the same step as one kernel launch PER GRID, in plan order on one stream (what the reference

@@ -139,6 +139,31 @@ def test_unfused_attention_phases_and_separate_topk_give_the_same_tokens():
     assert np.abs(kg - ka).max() <= 2e-2 * np.abs(ka).max() and np.abs(vg - va).max() <= 2e-2 * np.abs(va).max()
 
 
+def test_lean_kernel_is_picked_for_decode_plans_and_matches_the_full_kernel():
+    """The library runs fused decode plans on the lean kernel variant (only the tiles such a plan uses) and anything else
+    on the full kernel; both give bit-identical results."""
+    od = SMALL_MOE
+    W = O.SyntheticWeights(od, seed=11, gamma="ones")
+    prompt = np.random.default_rng(12).integers(0, od.V, 9)
+    res = []
+    for full in (0, 1):
+        p = make_program(od, W, 64)
+        p.session.set_option("full_kernel", full)
+        res.append((p.generate(prompt, 10), p.read("logits"), *p.read_kv(1, 18)))
+        gq = p.sizing.attn[0]
+        assert p.session.status().kernel_variant == (0 if full else {1: 1, 2: 2, 4: 3, 8: 4}[gq])
+        p.close()
+    (ta, la, ka, va), (tb, lb, kb, vb) = res
+    assert ta.tolist() == tb.tolist() and np.array_equal(la, lb) and np.array_equal(ka, kb) and np.array_equal(va, vb)
+    for kw in ({"fused_attn": False, "fold_topk": False}, {"fused_attn": "general"}):      # plans with other tiles: the full kernel
+        p = make_program(od, W, 64, **kw)
+        assert p.session.status().kernel_variant == 0
+        p.close()
+    dense = make_program(SMALL_DENSE, O.SyntheticWeights(SMALL_DENSE, seed=1, gamma="ones"), 64)
+    assert dense.session.status().kernel_variant == 0                                    # head_dim 64: the general attention tile
+    dense.close()
+
+
 def test_launch_per_grid_baseline_gives_the_same_tokens():
     """The unfused baseline (one launch per grid) runs the same tiles in the same order: identical tokens, logits and cache."""
     od = SMALL_MOE
