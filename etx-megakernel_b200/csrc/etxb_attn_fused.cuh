@@ -15,20 +15,23 @@ namespace etxb {
 
 // One head row in shared memory (xh, HD floats; d = lane * epl + j held by lane): optional RMSNorm with weight nw, then
 // neox rotary with the cos | sin row cs (both as floats in shared memory).  o[j] = the bf16-rounded results.  One warp.
-__device__ __forceinline__ void head_norm_rope_s(const float* xh, const float* nw, const float* cs, int HD, float eps, float* o) {
+template <int HDT>
+__device__ __noinline__ void head_norm_rope_s(const float* xh, const float* nw, const float* cs, int HDr, float eps, float* o) {
+  const int HD = HDT ? HDT : HDr;                                  // HDT: head_dim as a compile-time constant (0: read it)
   const int lane = tidx() & 31, half = HD >> 1, epl = HD >> 5;
-  float v[8];
+  constexpr int EPL = HDT ? HDT / 32 : 8;
+  float v[EPL];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] = j < epl ? xh[lane * epl + j] : 0.f;
+  for (int j = 0; j < EPL; ++j) v[j] = j < epl ? xh[lane * epl + j] : 0.f;
   if (nw != nullptr) {
-    const float ss = head_sumsq(xh, HD);
+    const float ss = HDT == 128 ? sumsq128_numpy_order_warp(xh) : head_sumsq(xh, HD);
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)HD), eps)));
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < EPL; ++j)
       if (j < epl) v[j] = bfr(__fmul_rn(nw[lane * epl + j], bfr(__fmul_rn(v[j], r))));
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
+  for (int j = 0; j < EPL; ++j) {
     const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);    // element d +- HD/2 lives 16 lanes away
     if (j < epl) {
       const int dd = lane * epl + j;
@@ -108,12 +111,12 @@ __device__ __forceinline__ void attn_fused_prep(const etxb_attnf_args& d, const 
   const int lb_new = (int)(pos / BS) - part * P / BS, lo_new = (int)(pos % BS);
   if (warp < G) {
     float o[8];
-    head_norm_rope_s(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
+    head_norm_rope_s<0>(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
 #pragma unroll
     for (int j = 0; j < 8; ++j) if (j < epl) s.qs[warp * HD + lane * epl + j] = o[j];
   } else if (warp == G && owner) {
     float o[8];
-    head_norm_rope_s(s.raw + G * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
+    head_norm_rope_s<0>(s.raw + G * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
     __nv_bfloat16* kc = (__nv_bfloat16*)d.kc;
 #pragma unroll
     for (int j = 0; j < 8; ++j)

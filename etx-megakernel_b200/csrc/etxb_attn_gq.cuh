@@ -41,7 +41,7 @@ static_assert(((8 + 2) + 3 + 8 + 2 + 32 + 8 + 32) * 128 * 4 + 128 <= ETXB_GEN_BY
 // out[hq][:] = bf16(sum_p w_p * tmp[p][:] / sum_p w_p * l_p), w_p = exp(m_p - max m), for q heads hq0 .. hq0 + GQ - 1.
 // Run by the last task of the q group; reads the partials the other CTAs wrote (L2).  GQ * np <= 4096.
 template <int GQ>
-__device__ __forceinline__ void attn_gq_merge(const etxb_attnf_args& d, const Smem& sm, int hq0, int np) {
+__device__ __noinline__ void attn_gq_merge(const etxb_attnf_args& d, const Smem& sm, int hq0, int np) {
   constexpr int HD = 128;
   const int lane = tidx() & 31, warp = tidx() >> 5;
   float* wl = sm.xs;                                              // [GQ][np] max logits, then weights
@@ -151,12 +151,12 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
     // ---- norm + rope of the q heads (warps 0..GQ-1), of the new k row (warp GQ); the new v row (warp GQ + 1)
     if (warp < GQ) {
       float o[8];
-      head_norm_rope_s(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
+      head_norm_rope_s<128>(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
 #pragma unroll
       for (int j = 0; j < 4; ++j) s.qs[warp * HD + lane * 4 + j] = o[j];
     } else if (warp == GQ && owner) {
       float o[8];
-      head_norm_rope_s(s.raw + GQ * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
+      head_norm_rope_s<128>(s.raw + GQ * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
       const long long cb = slot / BS; const int off = (int)(slot % BS);
       __nv_bfloat16* kc = (__nv_bfloat16*)d.kc;
 #pragma unroll

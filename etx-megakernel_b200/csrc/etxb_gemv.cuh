@@ -133,6 +133,7 @@ __device__ __forceinline__ void warp_topk_n(const void* logits, int E, int K, bo
       c[j - 1] = hi; c[j] = lo;
     }
   float myw = 0.f; int myid = 0x7fffffff;
+#pragma unroll 1
   for (int t = 0; t < K; ++t) {
     const uint32_t hk = (uint32_t)(c[0] >> 32), hi_ = (uint32_t)c[0];
     const uint32_t top = __reduce_max_sync(0xffffffffu, hk);
@@ -150,6 +151,7 @@ __device__ __forceinline__ void warp_topk_n(const void* logits, int E, int K, bo
     float tot;
     if (K < 8) {
       tot = 0.f;
+#pragma unroll 1
       for (int t = 0; t < K; ++t) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, myw, t));
     } else {
       float r = lane < 8 ? myw : 0.f;                              // accumulator j = lane j
@@ -158,6 +160,7 @@ __device__ __forceinline__ void warp_topk_n(const void* logits, int E, int K, bo
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, o));
       tot = __shfl_sync(0xffffffffu, r, 0);
+#pragma unroll 1
       for (int t = (K >= 16 ? 16 : 8); t < K; ++t) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, myw, t));
     }
     myw = __fdiv_rn(myw, tot);
@@ -334,6 +337,7 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
   }
   const int nv = K >> 3;
   uint4 lw[2];                                                     // norm weights of this thread's (at most two) vectors, fetched with the rows
+#pragma unroll 1
   for (int i = tidx(), it = 0; i < nv; i += ETXB_CONSUMERS, ++it) {
     float z[8];
     if (it < 2) lw[it] = __ldg((const uint4*)((const __nv_bfloat16*)ln + 8 * i));
@@ -379,6 +383,7 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
   csync();
   const float ss = sumsq_numpy_order(xf, K, scr);
   const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), eps)));
+#pragma unroll 1
   for (int i = tidx(), it = 0; i < nv; i += ETXB_CONSUMERS, ++it) {
     const uint4 w = it == 0 ? lw[0] : lw[1];
     const float wf[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};

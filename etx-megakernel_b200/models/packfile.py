@@ -127,7 +127,7 @@ def read_vl(src_dir, theta: float = 1e6) -> tuple:
 def to_device(packed: dict, device):
     """uint16 views -> bf16 device tensors (one host copy per tensor)."""
     import torch
-    return {k: torch.from_numpy(np.ascontiguousarray(v).view(np.int16)).to(device).view(torch.bfloat16) for k, v in packed.items()}
+    return {k: torch.from_numpy(np.array(v, dtype=np.uint16).view(np.int16)).to(device).view(torch.bfloat16) for k, v in packed.items()}
 
 
 # ---------------------------------------------------------------------------------------------- golden token files
