@@ -246,9 +246,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ledger = O.step_bytes(O.dims_from_config(oracle_cfg(O), MODEL, layers=d.L), ctx)
     peak, peak_src = measured_peaks()
     achieved = ledger["total"] / (dev_ms * 1e-3) / 1e9
-    # DRAM bytes per launch: dram__bytes_read + write of one ncu capture on the 2-layer case (863.93 MB against 854.11 MB
+    # DRAM bytes per launch: dram__bytes_read + write of one ncu capture on the 2-layer case (862.12 MB against 854.11 MB
     # algorithmic, profiles/megakernel_qwen3-30b-a3b_2layers_ctx1024.md), scaled by the algorithmic bytes of this launch
-    traffic = ledger["total"] * (863.93 / 854.11)
+    traffic = ledger["total"] * (862.12 / 854.11)
     line = {"metric": METRIC, "value": dev_ms / world, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload(d.L, P), "prefill": "the prompt is fed token by token through the same kernel",
