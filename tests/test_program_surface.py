@@ -86,7 +86,7 @@ def test_machine_model_b200():
     assert m.total_cus() == 148 and m.workers() == 148 and m.wave_size == 32 and not m.has_domain_level
     from etx_megakernel_b200.ir import Scope
     assert m.effective_scope(Scope.DOMAIN) == Scope.DEVICE and m.effective_scope(Scope.SYSTEM) == Scope.SYSTEM
-    assert m.vis(Scope.DEVICE).poll.startswith("ld.acquire.gpu") and m.supports("tma") and not m.supports("tma_multicast")
+    assert m.vis(Scope.DEVICE).poll.startswith("ld.acquire.gpu") and m.supports("tma") and not m.supports("tma_cluster_broadcast")
     assert m.gemv_tasks(5120) == (147, 35) and m.gemv_tasks(128) == (128, 1)
     assert m.hbm_bw_bytes_per_us() == 8.0e6
     with pytest.raises(FileNotFoundError):
