@@ -334,3 +334,30 @@ def test_wait_deadline_returns_status():
     s2 = Session(plan2, {}, bytes(16))
     s2.run(5.0)
     s2.close(); s.close()
+
+
+def test_full_size_model_properties():
+    """Qwen3-30B-A3B at its full size (48 layers, random weights generated on the device): the oracle cannot follow at
+    this size in seconds, so size-independent properties stand in -- the single launch, the launch-per-grid baseline,
+    the full kernel variant and the host-buffer entry all produce the same greedy tokens, twice."""
+    d = Q.load_dims("qwen3-30b-a3b")
+    dev = torch.device("cuda:0")
+    w = D.random_packed_weights(d, 128, dev, seed=0, gamma="ones")
+    prompt = np.random.default_rng(3).integers(0, d.V, 24)
+    runs = {}
+    for name in ("lean", "lean again", "full kernel", "launch per grid"):
+        prog = D.DecodeProgram(d, w, device=0, maxlen=128)
+        if name == "full kernel":
+            prog.session.set_option("full_kernel", 1)
+        assert prog.session.status().kernel_variant == (0 if name == "full kernel" else {1: 1, 2: 2, 4: 3, 8: 4}[prog.sizing.attn[0]])
+        runs[name] = prog.generate(prompt, 8, unfused=(name == "launch per grid")).tolist()
+        if name == "lean":
+            logits = prog.read("logits")
+            assert np.isfinite(logits).all() and logits.std() > 0
+            host, _ = prog.session.decode_host(np.asarray(prompt, np.int32), len(prompt) + 8 - 1, 0)
+            runs["host buffers"] = host[len(prompt) - 1:].tolist()
+        prog.close()
+    first = runs["lean"]
+    assert len(set(first)) > 1, "degenerate generation"
+    for name, toks in runs.items():
+        assert toks == first, f"{name}: {toks} != {first}"
