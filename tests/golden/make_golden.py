@@ -139,7 +139,52 @@ def moe_block_case():
     print("moe_block.npz", suite["passed"], len(suite["cases"]))
 
 
+MLA_FILE = "examples/dsv2lite/results/2026-10-14-k1/b_alld4r0l1kvs_stamps/fleet_src/host/reference_decode.py"
+
+
+def mla_case():
+    """One absorbed-MLA + MoE layer and one dense layer, 24 decode positions each, run by the NumPy reference archived in
+    the reference tree (bf16 rounding on).  Inputs and weights are regenerated from the seeds by the test."""
+    import importlib.util
+    from oracle import ref_mla as M
+    from tests.golden.cases import MLA_SMALL
+    spec = importlib.util.spec_from_file_location("fleet_reference_decode", REF / MLA_FILE)
+    R = importlib.util.module_from_spec(spec)
+    sys.modules["fleet_reference_decode"] = R
+    spec.loader.exec_module(R)
+    out, n = {}, 24
+    for tag, dense in (("moe", 0), ("dense", 96)):
+        d = M.MlaDims(**MLA_SMALL, dense_inter=dense)
+        L = M.synthetic_layer(d, seed=5)
+        cfg = R.ModelConfig(hidden=d.hidden, heads=d.heads, kv_lora_rank=d.kv_lora, qk_nope=d.qk_nope, qk_rope=d.qk_rope, v_head=d.v_head,
+                            moe_inter=d.moe_inter, n_routed=d.n_routed, top_k=d.top_k, bf16=True)
+        kw = dict(input_layernorm=L.input_layernorm, q_proj=L.q_proj, kv_a_proj_with_mqa=L.kv_a_proj_with_mqa, kv_a_layernorm=L.kv_a_layernorm,
+                  kv_b_proj=L.kv_b_proj, o_proj=L.o_proj, post_attention_layernorm=L.post_attention_layernorm)
+        if dense:
+            kw.update(mlp_gate=L.mlp["gate"], mlp_up=L.mlp["up"], mlp_down=L.mlp["down"])
+        else:
+            kw.update(gate_weight=L.mlp["router"], experts_gate=L.mlp["egate"], experts_up=L.mlp["eup"], experts_down=L.mlp["edown"],
+                      shared_gate=L.mlp["sgate"], shared_up=L.mlp["sup"], shared_down=L.mlp["sdown"])
+        W = R.LayerWeights(**kw)
+        cos, sin = R.yarn_cos_sin(d.qk_rope, n, cfg.rope_theta, cfg.rope_factor, cfg.rope_original_max, cfg.beta_fast, cfg.beta_slow,
+                                  cfg.mscale, cfg.mscale_all_dim)
+        rng = np.random.default_rng(1)
+        cache = np.zeros((n, d.kv_lora + d.qk_rope), np.float32)
+        ys = []
+        for pos in range(n):
+            x = O.bfr(rng.standard_normal(d.hidden, dtype=np.float32))
+            ys.append(R.decoder_layer(cfg, W, x, cache, pos, cos, sin))
+        out.update({f"{tag}_y": np.stack(ys), f"{tag}_cache": cache, f"{tag}_cos": cos.astype(np.float32), f"{tag}_sin": sin.astype(np.float32),
+                    f"{tag}_scale": np.float64(cfg.softmax_scale)})
+    np.savez_compressed(HERE / "mla_layer.npz", seed=5, xseed=1, n=n, dense_inter=96, **out)
+    print("mla_layer.npz", {k: v.shape for k, v in out.items() if hasattr(v, "shape")})
+
+
 if __name__ == "__main__":
+    if "--mla-only" in sys.argv:
+        mla_case()
+        raise SystemExit(0)
+    mla_case()
     decode_case(SMALL_MOE, seed=3, n_prompt=8, n_gen=8, gamma="ones", out="decode_small_moe.npz")
     decode_case(SMALL_DENSE, seed=4, n_prompt=6, n_gen=6, gamma="normal", out="decode_small_dense.npz")
     topk_case()

@@ -144,3 +144,31 @@ def test_byte_ledger_matches_reference_figures():
     assert abs(b["total"] / 1e9 - 6.1845) < 0.001
     d8 = O.dims_from_config(O.QWEN3_8B)
     assert abs(O.step_bytes(d8, 1024)["total"] / 1e9 - 15.288) < 0.002
+
+
+def test_mla_oracle_matches_the_reference_fixture(golden_dir):
+    """oracle/ref_mla.py (absorbed MLA + DeepSeek MoE / dense layer) against outputs of the NumPy reference archived in
+    the reference tree (tests/golden/make_golden.py: mla_case): layer outputs and latent cache rows bit-exact over 24
+    decode positions, YaRN tables and softmax scale equal."""
+    from oracle import ref_mla as M
+    from tests.golden.cases import MLA_SMALL
+    g = np.load(golden_dir / "mla_layer.npz")
+    n = int(g["n"])
+    for tag, dense in (("moe", 0), ("dense", int(g["dense_inter"]))):
+        d = M.MlaDims(**MLA_SMALL, dense_inter=dense)
+        L = M.synthetic_layer(d, seed=int(g["seed"]))
+        cos, sin = M.yarn_tables(d, n)
+        assert np.array_equal(cos.astype(np.float32), g[f"{tag}_cos"]) and np.array_equal(sin.astype(np.float32), g[f"{tag}_sin"])
+        assert d.scale == float(g[f"{tag}_scale"])
+        rng = np.random.default_rng(int(g["xseed"]))
+        cache = np.zeros((n, d.kv_lora + d.qk_rope), np.float32)
+        for pos in range(n):
+            x = O.bfr(rng.standard_normal(d.hidden, dtype=np.float32))
+            tr = {}
+            y = M.layer(d, L, x, cache, pos, cos, sin, tr)
+            assert np.array_equal(y, g[f"{tag}_y"][pos]), (tag, pos)
+            if not dense:
+                assert len(set(tr["ids"].tolist())) == d.top_k and abs(float(tr["wts"].sum())) <= 1.0 + 1e-6
+        assert np.array_equal(cache, g[f"{tag}_cache"])
+    full = M.MlaDims(**M.DSV2_LITE)
+    assert full.q_head == 192 and abs(M.layer_bytes(full, 1025) - 167.38e6) / 167.38e6 < 0.01          # the reference's 167.38 MB per MoE layer
