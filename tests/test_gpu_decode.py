@@ -164,6 +164,15 @@ def test_lean_kernel_is_picked_for_decode_plans_and_matches_the_full_kernel():
     dense.close()
 
 
+def test_decode_across_partition_and_block_boundaries_up_to_the_last_cache_position():
+    """A context that grows through the 128-position partition boundary of the grouped attention tile, through 16-position
+    cache block boundaries, and ends on the very last position the cache has: tokens against the oracle (tie rule)."""
+    od = O.Dims(name="edge", H=256, NH=4, NKV=2, HD=128, INTER=0, L=2, V=512, qk_norm=True, moe=True, E=8, TOPK=2, MI=64, norm_topk=True)
+    W = O.SyntheticWeights(od, seed=21, gamma="ones")
+    prompt = np.random.default_rng(22).integers(0, od.V, 118)
+    check_greedy(od, W, prompt, 27, 144)                                    # positions 0 .. 143 = maxlen - 1
+
+
 def test_launch_per_grid_baseline_gives_the_same_tokens():
     """The unfused baseline (one launch per grid) runs the same tiles in the same order: identical tokens, logits and cache."""
     od = SMALL_MOE
