@@ -294,7 +294,7 @@ __device__ __forceinline__ void consume_task(int total, int rows_per_range, int 
       const uint4* wv = (const uint4*)(stage + (size_t)j * row_bytes);
       const uint4* xv = (const uint4*)(xb + (size_t)((q0 + j) / rows_per_range) * xstride);
       float acc = 0.f;
-#pragma unroll 4
+#pragma unroll 8
       for (int v = lane; v < nvec; v += 32) acc = dot8(wv[v], xv[v], acc);
       acc = warp_sum(acc);
       if (lane == 0) epi(q0 + j, acc);
