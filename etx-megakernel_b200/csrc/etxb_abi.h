@@ -15,8 +15,9 @@
 #define ETXB_NWARPS ETXB_CONSUMER_WARPS
 #define ETXB_MAX_ARGS 4              // tensor pointers a task type may name (Graph.call_device(args=[...]))
 // shared memory of the persistent CTA
-#define ETXB_STAGE_BYTES 32768       // one ring stage: whole weight rows, so a row is at most 32 KB (K <= 16384)
-#define ETXB_NSTAGE 5                // 160 KB of weights in flight per SM
+#define ETXB_STAGE_BYTES 24576       // one ring stage: whole weight rows, so a row is at most 24 KB (K <= 12288); 24 KB holds 6 / 3 / 1
+                                     // rows of K = 2048 / 4096 / 12288 and 16 rows of K = 768 without a remainder
+#define ETXB_NSTAGE 6                // 144 KB of weights in flight per SM (measured against 5 x 32 KB: 0.8 % / 2.3 % faster on the MoE / dense model)
 #define ETXB_RING_BYTES (ETXB_STAGE_BYTES * ETXB_NSTAGE)
 #define ETXB_GEN_BYTES 65536         // activations: fp32 scratch [0,32K), bf16 x [32K,56K), row results [56K,64K); attention tiles use all of it
 #define ETXB_XF_FLOATS 8192          // norm fold works on K <= 8192 floats

@@ -12,7 +12,7 @@
 //
 // Weight streaming.  The weight rows of a task are one or two contiguous byte ranges.  The CTA's producer warp walks
 // the task queue AHEAD of the consumer warps and copies those ranges, whole rows at a time, into a ring of
-// ETXB_NSTAGE x 32 KB shared-memory stages with bulk asynchronous copies (cp.async.bulk, the TMA engine; completion
+// ETXB_NSTAGE x 24 KB shared-memory stages with bulk asynchronous copies (cp.async.bulk, the TMA engine; completion
 // on an mbarrier per stage).  Weights depend on no event (expert weights: only on the routing), so the stream keeps
 // running while the consumers wait for their activations: HBM stays busy across phase boundaries.  The consumer
 // warps take the stages in order; warp w owns the rows q with q % 16 == w, reads 16-byte weight and activation

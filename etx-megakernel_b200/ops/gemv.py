@@ -64,7 +64,7 @@ def check_shape(export: str, *, M: int, K: int, rpt: int, nb: int = 1, mode: int
             raise ValueError(f"{export}: batched form takes nb <= 8, nb * (2 K + 64) <= {NB_STAGE_BYTES} bytes of staged activations and "
                              f"at most 1024 rows per task (nb={nb}, K={K}, rpt={rpt})")
     elif K > MAX_K:
-        raise ValueError(f"{export}: K={K} exceeds {MAX_K} (one row must fit a 32 KB ring stage)")
+        raise ValueError(f"{export}: K={K} exceeds {MAX_K} (one row must fit a 24 KB ring stage)")
     if (mode & 0xff) == MODE_NORM and K > MAX_K_NORM:
         raise ValueError(f"{export}: norm fold over K={K} > {MAX_K_NORM}")
     spt = ((mode >> 16) & 0xff) or 1
