@@ -60,6 +60,13 @@ struct etxb_session {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = 0.f;
   int workers = 0;
+  // sharded model (etxb_set_exchange)
+  std::vector<unsigned char> h_pool;   // host copy of the argument pool (the rows an exchanged task writes are derived from it)
+  std::vector<int32_t> evcount_eff;    // arrivals per step including the peers' (exchanged events: x n_ranks)
+  int n_ranks = 1, rank = 0;
+  unsigned char* xbase = nullptr; size_t xbytes = 0;
+  unsigned char* xpeer[ETXB_MAX_PEERS] = {};
+  bool events_external = false;        // the counters live at the start of the caller's exchange region
 };
 
 static int g_kernel_ready[64];
@@ -213,6 +220,8 @@ static int32_t parse_plan(etxb_session* s, const unsigned char* b, size_t n) {
   CU(up((void**)&s->d_inwords, s->inwords.data(), h.n_in * 4));
   CU(up((void**)&s->d_outwords, s->outwords.data(), h.n_out * 4));
   s->variant = select_variant(s, pool);
+  s->h_pool = pool;
+  s->evcount_eff = s->evcount;
   pool.resize(pool.size() + 256, 0);                               // the context prefetch reads 192 bytes from a block start
   CU(up((void**)&s->d_pool, pool.data(), pool.size()));
   CU(cudaMalloc((void**)&s->d_type_args, (size_t)h.n_types * ETXB_MAX_ARGS * sizeof(void*)));
@@ -251,7 +260,7 @@ extern "C" int32_t etxb_destroy(etxb_session* s) {
   if (!s) return ETXB_OK;
   cudaSetDevice(s->device);
   if (s->launched) cudaDeviceSynchronize();
-  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_urecs, s->d_uqbegin, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
+  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_urecs, s->d_uqbegin, s->d_qbegin, s->d_types, s->d_type_args, s->events_external ? nullptr : s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
                   s->d_ctrl, s->d_trace, s->d_exec, s->d_pool};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (s->h_ctrl) cudaFreeHost(s->h_ctrl);
@@ -298,6 +307,109 @@ extern "C" int32_t etxb_set_option(etxb_session* s, const char* key, int64_t val
   return fail(ETXB_E_ARG, std::string("unknown option ") + key);
 }
 
+// ---- sharded model: exchange regions ------------------------------------------------------------------------------
+// One region per rank, allocated here so that it is its own device allocation (an inter-process handle names a whole
+// allocation), zeroed, and exported as a 64-byte handle the other ranks' processes open.
+static_assert(sizeof(cudaIpcMemHandle_t) == ETXB_IPC_HANDLE_BYTES, "handle size");
+
+extern "C" int32_t etxb_exchange_alloc(int device, size_t bytes, void** dev_ptr, unsigned char* handle) {
+  if (!dev_ptr || !handle || bytes == 0) return fail(ETXB_E_ARG, "bad argument");
+  CU(cudaSetDevice(device));
+  const size_t gran = size_t(2) << 20;
+  const size_t sz = (bytes + gran - 1) / gran * gran;
+  void* p = nullptr;
+  CU(cudaMalloc(&p, sz));
+  cudaError_t e = cudaMemset(p, 0, sz);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return fail(ETXB_E_CUDA, std::string("exchange_alloc: ") + cudaGetErrorString(e)); }
+  memcpy(handle, &h, sizeof h);
+  *dev_ptr = p;
+  return ETXB_OK;
+}
+extern "C" int32_t etxb_exchange_free(int device, void* dev_ptr) {
+  CU(cudaSetDevice(device));
+  if (dev_ptr) CU(cudaFree(dev_ptr));
+  return ETXB_OK;
+}
+extern "C" int32_t etxb_exchange_open(int device, const unsigned char* handle, void** peer_ptr) {
+  if (!handle || !peer_ptr) return fail(ETXB_E_ARG, "null argument");
+  CU(cudaSetDevice(device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof h);
+  CU(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return ETXB_OK;
+}
+extern "C" int32_t etxb_exchange_close(int device, void* peer_ptr) {
+  CU(cudaSetDevice(device));
+  if (peer_ptr) CU(cudaIpcCloseMemHandle(peer_ptr));
+  return ETXB_OK;
+}
+
+extern "C" int32_t etxb_set_exchange(etxb_session* s, int32_t rank, int32_t n_ranks, void* local_base, size_t bytes, void* const* peer_bases) {
+  if (!s || !local_base || !peer_bases) return fail(ETXB_E_ARG, "null argument");
+  if (n_ranks < 2 || n_ranks > ETXB_MAX_PEERS + 1 || rank < 0 || rank >= n_ranks) return fail(ETXB_E_ARG, "set_exchange: 2 <= n_ranks <= 8, 0 <= rank < n_ranks");
+  if (s->epoch != 0 || s->launched || s->n_ranks != 1) return fail(ETXB_E_ARG, "set_exchange: once, before the first step");
+  const size_t evbytes = (size_t)s->h.n_events * ETXB_EV_STRIDE * 4;
+  if (bytes < evbytes + 2 || ((uintptr_t)local_base & 127)) return fail(ETXB_E_ARG, "set_exchange: the region starts with the event counters (128 bytes per event, 128-byte aligned)");
+  bool any = false;
+  for (const etxb_type& ty : s->types) any = any || ty.exchange != 0;
+  if (!any) return fail(ETXB_E_PLAN, "set_exchange: the plan marks no grid as exchanged");
+  int q = 0;
+  for (int r = 0; r < n_ranks; ++r) {
+    if (r == rank) continue;
+    if (!peer_bases[r] || ((uintptr_t)peer_bases[r] & 127)) return fail(ETXB_E_ARG, "set_exchange: a peer's region is missing or misaligned");
+    s->xpeer[q++] = (unsigned char*)peer_bases[r];
+  }
+  CU(cudaSetDevice(s->device));
+  CU(cudaMemset(local_base, 0, evbytes));
+  if (!s->events_external && s->d_events) CU(cudaFree(s->d_events));
+  s->d_events = (int32_t*)local_base; s->events_external = true;
+  s->xbase = (unsigned char*)local_base; s->xbytes = bytes; s->rank = rank; s->n_ranks = n_ranks;
+  // every rank's tasks arrive on an exchanged grid's events
+  std::vector<char> xev(s->h.n_events, 0);
+  for (const etxb_task& t : s->tasks)
+    if (s->types[t.type].exchange)
+      for (int k = 0; k < t.out_n; ++k) xev[s->outwords[t.out_off + k]] = 1;
+  for (uint32_t e = 0; e < s->h.n_events; ++e) s->evcount_eff[e] = s->evcount[e] * (xev[e] ? n_ranks : 1);
+  CU(cudaMemcpy(s->d_evcount, s->evcount_eff.data(), (size_t)s->h.n_events * 4, cudaMemcpyHostToDevice));
+  s->args_dirty = true;
+  return ETXB_OK;
+}
+
+// The rows an exchanged task writes, as (first bf16 element from the exchange region's base, count): task c0 of a plain
+// GEMV or of a MoE-down grid that leaves one row vector (one slot, or every slot summed) writes out[r0 .. r0 + n).
+static int32_t exchange_rows(const etxb_session* s, const etxb_type& ty, const etxb_task& t, uint32_t* mirror) {
+  *mirror = 0;
+  if (ty.body != ETXB_BODY_GEMV && ty.body != ETXB_BODY_MOE_DOWN) return fail(ETXB_E_UNSUPPORTED, "exchange: only GEMV and MoE-down grids can be exchanged");
+  if (ty.args[0] != 0 || ty.cst[1] != 0 || ty.cst[0] < 0 || (size_t)ty.cst[0] + sizeof(etxb_gemv_args) > s->h_pool.size())
+    return fail(ETXB_E_UNSUPPORTED, "exchange: the grid's argument block must be in the pool");
+  etxb_gemv_args a;
+  memcpy(&a, s->h_pool.data() + ty.cst[0], sizeof a);
+  const int blk = t.coord[0];
+  if (blk >= (int)a.nblocks || a.rpt <= 0) return ETXB_OK;
+  int r0;
+  if (ty.body == ETXB_BODY_GEMV) {
+    if ((a.mode & 0xff) != 0) return fail(ETXB_E_UNSUPPORTED, "exchange: a folded GEMV writes no partial rows");
+    r0 = blk * a.rpt;
+  } else {
+    const int spt = ((a.mode >> 16) & 0xff) ? ((a.mode >> 16) & 0xff) : 1;
+    if (a.tpe <= 0 || blk / a.tpe != 0 || (!(a.mode & ETXB_MODE_SUM_SLOTS) && spt != 1))
+      return fail(ETXB_E_UNSUPPORTED, "exchange: the MoE-down grid must leave one row vector (one slot, or every slot summed by the task)");
+    r0 = (blk % a.tpe) * a.rpt;
+  }
+  const int r1 = std::min(a.M, r0 + a.rpt);
+  if (r0 >= r1) return ETXB_OK;
+  const unsigned char* out = (const unsigned char*)a.out + (size_t)r0 * 2;
+  const size_t bytes = (size_t)(r1 - r0) * 2;
+  if (out < s->xbase + (size_t)s->h.n_events * ETXB_EV_STRIDE * 4 || out + bytes > s->xbase + s->xbytes)
+    return fail(ETXB_E_ARG, "exchange: an exchanged grid writes outside the exchange region (or into its counters)");
+  const size_t off = (size_t)(out - s->xbase) / 2;
+  if (((out - s->xbase) & 1) || off >= (1u << 20) || (r1 - r0) >= 4096) return fail(ETXB_E_UNSUPPORTED, "exchange: row range does not fit the task record");
+  *mirror = (uint32_t)off | ((uint32_t)(r1 - r0) << 20);
+  return ETXB_OK;
+}
+
 static int32_t upload_type_args(etxb_session* s) {
   std::vector<void*> ta((size_t)s->h.n_types * ETXB_MAX_ARGS, nullptr);
   for (size_t t = 0; t < s->types.size(); ++t)
@@ -317,13 +429,17 @@ static int32_t upload_type_args(etxb_session* s) {
     memset(&r, 0, sizeof r);
     r.body = ty.body; r.c0 = t.coord[0]; r.c1 = t.coord[1]; r.id = t.id;
     r.in_n = t.in_n; r.out_n = t.out_n; r.in_off = t.in_off; r.out_off = t.out_off;
-    for (int k = 0; k < 4 && k < t.in_n; ++k) { r.in_word[k] = s->inwords[t.in_off + k]; r.in_cnt[k] = s->evcount[r.in_word[k]]; }
+    for (int k = 0; k < 4 && k < t.in_n; ++k) { r.in_word[k] = s->inwords[t.in_off + k]; r.in_cnt[k] = s->evcount_eff[r.in_word[k]]; }
     for (int k = 0; k < 4 && k < t.out_n; ++k) r.out_word[k] = s->outwords[t.out_off + k];
     // tiles below the GEMV family take no argument block: point them at the pool so the 192-byte prefetch stays in bounds
     const bool has_block = ty.body >= ETXB_BODY_GEMV && ty.args[0] >= 0;
     r.args = has_block ? (uint64_t)(uintptr_t)ta[(size_t)t.type * ETXB_MAX_ARGS] + (uint64_t)ty.cst[0] + (uint64_t)t.coord[1] * (uint64_t)ty.cst[1]
                        : (uint64_t)(uintptr_t)s->d_pool;
     r.stream_word = ty.stream_word;
+    if (s->n_ranks > 1 && ty.exchange) {
+      int32_t rc = exchange_rows(s, ty, t, &r.mirror);
+      if (rc) return rc;
+    }
   }
   if (!s->d_recs) CU(cudaMalloc((void**)&s->d_recs, recs.size() * sizeof(etxb_rec) + 96));
   CU(cudaMemcpy(s->d_recs, recs.data(), recs.size() * sizeof(etxb_rec), cudaMemcpyHostToDevice));
@@ -360,6 +476,8 @@ static void fill_params(etxb_session* s, etxb_params& p) {
   p.ctrl = s->d_ctrl; p.trace = s->trace ? s->d_trace : nullptr; p.exec_count = s->trace ? s->d_exec : nullptr;
   p.step_dev = nullptr; p.timeout_ns = s->timeout_ns; p.epoch = s->epoch; p.n_workers = (int32_t)s->h.n_workers;
   p.step = s->step;
+  p.n_peers = s->n_ranks - 1; p.pad = 0; p.xbase = s->xbase;
+  for (int q = 0; q < ETXB_MAX_PEERS; ++q) p.xpeer[q] = s->xpeer[q];
 }
 
 static int32_t launch_kernel(const etxb_params& p, int grid, cudaStream_t st, int variant = 0) {
@@ -378,7 +496,7 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   etxb_params p;
   fill_params(s, p);
   CU(cudaEventRecord(s->ev0, s->stream));
-  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full || s->n_ranks > 1) ? 0 : s->variant);
   if (rc) return rc;
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
@@ -394,6 +512,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaSetDevice(s->device));
   if (s->args_dirty) { int32_t rc = upload_type_args(s); if (rc) return rc; }
   if (!s->grid_order_ok) return fail(ETXB_E_UNSUPPORTED, "a grid waits for a grid that comes later in the plan: no launch-per-grid order");
+  if (s->n_ranks > 1) return fail(ETXB_E_UNSUPPORTED, "a sharded model runs as the single launch only");
   s->stream = cuda_stream ? (cudaStream_t)cuda_stream : s->own_stream;
   if (s->trace && s->d_exec) CU(cudaMemsetAsync(s->d_exec, 0, (size_t)s->h.n_tasks * 4, s->stream));
   ++s->epoch;
@@ -403,7 +522,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   for (uint32_t t = 0; t < s->h.n_types; ++t) {
     p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
-    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full || s->n_ranks > 1) ? 0 : s->variant);
     if (rc) return rc;
   }
   CU(cudaEventRecord(s->ev1, s->stream));
@@ -421,7 +540,7 @@ static int32_t read_ctrl(etxb_session* s) {
 // step starts clean (the reference forces a full host reset after a failed step, host.h:388).
 static int32_t recover(etxb_session* s) {
   std::vector<int32_t> ev((size_t)s->h.n_events * ETXB_EV_STRIDE, 0);
-  for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount[e]);
+  for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount_eff[e]);
   if (!ev.empty()) CU(cudaMemcpy(s->d_events, ev.data(), ev.size() * 4, cudaMemcpyHostToDevice));
   CU(cudaMemset(s->d_ctrl, 0, 64));
   return ETXB_OK;
@@ -475,7 +594,7 @@ extern "C" int32_t etxb_status(etxb_session* s, etxb_status_t* out) {
   out->ctrl = s->h_ctrl ? s->h_ctrl[0] : 0; out->stuck_task = s->h_ctrl && s->h_ctrl[0] ? s->h_ctrl[1] : -1;
   out->stuck_event = s->h_ctrl[2]; out->stuck_value = s->h_ctrl[3]; out->stuck_target = s->h_ctrl[4];
   out->tasks_run = 0; out->epoch = s->epoch; out->last_ms = s->last_ms;
-  out->kernel_variant = s->force_full ? 0 : s->variant;
+  out->kernel_variant = (s->force_full || s->n_ranks > 1) ? 0 : s->variant;
   if (s->trace && s->d_exec) {
     std::vector<int32_t> ex(s->h.n_tasks);
     CU(cudaSetDevice(s->device));

@@ -30,6 +30,7 @@
 #define ETXB_CTX_SLOTS 4
 #define ETXB_SMEM_BYTES (ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512 + ETXB_CTX_SLOTS * ETXB_CTX_BYTES)
 #define ETXB_ATTN_PART 32            // KV positions per attention task
+#define ETXB_MAX_PEERS 7           // ranks of a sharded model besides this one
 #define ETXB_MAX_NB 8                // activation columns of the stand-alone batched GEMV kernel
 
 // ---- plan blob ------------------------------------------------------------------------------------------------
@@ -57,7 +58,9 @@ struct etxb_type {
   int32_t flags;                // bit0: the tile streams weights through the ring
   int32_t stream_word;          // event the producer warp waits for before it reads the weight addresses of a task:
                                 // -1 none (static weights: stream ahead freely), -2 the task's own in-events, >= 0 that event
-  int32_t pad;
+  int32_t exchange;             // 1: a row-parallel GEMV / MoE-down grid of a sharded model -- every rank runs the same grid on its
+                                // shard and the rows a task wrote are copied into every peer's exchange region, its arrivals
+                                // delivered to every peer's counters too (etxb_set_exchange); 0 otherwise
 };
 
 struct etxb_task {
@@ -74,7 +77,9 @@ struct etxb_rec {
   int32_t body, c0, c1, id, in_n, out_n, in_off, out_off;
   int32_t in_word[4], in_cnt[4], out_word[4];      // the first four of each list; longer lists continue in inwords / outwords
   uint64_t args;                                   // device address of the task's argument block
-  int32_t stream_word, pad;
+  int32_t stream_word;
+  uint32_t mirror;                                 // exchanged task: bits 0..19 first bf16 element (from the exchange region's base),
+                                                   // bits 20..31 element count of the rows it wrote; 0 = nothing to copy to the peers
 };
 
 // ---- step parameters (the reference's VlParams, examples/vllm_llm/vl_tiles.hip:13-24) ---------------------------
@@ -103,6 +108,11 @@ struct etxb_params {
   uint32_t epoch;
   int32_t n_workers;
   etxb_stepv step;
+  // sharded model (etxb_set_exchange): the other ranks' exchange regions as mapped into this process.  A region starts
+  // with that rank's event counters (same indices as `events`), the exchanged rows follow at the same offsets on every rank.
+  int32_t n_peers, pad;
+  unsigned char* xbase;                            // this rank's region (events == (int32_t*)xbase)
+  unsigned char* xpeer[ETXB_MAX_PEERS];
 };
 
 // ctrl[0] bits

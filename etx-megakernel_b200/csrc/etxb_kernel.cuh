@@ -246,7 +246,8 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
         int word, cnt;
         if (i < 4) { word = c->r.in_word[i]; cnt = c->r.in_cnt[i]; }
         else { word = p.inwords[c->r.in_off + i]; cnt = p.evcount[word]; }
-        ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
+        if (GQV == 0 && p.n_peers > 0) ok = wait_event_sys(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
+        else ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
       }
       if (!ok) s_stop = 1;
       if (p.trace) p.trace[8 * (size_t)c->r.id + 1] = globaltimer();
@@ -258,12 +259,27 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     run_body<GQV>(p, c, cur, sm, n);
     if (fetcher) cp_async_wait_all();
     csync();                                                       // every consumer thread's stores are issued, the next contexts landed
+    // Sharded model: copy the bf16 rows this task wrote into every peer's exchange region (plain stores over NVLink),
+    // so that each rank's next norm fold finds all ranks' partial rows in its own memory.  The condition is the same
+    // for every consumer thread (it must not read s_stop: thread 0 may already be past this point of the next task).
+    const uint32_t mirror = GQV == 0 && p.n_peers > 0 ? c->r.mirror : 0u;
+    if (mirror != 0u) {
+      const uint32_t off = mirror & 0xfffffu, len = mirror >> 20;
+      const unsigned short* src = (const unsigned short*)p.xbase + off;
+      for (uint32_t i = threadIdx.x; i < len; i += ETXB_CONSUMERS) {
+        const unsigned short v = __ldcg(src + i);
+        for (int q = 0; q < p.n_peers; ++q) ((unsigned short*)p.xpeer[q])[off + i] = v;
+      }
+      csync();
+    }
     if (threadIdx.x == 0) {
       const int out_n = c->r.out_n, id = c->r.id;
       if (s_stop == 0)                                             // (set when a stage wait gave up inside the body: no arrivals then)
         for (int i = 0; i < out_n; ++i) {                          // release: orders the CTA's stores (seen through the barrier) before the count
           const int word = i < 4 ? c->r.out_word[i] : p.outwords[c->r.out_off + i];
           red_release_add(p.events + (size_t)word * ETXB_EV_STRIDE, 1);
+          if (mirror != 0u)                                        // and the peers' counters: release at system scope covers the copies above
+            for (int q = 0; q < p.n_peers; ++q) red_release_sys_add((int32_t*)p.xpeer[q] + (size_t)word * ETXB_EV_STRIDE, 1);
         }
       if (p.trace) { p.trace[8 * (size_t)id + 2] = globaltimer(); p.trace[8 * (size_t)id + 3] = blockIdx.x; }
       if (p.exec_count) atomicAdd(p.exec_count + id, 1);

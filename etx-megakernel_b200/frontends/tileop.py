@@ -15,9 +15,10 @@ def hip_link(source, symbol, prefetch=None, pre_wait=None, touch=None, coherence
                     coherence=coherence, arg_bytes=arg_bytes, coherence_caps=tuple(coherence_caps))
 
 
-def cuda_link(source, symbol, prefetch=None, stream_after=None):
-    """`stream_after`: see TileBody.stream_after ("" = static weights, an event name, or None = the task's in-events)."""
-    return TileBody(kind="cuda_link", symbol=symbol, source=source, prefetch=prefetch, stream_after=stream_after)
+def cuda_link(source, symbol, prefetch=None, stream_after=None, exchange=False):
+    """`stream_after`: see TileBody.stream_after ("" = static weights, an event name, or None = the task's in-events);
+    `exchange`: TileBody.exchange (a row-parallel grid of a sharded model)."""
+    return TileBody(kind="cuda_link", symbol=symbol, source=source, prefetch=prefetch, stream_after=stream_after, exchange=bool(exchange))
 
 
 def triton_fn(module, name):

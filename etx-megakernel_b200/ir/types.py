@@ -85,6 +85,8 @@ class TileBody:
     stream_after: str | None = None    # B200 backend: what the tile's WEIGHT ADDRESSES depend on -- "" nothing (static weights:
                                        # the producer warp streams them ahead of the task's events), an event name (a
                                        # single-counter event, e.g. the router's for expert weights), None = the task's in-events
+    exchange: bool = False             # B200 backend, sharded model: a row-parallel grid whose partial rows and arrivals also go
+                                       # to the other ranks (see runtime.Session.set_exchange)
 
 
 @dataclass

@@ -11,9 +11,10 @@ import torch
 
 from ..machine import load_machine
 from ..passes import PassOptions, compile_graph
-from ..runtime import Session
+from ..runtime import ExchangeRegion, Session
 from . import qwen as Q
 
+XROWS_OFF = 1 << 20        # byte offset of the exchanged rows in a rank's exchange region (the counters come first)
 _DT = {"bf16": torch.bfloat16, "f32": torch.float32, "i32": torch.int32, "i64": torch.int64}
 
 
@@ -44,8 +45,11 @@ def to_device_weights(packed: dict, device) -> dict:
 
 class DecodeProgram:
     def __init__(self, dims: Q.Dims, weights: dict, device: int = 0, maxlen: int = 1072, steps: int | None = None, machine="b200",
-                 fold_topk: bool = True, fused_attn: bool | str = True, workers: int | None = None):
+                 fold_topk: bool = True, fused_attn: bool | str = True, workers: int | None = None, ranks: int = 1, rank: int = 0):
+        """ranks > 1: rank `rank` of a model sharded `ranks` ways -- `dims` and `weights` are the rank's shard
+        (Q.shard_dims / Q.shard_weights); call connect() with every rank's `region.handle` before the first step."""
         self.d, self.maxlen = dims, maxlen
+        self.ranks, self.rank, self.region, self.xaddr = ranks, rank, None, {}
         self.dev = torch.device("cuda", device)
         self.machine = load_machine(machine) if isinstance(machine, str) else machine
         self.steps = steps or maxlen
@@ -59,19 +63,37 @@ class DecodeProgram:
         self.buf["block_tables"].copy_(torch.arange(self.buf["block_tables"].numel(), dtype=torch.int32))
         self.vl = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
+        if ranks > 1:
+            # exchange region: 1 MiB reserved for the event counters, then the [ranks][H] blocks of o_proj and down rows
+            self.region = ExchangeRegion(2 << 20, device)
+            self.xaddr = {"o": self.region.ptr + XROWS_OFF, "moe_out": self.region.ptr + XROWS_OFF + ranks * dims.H * 2}
+            if XROWS_OFF + 2 * ranks * dims.H * 2 > self.region.nbytes:
+                raise ValueError("hidden size too large for the exchange region")
+
         def ptr(name):
+            if name in self.xaddr:
+                return self.xaddr[name]
             t = self.buf.get(name)
             if t is None:
                 t = self.w[name]
             return t.data_ptr()
-        self.graph, self.pool, self.sizing = Q.build_graph(dims, ptr, maxlen, self.machine, fold_topk=fold_topk, fused_attn=fused_attn)
+        self.graph, self.pool, self.sizing = Q.build_graph(dims, ptr, maxlen, self.machine, fold_topk=fold_topk, fused_attn=fused_attn,
+                                                              ranks=ranks, rank=rank)
         pool = self.pool.bytes()
         self.plan = compile_graph(self.graph, self.machine, {"POOL": len(pool)}, options=PassOptions(workers=workers))
+        if ranks > 1 and self.plan.event_words * 128 > XROWS_OFF:
+            raise ValueError("too many events for the exchange region's counter area")
         self.session = Session(self.plan, {"vl": self.vl}, pool, device)
         b = self.buf
         self.session.set_step(tok=0, pos=0, write_next=0, H=dims.H, V=dims.V, nrep=1, embed=self.w["embed"], resid=b["resid"],
                               positions=b["positions"], seq_lens=b["seq_lens"], slot_mapping=b["slot_mapping"], logits=b["logits"],
                               token_in=b["token_in"], token_out=b["token_out"], token_time=b["token_time"])
+
+    def connect(self, handles: list):
+        """handles[r] = rank r's `region.handle` (all-gathered by the caller).  After this, and a barrier so that no
+        rank steps before every rank is connected, the ranks step in lock step."""
+        self.region.connect(self.rank, handles)
+        self.session.set_exchange(self.rank, self.ranks, self.region)
 
     # ---- KV cache helpers (contiguous [ctx][NKV][HD] <-> the paged layout)
     def load_kv(self, layer: int, K: np.ndarray, V: np.ndarray):
@@ -133,4 +155,9 @@ class DecodeProgram:
         return toks[len(prompt) - 1:], ms
 
     def close(self):
+        """Sharded: every rank must have finished its last step (synchronise, then a barrier) before any rank closes --
+        a running peer still stores into this rank's region."""
         self.session.close()
+        if self.region is not None:
+            self.region.close()
+            self.region = None

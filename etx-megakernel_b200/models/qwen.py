@@ -123,6 +123,50 @@ def rope_table(theta: float, hd: int, maxlen: int) -> np.ndarray:
     return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
 
 
+# ------------------------------------------------------------------------------------------------ sharding
+def shard_dims(d: Dims, ranks: int) -> Dims:
+    """The model one of `ranks` tensor-parallel ranks runs: its share of the q and kv heads and of the MLP (or of every
+    expert's) intermediate rows; hidden size, vocabulary, experts and router stay whole."""
+    from dataclasses import replace
+    if ranks == 1:
+        return d
+    mi = d.MI if d.moe else d.INTER
+    if d.NH % ranks or d.NKV % ranks or mi % ranks or (mi // ranks) % 8:
+        raise ValueError(f"{d.name}: {d.NH} q heads / {d.NKV} kv heads / {mi} intermediate rows do not split {ranks} ways")
+    return replace(d, name=f"{d.name}/tp{ranks}", NH=d.NH // ranks, NKV=d.NKV // ranks, MI=d.MI // ranks if d.moe else d.MI,
+                   INTER=d.INTER if d.moe else d.INTER // ranks)
+
+
+def shard_weights(w: dict, d: Dims, ranks: int, rank: int) -> dict:
+    """Packed weights of the whole model `d` (weight_shapes) -> those of rank `rank` of shard_dims(d, ranks): q / k / v rows
+    and gate / up rows by columns of the output (column-parallel), o_proj and down by columns of the input
+    (row-parallel), everything else replicated.  Works on numpy arrays and torch tensors alike."""
+    if ranks == 1:
+        return dict(w)
+    cat = (lambda xs, axis: np.concatenate(xs, axis)) if isinstance(w["embed"], np.ndarray) else \
+        (lambda xs, axis: __import__("torch").cat(xs, axis))
+    cont = (lambda a: np.ascontiguousarray(a)) if isinstance(w["embed"], np.ndarray) else (lambda a: a.contiguous())
+    nq, nk = d.NH * d.HD, d.NKV * d.HD
+    ql, kl = nq // ranks, nk // ranks
+    mi = d.MI if d.moe else d.INTER
+    ml = mi // ranks
+    out = {}
+    for name, a in w.items():
+        kind = name.rsplit(".", 1)[-1]
+        if kind in ("wqkv", "bqkv"):
+            a = cat([a[rank * ql:(rank + 1) * ql], a[nq + rank * kl:nq + (rank + 1) * kl], a[nq + nk + rank * kl:nq + nk + (rank + 1) * kl]], 0)
+        elif kind == "wo":
+            a = cont(a[:, rank * ql:(rank + 1) * ql])
+        elif kind == "w13":
+            a = cat([a[:, rank * ml:(rank + 1) * ml], a[:, mi + rank * ml:mi + (rank + 1) * ml]], 1)
+        elif kind == "wgu":
+            a = cat([a[rank * ml:(rank + 1) * ml], a[mi + rank * ml:mi + (rank + 1) * ml]], 0)
+        elif kind in ("w2", "wd"):
+            a = cont(a[..., rank * ml:(rank + 1) * ml])
+        out[name] = a
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ sizing
 @dataclass
 class Sizing:
@@ -286,8 +330,13 @@ class ArgPool:
 
 
 def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = "b200", *, fold_topk: bool = True,
-                fused_attn: bool | str = True):
+                fused_attn: bool | str = True, ranks: int = 1, rank: int = 0):
     """The decode step of `d` as a Graph plus its argument pool.
+
+    ranks > 1: the step of ONE rank of a model sharded `ranks` ways (`d` = shard_dims(full, ranks): its share of the
+    heads and of the MLP / expert rows).  ptr("o") and ptr("moe_out") then name [ranks][H] row blocks inside the rank's
+    exchange region: the row-parallel grids (o_proj, down) write row `rank` and are marked `exchange`, the norm folds
+    that follow add all `ranks` rows in rank order.
 
     ptr(name) -> device address (int) of a buffer (buffer_shapes) or packed weight (weight_shapes); "kc" / "vc" are the
     whole [L, ...] caches (layer slices are addressed by offset here).  Returns (graph, pool: ArgPool, sizing)."""
@@ -311,15 +360,19 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
     scale = float(np.float32(1.0 / np.sqrt(d.HD)))
     hf_mode = op_gemv.MODE_BF16_WTS
 
-    def tile(symbol, stream_after=None):
-        return cuda_link(SRC, symbol, stream_after=stream_after)
+    if not (1 <= ranks <= 8 and 0 <= rank < ranks):
+        raise ValueError("1 <= ranks <= 8 and 0 <= rank < ranks")
+    xrow = rank * d.H * 2                                                   # this rank's row of an exchanged [ranks][H] block
 
-    def add(name, export, role, layer, blob, tasks, grid, in_ev, in_map, out_ev, out_map, out_shape, out_count, M=0, K=0, after=None):
+    def tile(symbol, stream_after=None, exchange=False):
+        return cuda_link(SRC, symbol, stream_after=stream_after, exchange=exchange)
+
+    def add(name, export, role, layer, blob, tasks, grid, in_ev, in_map, out_ev, out_map, out_shape, out_count, M=0, K=0, after=None, exchange=False):
         off = pool.add(blob)
         pool.rows.append((name, export, role, layer, off, tasks, M, K))
         g.etensor(out_ev, out_shape, wait_count=out_count)
         slots = (d.TOPK if role in ("moe_up", "moe_down") else 1) * (2 if role in ("moe_up", "gate_up") else 1)
-        g.call_device(name, grid, tile("etx_tile_" + export, after), resource=res, args=["impargs"], consts=(off,),
+        g.call_device(name, grid, tile("etx_tile_" + export, after, exchange and ranks > 1), resource=res, args=["impargs"], consts=(off,),
                       in_edges={in_ev: in_map}, out_edges={out_ev: out_map},
                       duration_us=round(m.tile_duration_us(role, 2.0 * slots * M * K / max(1, tasks)), 2))
         return out_ev
@@ -337,7 +390,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         first = L == 0
         blob = gemv_block("dsl_gemv_fold", t, W=W("wqkv"), x=ptr("hn"), out=ptr("qkv"), M=d.NQKV, K=d.H, rpt=rpt, tpe=1,
                           rows=0 if first else ptr("moe_out"), resid_in=ptr("resid") if first else ptr("resid2"),
-                          resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else 1, eps=d.eps,
+                          resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else ranks, eps=d.eps,
                           ids=0, wts=W("bqkv") if d.bias else 0,
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0), nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
@@ -374,13 +427,13 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
 
         # ---- o_proj
         t, rpt = sz.o
-        blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1)
-        prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD, after="")
+        blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o") + xrow, M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1)
+        prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD, after="", exchange=True)
         if d.moe:
             # ---- router with the post-attention norm fold: task 0 stores resid2 and the normed vector
             t, rpt = sz.router
             blob = gemv_block("dsl_gemv_fold", t, W=W("wr"), x=ptr("o_norm"), out=ptr("rlog"), M=d.E, K=d.H, rpt=rpt, tpe=1, rows=ptr("o"),
-                              resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=1, eps=d.eps, mode=op_gemv.MODE_NORM, nb=1)
+                              resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps, mode=op_gemv.MODE_NORM, nb=1)
             prev = add(f"router_{L}", "dsl_gemv_fold", "router", L, blob, t, (t,), prev, "i->(0)", f"E_rt_{L}", "i->(0)", (1,), t, d.E, d.H, after="")
             topk_mode = (op_gemv.MODE_TOPK_RENORM if d.norm_topk else op_gemv.MODE_TOPK) | hf_mode
             if not fold_topk:
@@ -400,27 +453,27 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                        prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), groups * tpe, d.MI, d.H)
             tpe, rpt = sz.down
             dn_export = "dsl_moe_down_fold" if fold_topk else "dsl_moe_down"
-            blob = gemv_block(dn_export, tpe, W=W("w2"), x=ptr("mc2"), out=ptr("moe_out"), ids=ptr("ti"), wts=ptr("tw"),
+            blob = gemv_block(dn_export, tpe, W=W("w2"), x=ptr("mc2"), out=ptr("moe_out") + xrow, ids=ptr("ti"), wts=ptr("tw"),
                               estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps,
                               mode=(topk_mode | op_gemv.MODE_ROUTE_READY if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS, E=d.E, logits=ptr("rlog"), nb=1)
             # expert weights depend on the routing only: with the top-k folded in, the stream may start once the router is done
             prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, tpe, (tpe,), prev, "i->(0)",
-                       f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None)
+                       f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None, exchange=True)
         else:
             # ---- dense SwiGLU: gate+up with the post-attention norm fold, then down
             spt, tpe, rpt = sz.up
             blob = gemv_block("dsl_moe_up", tpe, W=W("wgu"), x=ptr("o_norm"), out=ptr("mc2"), estride=0, M=d.INTER, K=d.H, rpt=rpt, tpe=tpe,
-                              rows=ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=1, eps=d.eps,
+                              rows=ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps,
                               mode=op_gemv.MODE_NORM, nb=1)
             prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H, after="")
             tpe, rpt = sz.down
-            blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("moe_out"), estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
+            blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("moe_out") + xrow, estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
                               eps=d.eps, nb=1)
-            prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="")
+            prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="", exchange=True)
     # ---- lm_head with the final-norm fold, then greedy sampling
     t, rpt = sz.lm
     blob = gemv_block("dsl_gemv_fold", t, W=ptr("embed") if d.tie else ptr("lm_head"), x=ptr("hn"), out=ptr("logits"), M=d.V, K=d.H, rpt=rpt,
-                      tpe=1, rows=ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=1, eps=d.eps,
+                      tpe=1, rows=ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=ranks, eps=d.eps,
                       ids=0, mode=op_gemv.MODE_NORM, nb=1)
     prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)

@@ -164,7 +164,7 @@ class Plan:
                 if not any(after in self.graph.grid(p.grid).out_edges for p in self.tasks if p.id < self.task_index[(gname, self.inst.tasks[gname][0])]):
                     raise ValueError(f"grid {gname!r}: stream_after={after!r} is not produced before it")
                 sword = self.events[after].offset
-            types += struct.pack("<i4i4iiii", body, *cst, *idx, 1 if 3 <= body <= 5 else 0, sword, 0)
+            types += struct.pack("<i4i4iiii", body, *cst, *idx, 1 if 3 <= body <= 5 else 0, sword, 1 if g.body.exchange else 0)
         W = self.workers_per_device()
         qbegin, rows, inw, outw = [0], [], [], []
         for w in range(W):

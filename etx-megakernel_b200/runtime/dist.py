@@ -21,3 +21,28 @@ def slowest(values, dist=None, device=None):
 def replica_metric(step_ms: float, world: int) -> dict:
     """Whole-job figures of `world` replicas that each decode one sequence: every step yields `world` tokens."""
     return {"ms_per_token": step_ms / world, "tokens_per_s": 1000.0 * world / step_ms}
+
+
+def gather_handles(handle: bytes, dist) -> list:
+    """Every rank's exchange-region handle, in rank order (the handles are plain bytes: any transport will do; this one
+    is the process group the ranks already share)."""
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, bytes(handle))
+    return out
+
+
+def connect_ranks(program, dist):
+    """Sharded DecodeProgram: exchange the region handles, map the peers, and hold every rank until all are connected
+    (no rank may step before its peers' counters are in place)."""
+    program.connect(gather_handles(program.region.handle, dist))
+    dist.barrier()
+
+
+def close_ranks(program, dist):
+    """Close a sharded program: wait for this rank's last kernel, then for every rank's, and only then unmap and free
+    (a peer that is still running stores into this rank's region)."""
+    import torch
+    torch.cuda.synchronize(program.dev)
+    dist.barrier()
+    program.close()
+    dist.barrier()

@@ -26,7 +26,9 @@ BODY = {"nop": 0, "prologue": 1, "argmax": 2, "gemv": 3, "moe_up": 4, "moe_down"
 # every symbol include/etxb200.h declares
 SYMBOLS = ["etxb_version", "etxb_last_error", "etxb_device_info", "etxb_create", "etxb_bind", "etxb_set_step", "etxb_set_option",
            "etxb_launch", "etxb_launch_unfused", "etxb_wait", "etxb_step", "etxb_status", "etxb_trace", "etxb_exec_counts", "etxb_destroy",
-           "etxb_decode_host", "etxb_op_launch", "etxb_attn_fused_static"]
+           "etxb_decode_host", "etxb_op_launch", "etxb_attn_fused_static", "etxb_exchange_alloc", "etxb_exchange_free", "etxb_exchange_open",
+           "etxb_exchange_close", "etxb_set_exchange"]
+IPC_HANDLE_BYTES = 64
 
 
 class EtxbError(RuntimeError):
@@ -98,6 +100,9 @@ def load():
         "etxb_trace": [vp, vp, sz], "etxb_exec_counts": [vp, vp, sz], "etxb_destroy": [vp],
         "etxb_decode_host": [vp, vp, i32, i32, i32, vp, vp], "etxb_op_launch": [C.c_int, i32, vp, sz, i32, C.POINTER(StepParams), vp],
         "etxb_attn_fused_static": [C.c_int, vp, sz, vp],
+        "etxb_exchange_alloc": [C.c_int, sz, C.POINTER(vp), vp], "etxb_exchange_free": [C.c_int, vp],
+        "etxb_exchange_open": [C.c_int, vp, C.POINTER(vp)], "etxb_exchange_close": [C.c_int, vp],
+        "etxb_set_exchange": [vp, i32, i32, vp, sz, C.POINTER(vp)],
     }
     for name, args in proto.items():
         fn = getattr(lib, name)

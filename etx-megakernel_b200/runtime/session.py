@@ -50,6 +50,13 @@ class Session:
             setattr(self.step_params, k, v)
         L.check(self.lib.etxb_set_step(self._h, C.byref(self.step_params)))
 
+    def set_exchange(self, rank: int, n_ranks: int, region: "ExchangeRegion"):
+        """Make this session rank `rank` of a model sharded over `n_ranks` processes: counters move into `region`, the
+        grids the graph marks `exchange=True` deliver their rows and arrivals to every peer (region.connect first)."""
+        bases = (C.c_void_p * n_ranks)(*[region.peers.get(r, 0) or None for r in range(n_ranks)])
+        L.check(self.lib.etxb_set_exchange(self._h, rank, n_ranks, C.c_void_p(region.ptr), region.nbytes, bases))
+        self._keep["__exchange__"] = region
+
     def launch(self, stream: int | None = None):
         L.check(self.lib.etxb_launch(self._h, C.c_void_p(stream or 0)))
 
@@ -103,3 +110,35 @@ def attn_fused_static(argblock: bytes, device: int = 0, stream: int | None = Non
     """The fused attention phase through the entry point that allocates nothing (scratch in a static device array of the
     library: NH <= 64, max_parts <= 64, HD <= 128).  `argblock`: an attn_fused block; its scratch pointers are ignored."""
     L.check(L.load().etxb_attn_fused_static(device, argblock, len(argblock), C.c_void_p(stream or 0)))
+
+
+class ExchangeRegion:
+    """One rank's exchange region of a sharded model: a device allocation of the library's ([event counters][rows]) with
+    its 64-byte inter-process handle, and the mappings of the peers' regions once `connect` opened their handles."""
+
+    def __init__(self, nbytes: int, device: int = 0):
+        self.device, self.nbytes = device, int(nbytes)
+        p, h = C.c_void_p(), (C.c_ubyte * L.IPC_HANDLE_BYTES)()
+        L.check(L.load().etxb_exchange_alloc(device, self.nbytes, C.byref(p), C.cast(h, C.c_void_p)))
+        self.ptr, self.handle = int(p.value), bytes(h)
+        self.peers = {}
+
+    def connect(self, rank: int, handles: list):
+        """handles[r]: rank r's handle (entry `rank` is this region's own and is not opened)."""
+        for r, h in enumerate(handles):
+            if r == rank or r in self.peers:
+                continue
+            if len(h) != L.IPC_HANDLE_BYTES:
+                raise ValueError(f"rank {r}: a handle is {L.IPC_HANDLE_BYTES} bytes")
+            p = C.c_void_p()
+            L.check(L.load().etxb_exchange_open(self.device, h, C.byref(p)))
+            self.peers[r] = int(p.value)
+
+    def close(self):
+        lib = L.load()
+        for p in self.peers.values():
+            lib.etxb_exchange_close(self.device, C.c_void_p(p))
+        self.peers = {}
+        if self.ptr:
+            lib.etxb_exchange_free(self.device, C.c_void_p(self.ptr))
+            self.ptr = 0

@@ -119,8 +119,32 @@ int32_t etxb_launch(etxb_session* s, void* cuda_stream);
  * refused (ETXB_E_UNSUPPORTED) when a grid waits for a grid that comes later in the plan. */
 int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream);
 int32_t etxb_wait(etxb_session* s, double timeout_s);
+
 int32_t etxb_step(etxb_session* s, void* cuda_stream, double timeout_s);
 int32_t etxb_status(etxb_session* s, etxb_status_t* out);
+
+/* ---- sharded model: one rank (process + GPU) per shard, partial rows exchanged inside the kernel ------------------
+ * The reference shards a program over devices with device-scoped events and multi-device plans
+ * (etx/passes/plan.py:58-86 device_of_task, etx/runtime/include/etx/host.h:79-210 one event region per device); here
+ * every rank runs the SAME single-device plan on its shard of the weights and the ranks meet at the row-parallel grids
+ * the plan marks as exchanged (o_proj, MoE / MLP down): a task of such a grid copies the bf16 rows it wrote into every
+ * peer's exchange region (plain stores to peer memory over NVLink) and arrives on every peer's counters with a
+ * system-scope release; the consumers (the next norm fold, with R = n_ranks rows) then wait for n_ranks times the
+ * arrivals and add the ranks' rows in rank order, so every rank computes bit-identical hidden states.
+ *
+ * A region is one device allocation: [event counters, 128 bytes per plan event][the exchanged rows, at offsets the
+ * caller chooses -- the same on every rank].  etxb_exchange_alloc zeroes it and exports a 64-byte inter-process handle;
+ * the caller passes the handles around (any transport) and opens the peers' with etxb_exchange_open.
+ * etxb_set_exchange (once, before the first step) moves the session's counters to the start of `local_base`, records
+ * the peers' mappings (peer_bases[r] for r != rank; entry `rank` is ignored) and selects the full kernel.  All ranks
+ * must run the same steps; a rank whose peers stop arriving returns ETXB_E_TIMEOUT at its deadline, after which the
+ * sessions of all ranks must be recreated.  etxb_launch_unfused is refused on a sharded session. */
+#define ETXB_IPC_HANDLE_BYTES 64
+int32_t etxb_exchange_alloc(int device, size_t bytes, void** dev_ptr, unsigned char* handle /*[64]*/);
+int32_t etxb_exchange_free(int device, void* dev_ptr);
+int32_t etxb_exchange_open(int device, const unsigned char* handle /*[64]*/, void** peer_ptr);
+int32_t etxb_exchange_close(int device, void* peer_ptr);
+int32_t etxb_set_exchange(etxb_session* s, int32_t rank, int32_t n_ranks, void* local_base, size_t bytes, void* const* peer_bases);
 /* Copies 8 x uint64 per task of the last traced step: {taken, deps ready, body done, worker, 4 in-body marks}
  * (globaltimer ns; a mark a tile did not set is 0). */
 int32_t etxb_trace(etxb_session* s, void* host_buf, size_t bytes);

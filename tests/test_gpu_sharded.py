@@ -1,0 +1,139 @@
+"""The sharded (tensor-parallel) decode step on the GPU.
+
+One GPU: a rank whose "peer" is its own exchange region (its rows and arrivals loop back to itself) must reproduce, bit
+for bit, the same shard run as an ordinary single-rank program -- that covers the system-scope waits, the row copies,
+the peer arrivals and the doubled counts inside ONE launch.  Two GPUs (skipped with fewer): two processes, one shard
+each, against the whole model on one GPU and the oracle's tokens."""
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import etx_megakernel_b200  # noqa: E402,F401
+from etx_megakernel_b200.models import decode as D  # noqa: E402
+from etx_megakernel_b200.models import qwen as Q  # noqa: E402
+from etx_megakernel_b200.runtime import EtxbError, ExchangeRegion  # noqa: E402
+from oracle import ref_decode as O  # noqa: E402
+from tests.golden.cases import SMALL_DENSE, SMALL_MOE  # noqa: E402
+
+FIELDS = ("name", "H", "NH", "NKV", "HD", "INTER", "L", "V", "eps", "theta", "tie", "bias", "qk_norm", "moe", "E", "TOPK", "MI", "norm_topk")
+MAXLEN, N_PROMPT, N_GEN = 64, 6, 20
+
+
+def qdims(od):
+    return Q.Dims(**{f: getattr(od, f) for f in FIELDS})
+
+
+def shard_on(od, ranks, rank, device, seed=1):
+    d = qdims(od)
+    full = Q.pack_hf(d, O.SyntheticWeights(od, seed=seed, gamma="ones").get, MAXLEN)
+    return Q.shard_dims(d, ranks), D.to_device_weights(Q.shard_weights(full, d, ranks, rank), f"cuda:{device}")
+
+
+def prompt_of(od):
+    return np.random.default_rng(7).integers(0, od.V, N_PROMPT)
+
+
+@pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
+def test_rank_looped_back_to_itself_equals_the_plain_program(od):
+    sd, w = shard_on(od, 2, 0, 0)
+    plain = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN)
+    want = plain.generate(prompt_of(od), N_GEN)
+    want_logits = plain.read("logits")
+    plain.close()
+    prog = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN, ranks=2, rank=0)
+    prog.region.peers[1] = prog.region.ptr                     # the peer is this rank's own region
+    prog.session.set_exchange(0, 2, prog.region)
+    prog.region.peers = {}                                     # (nothing was opened: nothing to close)
+    got = prog.generate(prompt_of(od), N_GEN)
+    assert prog.session.status().kernel_variant == 0           # a sharded session runs the full kernel
+    assert got.tolist() == want.tolist()
+    assert np.array_equal(prog.read("logits"), want_logits)
+    with pytest.raises(EtxbError):
+        prog.session.launch_unfused()
+    prog.close()
+
+
+def test_exchange_region_and_argument_checks():
+    reg = ExchangeRegion(4096, 0)
+    assert reg.ptr % 256 == 0 and len(reg.handle) == 64 and any(reg.handle)
+    sd, w = shard_on(SMALL_MOE, 2, 0, 0)
+    unsharded = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN)
+    reg.peers[1] = reg.ptr
+    with pytest.raises(EtxbError, match="marks no grid"):
+        unsharded.session.set_exchange(0, 2, reg)              # the plan of a single-rank program exchanges nothing
+    unsharded.close()
+    prog = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN, ranks=2, rank=0)
+    with pytest.raises(EtxbError):
+        prog.session.set_exchange(0, 2, prog.region)           # no peer mapped yet
+    with pytest.raises(EtxbError):
+        prog.session.set_exchange(2, 2, prog.region)           # rank out of range
+    # an exchanged grid that writes outside the region is refused when the records are built (before any launch)
+    prog.region.peers[1] = prog.region.ptr
+    small = ExchangeRegion(4096, 0)
+    small.peers[1] = small.ptr
+    prog.session.set_exchange(0, 2, small)
+    with pytest.raises(EtxbError, match="outside the exchange region"):
+        prog.session.launch()
+    prog.region.peers, small.peers, reg.peers = {}, {}, {}
+    prog.close(); small.close(); reg.close()
+
+
+# ------------------------------------------------------------------------------------------------ two GPUs, two processes
+def _rank(rank, world, port, od_name, q):
+    import torch.distributed as dist
+    from etx_megakernel_b200.runtime import dist as RD
+    od = {"moe": SMALL_MOE, "dense": SMALL_DENSE}[od_name]
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(rank)
+    sd, w = shard_on(od, world, rank, rank)
+    prog = D.DecodeProgram(sd, w, device=rank, maxlen=MAXLEN, ranks=world, rank=rank)
+    prog.session.set_option("timeout_ms", 5000)
+    err = None
+    try:
+        RD.connect_ranks(prog, dist)
+        got = prog.generate(prompt_of(od), N_GEN)
+        q.put((rank, got.tolist(), prog.read("logits"), prog.read("resid")))
+    except Exception as e:                                     # report, then leave together
+        err = repr(e)
+        q.put((rank, err, None, None))
+    RD.close_ranks(prog, dist)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("od_name", ["moe", "dense"])
+def test_two_ranks_on_two_gpus_match_the_whole_model(od_name):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    od = {"moe": SMALL_MOE, "dense": SMALL_DENSE}[od_name]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank, args=(r, 2, 29641 + (od_name == "dense"), od_name, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted((q.get(timeout=300) for _ in procs), key=lambda t: t[0])
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    for rank, toks, logits, resid in out:
+        assert logits is not None, f"rank {rank}: {toks}"
+    # both ranks hold bit-identical hidden states and logits (same rows added in the same order)
+    assert out[0][1] == out[1][1]
+    assert np.array_equal(out[0][2], out[1][2]) and np.array_equal(out[0][3], out[1][3])
+    # against the whole model on one GPU: logits within the bf16 tolerance, tokens equal up to a near-tie
+    d = qdims(od)
+    W = O.SyntheticWeights(od, seed=1, gamma="ones")
+    whole = D.DecodeProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, MAXLEN), "cuda:0"), device=0, maxlen=MAXLEN)
+    want = whole.generate(prompt_of(od), N_GEN).tolist()
+    wl = whole.read("logits")
+    whole.close()
+    first = next((i for i, (a, b) in enumerate(zip(out[0][1], want)) if a != b), None)
+    if first is None:
+        assert np.abs(out[0][2] - wl).max() <= 2e-2 * np.abs(wl).max()
+    else:
+        assert first >= 4, f"sharded tokens {out[0][1]} leave the whole model's {want} at step {first}"

@@ -1,0 +1,132 @@
+"""Host side of the sharded (tensor-parallel) decode step, on CPU: the weight split recombines to the whole model's
+result, a rank's graph compiles and verifies as a single-device program with its exchanged grids flagged in the plan
+blob, and two gloo ranks pass their region handles around."""
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import etx_megakernel_b200  # noqa: F401
+from etx_megakernel_b200.models import qwen as Q
+from etx_megakernel_b200.passes import compile_graph
+from etx_megakernel_b200.passes.plan import verify_plan
+from etx_megakernel_b200.sim.protocol import simulate
+from oracle import ref_decode as O
+from tests.golden.cases import SMALL_DENSE, SMALL_MOE
+
+FIELDS = ("name", "H", "NH", "NKV", "HD", "INTER", "L", "V", "eps", "theta", "tie", "bias", "qk_norm", "moe", "E", "TOPK", "MI", "norm_topk")
+
+
+def qdims(od):
+    return Q.Dims(**{f: getattr(od, f) for f in FIELDS})
+
+
+def f32(u):
+    return (np.asarray(u).astype(np.uint32) << 16).view(np.float32)
+
+
+@pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
+def test_shards_recombine_to_the_whole_model(od):
+    d = qdims(od)
+    full = Q.pack_hf(d, O.SyntheticWeights(od, seed=3, gamma="ones").get, 64)
+    ranks = 2
+    sd = Q.shard_dims(d, ranks)
+    shards = [Q.shard_weights(full, d, ranks, r) for r in range(ranks)]
+    want = Q.weight_shapes(sd, 64)
+    for s in shards:
+        assert {k: tuple(v.shape) for k, v in s.items()} == {k: tuple(v) for k, v in want.items()}
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(d.H).astype(np.float32)
+    # column-parallel qkv: the ranks' rows are a permutation of the whole model's rows
+    qkv = f32(full["0.wqkv"]) @ x
+    nq, nk = d.NH * d.HD, d.NKV * d.HD
+    parts = [f32(s["0.wqkv"]) @ x for s in shards]
+    ql, kl = nq // ranks, nk // ranks
+    assert np.array_equal(np.concatenate([p[:ql] for p in parts]), qkv[:nq])
+    assert np.array_equal(np.concatenate([p[ql:ql + kl] for p in parts]), qkv[nq:nq + nk])
+    assert np.array_equal(np.concatenate([p[ql + kl:] for p in parts]), qkv[nq + nk:])
+    # row-parallel o_proj: the ranks' partial rows add up to the whole row
+    a = rng.standard_normal(nq).astype(np.float32)
+    o = f32(full["0.wo"]).astype(np.float64) @ a
+    o_parts = sum(f32(s["0.wo"]).astype(np.float64) @ a[r * ql:(r + 1) * ql] for r, s in enumerate(shards))
+    assert np.allclose(o, o_parts, rtol=1e-12, atol=1e-12)
+    # MLP / one expert: gate+up by rows, down by columns
+    if d.moe:
+        e = 5
+        w13, w2 = f32(full["0.w13"])[e].astype(np.float64), f32(full["0.w2"])[e].astype(np.float64)
+        s13 = [f32(s["0.w13"])[e].astype(np.float64) for s in shards]
+        s2 = [f32(s["0.w2"])[e].astype(np.float64) for s in shards]
+        mi = d.MI
+    else:
+        w13, w2 = f32(full["0.wgu"]).astype(np.float64), f32(full["0.wd"]).astype(np.float64)
+        s13 = [f32(s["0.wgu"]).astype(np.float64) for s in shards]
+        s2 = [f32(s["0.wd"]).astype(np.float64) for s in shards]
+        mi = d.INTER
+
+    def mlp(w13, w2, m):
+        g, u = w13[:m] @ x, w13[m:] @ x
+        return w2 @ (g / (1 + np.exp(-g)) * u)
+    assert np.allclose(mlp(w13, w2, mi), sum(mlp(a13, a2, mi // ranks) for a13, a2 in zip(s13, s2)), rtol=1e-10, atol=1e-12)
+
+
+def test_shard_dims_refuses_uneven_splits():
+    d = qdims(SMALL_MOE)
+    assert Q.shard_dims(d, 1) is d
+    with pytest.raises(ValueError):
+        Q.shard_dims(d, 4)                     # 2 kv heads do not split 4 ways
+
+
+@pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
+def test_rank_graph_is_a_valid_single_device_program_with_flagged_grids(od):
+    ranks, rank = 2, 1
+    sd = Q.shard_dims(qdims(od), ranks)
+    base = {"o": 1 << 30, "moe_out": (1 << 30) + ranks * sd.H * 2}
+    g, pool, sz = Q.build_graph(sd, lambda n: base.get(n, 4096), 64, ranks=ranks, rank=rank)
+    blob_pool = pool.bytes()
+    plan = compile_graph(g, "b200", {"POOL": len(blob_pool)})
+    assert verify_plan(plan) == []
+    assert not simulate(plan).deadlock
+    flagged = sorted(gr.name for gr in g.grids if gr.body.exchange)
+    assert flagged == sorted([f"o_proj_{L}" for L in range(sd.L)] + [f"{'moe_down' if sd.moe else 'down'}_{L}" for L in range(sd.L)])
+    # the blob carries the flag in the last word of each 48-byte type row
+    blob = plan.to_blob([("impargs", len(blob_pool)), ("vl", 8)], blob_pool)
+    n_types, n_tensors = struct.unpack_from("<I", blob, 20)[0], struct.unpack_from("<I", blob, 36)[0]
+    toff = 64 + 64 * n_tensors
+    flags = [struct.unpack_from("<i", blob, toff + 48 * i + 44)[0] for i in range(n_types)]
+    by_id = {tid: name for name, tid in plan.type_ids.items()}
+    assert sorted(by_id[i] for i, f in enumerate(flags) if f) == flagged
+    # row `rank` of the exchanged blocks is where the row-parallel grids write; the folds after them add `ranks` rows
+    rows = {r[0]: r for r in pool.rows}
+    out_ptr = struct.unpack_from("<Q", blob_pool, rows["o_proj_0"][4] + 16)[0]
+    assert out_ptr == base["o"] + rank * sd.H * 2
+    nxt = "router_0" if sd.moe else "gate_up_0"
+    assert struct.unpack_from("<i", blob_pool, rows[nxt][4] + 96)[0] == ranks
+    assert struct.unpack_from("<i", blob_pool, rows["lm_head"][4] + 96)[0] == ranks
+    assert struct.unpack_from("<i", blob_pool, rows["qkv_0"][4] + 96)[0] == 0 and struct.unpack_from("<i", blob_pool, rows["qkv_1"][4] + 96)[0] == ranks
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from etx_megakernel_b200.runtime import dist as D
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    got = D.gather_handles(bytes([rank]) * 64, dist)
+    dist.barrier()
+    q.put((rank, got))
+    dist.destroy_process_group()
+
+
+def test_two_ranks_pass_their_region_handles_around():
+    mp = pytest.importorskip("torch.multiprocessing")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, 29633, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, got in out:
+        assert got == [bytes([0]) * 64, bytes([1]) * 64]
