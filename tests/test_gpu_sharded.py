@@ -37,6 +37,10 @@ def prompt_of(od):
     return np.random.default_rng(7).integers(0, od.V, N_PROMPT)
 
 
+def long_prompt(od):
+    return np.random.default_rng(8).integers(0, od.V, 24)
+
+
 @pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
 def test_rank_looped_back_to_itself_equals_the_plain_program(od):
     sd, w = shard_on(od, 2, 0, 0)
@@ -96,8 +100,11 @@ def _rank(rank, world, port, od_name, q):
     err = None
     try:
         RD.connect_ranks(prog, dist)
+        forced = prog.generate(long_prompt(od), 1)                # every input token given: the states depend on no sampled token
+        fl, fr = prog.read("logits"), prog.read("resid")
+        dist.barrier()
         got = prog.generate(prompt_of(od), N_GEN)
-        q.put((rank, got.tolist(), prog.read("logits"), prog.read("resid")))
+        q.put((rank, got.tolist(), prog.read("logits"), (forced.tolist(), fl, fr)))
     except Exception as e:                                     # report, then leave together
         err = repr(e)
         q.put((rank, err, None, None))
@@ -122,18 +129,23 @@ def test_two_ranks_on_two_gpus_match_the_whole_model(od_name):
         assert p.exitcode == 0
     for rank, toks, logits, resid in out:
         assert logits is not None, f"rank {rank}: {toks}"
-    # both ranks hold bit-identical hidden states and logits (same rows added in the same order)
-    assert out[0][1] == out[1][1]
-    assert np.array_equal(out[0][2], out[1][2]) and np.array_equal(out[0][3], out[1][3])
-    # against the whole model on one GPU: logits within the bf16 tolerance, tokens equal up to a near-tie
+    # both ranks hold bit-identical hidden states and logits (same rows added in the same order), sampled or forced
+    assert out[0][1] == out[1][1] and np.array_equal(out[0][2], out[1][2])
+    assert out[0][3][0] == out[1][3][0] and np.array_equal(out[0][3][1], out[1][3][1]) and np.array_equal(out[0][3][2], out[1][3][2])
+    # against the whole model on one GPU with every input token given: hidden state and logits within the bf16 tolerance
+    # (a rank rounds its partial rows to bf16 before they are added, the whole model rounds the whole row once)
     d = qdims(od)
     W = O.SyntheticWeights(od, seed=1, gamma="ones")
     whole = D.DecodeProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, MAXLEN), "cuda:0"), device=0, maxlen=MAXLEN)
+    wtok = whole.generate(long_prompt(od), 1).tolist()
+    wl, wr = whole.read("logits"), whole.read("resid")
+    _, fl, fr = out[0][3]
+    el, er = np.abs(fl - wl).max() / np.abs(wl).max(), np.abs(fr - wr).max() / np.abs(wr).max()
+    assert el <= 2e-2 and er <= 2e-2, f"logits off by {el:.4f}, hidden state by {er:.4f} (relative to the largest value)"
+    top2 = np.sort(wl)[-2:]
+    if top2[1] - top2[0] > 4e-2 * np.abs(wl).max():
+        assert out[0][3][0] == wtok
+    # sampled tokens: equal to the whole model's until a step whose top-2 margin is inside that tolerance
     want = whole.generate(prompt_of(od), N_GEN).tolist()
-    wl = whole.read("logits")
     whole.close()
-    first = next((i for i, (a, b) in enumerate(zip(out[0][1], want)) if a != b), None)
-    if first is None:
-        assert np.abs(out[0][2] - wl).max() <= 2e-2 * np.abs(wl).max()
-    else:
-        assert first >= 4, f"sharded tokens {out[0][1]} leave the whole model's {want} at step {first}"
+    print("relative error: logits", el, "hidden", er, "tokens equal for", next((i for i, (a, b) in enumerate(zip(out[0][1], want)) if a != b), N_GEN), "steps")
