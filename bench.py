@@ -10,7 +10,8 @@ device), e2e = the same through the C ABI's host-buffer decode (token id host->d
 roofline = algorithmic bytes of a step / measured launch time against the measured HBM copy peak, cpu_baseline = the
 oracle (numpy restatement of the reference's CPU path) timed on this box's cores on a bounded sample.
 With --impl reference the CPU path itself is the thing measured (same metric / config), on rank 0 only.
-N > 1: N independent replicas (one process per GPU, no collective: tensor / expert parallel sharding is not built yet).
+N > 1: N independent replicas (one process per GPU, no collective); --shard tp runs ONE request sharded over the N GPUs
+instead (tensor parallel: the ranks exchange partial rows inside the kernel).
 """
 from __future__ import annotations
 
@@ -181,9 +182,22 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     d = Q.load_dims(MODEL, layers=args.layers or None)
     P, K, Wm = args.prompt, args.steps, args.warmup
     maxlen = ((P + Wm + K + 40 + 15) // 16) * 16
-    weights = D.random_packed_weights(d, maxlen, dev, seed=rank, gamma="ones")
-    prog = D.DecodeProgram(d, weights, device=local_rank, maxlen=maxlen, steps=maxlen)
-    prompt = np.random.default_rng(1000 + rank).integers(0, d.V, P)
+    tp = world if (args.shard == "tp" and world > 1) else 1
+    if tp > 1:
+        # one request over all ranks: every rank draws the whole model from the same seed, keeps its shard, and the ranks
+        # meet inside the kernel at the row-parallel grids (no collective library call on the data path)
+        from etx_megakernel_b200.runtime import dist as RD
+        whole = D.random_packed_weights(d, maxlen, dev, seed=0, gamma="ones")
+        weights = Q.shard_weights(whole, d, tp, rank)
+        del whole
+        torch.cuda.empty_cache()
+        prog = D.DecodeProgram(Q.shard_dims(d, tp), weights, device=local_rank, maxlen=maxlen, steps=maxlen, ranks=tp, rank=rank)
+        prog.session.set_option("timeout_ms", 10000)
+        RD.connect_ranks(prog, dist)
+    else:
+        weights = D.random_packed_weights(d, maxlen, dev, seed=rank, gamma="ones")
+        prog = D.DecodeProgram(d, weights, device=local_rank, maxlen=maxlen, steps=maxlen)
+    prompt = np.random.default_rng(1000 + (0 if tp > 1 else rank)).integers(0, d.V, P)
     # prefill: the prompt token by token through the same kernel (fills the KV caches), plus W warm-up decode steps
     tin = torch.zeros_like(prog.buf["token_in"]); tin[:P] = torch.tensor(prompt, dtype=torch.int32)
     prog.buf["token_in"].copy_(tin)
@@ -223,7 +237,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         toks_host, ms_host = prog.session.decode_host(np.asarray([first], np.int32), K, P + Wm)
         host_ms = (time.perf_counter() - h0) * 1e3 / K
         # the unfused baseline: the same steps as one launch per grid (what the single launch is compared with)
-        Ku = min(K, 4)
+        Ku = 0 if tp > 1 else min(K, 4)                                          # (a sharded session runs as the single launch only)
         u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             u0.record(stream)
@@ -234,7 +248,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             u1.record(stream)
         torch.cuda.synchronize(dev)
         prog.session.wait(120.0)
-        unfused_ms = u0.elapsed_time(u1) / Ku
+        unfused_ms = u0.elapsed_time(u1) / Ku if Ku else None
         gen_unfused = prog.buf["token_out"][P + Wm:P + Wm + Ku].cpu().numpy()
     finally:
         clk.__exit__(None, None, None)
@@ -249,17 +263,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # DRAM bytes per launch: dram__bytes_read + write of one ncu capture on the 2-layer case (862.12 MB against 854.11 MB
     # algorithmic, profiles/megakernel_qwen3-30b-a3b_2layers_ctx1024.md), scaled by the algorithmic bytes of this launch
     traffic = ledger["total"] * (862.12 / 854.11)
-    line = {"metric": METRIC, "value": dev_ms / world, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms,
-            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+    jobs = 1 if tp > 1 else world                                                # sequences decoded at once by the whole job
+    peak_all = peak * (tp if tp > 1 else 1)
+    line = {"metric": METRIC, "value": dev_ms / jobs, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms,
+            "higher_is_better": False, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload(d.L, P), "prefill": "the prompt is fed token by token through the same kernel",
-                       "context": ctx, "parallelism": "single" if world == 1 else f"replicas x{world}", "norm_gamma": "ones", "l2": f"each step streams {ledger['total'] / 1e9:.1f} GB (> 126 MB L2)",
-                       "tokens_per_s": 1000.0 / dev_ms * world, "prefill_s": round(prefill_s, 2), "host_tokens_equal_device_tokens": same_tokens,
+                       "context": ctx, "parallelism": "single" if world == 1 else f"tp{tp} (one request, in-kernel exchange)" if tp > 1 else f"replicas x{world}", "norm_gamma": "ones", "l2": f"each step streams {ledger['total'] / 1e9:.1f} GB (> 126 MB L2)",
+                       "tokens_per_s": 1000.0 / dev_ms * jobs, "prefill_s": round(prefill_s, 2), "host_tokens_equal_device_tokens": same_tokens,
                        "unfused_baseline": {"ms_per_token": unfused_ms, "launches_per_token": len(prog.plan.graph.grids), "steps": Ku,
                                             "same_tokens": bool(np.array_equal(gen_unfused, gen_dev[1:Ku + 1])),
                                             "what": "the same tiles, one kernel launch per grid on one stream"}},
-            "e2e": {"value": host_ms / world, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "e2e": {"value": host_ms / jobs, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": K, "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_all, "unit": "GB/s", "frac": achieved / peak_all, "traffic": traffic,
                          "peak_source": peak_src, "algorithmic_bytes_per_launch": ledger["total"], "kernel": "etxb_megakernel"}}
     if rank == 0 and world == 1 and not args.no_cpu:
         def layer_w(L):
@@ -267,7 +283,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         f = lambda t: (t.view(torch.int16).cpu().numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)     # noqa: E731
         ms, sample = oracle_sample(oracle_cfg(O), d.L, P, layer_w, f(weights["lm_head"]), f(weights["final_norm"]), f(weights["embed"][int(prompt[0])]))
         line["cpu_baseline"] = {"value": ms, "unit": UNIT, "cores": blas_threads(), "kind": "port", "sample": sample}
-    prog.close()
+    if tp > 1:
+        RD.close_ranks(prog, dist)
+    else:
+        prog.close()
     if rank == 0:
         print(json.dumps(line))
     if dist:
@@ -284,6 +303,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (debugging only; 0 = all)")
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--shard", default="replicas", choices=["replicas", "tp"],
+                    help="N > 1: N independent requests (default, weak scaling) or ONE request sharded over the N GPUs (tensor parallel, strong scaling)")
     a = ap.parse_args()
     globals()["MODEL"] = a.model
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))

@@ -62,11 +62,10 @@ struct etxb_session {
   int workers = 0;
   // sharded model (etxb_set_exchange)
   std::vector<unsigned char> h_pool;   // host copy of the argument pool (the rows an exchanged task writes are derived from it)
-  std::vector<int32_t> evcount_eff;    // arrivals per step including the peers' (exchanged events: x n_ranks)
   int n_ranks = 1, rank = 0;
   unsigned char* xbase = nullptr; size_t xbytes = 0;
   unsigned char* xpeer[ETXB_MAX_PEERS] = {};
-  bool events_external = false;        // the counters live at the start of the caller's exchange region
+  bool has_exchange = false;           // the plan is one rank's step of a sharded model (some grid is marked exchanged)
 };
 
 static int g_kernel_ready[64];
@@ -98,7 +97,7 @@ static int select_variant(const etxb_session* s, const std::vector<unsigned char
       etxb_gemv_args a;
       memcpy(&a, pool.data() + off, sizeof a);
       const int fold = a.mode & 0xff;
-      if (fold == ETXB_MODE_NORM && a.R > 1) return 0;
+      if (fold == ETXB_MODE_NORM && a.R > 1 && !(a.mode & ETXB_MODE_FLAGGED)) return 0;
       if (fold >= 2 && a.E > 128) return 0;
     }
   }
@@ -221,7 +220,7 @@ static int32_t parse_plan(etxb_session* s, const unsigned char* b, size_t n) {
   CU(up((void**)&s->d_outwords, s->outwords.data(), h.n_out * 4));
   s->variant = select_variant(s, pool);
   s->h_pool = pool;
-  s->evcount_eff = s->evcount;
+  for (const etxb_type& ty : s->types) s->has_exchange = s->has_exchange || ty.exchange != 0;
   pool.resize(pool.size() + 256, 0);                               // the context prefetch reads 192 bytes from a block start
   CU(up((void**)&s->d_pool, pool.data(), pool.size()));
   CU(cudaMalloc((void**)&s->d_type_args, (size_t)h.n_types * ETXB_MAX_ARGS * sizeof(void*)));
@@ -260,7 +259,7 @@ extern "C" int32_t etxb_destroy(etxb_session* s) {
   if (!s) return ETXB_OK;
   cudaSetDevice(s->device);
   if (s->launched) cudaDeviceSynchronize();
-  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_urecs, s->d_uqbegin, s->d_qbegin, s->d_types, s->d_type_args, s->events_external ? nullptr : s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
+  void* ptrs[] = {s->d_tasks, s->d_recs, s->d_urecs, s->d_uqbegin, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
                   s->d_ctrl, s->d_trace, s->d_exec, s->d_pool};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (s->h_ctrl) cudaFreeHost(s->h_ctrl);
@@ -350,35 +349,22 @@ extern "C" int32_t etxb_set_exchange(etxb_session* s, int32_t rank, int32_t n_ra
   if (!s || !local_base || !peer_bases) return fail(ETXB_E_ARG, "null argument");
   if (n_ranks < 2 || n_ranks > ETXB_MAX_PEERS + 1 || rank < 0 || rank >= n_ranks) return fail(ETXB_E_ARG, "set_exchange: 2 <= n_ranks <= 8, 0 <= rank < n_ranks");
   if (s->epoch != 0 || s->launched || s->n_ranks != 1) return fail(ETXB_E_ARG, "set_exchange: once, before the first step");
-  const size_t evbytes = (size_t)s->h.n_events * ETXB_EV_STRIDE * 4;
-  if (bytes < evbytes + 2 || ((uintptr_t)local_base & 127)) return fail(ETXB_E_ARG, "set_exchange: the region starts with the event counters (128 bytes per event, 128-byte aligned)");
-  bool any = false;
-  for (const etxb_type& ty : s->types) any = any || ty.exchange != 0;
-  if (!any) return fail(ETXB_E_PLAN, "set_exchange: the plan marks no grid as exchanged");
+  if (bytes < 4 || bytes > (size_t(1) << 24) || ((uintptr_t)local_base & 15)) return fail(ETXB_E_ARG, "set_exchange: a region is 16-byte aligned and at most 16 MiB");
+  if (!s->has_exchange) return fail(ETXB_E_PLAN, "set_exchange: the plan marks no grid as exchanged");
   int q = 0;
   for (int r = 0; r < n_ranks; ++r) {
     if (r == rank) continue;
-    if (!peer_bases[r] || ((uintptr_t)peer_bases[r] & 127)) return fail(ETXB_E_ARG, "set_exchange: a peer's region is missing or misaligned");
+    if (!peer_bases[r] || ((uintptr_t)peer_bases[r] & 15)) return fail(ETXB_E_ARG, "set_exchange: a peer's region is missing or misaligned");
     s->xpeer[q++] = (unsigned char*)peer_bases[r];
   }
-  CU(cudaSetDevice(s->device));
-  CU(cudaMemset(local_base, 0, evbytes));
-  if (!s->events_external && s->d_events) CU(cudaFree(s->d_events));
-  s->d_events = (int32_t*)local_base; s->events_external = true;
   s->xbase = (unsigned char*)local_base; s->xbytes = bytes; s->rank = rank; s->n_ranks = n_ranks;
-  // every rank's tasks arrive on an exchanged grid's events
-  std::vector<char> xev(s->h.n_events, 0);
-  for (const etxb_task& t : s->tasks)
-    if (s->types[t.type].exchange)
-      for (int k = 0; k < t.out_n; ++k) xev[s->outwords[t.out_off + k]] = 1;
-  for (uint32_t e = 0; e < s->h.n_events; ++e) s->evcount_eff[e] = s->evcount[e] * (xev[e] ? n_ranks : 1);
-  CU(cudaMemcpy(s->d_evcount, s->evcount_eff.data(), (size_t)s->h.n_events * 4, cudaMemcpyHostToDevice));
   s->args_dirty = true;
   return ETXB_OK;
 }
 
-// The rows an exchanged task writes, as (first bf16 element from the exchange region's base, count): task c0 of a plain
-// GEMV or of a MoE-down grid that leaves one row vector (one slot, or every slot summed) writes out[r0 .. r0 + n).
+// What an exchanged task publishes: the rows it wrote, out[r0 .. r0 + n) of a plain GEMV or of a MoE-down grid that leaves
+// one row vector (one slot, or every slot summed), go as flagged words to row `rank` of the [ranks][M] block the grid's
+// argument block names in `rows`.  Returns (first word from the region's base) | n << 22.
 static int32_t exchange_rows(const etxb_session* s, const etxb_type& ty, const etxb_task& t, uint32_t* mirror) {
   *mirror = 0;
   if (ty.body != ETXB_BODY_GEMV && ty.body != ETXB_BODY_MOE_DOWN) return fail(ETXB_E_UNSUPPORTED, "exchange: only GEMV and MoE-down grids can be exchanged");
@@ -386,6 +372,7 @@ static int32_t exchange_rows(const etxb_session* s, const etxb_type& ty, const e
     return fail(ETXB_E_UNSUPPORTED, "exchange: the grid's argument block must be in the pool");
   etxb_gemv_args a;
   memcpy(&a, s->h_pool.data() + ty.cst[0], sizeof a);
+  if (!(a.mode & ETXB_MODE_FLAGGED) || a.rows == nullptr) return fail(ETXB_E_ARG, "exchange: the grid's argument block must carry the flagged mode bit and name its block in `rows`");
   const int blk = t.coord[0];
   if (blk >= (int)a.nblocks || a.rpt <= 0) return ETXB_OK;
   int r0;
@@ -400,13 +387,12 @@ static int32_t exchange_rows(const etxb_session* s, const etxb_type& ty, const e
   }
   const int r1 = std::min(a.M, r0 + a.rpt);
   if (r0 >= r1) return ETXB_OK;
-  const unsigned char* out = (const unsigned char*)a.out + (size_t)r0 * 2;
-  const size_t bytes = (size_t)(r1 - r0) * 2;
-  if (out < s->xbase + (size_t)s->h.n_events * ETXB_EV_STRIDE * 4 || out + bytes > s->xbase + s->xbytes)
-    return fail(ETXB_E_ARG, "exchange: an exchanged grid writes outside the exchange region (or into its counters)");
-  const size_t off = (size_t)(out - s->xbase) / 2;
-  if (((out - s->xbase) & 1) || off >= (1u << 20) || (r1 - r0) >= 4096) return fail(ETXB_E_UNSUPPORTED, "exchange: row range does not fit the task record");
-  *mirror = (uint32_t)off | ((uint32_t)(r1 - r0) << 20);
+  const unsigned char* block = (const unsigned char*)a.rows;
+  if (block < s->xbase || block + (size_t)s->n_ranks * a.M * 4 > s->xbase + s->xbytes || ((block - s->xbase) & 15))
+    return fail(ETXB_E_ARG, "exchange: an exchanged grid's block lies outside the exchange region");
+  const size_t off = (size_t)(block - s->xbase) / 4 + (size_t)s->rank * a.M + r0;
+  if (off >= (size_t(1) << 22) || (r1 - r0) >= 1024) return fail(ETXB_E_UNSUPPORTED, "exchange: row range does not fit the task record");
+  *mirror = (uint32_t)off | ((uint32_t)(r1 - r0) << 22);
   return ETXB_OK;
 }
 
@@ -429,7 +415,7 @@ static int32_t upload_type_args(etxb_session* s) {
     memset(&r, 0, sizeof r);
     r.body = ty.body; r.c0 = t.coord[0]; r.c1 = t.coord[1]; r.id = t.id;
     r.in_n = t.in_n; r.out_n = t.out_n; r.in_off = t.in_off; r.out_off = t.out_off;
-    for (int k = 0; k < 4 && k < t.in_n; ++k) { r.in_word[k] = s->inwords[t.in_off + k]; r.in_cnt[k] = s->evcount_eff[r.in_word[k]]; }
+    for (int k = 0; k < 4 && k < t.in_n; ++k) { r.in_word[k] = s->inwords[t.in_off + k]; r.in_cnt[k] = s->evcount[r.in_word[k]]; }
     for (int k = 0; k < 4 && k < t.out_n; ++k) r.out_word[k] = s->outwords[t.out_off + k];
     // tiles below the GEMV family take no argument block: point them at the pool so the 192-byte prefetch stays in bounds
     const bool has_block = ty.body >= ETXB_BODY_GEMV && ty.args[0] >= 0;
@@ -489,6 +475,7 @@ static int32_t launch_kernel(const etxb_params& p, int grid, cudaStream_t st, in
 extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   if (!s) return fail(ETXB_E_ARG, "null session");
   CU(cudaSetDevice(s->device));
+  if (s->has_exchange && s->n_ranks < 2) return fail(ETXB_E_ARG, "the plan is one rank of a sharded model: etxb_set_exchange comes before the first step");
   if (s->args_dirty) { int32_t rc = upload_type_args(s); if (rc) return rc; }
   s->stream = cuda_stream ? (cudaStream_t)cuda_stream : s->own_stream;
   if (s->trace && s->d_exec) CU(cudaMemsetAsync(s->d_exec, 0, (size_t)s->h.n_tasks * 4, s->stream));
@@ -496,7 +483,7 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   etxb_params p;
   fill_params(s, p);
   CU(cudaEventRecord(s->ev0, s->stream));
-  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full || s->n_ranks > 1) ? 0 : s->variant);
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
   if (rc) return rc;
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
@@ -522,7 +509,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   for (uint32_t t = 0; t < s->h.n_types; ++t) {
     p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
-    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full || s->n_ranks > 1) ? 0 : s->variant);
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
     if (rc) return rc;
   }
   CU(cudaEventRecord(s->ev1, s->stream));
@@ -540,7 +527,7 @@ static int32_t read_ctrl(etxb_session* s) {
 // step starts clean (the reference forces a full host reset after a failed step, host.h:388).
 static int32_t recover(etxb_session* s) {
   std::vector<int32_t> ev((size_t)s->h.n_events * ETXB_EV_STRIDE, 0);
-  for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount_eff[e]);
+  for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount[e]);
   if (!ev.empty()) CU(cudaMemcpy(s->d_events, ev.data(), ev.size() * 4, cudaMemcpyHostToDevice));
   CU(cudaMemset(s->d_ctrl, 0, 64));
   return ETXB_OK;
@@ -594,7 +581,7 @@ extern "C" int32_t etxb_status(etxb_session* s, etxb_status_t* out) {
   out->ctrl = s->h_ctrl ? s->h_ctrl[0] : 0; out->stuck_task = s->h_ctrl && s->h_ctrl[0] ? s->h_ctrl[1] : -1;
   out->stuck_event = s->h_ctrl[2]; out->stuck_value = s->h_ctrl[3]; out->stuck_target = s->h_ctrl[4];
   out->tasks_run = 0; out->epoch = s->epoch; out->last_ms = s->last_ms;
-  out->kernel_variant = (s->force_full || s->n_ranks > 1) ? 0 : s->variant;
+  out->kernel_variant = s->force_full ? 0 : s->variant;
   if (s->trace && s->d_exec) {
     std::vector<int32_t> ex(s->h.n_tasks);
     CU(cudaSetDevice(s->device));

@@ -59,8 +59,8 @@ struct etxb_type {
   int32_t stream_word;          // event the producer warp waits for before it reads the weight addresses of a task:
                                 // -1 none (static weights: stream ahead freely), -2 the task's own in-events, >= 0 that event
   int32_t exchange;             // 1: a row-parallel GEMV / MoE-down grid of a sharded model -- every rank runs the same grid on its
-                                // shard and the rows a task wrote are copied into every peer's exchange region, its arrivals
-                                // delivered to every peer's counters too (etxb_set_exchange); 0 otherwise
+                                // shard and a task publishes the rows it wrote, as flagged words, into the block its argument
+                                // block names in `rows`, in every rank's exchange region (etxb_set_exchange); 0 otherwise
 };
 
 struct etxb_task {
@@ -78,8 +78,8 @@ struct etxb_rec {
   int32_t in_word[4], in_cnt[4], out_word[4];      // the first four of each list; longer lists continue in inwords / outwords
   uint64_t args;                                   // device address of the task's argument block
   int32_t stream_word;
-  uint32_t mirror;                                 // exchanged task: bits 0..19 first bf16 element (from the exchange region's base),
-                                                   // bits 20..31 element count of the rows it wrote; 0 = nothing to copy to the peers
+  uint32_t mirror;                                 // exchanged task: bits 0..21 first 4-byte word (from the exchange region's base) of the
+                                                   // flagged words it publishes, bits 22..31 how many (the rows it wrote); 0 = none
 };
 
 // ---- step parameters (the reference's VlParams, examples/vllm_llm/vl_tiles.hip:13-24) ---------------------------
@@ -108,10 +108,10 @@ struct etxb_params {
   uint32_t epoch;
   int32_t n_workers;
   etxb_stepv step;
-  // sharded model (etxb_set_exchange): the other ranks' exchange regions as mapped into this process.  A region starts
-  // with that rank's event counters (same indices as `events`), the exchanged rows follow at the same offsets on every rank.
+  // sharded model (etxb_set_exchange): this rank's exchange region and the other ranks' as mapped into this process;
+  // the blocks of flagged rows sit at the same offsets in every rank's region.
   int32_t n_peers, pad;
-  unsigned char* xbase;                            // this rank's region (events == (int32_t*)xbase)
+  unsigned char* xbase;
   unsigned char* xpeer[ETXB_MAX_PEERS];
 };
 
@@ -140,6 +140,9 @@ struct etxb_gemv_args {
 #define ETXB_MODE_BF16_WTS 0x100
 #define ETXB_MODE_BIAS 0x200
 #define ETXB_MODE_SUM_SLOTS 0x400     // MoE down: the task covers every slot and writes their bf16 sum in ascending expert id
+#define ETXB_MODE_FLAGGED 0x1000      // sharded model.  Norm fold: `rows` holds R rows of K flagged words (4 bytes: bf16 value | step flag
+                                      // << 16) that the ranks publish; the fold re-reads a word until its flag is this step's.  Plain GEMV /
+                                      // MoE down of an exchanged grid: `rows` names the [ranks][M] block of flagged words to publish into
 #define ETXB_MODE_ROUTE_READY 0x800   // MoE down with the top-k fold: the gate/up tiles it waits for have published the routing in
                                       // ids / wts, so the consumer warps read it there (one load) instead of redoing the top-k;
                                       // the producer warp, which runs ahead of the gate/up phase, still derives it from the logits

@@ -316,11 +316,15 @@ __device__ __forceinline__ void stage_xb(const void* x, int K, __nv_bfloat16* xb
 // itself; rows == null: z = resid_in), then x = bf16(ln * bf16(z * r)), r = 1 / sqrt(mean(z^2) + eps) with the mean summed
 // in numpy's order.  x goes to shared memory (xb); `store`: this task also writes resid_out (z) and xout (x).  K <= 8192.
 // LEAN: the form the host picks when every norm fold of the plan adds at most one row (R <= 1): no ordering, no row loop.
+// fl != 0 (sharded model): `rows` holds R rows of K flagged words published by the ranks (row r by rank r); every word is
+// re-read until its flag is `fl` (bounded like every wait: on a give-up the step is abandoned through sm.stop), then the
+// rows are added in rank order -- every rank adds the same values in the same order and gets the same bits.
 template <bool LEAN>
 __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, void* rout, void* xout, const void* ln,
-                                            const int32_t* ids, int R, int K, float eps, float* xf, __nv_bfloat16* xb, float* scr, bool store) {
+                                            const int32_t* ids, int R, int K, float eps, float* xf, __nv_bfloat16* xb, float* scr, bool store,
+                                            uint32_t fl = 0u, const Smem* smp = nullptr) {
   int* order = (int*)(scr + 64);
-  if (!LEAN && R > 1) {
+  if (!LEAN && R > 1 && fl == 0u) {
     if (tidx() < R) {
       int rank = tidx();
       if (ids) {
@@ -346,6 +350,34 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
     if (rows == nullptr || R == 0) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) z[j] = rf[j];
+    } else if (fl != 0u) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll 1
+      for (int s0 = 0; s0 < R; ++s0) {
+        const uint32_t* src = (const uint32_t*)rows + (size_t)s0 * K + 8 * i;
+        uint4 a, b;
+        uint32_t spins = 0;
+        for (;;) {
+          a = ld_volatile16(src); b = ld_volatile16(src + 4);
+          if ((((a.x ^ fl) | (a.y ^ fl) | (a.z ^ fl) | (a.w ^ fl) | (b.x ^ fl) | (b.y ^ fl) | (b.z ^ fl) | (b.w ^ fl)) >> 16) == 0u) break;
+          if ((++spins & 63u) == 0) {
+            if (ld_relaxed(smp->ctrl) != 0) { *(volatile int*)smp->stop = 1; break; }
+            if ((spins & 1023u) == 0 && globaltimer() > *smp->deadline) {
+              if (atomicOr(smp->ctrl, ETXB_CTRL_TIMEOUT) == 0) { smp->ctrl[1] = smp->cur; smp->ctrl[2] = -2 - s0; smp->ctrl[3] = (int32_t)(a.x >> 16); smp->ctrl[4] = (int32_t)(fl >> 16); }
+              *(volatile int*)smp->stop = 1;
+              break;
+            }
+            __nanosleep(32);
+          }
+        }
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = bfr(__fadd_rn(acc[j], __uint_as_float(w[j] << 16)));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) z[j] = bfr(__fadd_rn(rf[j], acc[j]));
     } else if (LEAN) {
       const uint4 rv = ld_act16((const __nv_bfloat16*)rows + 8 * i);
       const float v[8] = {bf_lo(rv.x), bf_hi(rv.x), bf_lo(rv.y), bf_hi(rv.y), bf_lo(rv.z), bf_hi(rv.z), bf_lo(rv.w), bf_hi(rv.w)};
@@ -406,7 +438,8 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
   const int r0 = t.r0;
   __nv_bfloat16* xb = smem_xb(sm);
   if ((d.mode & 0xff) == ETXB_MODE_NORM)
-    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
+    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0,
+                         (d.mode & ETXB_MODE_FLAGGED) ? row_flag(sm.epoch) : 0u, &sm);
   else
     stage_xb(d.x, d.K, xb);
   const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
@@ -439,7 +472,8 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
   }
   __nv_bfloat16* xb = smem_xb(sm);
   if (fold == ETXB_MODE_NORM)                                      // dense MLP: the post-attention norm folded in
-    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0);
+    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0,
+                         (d.mode & ETXB_MODE_FLAGGED) ? row_flag(sm.epoch) : 0u, &sm);
   else
     stage_xb(d.x, d.K, xb);
   float* g = smem_g(sm);                                           // per slot: n gate results, then n up results

@@ -211,6 +211,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   sm.ctrl = p.ctrl;
   sm.stop = &s_stop;
   sm.tr = nullptr;
+  sm.epoch = p.epoch;
   if (threadIdx.x == 0) {
     s_stop = 0;
     s_deadline = globaltimer() + p.timeout_ns;
@@ -246,8 +247,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
         int word, cnt;
         if (i < 4) { word = c->r.in_word[i]; cnt = c->r.in_cnt[i]; }
         else { word = p.inwords[c->r.in_off + i]; cnt = p.evcount[word]; }
-        if (GQV == 0 && p.n_peers > 0) ok = wait_event_sys(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
-        else ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
+        ok = wait_event(p, word, (int32_t)(p.epoch * (uint32_t)cnt), cur, s_deadline);
       }
       if (!ok) s_stop = 1;
       if (p.trace) p.trace[8 * (size_t)c->r.id + 1] = globaltimer();
@@ -256,21 +256,25 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     if (s_stop) break;
     if (fetcher) fetch_ctx(p, ctx, q0, cur + 2 < q1 ? cur + 2 : -1, cur + 1 < q1 ? cur + 1 : -1);   // asynchronous
     sm.tr = p.trace ? p.trace + 8 * (size_t)c->r.id : nullptr;
+    sm.cur = cur;
     run_body<GQV>(p, c, cur, sm, n);
     if (fetcher) cp_async_wait_all();
     csync();                                                       // every consumer thread's stores are issued, the next contexts landed
-    // Sharded model: copy the bf16 rows this task wrote into every peer's exchange region (plain stores over NVLink),
-    // so that each rank's next norm fold finds all ranks' partial rows in its own memory.  The condition is the same
-    // for every consumer thread (it must not read s_stop: thread 0 may already be past this point of the next task).
-    const uint32_t mirror = GQV == 0 && p.n_peers > 0 ? c->r.mirror : 0u;
-    if (mirror != 0u) {
-      const uint32_t off = mirror & 0xfffffu, len = mirror >> 20;
-      const unsigned short* src = (const unsigned short*)p.xbase + off;
-      for (uint32_t i = threadIdx.x; i < len; i += ETXB_CONSUMERS) {
-        const unsigned short v = __ldcg(src + i);
-        for (int q = 0; q < p.n_peers; ++q) ((unsigned short*)p.xpeer[q])[off + i] = v;
+    // Sharded model: warp 1 publishes the bf16 rows this task wrote as flagged words (value | this step's flag) into the
+    // grid's block of every rank's exchange region, its own included -- plain 4-byte stores, over NVLink for the peers.
+    // Value and flag travel in one word, so nothing has to be ordered: no fence, no barrier, no remote counter; the
+    // arrival below only tells this rank's consumers that the local phase is over, the folds then poll the flags.
+    const uint32_t mirror = c->r.mirror;                             // 0 unless the session is sharded and the grid exchanged
+    if (mirror != 0u && (threadIdx.x >> 5) == 1) {
+      const etxb_gemv_args& d = *(const etxb_gemv_args*)c->args;
+      const int r0 = (c->r.body == 3 ? c->r.c0 : c->r.c0 % d.tpe) * d.rpt;
+      const unsigned short* src = (const unsigned short*)d.out + r0;
+      const uint32_t off = mirror & 0x3fffffu, len = mirror >> 22, fl = row_flag(p.epoch);
+      for (uint32_t i = threadIdx.x & 31; i < len; i += 32) {
+        const uint32_t v = (uint32_t)__ldcg(src + i) | fl;
+        for (int q = 0; q < p.n_peers; ++q) ((uint32_t*)p.xpeer[q])[off + i] = v;
+        ((uint32_t*)p.xbase)[off + i] = v;
       }
-      csync();
     }
     if (threadIdx.x == 0) {
       const int out_n = c->r.out_n, id = c->r.id;
@@ -278,8 +282,6 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
         for (int i = 0; i < out_n; ++i) {                          // release: orders the CTA's stores (seen through the barrier) before the count
           const int word = i < 4 ? c->r.out_word[i] : p.outwords[c->r.out_off + i];
           red_release_add(p.events + (size_t)word * ETXB_EV_STRIDE, 1);
-          if (mirror != 0u)                                        // and the peers' counters: release at system scope covers the copies above
-            for (int q = 0; q < p.n_peers; ++q) red_release_sys_add((int32_t*)p.xpeer[q] + (size_t)word * ETXB_EV_STRIDE, 1);
         }
       if (p.trace) { p.trace[8 * (size_t)id + 2] = globaltimer(); p.trace[8 * (size_t)id + 3] = blockIdx.x; }
       if (p.exec_count) atomicAdd(p.exec_count + id, 1);

@@ -71,15 +71,6 @@ __device__ __forceinline__ int32_t ld_relaxed(const int32_t* p) {
 __device__ __forceinline__ void red_release_add(int32_t* p, int32_t v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// system scope: counters another GPU arrives on over NVLink, and arrivals on a peer's counters
-__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
-  int32_t v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_release_sys_add(int32_t* p, int32_t v) {
-  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ unsigned long long globaltimer() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -112,24 +103,6 @@ __device__ __forceinline__ bool wait_event(const int32_t* events, int32_t* ctrl,
 __device__ __forceinline__ bool wait_event(const etxb_params& p, int word, int32_t target, int task_id, unsigned long long deadline) {
   return wait_event(p.events, p.ctrl, word, target, task_id, deadline);
 }
-// The same wait with a system-scope acquire: the counter may be one other ranks arrive on from their GPUs.  Bounded the
-// same way; a rank whose peers never arrive gives up at its deadline and reports the event.
-__device__ __noinline__ bool wait_event_sys(const etxb_params& p, int word, int32_t target, int task_id, unsigned long long deadline) {
-  const int32_t* e = p.events + (size_t)word * ETXB_EV_STRIDE;
-  uint32_t n = 0;
-  for (;;) {
-    const int32_t v = ld_acquire_sys(e);
-    if ((int32_t)(v - target) >= 0) return true;
-    if ((++n & 63u) == 0) {
-      if (ld_relaxed(p.ctrl) != 0) return false;
-      if ((n & 1023u) == 0 && globaltimer() > deadline) {
-        if (atomicOr(p.ctrl, ETXB_CTRL_TIMEOUT) == 0) { p.ctrl[1] = task_id; p.ctrl[2] = word; p.ctrl[3] = v; p.ctrl[4] = target; }
-        return false;
-      }
-      __nanosleep(64);
-    }
-  }
-}
 
 // ---------------------------------------------------------------------------------------------- bf16
 __device__ __forceinline__ float bfr(float x) {                    // RNE to bf16, kept as float (ref_numpy.py:26-32)
@@ -158,6 +131,17 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 }
 // 16-byte load of activations another CTA produced this step: L2 only (L1 is not coherent across SMs)
 __device__ __forceinline__ uint4 ld_act16(const void* p) { return __ldcg((const uint4*)p); }
+
+// Flagged words of a sharded model's exchanged rows: a bf16 value in the low half, a 16-bit flag derived from the step
+// in the high half.  A 4-byte store is atomic on every path (NVLink included), so value and flag arrive together and the
+// reader needs no fence and no counter: it re-reads until the flag is this step's.  The flag is never 0 (a zeroed buffer
+// is never valid) and differs from the previous step's (every buffer is rewritten once per step).
+__device__ __forceinline__ uint32_t row_flag(uint32_t epoch) { return ((epoch & 0x7fffu) | 0x8000u) << 16; }
+__device__ __forceinline__ uint4 ld_volatile16(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 
 // ---------------------------------------------------------------------------------------------- reductions
 __device__ __forceinline__ float warp_sum(float v) {               // xor butterfly 16..1: same value in every lane

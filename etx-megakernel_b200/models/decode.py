@@ -14,7 +14,6 @@ from ..passes import PassOptions, compile_graph
 from ..runtime import ExchangeRegion, Session
 from . import qwen as Q
 
-XROWS_OFF = 1 << 20        # byte offset of the exchanged rows in a rank's exchange region (the counters come first)
 _DT = {"bf16": torch.bfloat16, "f32": torch.float32, "i32": torch.int32, "i64": torch.int64}
 
 
@@ -64,11 +63,8 @@ class DecodeProgram:
         self.vl = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
         if ranks > 1:
-            # exchange region: 1 MiB reserved for the event counters, then the [ranks][H] blocks of o_proj and down rows
-            self.region = ExchangeRegion(2 << 20, device)
-            self.xaddr = {"o": self.region.ptr + XROWS_OFF, "moe_out": self.region.ptr + XROWS_OFF + ranks * dims.H * 2}
-            if XROWS_OFF + 2 * ranks * dims.H * 2 > self.region.nbytes:
-                raise ValueError("hidden size too large for the exchange region")
+            self.region = ExchangeRegion(Q.exchange_bytes(dims, ranks), device)      # the blocks of flagged rows the ranks publish into
+            self.xaddr = {"xrows": self.region.ptr}
 
         def ptr(name):
             if name in self.xaddr:
@@ -81,8 +77,6 @@ class DecodeProgram:
                                                               ranks=ranks, rank=rank)
         pool = self.pool.bytes()
         self.plan = compile_graph(self.graph, self.machine, {"POOL": len(pool)}, options=PassOptions(workers=workers))
-        if ranks > 1 and self.plan.event_words * 128 > XROWS_OFF:
-            raise ValueError("too many events for the exchange region's counter area")
         self.session = Session(self.plan, {"vl": self.vl}, pool, device)
         b = self.buf
         self.session.set_step(tok=0, pos=0, write_next=0, H=dims.H, V=dims.V, nrep=1, embed=self.w["embed"], resid=b["resid"],

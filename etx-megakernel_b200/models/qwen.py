@@ -137,6 +137,11 @@ def shard_dims(d: Dims, ranks: int) -> Dims:
                    INTER=d.INTER if d.moe else d.INTER // ranks)
 
 
+def exchange_bytes(d: Dims, ranks: int) -> int:
+    """Size of a rank's exchange region: per layer one [ranks][H] block of flagged 4-byte words for o_proj and one for down."""
+    return 2 * d.L * ranks * d.H * 4
+
+
 def shard_weights(w: dict, d: Dims, ranks: int, rank: int) -> dict:
     """Packed weights of the whole model `d` (weight_shapes) -> those of rank `rank` of shard_dims(d, ranks): q / k / v rows
     and gate / up rows by columns of the output (column-parallel), o_proj and down by columns of the input
@@ -334,9 +339,10 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
     """The decode step of `d` as a Graph plus its argument pool.
 
     ranks > 1: the step of ONE rank of a model sharded `ranks` ways (`d` = shard_dims(full, ranks): its share of the
-    heads and of the MLP / expert rows).  ptr("o") and ptr("moe_out") then name [ranks][H] row blocks inside the rank's
-    exchange region: the row-parallel grids (o_proj, down) write row `rank` and are marked `exchange`, the norm folds
-    that follow add all `ranks` rows in rank order.
+    heads and of the MLP / expert rows).  ptr("xrows") then names the rank's exchange region: 2 * L blocks of
+    [ranks][H] flagged words (exchange_bytes); the row-parallel grids (o_proj, down) are marked `exchange` and publish
+    the rows they wrote into row `rank` of their block on every rank, the norm folds that follow read all `ranks`
+    rows from their own rank's copy and add them in rank order.
 
     ptr(name) -> device address (int) of a buffer (buffer_shapes) or packed weight (weight_shapes); "kc" / "vc" are the
     whole [L, ...] caches (layer slices are addressed by offset here).  Returns (graph, pool: ArgPool, sizing)."""
@@ -362,7 +368,11 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
 
     if not (1 <= ranks <= 8 and 0 <= rank < ranks):
         raise ValueError("1 <= ranks <= 8 and 0 <= rank < ranks")
-    xrow = rank * d.H * 2                                                   # this rank's row of an exchanged [ranks][H] block
+    xmode = op_gemv.MODE_FLAGGED if ranks > 1 else 0
+
+    def xblock(layer, kind):
+        """The block of flagged rows o_proj (kind 0) / down (kind 1) of `layer` publish into; 0 when not sharded."""
+        return ptr("xrows") + (2 * layer + kind) * ranks * d.H * 4 if ranks > 1 else 0
 
     def tile(symbol, stream_after=None, exchange=False):
         return cuda_link(SRC, symbol, stream_after=stream_after, exchange=exchange)
@@ -389,10 +399,10 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         t, rpt = sz.qkv
         first = L == 0
         blob = gemv_block("dsl_gemv_fold", t, W=W("wqkv"), x=ptr("hn"), out=ptr("qkv"), M=d.NQKV, K=d.H, rpt=rpt, tpe=1,
-                          rows=0 if first else ptr("moe_out"), resid_in=ptr("resid") if first else ptr("resid2"),
+                          rows=0 if first else (xblock(L - 1, 1) or ptr("moe_out")), resid_in=ptr("resid") if first else ptr("resid2"),
                           resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else ranks, eps=d.eps,
                           ids=0, wts=W("bqkv") if d.bias else 0,
-                          mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0), nb=1)
+                          mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0) | (0 if first else xmode), nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
         if fused_attn:
             # ---- the attention phase as one grid: prep + split-KV partitions + merge by the last task to finish
@@ -427,13 +437,14 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
 
         # ---- o_proj
         t, rpt = sz.o
-        blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o") + xrow, M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1)
+        blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1,
+                          rows=xblock(L, 0), mode=xmode)
         prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD, after="", exchange=True)
         if d.moe:
             # ---- router with the post-attention norm fold: task 0 stores resid2 and the normed vector
             t, rpt = sz.router
-            blob = gemv_block("dsl_gemv_fold", t, W=W("wr"), x=ptr("o_norm"), out=ptr("rlog"), M=d.E, K=d.H, rpt=rpt, tpe=1, rows=ptr("o"),
-                              resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps, mode=op_gemv.MODE_NORM, nb=1)
+            blob = gemv_block("dsl_gemv_fold", t, W=W("wr"), x=ptr("o_norm"), out=ptr("rlog"), M=d.E, K=d.H, rpt=rpt, tpe=1, rows=xblock(L, 0) or ptr("o"),
+                              resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps, mode=op_gemv.MODE_NORM | xmode, nb=1)
             prev = add(f"router_{L}", "dsl_gemv_fold", "router", L, blob, t, (t,), prev, "i->(0)", f"E_rt_{L}", "i->(0)", (1,), t, d.E, d.H, after="")
             topk_mode = (op_gemv.MODE_TOPK_RENORM if d.norm_topk else op_gemv.MODE_TOPK) | hf_mode
             if not fold_topk:
@@ -453,9 +464,9 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                        prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), groups * tpe, d.MI, d.H)
             tpe, rpt = sz.down
             dn_export = "dsl_moe_down_fold" if fold_topk else "dsl_moe_down"
-            blob = gemv_block(dn_export, tpe, W=W("w2"), x=ptr("mc2"), out=ptr("moe_out") + xrow, ids=ptr("ti"), wts=ptr("tw"),
+            blob = gemv_block(dn_export, tpe, W=W("w2"), x=ptr("mc2"), out=ptr("moe_out"), ids=ptr("ti"), wts=ptr("tw"), rows=xblock(L, 1),
                               estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps,
-                              mode=(topk_mode | op_gemv.MODE_ROUTE_READY if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS, E=d.E, logits=ptr("rlog"), nb=1)
+                              mode=(topk_mode | op_gemv.MODE_ROUTE_READY if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS | xmode, E=d.E, logits=ptr("rlog"), nb=1)
             # expert weights depend on the routing only: with the top-k folded in, the stream may start once the router is done
             prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, tpe, (tpe,), prev, "i->(0)",
                        f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None, exchange=True)
@@ -463,18 +474,18 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
             # ---- dense SwiGLU: gate+up with the post-attention norm fold, then down
             spt, tpe, rpt = sz.up
             blob = gemv_block("dsl_moe_up", tpe, W=W("wgu"), x=ptr("o_norm"), out=ptr("mc2"), estride=0, M=d.INTER, K=d.H, rpt=rpt, tpe=tpe,
-                              rows=ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps,
-                              mode=op_gemv.MODE_NORM, nb=1)
+                              rows=xblock(L, 0) or ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps,
+                              mode=op_gemv.MODE_NORM | xmode, nb=1)
             prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H, after="")
             tpe, rpt = sz.down
-            blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("moe_out") + xrow, estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
-                              eps=d.eps, nb=1)
+            blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("moe_out"), estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
+                              eps=d.eps, nb=1, rows=xblock(L, 1), mode=xmode)
             prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="", exchange=True)
     # ---- lm_head with the final-norm fold, then greedy sampling
     t, rpt = sz.lm
     blob = gemv_block("dsl_gemv_fold", t, W=ptr("embed") if d.tie else ptr("lm_head"), x=ptr("hn"), out=ptr("logits"), M=d.V, K=d.H, rpt=rpt,
-                      tpe=1, rows=ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=ranks, eps=d.eps,
-                      ids=0, mode=op_gemv.MODE_NORM, nb=1)
+                      tpe=1, rows=xblock(d.L - 1, 1) or ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=ranks, eps=d.eps,
+                      ids=0, mode=op_gemv.MODE_NORM | xmode, nb=1)
     prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},

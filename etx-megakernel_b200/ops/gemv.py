@@ -11,7 +11,9 @@ Forms:
 mode: 0 plain, 1 norm fold, 2 / 3 top-k fold without / with renormalisation; | 0x100 bf16 routing weights (the numerics
 of the reference's CPU path), | 0x200 bf16 bias row passed in `wts` (plain form), | 0x400 MoE down: the task covers
 every slot and writes out[r] = the slots' results added in bf16 in ascending expert id (the expert combine), bits
-16..23 expert slots per task (task blk -> slots [blk / tpe * spt, ...), row chunk blk % tpe).
+16..23 expert slots per task (task blk -> slots [blk / tpe * spt, ...), row chunk blk % tpe); | 0x1000 sharded model:
+`rows` names a [ranks][.] block of flagged 4-byte words (bf16 value | step flag << 16) -- an exchanged plain / down grid
+publishes the rows it wrote into row `rank` of it on every rank, a norm fold reads its R = ranks rows from it.
 """
 from __future__ import annotations
 
@@ -29,6 +31,7 @@ PARAMS = [("W", "ptr addrspace(1)", 0, 8), ("x", "ptr addrspace(1)", 8, 8), ("ou
 FORMS = {"dsl_gemv": "plain", "dsl_moe_up": "silu_mul", "dsl_moe_down": "scale",
          "dsl_gemv_fold": "plain", "dsl_moe_up_fold": "silu_mul", "dsl_moe_down_fold": "scale"}
 MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS, MODE_SUM_SLOTS, MODE_ROUTE_READY = 1, 2, 3, 0x100, 0x200, 0x400, 0x800
+MODE_FLAGGED = 0x1000      # sharded model: `rows` is a [ranks][M or K] block of flagged words (see build_graph(ranks=...))
 
 
 def mode_spt(spt: int) -> int:

@@ -127,18 +127,22 @@ int32_t etxb_status(etxb_session* s, etxb_status_t* out);
  * The reference shards a program over devices with device-scoped events and multi-device plans
  * (etx/passes/plan.py:58-86 device_of_task, etx/runtime/include/etx/host.h:79-210 one event region per device); here
  * every rank runs the SAME single-device plan on its shard of the weights and the ranks meet at the row-parallel grids
- * the plan marks as exchanged (o_proj, MoE / MLP down): a task of such a grid copies the bf16 rows it wrote into every
- * peer's exchange region (plain stores to peer memory over NVLink) and arrives on every peer's counters with a
- * system-scope release; the consumers (the next norm fold, with R = n_ranks rows) then wait for n_ranks times the
- * arrivals and add the ranks' rows in rank order, so every rank computes bit-identical hidden states.
+ * the plan marks as exchanged (o_proj, MoE / MLP down).  A task of such a grid publishes the bf16 rows it wrote as
+ * FLAGGED WORDS -- 4 bytes: the value in the low half, a 16-bit flag derived from the step in the high half -- into
+ * row `rank` of the grid's [n_ranks][M] block in EVERY rank's exchange region: plain 4-byte stores, over NVLink for
+ * the peers.  A store of 4 bytes is atomic, so value and flag arrive together: no fence, no remote counter, no
+ * collective call.  The norm fold that follows (mode bit 0x1000, R = n_ranks) reads the block in its own rank's
+ * memory, re-reads a word until its flag is this step's (bounded by the step's deadline like every wait), and adds
+ * the ranks' rows in rank order, so every rank computes bit-identical hidden states.
  *
- * A region is one device allocation: [event counters, 128 bytes per plan event][the exchanged rows, at offsets the
- * caller chooses -- the same on every rank].  etxb_exchange_alloc zeroes it and exports a 64-byte inter-process handle;
+ * A region is one device allocation holding the blocks at offsets the caller chooses -- the same on every rank (the
+ * argument blocks name them in `rows`).  etxb_exchange_alloc zeroes it and exports a 64-byte inter-process handle;
  * the caller passes the handles around (any transport) and opens the peers' with etxb_exchange_open.
- * etxb_set_exchange (once, before the first step) moves the session's counters to the start of `local_base`, records
- * the peers' mappings (peer_bases[r] for r != rank; entry `rank` is ignored) and selects the full kernel.  All ranks
- * must run the same steps; a rank whose peers stop arriving returns ETXB_E_TIMEOUT at its deadline, after which the
- * sessions of all ranks must be recreated.  etxb_launch_unfused is refused on a sharded session. */
+ * etxb_set_exchange (once, before the first step) records this rank's region and the peers' mappings (peer_bases[r]
+ * for r != rank; entry `rank` is ignored).  All ranks must run the same steps; a rank whose peers stop publishing
+ * returns ETXB_E_TIMEOUT at its deadline.  Every rank must have finished its last step before any rank frees or
+ * closes a region (a running peer still stores into it).  etxb_launch_unfused is refused on a sharded session, and
+ * etxb_launch on a rank's plan that has no exchange set. */
 #define ETXB_IPC_HANDLE_BYTES 64
 int32_t etxb_exchange_alloc(int device, size_t bytes, void** dev_ptr, unsigned char* handle /*[64]*/);
 int32_t etxb_exchange_free(int device, void* dev_ptr);

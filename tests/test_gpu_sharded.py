@@ -43,22 +43,31 @@ def long_prompt(od):
 
 @pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
 def test_rank_looped_back_to_itself_equals_the_plain_program(od):
+    """Rank 0 of 2 whose "peer" mapping is its own region shifted by one row: what it publishes for the peer lands in row
+    1 of its own blocks, so every fold adds the rank's rows twice.  With o_proj and down weights halved (exact in bf16)
+    that is bit for bit the plain single-rank program."""
     sd, w = shard_on(od, 2, 0, 0)
     plain = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN)
     want = plain.generate(prompt_of(od), N_GEN)
-    want_logits = plain.read("logits")
+    want_logits, want_resid = plain.read("logits"), plain.read("resid")
+    lean = plain.session.status().kernel_variant
     plain.close()
-    prog = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN, ranks=2, rank=0)
-    prog.region.peers[1] = prog.region.ptr                     # the peer is this rank's own region
-    prog.session.set_exchange(0, 2, prog.region)
-    prog.region.peers = {}                                     # (nothing was opened: nothing to close)
-    got = prog.generate(prompt_of(od), N_GEN)
-    assert prog.session.status().kernel_variant == 0           # a sharded session runs the full kernel
-    assert got.tolist() == want.tolist()
-    assert np.array_equal(prog.read("logits"), want_logits)
-    with pytest.raises(EtxbError):
-        prog.session.launch_unfused()
-    prog.close()
+    half = {k: (v * 0.5 if k.rsplit(".", 1)[-1] in ("wo", "w2", "wd") else v) for k, v in w.items()}
+    for full_kernel in (0, 1):
+        prog = D.DecodeProgram(sd, half, device=0, maxlen=MAXLEN, ranks=2, rank=0)
+        with pytest.raises(EtxbError, match="set_exchange comes before"):
+            prog.session.launch()                                  # a rank's plan does not run unconnected
+        prog.region.peers[1] = prog.region.ptr + sd.H * 4
+        prog.session.set_exchange(0, 2, prog.region)
+        prog.region.peers = {}                                     # (nothing was opened: nothing to close)
+        prog.session.set_option("full_kernel", full_kernel)
+        got = prog.generate(prompt_of(od), N_GEN)
+        assert prog.session.status().kernel_variant == (0 if full_kernel else lean)      # the lean kernels cover the sharded step
+        assert got.tolist() == want.tolist()
+        assert np.array_equal(prog.read("logits"), want_logits) and np.array_equal(prog.read("resid"), want_resid)
+        with pytest.raises(EtxbError):
+            prog.session.launch_unfused()
+        prog.close()
 
 
 def test_exchange_region_and_argument_checks():
@@ -75,15 +84,31 @@ def test_exchange_region_and_argument_checks():
         prog.session.set_exchange(0, 2, prog.region)           # no peer mapped yet
     with pytest.raises(EtxbError):
         prog.session.set_exchange(2, 2, prog.region)           # rank out of range
-    # an exchanged grid that writes outside the region is refused when the records are built (before any launch)
-    prog.region.peers[1] = prog.region.ptr
+    # an exchanged grid whose block lies outside the region is refused when the records are built (before any launch)
     small = ExchangeRegion(4096, 0)
     small.peers[1] = small.ptr
     prog.session.set_exchange(0, 2, small)
     with pytest.raises(EtxbError, match="outside the exchange region"):
         prog.session.launch()
-    prog.region.peers, small.peers, reg.peers = {}, {}, {}
+    small.peers, reg.peers = {}, {}
     prog.close(); small.close(); reg.close()
+
+
+def test_a_peer_that_never_publishes_ends_in_a_timeout_status():
+    """The bounded wait of the fold: the "peer" is a second region of this process that nothing reads or writes, so row 1
+    never carries this step's flag; the step gives up at its deadline and reports it, the context stays usable."""
+    sd, w = shard_on(SMALL_DENSE, 2, 0, 0)
+    prog = D.DecodeProgram(sd, w, device=0, maxlen=MAXLEN, ranks=2, rank=0)
+    other = ExchangeRegion(prog.region.nbytes, 0)
+    prog.region.peers[1] = other.ptr
+    prog.session.set_exchange(0, 2, prog.region)
+    prog.region.peers = {}
+    prog.session.set_option("timeout_ms", 200)
+    with pytest.raises(EtxbError) as e:
+        prog.generate(prompt_of(SMALL_DENSE), 2)
+    assert e.value.status == "E_TIMEOUT"
+    assert torch.zeros(4, device="cuda:0").sum().item() == 0.0     # the context is alive
+    prog.close(); other.close()
 
 
 # ------------------------------------------------------------------------------------------------ two GPUs, two processes

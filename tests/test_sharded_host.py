@@ -81,7 +81,7 @@ def test_shard_dims_refuses_uneven_splits():
 def test_rank_graph_is_a_valid_single_device_program_with_flagged_grids(od):
     ranks, rank = 2, 1
     sd = Q.shard_dims(qdims(od), ranks)
-    base = {"o": 1 << 30, "moe_out": (1 << 30) + ranks * sd.H * 2}
+    base = {"xrows": 1 << 30}
     g, pool, sz = Q.build_graph(sd, lambda n: base.get(n, 4096), 64, ranks=ranks, rank=rank)
     blob_pool = pool.bytes()
     plan = compile_graph(g, "b200", {"POOL": len(blob_pool)})
@@ -96,14 +96,23 @@ def test_rank_graph_is_a_valid_single_device_program_with_flagged_grids(od):
     flags = [struct.unpack_from("<i", blob, toff + 48 * i + 44)[0] for i in range(n_types)]
     by_id = {tid: name for name, tid in plan.type_ids.items()}
     assert sorted(by_id[i] for i, f in enumerate(flags) if f) == flagged
-    # row `rank` of the exchanged blocks is where the row-parallel grids write; the folds after them add `ranks` rows
+    # the exchanged grids name their block of flagged rows in `rows` and carry the flagged mode bit; the folds after
+    # them read `ranks` rows from the same block
     rows = {r[0]: r for r in pool.rows}
-    out_ptr = struct.unpack_from("<Q", blob_pool, rows["o_proj_0"][4] + 16)[0]
-    assert out_ptr == base["o"] + rank * sd.H * 2
-    nxt = "router_0" if sd.moe else "gate_up_0"
-    assert struct.unpack_from("<i", blob_pool, rows[nxt][4] + 96)[0] == ranks
-    assert struct.unpack_from("<i", blob_pool, rows["lm_head"][4] + 96)[0] == ranks
-    assert struct.unpack_from("<i", blob_pool, rows["qkv_0"][4] + 96)[0] == 0 and struct.unpack_from("<i", blob_pool, rows["qkv_1"][4] + 96)[0] == ranks
+    FL = 0x1000
+
+    def field(grid, off, fmt):
+        return struct.unpack_from(fmt, blob_pool, rows[grid][4] + off)[0]
+    blk = lambda L, kind: base["xrows"] + (2 * L + kind) * ranks * sd.H * 4      # noqa: E731
+    nxt, dn = ("router", "moe_down") if sd.moe else ("gate_up", "down")
+    for L in range(sd.L):
+        assert field(f"o_proj_{L}", 64, "<Q") == blk(L, 0) and field(f"o_proj_{L}", 104, "<i") & FL
+        assert field(f"{nxt}_{L}", 64, "<Q") == blk(L, 0) and field(f"{nxt}_{L}", 96, "<i") == ranks and field(f"{nxt}_{L}", 104, "<i") & FL
+        assert field(f"{dn}_{L}", 64, "<Q") == blk(L, 1) and field(f"{dn}_{L}", 104, "<i") & FL
+    assert field("qkv_0", 96, "<i") == 0 and not field("qkv_0", 104, "<i") & FL
+    assert field("qkv_1", 64, "<Q") == blk(0, 1) and field("qkv_1", 96, "<i") == ranks and field("qkv_1", 104, "<i") & FL
+    assert field("lm_head", 64, "<Q") == blk(sd.L - 1, 1) and field("lm_head", 96, "<i") == ranks
+    assert Q.exchange_bytes(sd, ranks) == blk(sd.L, 0) - base["xrows"]
 
 
 def _worker(rank, world, port, q):
