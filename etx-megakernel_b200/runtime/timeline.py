@@ -166,10 +166,23 @@ def main(argv=None) -> int:
         plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
         tl = Timeline.from_sim(plan, simulate(plan))
     else:
+        import os
         import torch
         from ..models import decode as D
-        dev = torch.device("cuda:0")
-        prog = D.DecodeProgram(d, D.random_packed_weights(d, a.maxlen, dev, seed=0), maxlen=a.maxlen)
+        from . import dist as RD
+        rank, world, local = RD.rank_env(os.environ)
+        dev = torch.device("cuda", local)
+        torch.cuda.set_device(dev)
+        w = D.random_packed_weights(d, a.maxlen, dev, seed=0)
+        if world > 1:
+            # under torchrun: ONE request sharded over the ranks (the timeline of rank 0 is printed)
+            import torch.distributed as dist
+            dist.init_process_group("gloo")
+            prog = D.DecodeProgram(Q.shard_dims(d, world), Q.shard_weights(w, d, world, rank), device=local, maxlen=a.maxlen, ranks=world, rank=rank)
+            prog.session.set_option("timeout_ms", 10000)
+            RD.connect_ranks(prog, dist)
+        else:
+            prog = D.DecodeProgram(d, w, device=local, maxlen=a.maxlen)
         prog.buf["kc"].normal_(0, 0.02); prog.buf["vc"].normal_(0, 0.02)
         for t in range(a.warm):
             prog.buf["token_in"][0] = 7
@@ -178,7 +191,13 @@ def main(argv=None) -> int:
         prog.session.set_option("trace", 1)
         prog.step(0, a.context + 9, False)
         tl = Timeline.from_trace(prog.plan, prog.session.trace())
-        prog.close()
+        if world > 1:
+            RD.close_ranks(prog, dist)
+            dist.destroy_process_group()
+            if rank != 0:
+                return 0
+        else:
+            prog.close()
     print(tl.text())
     if a.raw:
         tl.write_raw(a.raw)
