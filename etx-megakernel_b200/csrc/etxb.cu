@@ -65,6 +65,7 @@ struct etxb_session {
   int n_ranks = 1, rank = 0;
   unsigned char* xbase = nullptr; size_t xbytes = 0;
   unsigned char* xpeer[ETXB_MAX_PEERS] = {};
+  uint32_t xargmax = 0;                // byte offset of the sharded argmax block in a region (0: the lm_head is whole on every rank)
   bool has_exchange = false;           // the plan is one rank's step of a sharded model (some grid is marked exchanged)
 };
 
@@ -303,6 +304,13 @@ extern "C" int32_t etxb_set_option(etxb_session* s, const char* key, int64_t val
     return ETXB_OK;
   }
   if (!strcmp(key, "full_kernel")) { s->force_full = value != 0; return ETXB_OK; }
+  if (!strcmp(key, "exchange_argmax_offset")) {
+    // sharded lm_head: where in every rank's region the [n_ranks] 16-byte argmax slots sit (after etxb_set_exchange)
+    if (s->n_ranks < 2) return fail(ETXB_E_ARG, "exchange_argmax_offset: set the exchange first");
+    if (value <= 0 || (value & 15) || (size_t)value + 16 * (size_t)s->n_ranks > s->xbytes) return fail(ETXB_E_ARG, "exchange_argmax_offset: 16-byte aligned, non-zero, n_ranks x 16 bytes inside the region");
+    s->xargmax = (uint32_t)value;
+    return ETXB_OK;
+  }
   return fail(ETXB_E_ARG, std::string("unknown option ") + key);
 }
 
@@ -462,7 +470,7 @@ static void fill_params(etxb_session* s, etxb_params& p) {
   p.ctrl = s->d_ctrl; p.trace = s->trace ? s->d_trace : nullptr; p.exec_count = s->trace ? s->d_exec : nullptr;
   p.step_dev = nullptr; p.timeout_ns = s->timeout_ns; p.epoch = s->epoch; p.n_workers = (int32_t)s->h.n_workers;
   p.step = s->step;
-  p.n_peers = s->n_ranks - 1; p.pad = 0; p.xbase = s->xbase;
+  p.n_peers = s->n_ranks - 1; p.rank = s->rank; p.xargmax = s->xargmax; p.pad = 0; p.xbase = s->xbase;
   for (int q = 0; q < ETXB_MAX_PEERS; ++q) p.xpeer[q] = s->xpeer[q];
 }
 

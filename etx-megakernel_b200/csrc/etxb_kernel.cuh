@@ -26,7 +26,53 @@ __device__ __forceinline__ void tile_prologue(const etxb_stepv& S) {
 }
 
 // greedy sampling: first maximum of the bf16 logits (ties -> lower index, like argmax over float32)
-__device__ __forceinline__ void tile_argmax(const etxb_stepv& S, const Smem& sm) {
+// Sharded lm_head (p.xargmax != 0): the logits are this rank's V of ranks x V, so the rank's (maximum, global index) goes
+// into its slot of every rank's argmax block as two 8-byte (payload, step flag) stores -- each atomic, so no fence --
+// and the token is the best of all ranks' pairs, ties to the lower index: the same on every rank.
+__device__ __forceinline__ void st_volatile8(void* p, uint32_t a, uint32_t b) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_volatile8(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __noinline__ void argmax_exchange(const etxb_params& p, const Smem& sm, float& bv, int& bi) {
+  const uint32_t fl = row_flag(p.epoch);
+  bi += p.rank * p.step.V;
+  const int q_self = p.rank;
+  for (int q = 0; q <= p.n_peers; ++q) {                            // peers in xpeer order (ranks without this one), then this rank
+    unsigned char* base = q < p.n_peers ? p.xpeer[q] : p.xbase;
+    unsigned char* slot = base + p.xargmax + 16 * (size_t)q_self;
+    st_volatile8(slot, __float_as_uint(bv), fl);
+    st_volatile8(slot + 8, (uint32_t)bi, fl);
+  }
+  for (int r = 0; r <= p.n_peers; ++r) {
+    if (r == p.rank) continue;
+    const unsigned char* slot = p.xbase + p.xargmax + 16 * (size_t)r;
+    uint2 a, b;
+    uint32_t spins = 0;
+    for (;;) {
+      a = ld_volatile8(slot); b = ld_volatile8(slot + 8);
+      if (a.y == fl && b.y == fl) break;
+      if ((++spins & 63u) == 0) {
+        if (ld_relaxed(sm.ctrl) != 0) { *(volatile int*)sm.stop = 1; return; }
+        if ((spins & 1023u) == 0 && globaltimer() > *sm.deadline) {
+          if (atomicOr(sm.ctrl, ETXB_CTRL_TIMEOUT) == 0) { sm.ctrl[1] = sm.cur; sm.ctrl[2] = -100 - r; sm.ctrl[3] = (int32_t)(a.y >> 16); sm.ctrl[4] = (int32_t)(fl >> 16); }
+          *(volatile int*)sm.stop = 1;
+          return;
+        }
+        __nanosleep(32);
+      }
+    }
+    const float ov = __uint_as_float(a.x);
+    const int oi = (int)b.x;
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+}
+
+__device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm) {
+  const etxb_stepv& S = p.step;
   float bv = -INFINITY; int bi = 0x7fffffff;
   const uint4* lg4 = (const uint4*)S.logits;
   const int n4 = S.V / 8;
@@ -62,6 +108,7 @@ __device__ __forceinline__ void tile_argmax(const etxb_stepv& S, const Smem& sm)
   if (tidx() == 0) {
     for (int w = 1; w < ETXB_NWARPS; ++w)
       if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    if (p.n_peers > 0 && p.xargmax != 0u) argmax_exchange(p, sm, bv, bi);
     const int t = S.tok;
     S.token_out[t] = bi;
     if (S.write_next) S.token_in[t + 1] = bi;
@@ -128,7 +175,7 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
   switch (c->r.body) {
     case 0: break;
     case 1: tile_prologue(p.step); break;
-    case 2: tile_argmax(p.step, sm); break;
+    case 2: tile_argmax(p, sm); break;
     case 3: tile_gemv<LEAN>(args, c0, sm, n, cur); break;
     case 4: tile_moe_up<LEAN>(args, c0, sm, n, cur); break;
     case 5: tile_moe_down<LEAN>(args, c0, sm, n, cur); break;

@@ -79,7 +79,7 @@ class DecodeProgram:
         self.plan = compile_graph(self.graph, self.machine, {"POOL": len(pool)}, options=PassOptions(workers=workers))
         self.session = Session(self.plan, {"vl": self.vl}, pool, device)
         b = self.buf
-        self.session.set_step(tok=0, pos=0, write_next=0, H=dims.H, V=dims.V, nrep=1, embed=self.w["embed"], resid=b["resid"],
+        self.session.set_step(tok=0, pos=0, write_next=0, H=dims.H, V=dims.lm_rows, nrep=1, embed=self.w["embed"], resid=b["resid"],
                               positions=b["positions"], seq_lens=b["seq_lens"], slot_mapping=b["slot_mapping"], logits=b["logits"],
                               token_in=b["token_in"], token_out=b["token_out"], token_time=b["token_time"])
 
@@ -88,6 +88,8 @@ class DecodeProgram:
         rank steps before every rank is connected, the ranks step in lock step."""
         self.region.connect(self.rank, handles)
         self.session.set_exchange(self.rank, self.ranks, self.region)
+        if self.d.VL:                                            # lm_head split by vocabulary: the argmax tile exchanges (max, index) pairs
+            self.session.set_option("exchange_argmax_offset", Q.argmax_offset(self.d, self.ranks))
 
     # ---- KV cache helpers (contiguous [ctx][NKV][HD] <-> the paged layout)
     def load_kv(self, layer: int, K: np.ndarray, V: np.ndarray):

@@ -67,6 +67,11 @@ class Dims:
     TOPK: int = 0
     MI: int = 0
     norm_topk: bool = False
+    VL: int = 0            # rows of the lm_head this rank holds when a sharded model splits it by vocabulary (0: all V)
+
+    @property
+    def lm_rows(self) -> int:
+        return self.VL or self.V
 
     @property
     def G(self) -> int:
@@ -124,9 +129,10 @@ def rope_table(theta: float, hd: int, maxlen: int) -> np.ndarray:
 
 
 # ------------------------------------------------------------------------------------------------ sharding
-def shard_dims(d: Dims, ranks: int) -> Dims:
-    """The model one of `ranks` tensor-parallel ranks runs: its share of the q and kv heads and of the MLP (or of every
-    expert's) intermediate rows; hidden size, vocabulary, experts and router stay whole."""
+def shard_dims(d: Dims, ranks: int, shard_vocab: bool = True) -> Dims:
+    """The model one of `ranks` tensor-parallel ranks runs: its share of the q and kv heads, of the MLP (or of every
+    expert's) intermediate rows and -- shard_vocab, when the vocabulary splits into multiples of 8 -- of the lm_head's
+    rows; hidden size, embedding, experts and router stay whole."""
     from dataclasses import replace
     if ranks == 1:
         return d
@@ -134,15 +140,22 @@ def shard_dims(d: Dims, ranks: int) -> Dims:
     if d.NH % ranks or d.NKV % ranks or mi % ranks or (mi // ranks) % 8:
         raise ValueError(f"{d.name}: {d.NH} q heads / {d.NKV} kv heads / {mi} intermediate rows do not split {ranks} ways")
     return replace(d, name=f"{d.name}/tp{ranks}", NH=d.NH // ranks, NKV=d.NKV // ranks, MI=d.MI // ranks if d.moe else d.MI,
-                   INTER=d.INTER if d.moe else d.INTER // ranks)
+                   INTER=d.INTER if d.moe else d.INTER // ranks, VL=d.V // ranks if shard_vocab and d.V % (8 * ranks) == 0 else 0)
 
 
 def exchange_bytes(d: Dims, ranks: int) -> int:
     """Size of a rank's exchange region: per layer one [ranks][H] block of flagged 4-byte words for o_proj and one for down."""
+    return 2 * d.L * ranks * d.H * 4 + ARGMAX_BLOCK
+
+
+ARGMAX_BLOCK = 256         # tail of a region: [ranks] 16-byte slots of the sharded argmax (exchange_argmax_offset)
+
+
+def argmax_offset(d: Dims, ranks: int) -> int:
     return 2 * d.L * ranks * d.H * 4
 
 
-def shard_weights(w: dict, d: Dims, ranks: int, rank: int) -> dict:
+def shard_weights(w: dict, d: Dims, ranks: int, rank: int, shard_vocab: bool = True) -> dict:
     """Packed weights of the whole model `d` (weight_shapes) -> those of rank `rank` of shard_dims(d, ranks): q / k / v rows
     and gate / up rows by columns of the output (column-parallel), o_proj and down by columns of the input
     (row-parallel), everything else replicated.  Works on numpy arrays and torch tensors alike."""
@@ -155,6 +168,7 @@ def shard_weights(w: dict, d: Dims, ranks: int, rank: int) -> dict:
     ql, kl = nq // ranks, nk // ranks
     mi = d.MI if d.moe else d.INTER
     ml = mi // ranks
+    vl = shard_dims(d, ranks, shard_vocab).VL
     out = {}
     for name, a in w.items():
         kind = name.rsplit(".", 1)[-1]
@@ -168,6 +182,8 @@ def shard_weights(w: dict, d: Dims, ranks: int, rank: int) -> dict:
             a = cat([a[rank * ml:(rank + 1) * ml], a[mi + rank * ml:mi + (rank + 1) * ml]], 0)
         elif kind in ("w2", "wd"):
             a = cont(a[..., rank * ml:(rank + 1) * ml])
+        elif name == "lm_head" and vl:
+            a = a[rank * vl:(rank + 1) * vl]
         out[name] = a
     return out
 
@@ -210,7 +226,7 @@ def size_for(d: Dims, m: MachineModel, maxlen: int) -> Sizing:
         return best[1:]
     dt, drpt = m.gemv_tasks(d.H)
     return Sizing(workers=W, qkv=m.gemv_tasks(d.NQKV), o=m.gemv_tasks(d.H), router=m.gemv_tasks(d.E) if d.moe else (0, 0),
-                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.V, waves=1), parts=-(-maxlen // m.attention_part()),
+                  up=up_split(), down=(dt, drpt), lm=m.gemv_tasks(d.lm_rows, waves=1), parts=-(-maxlen // m.attention_part()),
                   attn=m.attention_groups(d.NH, d.NKV, d.HD, BS, maxlen))
 
 
@@ -238,7 +254,7 @@ def weight_shapes(d: Dims, maxlen: int) -> dict:
     """name -> shape of every packed weight tensor (bf16); per-layer names are prefixed "<layer>."."""
     s = {"embed": (d.V, d.H), "final_norm": (d.H,), "cos_sin": (maxlen, d.HD)}
     if not d.tie:
-        s["lm_head"] = (d.V, d.H)
+        s["lm_head"] = (d.lm_rows, d.H)
     for L in range(d.L):
         p = f"{L}."
         s[p + "ln1"], s[p + "ln2"] = (d.H,), (d.H,)
@@ -483,10 +499,12 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
             prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="", exchange=True)
     # ---- lm_head with the final-norm fold, then greedy sampling
     t, rpt = sz.lm
-    blob = gemv_block("dsl_gemv_fold", t, W=ptr("embed") if d.tie else ptr("lm_head"), x=ptr("hn"), out=ptr("logits"), M=d.V, K=d.H, rpt=rpt,
+    # (a sharded lm_head: this rank's d.VL rows -- of the whole embedding when the weights are tied -- and its logits only)
+    blob = gemv_block("dsl_gemv_fold", t, W=ptr("embed") + (rank * d.VL * d.H * 2 if d.VL else 0) if d.tie else ptr("lm_head"), x=ptr("hn"),
+                      out=ptr("logits"), M=d.lm_rows, K=d.H, rpt=rpt,
                       tpe=1, rows=xblock(d.L - 1, 1) or ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=ranks, eps=d.eps,
                       ids=0, mode=op_gemv.MODE_NORM | xmode, nb=1)
-    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.V, d.H, after="")
+    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.lm_rows, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},
                   out_edges={"E_argmax": "i->i"}, duration_us=8.5)

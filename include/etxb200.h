@@ -142,7 +142,11 @@ int32_t etxb_status(etxb_session* s, etxb_status_t* out);
  * for r != rank; entry `rank` is ignored).  All ranks must run the same steps; a rank whose peers stop publishing
  * returns ETXB_E_TIMEOUT at its deadline.  Every rank must have finished its last step before any rank frees or
  * closes a region (a running peer still stores into it).  etxb_launch_unfused is refused on a sharded session, and
- * etxb_launch on a rank's plan that has no exchange set. */
+ * etxb_launch on a rank's plan that has no exchange set.
+ * lm_head split by vocabulary: each rank's step parameters name its own V / n_ranks logits; after etxb_set_exchange,
+ * etxb_set_option(s, "exchange_argmax_offset", off) names n_ranks x 16 bytes of every region where the argmax tile
+ * exchanges the ranks' (maximum, global index) pairs as 8-byte (payload, step flag) stores and picks the same token
+ * on every rank. */
 #define ETXB_IPC_HANDLE_BYTES 64
 int32_t etxb_exchange_alloc(int device, size_t bytes, void** dev_ptr, unsigned char* handle /*[64]*/);
 int32_t etxb_exchange_free(int device, void* dev_ptr);

@@ -112,7 +112,9 @@ def test_rank_graph_is_a_valid_single_device_program_with_flagged_grids(od):
     assert field("qkv_0", 96, "<i") == 0 and not field("qkv_0", 104, "<i") & FL
     assert field("qkv_1", 64, "<Q") == blk(0, 1) and field("qkv_1", 96, "<i") == ranks and field("qkv_1", 104, "<i") & FL
     assert field("lm_head", 64, "<Q") == blk(sd.L - 1, 1) and field("lm_head", 96, "<i") == ranks
-    assert Q.exchange_bytes(sd, ranks) == blk(sd.L, 0) - base["xrows"]
+    assert Q.argmax_offset(sd, ranks) == blk(sd.L, 0) - base["xrows"] and Q.exchange_bytes(sd, ranks) == Q.argmax_offset(sd, ranks) + Q.ARGMAX_BLOCK
+    # the lm_head is split by vocabulary: this rank's rows and logits only
+    assert sd.VL == sd.V // ranks and field("lm_head", 48, "<i") == sd.VL
 
 
 def _worker(rank, world, port, q):
