@@ -108,8 +108,12 @@ static int select_variant(const etxb_session* s, const std::vector<unsigned char
 
 // The kernel variants: index 0 = the full kernel, 1..4 = the lean decode kernels for grouped attention with 1, 2, 4, 8
 // q heads per task (etxb_kernel.cuh, run_body).
-static const void* const g_kernels[5] = {(const void*)etxb::etxb_megakernel<0>, (const void*)etxb::etxb_megakernel<1>, (const void*)etxb::etxb_megakernel<2>,
-                                         (const void*)etxb::etxb_megakernel<4>, (const void*)etxb::etxb_megakernel<8>};
+// Entries 5..9: the same five with the exchange code of a sharded session compiled in (launch_kernel adds 5).
+static const void* const g_kernels[10] = {(const void*)etxb::etxb_megakernel<0>, (const void*)etxb::etxb_megakernel<1>, (const void*)etxb::etxb_megakernel<2>,
+                                          (const void*)etxb::etxb_megakernel<4>, (const void*)etxb::etxb_megakernel<8>,
+                                          (const void*)etxb::etxb_megakernel<0, true>, (const void*)etxb::etxb_megakernel<1, true>,
+                                          (const void*)etxb::etxb_megakernel<2, true>, (const void*)etxb::etxb_megakernel<4, true>,
+                                          (const void*)etxb::etxb_megakernel<8, true>};
 
 static int32_t prepare_kernel(int device, int* workers_out) {
   CU(cudaSetDevice(device));
@@ -491,7 +495,7 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   etxb_params p;
   fill_params(s, p);
   CU(cudaEventRecord(s->ev0, s->stream));
-  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->n_ranks > 1 ? 5 : 0));
   if (rc) return rc;
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
@@ -517,7 +521,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   for (uint32_t t = 0; t < s->h.n_types; ++t) {
     p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
-    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, s->force_full ? 0 : s->variant);
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->n_ranks > 1 ? 5 : 0));
     if (rc) return rc;
   }
   CU(cudaEventRecord(s->ev1, s->stream));

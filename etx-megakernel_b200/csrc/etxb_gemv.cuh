@@ -319,12 +319,14 @@ __device__ __forceinline__ void stage_xb(const void* x, int K, __nv_bfloat16* xb
 // fl != 0 (sharded model): `rows` holds R rows of K flagged words published by the ranks (row r by rank r); every word is
 // re-read until its flag is `fl` (bounded like every wait: on a give-up the step is abandoned through sm.stop), then the
 // rows are added in rank order -- every rank adds the same values in the same order and gets the same bits.
-template <bool LEAN>
+// XCH: the kernel variant of a sharded session; without it the flagged form is compiled out (the single-GPU kernels
+// carry none of the exchange code: it cost them about 5 % when it was a run-time branch).
+template <bool LEAN, bool XCH = false>
 __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, void* rout, void* xout, const void* ln,
                                             const int32_t* ids, int R, int K, float eps, float* xf, __nv_bfloat16* xb, float* scr, bool store,
                                             uint32_t fl = 0u, const Smem* smp = nullptr) {
   int* order = (int*)(scr + 64);
-  if (!LEAN && R > 1 && fl == 0u) {
+  if (!LEAN && R > 1 && (!XCH || fl == 0u)) {
     if (tidx() < R) {
       int rank = tidx();
       if (ids) {
@@ -350,7 +352,7 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
     if (rows == nullptr || R == 0) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) z[j] = rf[j];
-    } else if (fl != 0u) {
+    } else if (XCH && fl != 0u) {
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -430,7 +432,7 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
 }
 
 // ---------------------------------------------------------------------------------------------- plain / folded GEMV
-template <bool LEAN>
+template <bool LEAN, bool XCH = false>
 __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(3, d, blk);
@@ -438,8 +440,8 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
   const int r0 = t.r0;
   __nv_bfloat16* xb = smem_xb(sm);
   if ((d.mode & 0xff) == ETXB_MODE_NORM)
-    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0,
-                         (d.mode & ETXB_MODE_FLAGGED) ? row_flag(sm.epoch) : 0u, &sm);
+    stage_norm_col<LEAN, XCH>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, d.ids, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0,
+                              (XCH && (d.mode & ETXB_MODE_FLAGGED)) ? row_flag(sm.epoch) : 0u, &sm);
   else
     stage_xb(d.x, d.K, xb);
   const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
@@ -453,7 +455,7 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
 // ---------------------------------------------------------------------------------------------- MoE gate+up
 // task blk: expert slots [group * spt, ...), row chunk j = blk % tpe; expert e = ids[slot] (no ids and no fold: expert
 // 0, the dense SwiGLU MLP); act[slot][r] = bf16(bf16(silu(bf16 g)) * bf16 u), g = W_e[r,:].x, u = W_e[M + r,:].x.
-template <bool LEAN>
+template <bool LEAN, bool XCH = false>
 __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(4, d, blk);
@@ -472,8 +474,8 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
   }
   __nv_bfloat16* xb = smem_xb(sm);
   if (fold == ETXB_MODE_NORM)                                      // dense MLP: the post-attention norm folded in
-    stage_norm_col<LEAN>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0,
-                         (d.mode & ETXB_MODE_FLAGGED) ? row_flag(sm.epoch) : 0u, &sm);
+    stage_norm_col<LEAN, XCH>(d.rows, d.resid_in, d.resid_out, (void*)d.x, d.ln, nullptr, d.R, d.K, d.eps, sm.xs, xb, sm.scr, blk == 0,
+                              (XCH && (d.mode & ETXB_MODE_FLAGGED)) ? row_flag(sm.epoch) : 0u, &sm);
   else
     stage_xb(d.x, d.K, xb);
   float* g = smem_g(sm);                                           // per slot: n gate results, then n up results

@@ -71,6 +71,7 @@ __device__ __noinline__ void argmax_exchange(const etxb_params& p, const Smem& s
   }
 }
 
+template <bool XCH>
 __device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm) {
   const etxb_stepv& S = p.step;
   float bv = -INFINITY; int bi = 0x7fffffff;
@@ -108,7 +109,7 @@ __device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm
   if (tidx() == 0) {
     for (int w = 1; w < ETXB_NWARPS; ++w)
       if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
-    if (p.n_peers > 0 && p.xargmax != 0u) argmax_exchange(p, sm, bv, bi);
+    if constexpr (XCH) { if (p.n_peers > 0 && p.xargmax != 0u) argmax_exchange(p, sm, bv, bi); }
     const int t = S.tok;
     S.token_out[t] = bi;
     if (S.write_next) S.token_in[t + 1] = bi;
@@ -167,7 +168,7 @@ __device__ __forceinline__ void fetch_ctx(const etxb_params& p, TaskCtx* ctx, in
 // grouped attention tile with GQV q heads per task).  The host picks it from the plan (select_variant): the full
 // kernel is 550 KB of code, of which a decode step uses a fraction scattered through it, and the step runs about 10 %
 // faster from the 150 KB kernel (instruction fetch).
-template <int GQV>
+template <int GQV, bool XCH>
 __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c, int cur, const Smem& sm, uint32_t& n) {
   const unsigned char* args = c->args;
   const int c0 = c->r.c0, c1 = c->r.c1;
@@ -175,9 +176,9 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
   switch (c->r.body) {
     case 0: break;
     case 1: tile_prologue(p.step); break;
-    case 2: tile_argmax(p, sm); break;
-    case 3: tile_gemv<LEAN>(args, c0, sm, n, cur); break;
-    case 4: tile_moe_up<LEAN>(args, c0, sm, n, cur); break;
+    case 2: tile_argmax<XCH>(p, sm); break;
+    case 3: tile_gemv<LEAN, XCH>(args, c0, sm, n, cur); break;
+    case 4: tile_moe_up<LEAN, XCH>(args, c0, sm, n, cur); break;
     case 5: tile_moe_down<LEAN>(args, c0, sm, n, cur); break;
     case 12:
       if constexpr (LEAN) { if (c0 < (int)((const etxb_attnf_args*)args)->nblocks) attn_gq_impl<GQV ? GQV : 1>(*(const etxb_attnf_args*)args, c0, sm, p.step); }
@@ -242,7 +243,7 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
   }
 }
 
-template <int GQV>
+template <int GQV, bool XCH = false>
 __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_constant__ etxb_params p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int s_stop;
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   sm.ctrl = p.ctrl;
   sm.stop = &s_stop;
   sm.tr = nullptr;
-  sm.epoch = p.epoch;
+  if constexpr (XCH) sm.epoch = p.epoch;
   if (threadIdx.x == 0) {
     s_stop = 0;
     s_deadline = globaltimer() + p.timeout_ns;
@@ -303,16 +304,16 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     if (s_stop) break;
     if (fetcher) fetch_ctx(p, ctx, q0, cur + 2 < q1 ? cur + 2 : -1, cur + 1 < q1 ? cur + 1 : -1);   // asynchronous
     sm.tr = p.trace ? p.trace + 8 * (size_t)c->r.id : nullptr;
-    sm.cur = cur;
-    run_body<GQV>(p, c, cur, sm, n);
+    if constexpr (XCH) sm.cur = cur;
+    run_body<GQV, XCH>(p, c, cur, sm, n);
     if (fetcher) cp_async_wait_all();
     csync();                                                       // every consumer thread's stores are issued, the next contexts landed
     // Sharded model: warp 1 publishes the bf16 rows this task wrote as flagged words (value | this step's flag) into the
     // grid's block of every rank's exchange region, its own included -- plain 4-byte stores, over NVLink for the peers.
     // Value and flag travel in one word, so nothing has to be ordered: no fence, no barrier, no remote counter; the
     // arrival below only tells this rank's consumers that the local phase is over, the folds then poll the flags.
-    const uint32_t mirror = c->r.mirror;                             // 0 unless the session is sharded and the grid exchanged
-    if (mirror != 0u && (threadIdx.x >> 5) == 1) {
+    const uint32_t mirror = XCH ? c->r.mirror : 0u;                  // 0 unless the grid is exchanged
+    if (XCH && mirror != 0u && (threadIdx.x >> 5) == 1) {
       const etxb_gemv_args& d = *(const etxb_gemv_args*)c->args;
       const int r0 = (c->r.body == 3 ? c->r.c0 : c->r.c0 % d.tpe) * d.rpt;
       const unsigned short* src = (const unsigned short*)d.out + r0;
