@@ -75,7 +75,7 @@ static int g_sm_count[64];
 
 // Which kernel can run this plan?  The lean decode kernels hold only the tiles of a fused decode step; a plan qualifies
 // when every grid is one of those tiles with its argument block in the pool (one block per grid) and the blocks stay
-// inside what the lean forms cover: norm folds of at most one row, top-k folds over at most 128 experts, grouped
+// inside what the lean forms cover: norm folds of at most one row (or the flagged rows of a sharded model), top-k folds over at most 128 experts, grouped
 // attention (head_dim 128, cache blocks of 16, partitions of 128) with the same group size everywhere.
 static int select_variant(const etxb_session* s, const std::vector<unsigned char>& pool) {
   int gq = 0;

@@ -168,6 +168,8 @@ __device__ __forceinline__ void fetch_ctx(const etxb_params& p, TaskCtx* ctx, in
 // grouped attention tile with GQV q heads per task).  The host picks it from the plan (select_variant): the full
 // kernel is 550 KB of code, of which a decode step uses a fraction scattered through it, and the step runs about 10 %
 // faster from the 150 KB kernel (instruction fetch).
+// XCH: the variants a sharded session launches -- the same bodies plus the exchange code (flagged-row folds of R = ranks
+// rows, row publishing after the body, the argmax exchange); compiled out of the others.
 template <int GQV, bool XCH>
 __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c, int cur, const Smem& sm, uint32_t& n) {
   const unsigned char* args = c->args;
