@@ -10,8 +10,9 @@ device), e2e = the same through the C ABI's host-buffer decode (token id host->d
 roofline = algorithmic bytes of a step / measured launch time against the measured HBM copy peak, cpu_baseline = the
 oracle (numpy restatement of the reference's CPU path) timed on this box's cores on a bounded sample.
 With --impl reference the CPU path itself is the thing measured (same metric / config), on rank 0 only.
-N > 1: N independent replicas (one process per GPU, no collective); --shard tp runs ONE request sharded over the N GPUs
-instead (tensor parallel: the ranks exchange partial rows inside the kernel).
+N > 1: ONE request sharded over the N GPUs (tensor parallel: the ranks exchange partial rows inside the kernel; strong
+scaling, value = the request's ms/token); --shard replicas runs N independent requests instead (no exchange; value stays
+one request's ms/token, the job's aggregate tokens/s is in config).
 """
 from __future__ import annotations
 
@@ -30,6 +31,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 METRIC, UNIT = "decode_ms_per_token_bs1", "ms/token"
+DRAM_TRAFFIC_CAPTURE = (862.12e6, 854.11e6)   # (dram bytes read + written, algorithmic bytes) of the captured 2-layer launch
 MODEL = "qwen3-30b-a3b"          # the configuration the metric is quoted on; --model qwen3-8b reports the dense config beside it
 
 
@@ -127,12 +129,30 @@ def oracle_sample(dims_cfg, layers_total: int, context: int, get_layer_weights, 
     return ms, f"{len(layer_s)} decode steps of {ls} layers + lm_head at context {context}, median per-layer time x {layers_total} layers"
 
 
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def use_all_cores() -> int:
+    """Give numpy's BLAS every core this process may run on (a launcher such as torchrun exports OMP_NUM_THREADS=1, which
+    would otherwise pin the CPU arm to one thread) and return the thread count it then reports."""
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+        threadpool_limits(limits=host_cores())
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        return 1
+
+
 def blas_threads() -> int:
     try:
         from threadpoolctl import threadpool_info
-        return max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
     except Exception:
-        return os.cpu_count() or 1
+        return 1
 
 
 def run_reference(args, rank: int, world: int):
@@ -140,6 +160,7 @@ def run_reference(args, rank: int, world: int):
     if rank != 0:
         return
     from oracle import ref_decode as O
+    use_all_cores()
     cfg = oracle_cfg(O)
     layers_total = args.layers or cfg["num_hidden_layers"]
     od = O.dims_from_config(cfg, MODEL, layers=2)
@@ -182,7 +203,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     d = Q.load_dims(MODEL, layers=args.layers or None)
     P, K, Wm = args.prompt, args.steps, args.warmup
     maxlen = ((P + Wm + K + 40 + 15) // 16) * 16
-    tp = world if (args.shard == "tp" and world > 1) else 1
+    tp, why_not = 1, None
+    if world > 1 and args.shard in ("auto", "tp"):
+        try:
+            Q.shard_dims(d, world)
+            tp = world
+        except ValueError as e:                                            # the model does not split this many ways
+            if args.shard == "tp":
+                raise
+            why_not = str(e)
     if tp > 1:
         # one request over all ranks: every rank draws the whole model from the same seed, keeps its shard, and the ranks
         # meet inside the kernel at the row-parallel grids (no collective library call on the data path)
@@ -260,20 +289,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ledger = O.step_bytes(O.dims_from_config(oracle_cfg(O), MODEL, layers=d.L), ctx)
     peak, peak_src = measured_peaks()
     achieved = ledger["total"] / (dev_ms * 1e-3) / 1e9
-    # DRAM bytes per launch: dram__bytes_read + write of one ncu capture on the 2-layer case (862.12 MB against 854.11 MB
-    # algorithmic, profiles/megakernel_qwen3-30b-a3b_2layers_ctx1024.md), scaled by the algorithmic bytes of this launch
-    traffic = ledger["total"] * (862.12 / 854.11)
+    # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on a 2-layer
+    # model (DRAM_TRAFFIC_CAPTURE: measured bytes, algorithmic bytes of the captured launch), scaled to this launch by its
+    # algorithmic bytes -- a capture of the 61 GB launch itself is outside what a profiler run should hold
+    traffic = ledger["total"] * (DRAM_TRAFFIC_CAPTURE[0] / DRAM_TRAFFIC_CAPTURE[1])
     jobs = 1 if tp > 1 else world                                                # sequences decoded at once by the whole job
     peak_all = peak * (tp if tp > 1 else 1)
-    line = {"metric": METRIC, "value": dev_ms / jobs, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms,
+    line = {"metric": METRIC, "value": dev_ms, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms,
             "higher_is_better": False, "scaling": "strong" if tp > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload(d.L, P), "prefill": "the prompt is fed token by token through the same kernel",
-                       "context": ctx, "parallelism": "single" if world == 1 else f"tp{tp} (one request, in-kernel exchange)" if tp > 1 else f"replicas x{world}", "norm_gamma": "ones", "l2": f"each step streams {ledger['total'] / 1e9:.1f} GB (> 126 MB L2)",
+                       "context": ctx, "parallelism": "single" if world == 1 else f"tp{tp} (one request over {tp} GPUs, in-kernel exchange of partial rows"
+                                      + (f", kv heads replicated x{Q.kv_replication(d, tp)}" if Q.kv_replication(d, tp) > 1 else "") + ")" if tp > 1
+                       else f"replicas x{world} (independent requests; value is one request's latency" + (f"; not sharded: {why_not}" if why_not else "") + ")",
+                       "norm_gamma": "ones", "l2": f"each step streams {ledger['total'] / 1e9:.1f} GB (> 126 MB L2)",
                        "tokens_per_s": 1000.0 / dev_ms * jobs, "prefill_s": round(prefill_s, 2), "host_tokens_equal_device_tokens": same_tokens,
                        "unfused_baseline": {"ms_per_token": unfused_ms, "launches_per_token": len(prog.plan.graph.grids), "steps": Ku,
                                             "same_tokens": bool(np.array_equal(gen_unfused, gen_dev[1:Ku + 1])),
                                             "what": "the same tiles, one kernel launch per grid on one stream"}},
-            "e2e": {"value": host_ms / jobs, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
+            "e2e": {"value": host_ms, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": K, "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak_all, "unit": "GB/s", "frac": achieved / peak_all, "traffic": traffic,
                          "peak_source": peak_src, "algorithmic_bytes_per_launch": ledger["total"], "kernel": "etxb_megakernel"}}
@@ -303,8 +336,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (debugging only; 0 = all)")
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--shard", default="replicas", choices=["replicas", "tp"],
-                    help="N > 1: N independent requests (default, weak scaling) or ONE request sharded over the N GPUs (tensor parallel, strong scaling)")
+    ap.add_argument("--shard", default="auto", choices=["auto", "tp", "replicas"],
+                    help="N > 1: ONE request sharded over the N GPUs (tp; auto = tp when the model splits N ways, else replicas) or N independent requests (replicas)")
     a = ap.parse_args()
     globals()["MODEL"] = a.model
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))

@@ -11,30 +11,44 @@ from dataclasses import dataclass, field
 SCHEMA_VERSION = 1
 
 
-def _json_value(v):
-    if v is None or type(v) in (str, bool, int):
-        return v
-    if type(v) is float and math.isfinite(v):
-        return v
-    if isinstance(v, Mapping):
-        if any(type(k) is not str for k in v):
-            raise ValueError("configuration keys must be strings")
-        return {k: _json_value(x) for k, x in v.items()}
-    if isinstance(v, (list, tuple)):
-        return [_json_value(x) for x in v]
-    raise ValueError(f"configuration requires finite JSON values, got {type(v).__name__}")
+_SCALARS = (str, bool, int)
+
+
+def canonical(value, where: str = "configuration"):
+    """`value` rebuilt from plain JSON types only (dict with string keys, list, str, bool, int, finite float, None);
+    anything else is refused.  Exact types are required for the scalars: a subclass could carry state JSON would drop."""
+    stack_free = value is None or type(value) in _SCALARS or (type(value) is float and math.isfinite(value))
+    if stack_free:
+        return value
+    if isinstance(value, Mapping):
+        out = {}
+        for key, item in value.items():
+            if type(key) is not str:
+                raise ValueError(f"{where} keys must be strings")
+            out[key] = canonical(item, where)
+        return out
+    if isinstance(value, (list, tuple)):
+        return [canonical(item, where) for item in value]
+    raise ValueError(f"{where} requires finite JSON values, got {type(value).__name__}")
+
+
+def _dumps(value) -> str:
+    """The canonical text of a JSON value: sorted keys, no blanks, no NaN -- equal values give equal text."""
+    return json.dumps(value, sort_keys=True, separators=(",", ":"), allow_nan=False)
 
 
 class Configuration(Mapping):
-    """Immutable JSON value store; what it returns are detached copies."""
+    """An immutable JSON value: stored as its canonical text, handed out as detached copies."""
+
+    __slots__ = ("_text",)
 
     def __init__(self, values: Mapping):
         if not isinstance(values, Mapping):
             raise ValueError("configuration must be a mapping")
-        self._json = json.dumps(_json_value(values), sort_keys=True, separators=(",", ":"), allow_nan=False)
+        self._text = _dumps(canonical(values))
 
     def to_dict(self) -> dict:
-        return json.loads(self._json)
+        return json.loads(self._text)
 
     def __getitem__(self, key):
         return self.to_dict()[key]
@@ -46,19 +60,31 @@ class Configuration(Mapping):
         return len(self.to_dict())
 
     def __eq__(self, other):
-        return isinstance(other, Configuration) and other._json == self._json
+        return isinstance(other, Configuration) and self._text == other._text
 
     def __hash__(self):
-        return hash(self._json)
+        return hash(self._text)
 
 
-def _name(v):
-    if type(v) is not str or not v or v != v.strip():
-        raise ValueError("name must be a nonempty string without surrounding whitespace")
+def _require_name(value, what: str = "name"):
+    ok = type(value) is str and value != "" and value == value.strip()
+    if not ok:
+        raise ValueError(f"{what} must be a nonempty string without surrounding whitespace")
+
+
+def _require_schema(value, what: str):
+    if type(value) is not int or value != SCHEMA_VERSION:
+        raise ValueError(f"unsupported {what} schema")
+
+
+def _freeze(record, *names):
+    """Replace the named fields of a frozen record by Configuration copies."""
+    for n in names:
+        object.__setattr__(record, n, Configuration(getattr(record, n)))
 
 
 def _digest(d: dict) -> str:
-    return hashlib.sha256(json.dumps(d, sort_keys=True, separators=(",", ":"), allow_nan=False).encode()).hexdigest()
+    return hashlib.sha256(_dumps(d).encode()).hexdigest()
 
 
 @dataclass(frozen=True)
@@ -68,13 +94,14 @@ class WorkloadSpec:
     config: Configuration
     schema_version: int = SCHEMA_VERSION
 
+    KINDS = ("model", "graph", "imported", "native")
+
     def __post_init__(self):
-        _name(self.name)
-        if self.kind not in ("model", "graph", "imported", "native"):
+        _require_name(self.name)
+        _require_schema(self.schema_version, "workload")
+        if self.kind not in self.KINDS:
             raise ValueError("unknown workload kind")
-        if type(self.schema_version) is not int or self.schema_version != SCHEMA_VERSION:
-            raise ValueError("unsupported workload schema")
-        object.__setattr__(self, "config", Configuration(self.config))
+        _freeze(self, "config")
 
     def to_dict(self) -> dict:
         return dict(schema_version=self.schema_version, name=self.name, kind=self.kind, config=self.config.to_dict())
@@ -101,11 +128,11 @@ class PlanRequest:
     def __post_init__(self):
         if not isinstance(self.workload, WorkloadSpec):
             raise TypeError("plan request requires WorkloadSpec")
-        _name(self.target)
-        for n in ("bindings", "runtime", "options"):
-            object.__setattr__(self, n, Configuration(getattr(self, n)))
-        if any(type(x) is not int or x < 0 for x in self.bindings.values()):
-            raise ValueError("bindings require nonnegative integers")
+        _require_name(self.target)
+        _freeze(self, "bindings", "runtime", "options")
+        for value in self.bindings.values():
+            if type(value) is not int or value < 0:
+                raise ValueError("bindings require nonnegative integers")
 
     def to_dict(self) -> dict:
         return dict(workload=self.workload.to_dict(), target=self.target, bindings=self.bindings.to_dict(),
@@ -125,13 +152,12 @@ class PlannedWorkload:
     def __post_init__(self):
         if not isinstance(self.request, PlanRequest):
             raise TypeError("planned workload requires PlanRequest")
-        if type(self.schema_version) is not int or self.schema_version != SCHEMA_VERSION:
-            raise ValueError("unsupported plan schema")
-        for n in ("machine", "options", "report"):
-            object.__setattr__(self, n, Configuration(getattr(self, n)))
-        if any(type(x) is not str for x in self.decisions):
+        _require_schema(self.schema_version, "plan")
+        _freeze(self, "machine", "options", "report")
+        decisions = tuple(self.decisions)
+        if not all(type(x) is str for x in decisions):
             raise ValueError("decisions require strings")
-        object.__setattr__(self, "decisions", tuple(self.decisions))
+        object.__setattr__(self, "decisions", decisions)
 
     def to_dict(self) -> dict:
         return dict(schema_version=self.schema_version, request=self.request.to_dict(), machine=self.machine.to_dict(),
@@ -164,5 +190,5 @@ class SimulationResult:
             raise ValueError("simulation results cannot claim a device backend")
         if type(self.seed) is not int or type(self.deadlock) is not bool:
             raise ValueError("invalid simulation result")
-        object.__setattr__(self, "metrics", Configuration(self.metrics))
+        _freeze(self, "metrics")
         object.__setattr__(self, "blocked", tuple(self.blocked))

@@ -73,6 +73,70 @@ static int g_kernel_ready[64];
 
 static int g_sm_count[64];
 
+// ---- argument-block checks ----------------------------------------------------------------------------------------
+// What the tiles take, checked on the host for every block that reaches the device (a plan's pool when the records are
+// built, a single-tile launch's block): a block outside these limits would make a device loop that cannot advance or
+// overrun a shared-memory region, so it is refused with ETXB_E_UNSUPPORTED before anything is launched.  The Python
+// packers check the same limits earlier (ops/gemv.py check_shape, ops/attn.py check_fused).
+static int32_t check_gemv_block(int body, const etxb_gemv_args& a) {
+  char m[256];
+  const int fold = a.mode & 0xff;
+  const int spt = ((a.mode >> 16) & 0xff) ? ((a.mode >> 16) & 0xff) : 1;
+  const char* why = nullptr;
+  if (a.K <= 0 || a.K > ETXB_XB_ELEMS || (a.K % 8)) why = "0 < K <= 12288 and K % 8 == 0 (a row fills at most one 24 KB stage)";
+  else if (a.M < 1 || a.rpt < 1) why = "M >= 1 and rpt >= 1";
+  else if (body != ETXB_BODY_GEMV && a.tpe < 1) why = "tpe >= 1";
+  else if (fold == ETXB_MODE_NORM && a.K > ETXB_XF_FLOATS) why = "a norm fold works on K <= 8192";
+  else if (fold == ETXB_MODE_NORM && (a.R < 0 || a.R > 64)) why = "a norm fold adds 0 <= R <= 64 rows";
+  else if (fold > 3) why = "mode & 0xff is 0 (plain), 1 (norm fold), 2 or 3 (top-k fold)";
+  else if (fold >= 2 && (a.E < 1 || a.E > 256 || a.R < 1 || a.R > 16 || a.R > a.E || a.logits == nullptr)) why = "a top-k fold needs logits, 1 <= E <= 256 and 1 <= R <= min(16, E)";
+  else if (body == ETXB_BODY_GEMV && (a.mode & (ETXB_MODE_SUM_SLOTS | 0xff0000))) why = "slot bits are for the MoE forms only";
+  else if (body == ETXB_BODY_MOE_UP && 2 * spt * a.rpt > ETXB_G_FLOATS) why = "gate + up results of a task: 2 * slots * rpt <= 2048";
+  else if (body == ETXB_BODY_MOE_DOWN && ((long long)spt * a.K > ETXB_XB_ELEMS || spt * a.rpt > ETXB_G_FLOATS)) why = "down: slots * K <= 12288 activations and slots * rpt <= 2048 results per task";
+  else if (body != ETXB_BODY_GEMV && spt > 16) why = "at most 16 expert slots per task";
+  else if (body != ETXB_BODY_GEMV && ((long long)((a.nblocks + (uint32_t)a.tpe - 1) / (uint32_t)a.tpe) * spt > 16)) why = "slot groups x slots per task <= 16 slots";
+  if (!why) return ETXB_OK;
+  snprintf(m, sizeof m, "GEMV-family block (body %d, M=%d, K=%d, rpt=%d, tpe=%d, R=%d, E=%d, mode=0x%x) outside the tile: %s", body, a.M, a.K, a.rpt, a.tpe, a.R, a.E, a.mode, why);
+  return fail(ETXB_E_UNSUPPORTED, m);
+}
+static int32_t check_attnf_block(const etxb_attnf_args& a) {
+  const char* why = nullptr;
+  if (a.NKV < 1 || a.NH < a.NKV || a.NH % a.NKV) why = "NH must be a positive multiple of NKV";
+  else if (a.max_parts < 1 || a.X != 8 || (a.BS != 16 && a.BS != 32)) why = "max_parts >= 1, X = 8, BS 16 or 32";
+  else if (a.gq != 0) {
+    const int G = a.NH / a.NKV;
+    if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || G % a.gq) why = "gq is 1, 2, 4 or 8 and divides NH / NKV";
+    else if (a.HD != 128 || a.BS != 16 || a.part_len != 128) why = "the grouped form is head_dim 128, cache blocks of 16, partitions of 128";
+    else if (a.gq * a.max_parts > 4096) why = "gq * max_parts <= 4096";
+    else if (a.nblocks > (uint32_t)(a.max_parts * (a.NH / a.gq))) why = "the grid is at most max_parts * NH / gq tasks";
+  } else {
+    const int G = a.NH / a.NKV;
+    if (G + 2 > ETXB_CONSUMER_WARPS || G * a.HD > 2048 || a.HD % 32 || a.HD > 256) why = "general form: G + 2 <= 16, G * HD <= 2048, HD % 32 == 0";
+    else if (G * a.max_parts > 8192) why = "G * max_parts <= 8192";
+    else if (a.nblocks > (uint32_t)(a.max_parts * a.NKV)) why = "the grid is at most max_parts * NKV tasks";
+  }
+  if (!why) return ETXB_OK;
+  char m[256];
+  snprintf(m, sizeof m, "attn_fused block (NH=%d, NKV=%d, HD=%d, BS=%d, max_parts=%d, gq=%d) outside the tile: %s", a.NH, a.NKV, a.HD, a.BS, a.max_parts, a.gq, why);
+  return fail(ETXB_E_UNSUPPORTED, m);
+}
+// A block of `body` at `blk` (`bytes` readable).  Tiles whose blocks carry no loop bound the device depends on pass.
+static int32_t check_block(int body, const unsigned char* blk, size_t bytes) {
+  if (body == ETXB_BODY_GEMV || body == ETXB_BODY_MOE_UP || body == ETXB_BODY_MOE_DOWN) {
+    if (bytes < sizeof(etxb_gemv_args)) return fail(ETXB_E_ARG, "GEMV-family tile: the argument block is 160 bytes");
+    etxb_gemv_args a;
+    memcpy(&a, blk, sizeof a);
+    return check_gemv_block(body, a);
+  }
+  if (body == ETXB_BODY_ATTN_FUSED) {
+    if (bytes < sizeof(etxb_attnf_args)) return fail(ETXB_E_ARG, "attn_fused tile: the argument block is 176 bytes");
+    etxb_attnf_args a;
+    memcpy(&a, blk, sizeof a);
+    return check_attnf_block(a);
+  }
+  return ETXB_OK;
+}
+
 // Which kernel can run this plan?  The lean decode kernels hold only the tiles of a fused decode step; a plan qualifies
 // when every grid is one of those tiles with its argument block in the pool (one block per grid) and the blocks stay
 // inside what the lean forms cover: norm folds of at most one row (or the flagged rows of a sharded model), top-k folds over at most 128 experts, grouped
@@ -418,6 +482,13 @@ static int32_t upload_type_args(etxb_session* s) {
       ta[t * ETXB_MAX_ARGS + k] = s->tensor_ptr[idx];
     }
   CU(cudaMemcpy(s->d_type_args, ta.data(), ta.size() * sizeof(void*), cudaMemcpyHostToDevice));
+  // every argument block that lives in the plan's pool is checked against the tile's limits (a block in a tensor the
+  // caller fills later cannot be read here: such a program is the caller's to check)
+  for (const etxb_type& ty : s->types) {
+    if (ty.args[0] != 0 || ty.cst[0] < 0 || (size_t)ty.cst[0] >= s->h_pool.size()) continue;
+    int32_t rc = check_block(ty.body, s->h_pool.data() + ty.cst[0], s->h_pool.size() - (size_t)ty.cst[0]);
+    if (rc) return rc;
+  }
   // per-task records in queue order (the consumer loop prefetches them)
   std::vector<etxb_rec> recs(s->tasks.size());
   for (size_t i = 0; i < s->tasks.size(); ++i) {
@@ -541,6 +612,18 @@ static int32_t recover(etxb_session* s) {
   std::vector<int32_t> ev((size_t)s->h.n_events * ETXB_EV_STRIDE, 0);
   for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount[e]);
   if (!ev.empty()) CU(cudaMemcpy(s->d_events, ev.data(), ev.size() * 4, cudaMemcpyHostToDevice));
+  // The merge election of the fused attention grids counts arrivals in the caller's counters buffer (one int32 per kv
+  // head or q group, max_parts arrivals per step, elected when the count reaches a multiple of max_parts): a step
+  // abandoned in the middle of an attention phase leaves them off a multiple, and every later step would then elect
+  // its merging task too early.  Zero is a multiple: clear the counters of every fused attention grid of the pool.
+  for (const etxb_type& ty : s->types) {
+    if (ty.body != ETXB_BODY_ATTN_FUSED || ty.args[0] != 0 || ty.cst[0] < 0 || (size_t)ty.cst[0] + sizeof(etxb_attnf_args) > s->h_pool.size()) continue;
+    etxb_attnf_args a;
+    memcpy(&a, s->h_pool.data() + ty.cst[0], sizeof a);
+    if (a.counters == nullptr || a.NKV < 1 || a.NH < 1) continue;
+    const int n = a.gq > 0 ? a.NH / a.gq : a.NKV;
+    if (n > 0) CU(cudaMemset(a.counters, 0, (size_t)n * 4));
+  }
   CU(cudaMemset(s->d_ctrl, 0, 64));
   return ETXB_OK;
 }
@@ -662,6 +745,10 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   OpCtx& c = g_op[device];
   int32_t rc = prepare_kernel(device, &c.workers);
   if (rc) return rc;
+  if (!(body == ETXB_BODY_GEMV && bytes >= sizeof(etxb_gemv_args) && ((const etxb_gemv_args*)argblock)->nb > 1)) {
+    rc = check_block(body, (const unsigned char*)argblock, bytes);      // (the column-batched kernel checks its own limits below)
+    if (rc) return rc;
+  }
   cudaStream_t st = (cudaStream_t)cuda_stream;
   if (body == ETXB_BODY_GEMV && bytes >= sizeof(etxb_gemv_args) && ((const etxb_gemv_args*)argblock)->nb > 1) {
     // column-batched GEMV (the sweep with M = 2, 4, 8 tokens): its own kernel, one CTA per task
@@ -759,7 +846,7 @@ __global__ void __launch_bounds__(ETXB_CONSUMERS, 1) etxb_attn_static_kernel(con
   Smem sm;
   sm.xs = (float*)st_smem;
   sm.scr = (float*)(st_smem + ETXB_GEN_BYTES);
-  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.stop = nullptr; sm.tr = nullptr; sm.events = nullptr; sm.evcount = nullptr; sm.inwords = nullptr; sm.epoch = 0; sm.rec = nullptr; sm.cur = 0;
+  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.stop = nullptr; sm.tr = nullptr; sm.epoch = 0; sm.cur = 0;
   tile_attn_fused((const unsigned char*)&d, (int)blockIdx.x, sm, S);
 }
 }  // namespace etxb

@@ -295,7 +295,9 @@ __device__ __noinline__ void attn_fused_impl(const etxb_attnf_args& d, int blk, 
   }
   csync();
   mark(sm, 3);
-  if (*flag) attn_fused_merge(d, sm, h, (seq + P - 1) / P, HD);
+  // partitions that were computed: never more than the grid holds, whatever seq_lens says (a context past
+  // max_parts * 32 positions is the caller's error: the positions beyond are left out, nothing is read past the partials)
+  if (*flag) attn_fused_merge(d, sm, h, min((seq + P - 1) / P, d.max_parts), HD);
 }
 
 __device__ __forceinline__ void tile_attn_fused(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {

@@ -278,7 +278,7 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
   }
   csync();
   mark(sm, 3);
-  if (*flag) attn_gq_merge<GQ>(d, sm, hq0, (seq + PL - 1) / PL);
+  if (*flag) attn_gq_merge<GQ>(d, sm, hq0, min((seq + PL - 1) / PL, d.max_parts));   // never past the partials the grid computed
 }
 
 // Fused attention, either form: gq > 0 in the argument block selects the grouped form above (head_dim 128, cache

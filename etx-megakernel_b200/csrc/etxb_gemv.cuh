@@ -34,38 +34,13 @@ struct Smem {
   int32_t* ctrl;
   int* stop;                 // CTA-local: a wait inside a body gave up (the body's results are not to be announced)
   uint64_t* tr;              // 8 stamps of the running task when tracing, else null (slots 4..7 are in-body marks)
-  // what wait_inputs() needs, by value (reading the kernel parameters through a pointer is a global-memory access):
-  int32_t* events;           // null outside the persistent kernel: nothing to wait for
-  const int32_t* evcount;
-  const int32_t* inwords;
-  uint32_t epoch;
-  const etxb_rec* rec;       // the running task's record
+  uint32_t epoch;            // the step (sharded sessions: the flag of this step's exchanged words derives from it)
   int cur;                   // the running task's index in the queue order (reported when a wait gives up)
 };
 // in-body time stamp k (0..3) of the running task; thread 0 only, no-op unless tracing
 __device__ __forceinline__ void mark(const Smem& sm, int k) { if (sm.tr != nullptr && tidx() == 0) sm.tr[4 + k] = globaltimer(); }
 __device__ __forceinline__ __nv_bfloat16* smem_xb(const Smem& sm) { return (__nv_bfloat16*)((unsigned char*)sm.xs + ETXB_XB_OFF); }
 __device__ __forceinline__ float* smem_g(const Smem& sm) { return (float*)((unsigned char*)sm.xs + ETXB_G_OFF); }
-
-// Wait for the running task's in-events.  ONE thread calls; the others meet it at the next barrier and then read
-// *sm.stop.  Normally the kernel's task loop calls this before the body; a tile that can start loads which do not
-// depend on its inputs (the attention tile's K / V) is entered without the wait and calls it itself once those loads
-// are issued.  False: the step is being abandoned (sm.stop is set).
-__device__ __forceinline__ bool wait_inputs(const Smem& sm) {
-  bool ok = true;
-  if (sm.events != nullptr) {
-    const etxb_rec& r = *sm.rec;
-    for (int i = 0; ok && i < r.in_n; ++i) {
-      int word, cnt;
-      if (i < 4) { word = r.in_word[i]; cnt = r.in_cnt[i]; }
-      else { word = sm.inwords[r.in_off + i]; cnt = sm.evcount[word]; }
-      ok = wait_event(sm.events, sm.ctrl, word, (int32_t)(sm.epoch * (uint32_t)cnt), sm.cur, *sm.deadline);
-    }
-    if (!ok) *(volatile int*)sm.stop = 1;
-    if (sm.tr != nullptr) sm.tr[1] = globaltimer();
-  }
-  return ok;
-}
 
 // Bounded mbarrier wait: true when the phase completed; false when the step is being abandoned (another thread gave
 // up, the host aborted, or the deadline passed -- then this thread records it).
@@ -117,12 +92,15 @@ __device__ __forceinline__ void warp_topk_n(const void* logits, int E, int K, bo
   // zero probability above "no candidate" (0).  A candidate is the 64-bit pair (key, ~expert): the larger pair is the
   // larger probability or, on a tie, the lower expert.  Each lane sorts its NK candidates once (descending), so a
   // round only looks at the lane's head: two warp reductions (redux.sync) find the winner, whose lane pops its head.
-  // NaN logits are not supported.
+  // A NaN anywhere in the row makes the sum, and so every probability, NaN: no candidate is valid then and every round
+  // writes id 0x7fffffff with weight -1 (the behaviour the reference's model pins for its wave path,
+  // etx/ops/topk_key32.py:122-147; the expert tiles map such an id to expert 0 before they form an address).
   unsigned long long c[NK];
 #pragma unroll
   for (int k = 0; k < NK; ++k) {
     const int e = lane + 32 * k;
-    const uint32_t key = e < E ? __float_as_uint(__fdiv_rn(p[k], s)) + 1u : 0u;
+    const float pq = __fdiv_rn(p[k], s);
+    const uint32_t key = (e < E && pq == pq) ? __float_as_uint(pq) + 1u : 0u;
     c[k] = ((unsigned long long)key << 32) | (uint32_t)(0xffffffffu - (uint32_t)e);
   }
 #pragma unroll
@@ -225,7 +203,9 @@ __device__ __forceinline__ void gemv_routing(const etxb_gemv_args& d, int32_t* l
 __device__ __forceinline__ const unsigned char* gemv_range_base(int body, const etxb_gemv_args& d, const GemvTask& t, int i, const int32_t* lids) {
   if (body == 3) return (const unsigned char*)d.W + (size_t)t.r0 * t.row_bytes;
   const int slot = t.group * t.spt + (body == 4 ? i >> 1 : i);
-  const unsigned char* We = (const unsigned char*)d.W + (size_t)lids[slot] * d.estride * 2;
+  int e = lids[slot];
+  if (d.E > 0 && (unsigned)e >= (unsigned)d.E) e = 0;                // "no candidate" (a NaN row): never an address
+  const unsigned char* We = (const unsigned char*)d.W + (size_t)e * d.estride * 2;
   const int row = t.r0 + ((body == 4 && (i & 1)) ? d.M : 0);        // up rows follow the M gate rows
   return We + (size_t)row * t.row_bytes;
 }
@@ -238,6 +218,10 @@ __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, 
   if (total <= 0) return true;
   const int rps = ETXB_STAGE_BYTES / t.row_bytes;
   bool ok = true;
+  if (rps < 1 || t.row_bytes <= 0) {                               // a row longer than a stage: refused by the host; never loop on it
+    if ((tidx() & 31) == 0) { atomicOr(sm.ctrl, ETXB_CTRL_BADTASK); *(volatile int*)sm.stop = 1; }
+    return false;
+  }
   if ((tidx() & 31) == 0) {
     const uint64_t pol = l2_policy_evict_first();
     for (int q0 = 0; q0 < total && ok; q0 += rps) {
@@ -280,7 +264,8 @@ __device__ __forceinline__ void consume_task(int total, int rows_per_range, int 
                                              int xstride, int where, Epi epi) {
   if (total <= 0) return;
   const int lane = tidx() & 31, cw = tidx() >> 5;
-  const int rps = ETXB_STAGE_BYTES / row_bytes, nvec = row_bytes >> 4;
+  const int rps = row_bytes > 0 ? ETXB_STAGE_BYTES / row_bytes : 0, nvec = row_bytes >> 4;
+  if (rps < 1) return;                                             // (the producer raised the bad-task bit)
   bool alive = true;
   for (int q0 = 0; q0 < total; q0 += rps) {
     const uint32_t st = n % ETXB_NSTAGE, par = (n / ETXB_NSTAGE) & 1;

@@ -261,7 +261,8 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   sm.ctrl = p.ctrl;
   sm.stop = &s_stop;
   sm.tr = nullptr;
-  if constexpr (XCH) sm.epoch = p.epoch;
+  sm.epoch = p.epoch;
+  sm.cur = 0;
   if (threadIdx.x == 0) {
     s_stop = 0;
     s_deadline = globaltimer() + p.timeout_ns;
@@ -315,15 +316,15 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     // Value and flag travel in one word, so nothing has to be ordered: no fence, no barrier, no remote counter; the
     // arrival below only tells this rank's consumers that the local phase is over, the folds then poll the flags.
     const uint32_t mirror = XCH ? c->r.mirror : 0u;                  // 0 unless the grid is exchanged
-    if (XCH && mirror != 0u && (threadIdx.x >> 5) == 1) {
+    if (XCH && mirror != 0u && s_stop == 0 && (threadIdx.x >> 5) == 1) {   // (an abandoned body publishes nothing)
       const etxb_gemv_args& d = *(const etxb_gemv_args*)c->args;
       const int r0 = (c->r.body == 3 ? c->r.c0 : c->r.c0 % d.tpe) * d.rpt;
       const unsigned short* src = (const unsigned short*)d.out + r0;
       const uint32_t off = mirror & 0x3fffffu, len = mirror >> 22, fl = row_flag(p.epoch);
       for (uint32_t i = threadIdx.x & 31; i < len; i += 32) {
         const uint32_t v = (uint32_t)__ldcg(src + i) | fl;
-        for (int q = 0; q < p.n_peers; ++q) ((uint32_t*)p.xpeer[q])[off + i] = v;
-        ((uint32_t*)p.xbase)[off + i] = v;
+        for (int q = 0; q < p.n_peers; ++q) st_flagged((uint32_t*)p.xpeer[q] + off + i, v);
+        st_flagged((uint32_t*)p.xbase + off + i, v);
       }
     }
     if (threadIdx.x == 0) {

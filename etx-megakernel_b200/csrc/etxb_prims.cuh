@@ -137,6 +137,10 @@ __device__ __forceinline__ uint4 ld_act16(const void* p) { return __ldcg((const 
 // reader needs no fence and no counter: it re-reads until the flag is this step's.  The flag is never 0 (a zeroed buffer
 // is never valid) and differs from the previous step's (every buffer is rewritten once per step).
 __device__ __forceinline__ uint32_t row_flag(uint32_t epoch) { return ((epoch & 0x7fffu) | 0x8000u) << 16; }
+// (a strong store at system scope: the readers poll with volatile loads, possibly from another GPU)
+__device__ __forceinline__ void st_flagged(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint4 ld_volatile16(const void* p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");

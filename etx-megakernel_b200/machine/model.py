@@ -6,6 +6,7 @@ split and the attention partition.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any
@@ -54,17 +55,14 @@ class MachineModel:
     notes: list = field(default_factory=list)
     extra: dict = field(default_factory=dict)
 
-    # ---- topology
+    # ---- topology: the exec-domain tree is a list from the outermost level to the leaf that holds the compute units
     @property
     def leaf_domain(self) -> ExecDomain:
         return self.exec_domains[-1]
 
     @property
     def num_domains(self) -> int:
-        n = 1
-        for d in self.exec_domains:
-            n *= d.count
-        return n
+        return math.prod(level.count for level in self.exec_domains)
 
     @property
     def has_domain_level(self) -> bool:
@@ -74,53 +72,59 @@ class MachineModel:
         return self.leaf_domain.cus
 
     def total_cus(self) -> int:
-        return self.num_domains * self.cus_per_domain()
+        return self.cus_per_domain() * self.num_domains
 
-    # ---- scopes
+    # ---- scopes: an event's declared scope is lowered to the nearest level this machine really has.  A cluster scope
+    # needs cluster launch; without it, and for anything narrower than a domain, the event lives at domain level --
+    # or, on a machine that is a single domain (B200: one L2 serves every SM), at device level.
     def effective_scope(self, scope: Scope) -> Scope:
-        s = scope
-        if s == Scope.CLUSTER and not self.capabilities.get("cluster_launch", False):
-            s = Scope.DOMAIN
-        if s in (Scope.DOMAIN, Scope.WORKGROUP) and not self.has_domain_level:
-            s = Scope.DEVICE
-        elif s == Scope.WORKGROUP:
-            s = Scope.DOMAIN
-        return s
+        if scope == Scope.CLUSTER and self.capabilities.get("cluster_launch", False):
+            return scope
+        if scope in (Scope.CLUSTER, Scope.DOMAIN, Scope.WORKGROUP):
+            return Scope.DOMAIN if self.has_domain_level else Scope.DEVICE
+        return scope
 
     def vis(self, scope: Scope) -> Visibility:
-        s = self.effective_scope(scope)
-        if s not in self.visibility:
-            raise KeyError(f"{self.name}: no visibility entry for scope {s.name}")
-        return self.visibility[s]
+        lowered = self.effective_scope(scope)
+        try:
+            return self.visibility[lowered]
+        except KeyError:
+            raise KeyError(f"{self.name}: no visibility entry for scope {lowered.name}") from None
 
     def memory_for(self, scope: Scope) -> str:
-        m = self.vis(scope).memory
-        return "device" if m == "any" else m
+        kind = self.vis(scope).memory
+        return kind if kind != "any" else "device"
 
-    # ---- costs (microseconds)
+    # ---- costs (the arch file gives nanoseconds, callers get microseconds)
+    SYNC_COST_KEY = {Scope.DOMAIN: "t_local_ns", Scope.DEVICE: "t_cross_ns", Scope.SYSTEM: "t_dev_ns"}
+    SYNC_COST_GUESS_NS = {"t_local_ns": 200, "t_cross_ns": 800, "t_dev_ns": 10000}     # used (and noted) when the arch file has no figure
+
+    def _cost_ns(self, key: str, guess: float) -> float:
+        if self.costs.get(key) is None:
+            self.costs[key] = guess
+            self.notes.append(f"{self.name}: no calibrated {key}; assuming {guess} ns")
+        return float(self.costs[key])
+
     def t_sync_us(self, scope: Scope) -> float:
-        s = self.effective_scope(scope)
-        key = {Scope.DOMAIN: "t_local_ns", Scope.DEVICE: "t_cross_ns", Scope.SYSTEM: "t_dev_ns"}.get(s, "t_cross_ns")
-        if s == Scope.DEVICE and not self.has_domain_level:
-            key = "t_local_ns"
-        v = self.costs.get(key)
-        if v is None:
-            v = {"t_local_ns": 200, "t_cross_ns": 800, "t_dev_ns": 10000}[key]
-            self.notes.append(f"cost {key} uncalibrated on {self.name}; using {v} ns")
-            self.costs[key] = v
-        return float(v) / 1000.0
+        """One hand-off through an event of `scope`."""
+        lowered = self.effective_scope(scope)
+        key = self.SYNC_COST_KEY.get(lowered, "t_cross_ns")
+        if lowered == Scope.DEVICE and not self.has_domain_level:
+            key = "t_local_ns"                                             # a single-domain device pays no cross-domain hop
+        return self._cost_ns(key, self.SYNC_COST_GUESS_NS[key]) / 1e3
 
     def t_pop_us(self) -> float:
-        return float(self.costs.get("t_pop_ns", 300)) / 1000.0
+        return float(self.costs.get("t_pop_ns", 300)) / 1e3
 
     def t_push_us(self, cross_domain: bool) -> float:
-        return float(self.costs.get("t_push_ns", 300)) / 1000.0 + (self.t_sync_us(Scope.DEVICE) if cross_domain else 0.0)
+        push = float(self.costs.get("t_push_ns", 300)) / 1e3
+        return push + self.t_sync_us(Scope.DEVICE) if cross_domain else push
 
     def cache_bw_bytes_per_us(self) -> float:
-        return float(self.bandwidth.get("cache_bw_tbs", self.bandwidth["hbm_tbs"])) * 1e6
+        return 1e6 * float(self.bandwidth.get("cache_bw_tbs", self.bandwidth["hbm_tbs"]))
 
     def hbm_bw_bytes_per_us(self) -> float:
-        return float(self.bandwidth["hbm_tbs"]) * 1e6
+        return 1e6 * float(self.bandwidth["hbm_tbs"])
 
     def supports(self, cap: str) -> Any:
         return self.capabilities.get(cap, False)

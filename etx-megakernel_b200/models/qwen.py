@@ -129,17 +129,33 @@ def rope_table(theta: float, hd: int, maxlen: int) -> np.ndarray:
 
 
 # ------------------------------------------------------------------------------------------------ sharding
+def kv_replication(d: Dims, ranks: int) -> int:
+    """How many ranks hold a copy of each kv head when `d` is sharded `ranks` ways: 1 while the kv heads split evenly,
+    ranks / NKV when there are more ranks than kv heads (Qwen3-30B-A3B on 8 ranks: 4 kv heads, each on 2 ranks, which
+    hold different halves of its 8 q heads).  Raises where the heads do not split."""
+    if d.NH % ranks:
+        raise ValueError(f"{d.name}: {d.NH} q heads do not split {ranks} ways")
+    if d.NKV % ranks == 0:
+        return 1
+    qpr = d.NH // ranks                                                  # q heads per rank: all of them must share one kv head
+    if ranks % d.NKV or d.G % qpr:
+        raise ValueError(f"{d.name}: {d.NKV} kv heads neither split nor replicate over {ranks} ranks ({qpr} q heads per rank, {d.G} per kv head)")
+    return ranks // d.NKV
+
+
 def shard_dims(d: Dims, ranks: int, shard_vocab: bool = True) -> Dims:
-    """The model one of `ranks` tensor-parallel ranks runs: its share of the q and kv heads, of the MLP (or of every
-    expert's) intermediate rows and -- shard_vocab, when the vocabulary splits into multiples of 8 -- of the lm_head's
-    rows; hidden size, embedding, experts and router stay whole."""
+    """The model one of `ranks` tensor-parallel ranks runs: its share of the q heads, its kv heads (a share of them, or --
+    more ranks than kv heads -- the one kv head its q heads attend to, replicated: kv_replication), its share of the MLP
+    (or of every expert's) intermediate rows and -- shard_vocab, when the vocabulary splits into multiples of 8 -- of the
+    lm_head's rows; hidden size, embedding, experts and router stay whole."""
     from dataclasses import replace
     if ranks == 1:
         return d
     mi = d.MI if d.moe else d.INTER
-    if d.NH % ranks or d.NKV % ranks or mi % ranks or (mi // ranks) % 8:
-        raise ValueError(f"{d.name}: {d.NH} q heads / {d.NKV} kv heads / {mi} intermediate rows do not split {ranks} ways")
-    return replace(d, name=f"{d.name}/tp{ranks}", NH=d.NH // ranks, NKV=d.NKV // ranks, MI=d.MI // ranks if d.moe else d.MI,
+    rep = kv_replication(d, ranks)
+    if mi % ranks or (mi // ranks) % 8:
+        raise ValueError(f"{d.name}: {mi} intermediate rows do not split {ranks} ways into multiples of 8")
+    return replace(d, name=f"{d.name}/tp{ranks}", NH=d.NH // ranks, NKV=d.NKV // ranks if rep == 1 else 1, MI=d.MI // ranks if d.moe else d.MI,
                    INTER=d.INTER if d.moe else d.INTER // ranks, VL=d.V // ranks if shard_vocab and d.V % (8 * ranks) == 0 else 0)
 
 
@@ -165,7 +181,10 @@ def shard_weights(w: dict, d: Dims, ranks: int, rank: int, shard_vocab: bool = T
         (lambda xs, axis: __import__("torch").cat(xs, axis))
     cont = (lambda a: np.ascontiguousarray(a)) if isinstance(w["embed"], np.ndarray) else (lambda a: a.contiguous())
     nq, nk = d.NH * d.HD, d.NKV * d.HD
-    ql, kl = nq // ranks, nk // ranks
+    rep = kv_replication(d, ranks)
+    ql = nq // ranks
+    # this rank's k / v rows: its share of the kv heads, or the one (replicated) kv head its q heads belong to
+    kl, k0 = (nk // ranks, rank * (nk // ranks)) if rep == 1 else (d.HD, (rank // rep) * d.HD)
     mi = d.MI if d.moe else d.INTER
     ml = mi // ranks
     vl = shard_dims(d, ranks, shard_vocab).VL
@@ -173,7 +192,7 @@ def shard_weights(w: dict, d: Dims, ranks: int, rank: int, shard_vocab: bool = T
     for name, a in w.items():
         kind = name.rsplit(".", 1)[-1]
         if kind in ("wqkv", "bqkv"):
-            a = cat([a[rank * ql:(rank + 1) * ql], a[nq + rank * kl:nq + (rank + 1) * kl], a[nq + nk + rank * kl:nq + nk + (rank + 1) * kl]], 0)
+            a = cat([a[rank * ql:(rank + 1) * ql], a[nq + k0:nq + k0 + kl], a[nq + nk + k0:nq + nk + k0 + kl]], 0)
         elif kind == "wo":
             a = cont(a[:, rank * ql:(rank + 1) * ql])
         elif kind == "w13":

@@ -15,7 +15,7 @@ PKG = Path(__file__).resolve().parents[1]
 CSRC = PKG / "csrc"
 LIB_PATH = PKG / "libetxb200.so"
 SOURCES = ["etxb.cu"]
-HEADERS = ["etxb_abi.h", "etxb_prims.cuh", "etxb_gemv.cuh", "etxb_gemv_nb.cuh", "etxb_attn.cuh", "etxb_attn_fused.cuh", "etxb_kernel.cuh"]
+HEADERS = ["etxb_abi.h", "etxb_prims.cuh", "etxb_gemv.cuh", "etxb_gemv_nb.cuh", "etxb_attn.cuh", "etxb_attn_fused.cuh", "etxb_attn_gq.cuh", "etxb_kernel.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-shared", "-Xcompiler", "-fPIC"]
 

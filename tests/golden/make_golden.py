@@ -104,15 +104,17 @@ def topk_case():
     rows, meta, ids, wts = [], [], [], []
     for E, K in ((128, 8), (64, 6), (8, 2), (128, 1), (128, 16)):
         for renorm in (False, True):
-            for kind in range(6):
+            for kind in range(7):
                 if kind < 3:
                     v = rng.normal(0, 3 if kind else 1, E).astype(np.float32)
                 elif kind == 3:
                     v = rng.integers(-2, 3, E).astype(np.float32)                  # heavy ties
                 elif kind == 4:
                     v = rng.normal(0, 30, E).astype(np.float32); v[rng.random(E) < 0.1] = -np.inf
-                else:
+                elif kind == 5:
                     v = np.zeros(E, np.float32)                                     # all equal: ids 0..K-1
+                else:
+                    v = rng.normal(0, 1, E).astype(np.float32); v[rng.integers(0, E)] = np.nan   # a NaN logit: no candidate in any round
                 bits = RTK.bf16_bits(v)
                 i, w = RTK.ref_topk(bits, K, renorm)
                 row = np.zeros(128, np.uint16); row[:E] = bits
@@ -183,6 +185,9 @@ def mla_case():
 if __name__ == "__main__":
     if "--mla-only" in sys.argv:
         mla_case()
+        raise SystemExit(0)
+    if "--topk-only" in sys.argv:
+        topk_case()
         raise SystemExit(0)
     mla_case()
     decode_case(SMALL_MOE, seed=3, n_prompt=8, n_gen=8, gamma="ones", out="decode_small_moe.npz")

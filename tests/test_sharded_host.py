@@ -74,7 +74,39 @@ def test_shard_dims_refuses_uneven_splits():
     d = qdims(SMALL_MOE)
     assert Q.shard_dims(d, 1) is d
     with pytest.raises(ValueError):
-        Q.shard_dims(d, 4)                     # 2 kv heads do not split 4 ways
+        Q.shard_dims(d, 3)                     # 8 q heads do not split 3 ways
+    with pytest.raises(ValueError):
+        Q.shard_dims(qdims(SMALL_DENSE), 8)    # 4 q heads do not split 8 ways
+
+
+def test_more_ranks_than_kv_heads_replicates_the_kv_head():
+    """Qwen3-30B-A3B has 4 kv heads: on 8 ranks every rank takes 4 q heads and the ONE kv head they attend to (each kv
+    head lives on two ranks).  Checked on the small MoE model at 4 ranks (2 kv heads) value by value, and on the
+    30B-A3B shape by its dimensions."""
+    big = Q.shard_dims(Q.load_dims("qwen3-30b-a3b"), 8)
+    assert (big.NH, big.NKV, big.MI, big.VL) == (4, 1, 96, 151936 // 8) and Q.kv_replication(Q.load_dims("qwen3-30b-a3b"), 8) == 2
+    assert Q.kv_replication(Q.load_dims("qwen3-30b-a3b"), 4) == 1 and Q.kv_replication(Q.load_dims("qwen3-8b"), 8) == 1
+    od = SMALL_MOE
+    d = qdims(od)
+    ranks = 4
+    assert Q.kv_replication(d, ranks) == 2
+    sd = Q.shard_dims(d, ranks)
+    assert (sd.NH, sd.NKV, sd.G) == (2, 1, 2)
+    full = Q.pack_hf(d, O.SyntheticWeights(od, seed=3, gamma="ones").get, 64)
+    shards = [Q.shard_weights(full, d, ranks, r) for r in range(ranks)]
+    for s_ in shards:
+        assert {k: tuple(v.shape) for k, v in s_.items()} == {k: tuple(v) for k, v in Q.weight_shapes(sd, 64).items()}
+    nq, nk, hd = d.NH * d.HD, d.NKV * d.HD, d.HD
+    w = full["0.wqkv"]
+    for r, s_ in enumerate(shards):
+        q_rows, k_rows, v_rows = s_["0.wqkv"][:2 * hd], s_["0.wqkv"][2 * hd:3 * hd], s_["0.wqkv"][3 * hd:]
+        assert np.array_equal(q_rows, w[r * 2 * hd:(r + 1) * 2 * hd])
+        kvh = (2 * r) // d.G                                             # the kv head of the rank's q heads
+        assert np.array_equal(k_rows, w[nq + kvh * hd:nq + (kvh + 1) * hd]) and np.array_equal(v_rows, w[nq + nk + kvh * hd:nq + nk + (kvh + 1) * hd])
+    # a rank's graph is a valid single-device program
+    g, pool, sz = Q.build_graph(sd, lambda n: {"xrows": 1 << 30}.get(n, 4096), 64, ranks=ranks, rank=3)
+    plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
+    assert verify_plan(plan) == [] and not simulate(plan).deadlock
 
 
 @pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
