@@ -178,11 +178,17 @@ def run_reference(args, rank: int, world: int):
             vals.append(ms)
     v = float(np.median(vals))
     cores = blas_threads()
-    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-                      "ms_per_step": v, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                      "config": {"workload": workload(layers_total, args.prompt), "parallelism": "cpu", "norm_gamma": "ones"},
-                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
-                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+    B = max(1, args.batch)
+    metric, unit, hib, work = METRIC, UNIT, False, workload(layers_total, args.prompt)
+    if B > 1:                                                              # the CPU path decodes one sequence at a time: its tok/s does not grow with the batch
+        metric, unit, hib, v = f"decode_tok_per_s_bs{B}", "tok/s", True, 1000.0 / v
+        work = f"{MODEL} decode bs{B}, {layers_total} layers, {B} prompts of {args.prompt} random ids, then greedy tokens"
+        sample += "; one sequence at a time"
+    print(json.dumps({"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": 1000.0 / v if B > 1 else v, "higher_is_better": hib, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": work, "parallelism": "cpu", "norm_gamma": "ones"},
+                      "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+                      "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
@@ -314,12 +320,125 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         def layer_w(L):
             return Q.unpack_layer_hf(d, lambda n: weights[n].view(torch.int16).cpu().numpy().view(np.uint16), L)
         f = lambda t: (t.view(torch.int16).cpu().numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)     # noqa: E731
+        use_all_cores()
         ms, sample = oracle_sample(oracle_cfg(O), d.L, P, layer_w, f(weights["lm_head"]), f(weights["final_norm"]), f(weights["embed"][int(prompt[0])]))
         line["cpu_baseline"] = {"value": ms, "unit": UNIT, "cores": blas_threads(), "kind": "port", "sample": sample}
     if tp > 1:
         RD.close_ranks(prog, dist)
     else:
         prog.close()
+    if rank == 0:
+        print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+def run_batch(args, rank: int, world: int, local_rank: int):
+    """--batch B: B sequences per step in one persistent launch (the "tok/s @bs32" half of the metric).  One GPU per
+    process; N > 1 runs N independent batches (replicas).  value = tokens per second of the whole job."""
+    import torch
+    import etx_megakernel_b200  # noqa: F401
+    from etx_megakernel_b200.models import batched as BT
+    from etx_megakernel_b200.models import decode as D
+    from etx_megakernel_b200.models import qwen as Q
+    from etx_megakernel_b200.runtime.dist import slowest
+    from oracle import ref_decode as O                                     # the byte ledger and the cpu_baseline leg only
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    d = Q.load_dims(MODEL, layers=args.layers or None)
+    B, P, K, Wm = args.batch, args.prompt, args.steps, args.warmup
+    maxlen = ((P + Wm + 2 * K + 40 + 15) // 16) * 16
+    weights = D.random_packed_weights(d, maxlen, dev, seed=rank, gamma="ones")
+    prog = BT.BatchProgram(d, weights, B, device=local_rank, maxlen=maxlen, steps=maxlen)
+    prompts = np.random.default_rng(1000 + rank).integers(0, d.V, (B, P))
+    tin = torch.zeros_like(prog.buf["token_in"]); tin[:P] = torch.from_numpy(prompts.T.copy()).to(torch.int32)
+    prog.buf["token_in"].copy_(tin)
+    torch.cuda.synchronize(dev)
+    clk = ClockSampler(local_rank)
+    clk.__enter__()
+    t0 = time.perf_counter()
+    for t in range(P + Wm):                                               # prefill: the prompts position by position through the same kernel
+        prog.step(t, t, write_next=t + 1 >= P, wait=(t % 64 == 63))
+    prog.session.wait(300.0)
+    torch.cuda.synchronize(dev)
+    prefill_s = time.perf_counter() - t0
+    prog.active_experts()
+    stream = torch.cuda.Stream(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    try:
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(K):
+                t = P + Wm + i
+                prog.session.set_step(tok=t, pos=t, write_next=1)
+                prog.session.launch(stream.cuda_stream)
+            e1.record(stream)
+        torch.cuda.synchronize(dev)
+        prog.session.wait(300.0)
+        if dist:
+            dist.barrier()
+        dev_ms = e0.elapsed_time(e1) / K
+        active = prog.active_experts() / K                                 # per layer: experts that had a token, averaged over the timed steps
+        gen_dev = prog.buf["token_out"][P + Wm - 1:P + Wm + K].cpu().numpy()     # [K + 1][B]
+        # end to end with host buffers: every step the B token ids go host -> device from pinned memory and the B results
+        # come back, through the session's launch / wait (the call a host integration makes)
+        h_in = torch.empty(B, dtype=torch.int32).pin_memory(); h_out = torch.empty(B, dtype=torch.int32).pin_memory()
+        h_in.copy_(torch.from_numpy(gen_dev[0].astype(np.int32)))
+        toks_host = np.zeros((K, B), np.int32)
+        slot_in, slot_out = prog.buf["token_in"][0], prog.buf["token_out"][0]
+        h0 = time.perf_counter()
+        with torch.cuda.stream(stream):
+            for i in range(K):
+                slot_in.copy_(h_in, non_blocking=True)
+                prog.session.set_step(tok=0, pos=P + Wm + i, write_next=0)
+                prog.session.launch(stream.cuda_stream)
+                h_out.copy_(slot_out, non_blocking=True)
+                stream.synchronize()
+                prog.session.wait(300.0)
+                toks_host[i] = h_out.numpy()
+                h_in.copy_(h_out)
+        host_ms = (time.perf_counter() - h0) * 1e3 / K
+    finally:
+        clk.__exit__(None, None, None)
+    clocks = clk.summary()
+    same_tokens = bool(np.array_equal(toks_host, gen_dev[1:K + 1]))
+    dev_ms, host_ms = slowest([dev_ms, host_ms], dist, dev)
+    ctx = P + Wm + K // 2
+    od = O.dims_from_config(oracle_cfg(O), MODEL, layers=d.L)
+    ledger = O.step_bytes(od, ctx, batch=B, active_experts=float(np.mean(active)))
+    peak, peak_src = measured_peaks()
+    achieved = ledger["total"] / (dev_ms * 1e-3) / 1e9
+    line = {"metric": f"decode_tok_per_s_bs{B}", "value": world * B * 1000.0 / dev_ms, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": Wm,
+            "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{MODEL} decode bs{B}, {d.L} layers, {B} prompts of {P} random ids, then greedy tokens", "batch": B, "context": ctx,
+                       "prefill": "the prompts are fed position by position through the same kernel", "prefill_s": round(prefill_s, 2),
+                       "parallelism": "single" if world == 1 else f"replicas x{world} (independent batches)", "norm_gamma": "ones",
+                       "active_experts_per_layer": {"mean": float(np.mean(active)), "min": float(np.min(active)), "max": float(np.max(active)),
+                                                    "what": "experts with at least one token, measured by the routing tile over the timed steps"},
+                       "l2": f"each step streams {ledger['total'] / 1e9:.1f} GB (> 126 MB L2)", "host_tokens_equal_device_tokens": same_tokens},
+            "e2e": {"value": world * B * 1000.0 / host_ms, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+            "gpu_launches": K, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": ledger["total"], "kernel": "etxb_megakernel",
+                         "ledger": "dense weights once + (measured active experts) x 3 x MI x H x 2 per layer + B x KV + lm_head"}}
+    if rank == 0 and world == 1 and not args.no_cpu:
+        def layer_w(L):
+            return Q.unpack_layer_hf(d, lambda n: weights[n].view(torch.int16).cpu().numpy().view(np.uint16), L)
+        f = lambda t: (t.view(torch.int16).cpu().numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32)     # noqa: E731
+        use_all_cores()
+        ms, sample = oracle_sample(oracle_cfg(O), d.L, P, layer_w, f(weights["lm_head"]), f(weights["final_norm"]), f(weights["embed"][int(prompts[0, 0])]))
+        line["cpu_baseline"] = {"value": 1000.0 / ms, "unit": "tok/s", "cores": blas_threads(), "kind": "port",
+                                "sample": sample + "; the CPU path decodes one sequence at a time, so its tok/s does not grow with the batch"}
+    prog.close()
     if rank == 0:
         print(json.dumps(line))
     if dist:
@@ -336,6 +455,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (debugging only; 0 = all)")
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per step (1: the headline ms/token; 8 / 32: tok/s through the batched step)")
     ap.add_argument("--shard", default="auto", choices=["auto", "tp", "replicas"],
                     help="N > 1: ONE request sharded over the N GPUs (tp; auto = tp when the model splits N ways, else replicas) or N independent requests (replicas)")
     a = ap.parse_args()
@@ -343,6 +463,8 @@ def main():
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
     if a.impl == "reference":
         run_reference(a, rank, world)
+    elif a.batch > 1:
+        run_batch(a, rank, world, local)
     else:
         run_ours(a, rank, world, local)
 

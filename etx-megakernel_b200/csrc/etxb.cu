@@ -25,6 +25,9 @@ static_assert(sizeof(etxb_attn_args) == 128 && offsetof(etxb_attn_args, grid) ==
 static_assert(ETXB_SMEM_BYTES + 256 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may opt into");
 static_assert(sizeof(etxb_task) == 40 && sizeof(etxb_type) == 48, "plan table layouts");
 static_assert(sizeof(etxb_stepv) == sizeof(etxb_step_params), "step parameter layouts must agree");
+static_assert(sizeof(etxb::etxb_route_args) == 88 && offsetof(etxb::etxb_route_args, grid) == 72, "route block layout");
+static_assert(sizeof(etxb::etxb_batch_args) == 32 && offsetof(etxb::etxb_batch_args, grid) == 16, "column block layout");
+static_assert(ETXB_NBR_OFF + 2 * ETXB_NB_ROWS * ETXB_NBC * 4 <= ETXB_GEN_BYTES && ETXB_NBP_OFF + ETXB_NBP_UNITS * 512 <= ETXB_NBR_OFF, "batched tiles fit the general region");
 
 static thread_local std::string g_err;
 static int32_t fail(int32_t code, const std::string& msg) { g_err = msg; return code; }
@@ -106,7 +109,7 @@ static int32_t check_attnf_block(const etxb_attnf_args& a) {
   else if (a.gq != 0) {
     const int G = a.NH / a.NKV;
     if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || G % a.gq) why = "gq is 1, 2, 4 or 8 and divides NH / NKV";
-    else if (a.HD != 128 || a.BS != 16 || a.part_len != 128) why = "the grouped form is head_dim 128, cache blocks of 16, partitions of 128";
+    else if (a.HD != 128 || a.BS != 16 || (a.part_len & 0xffff) != 128) why = "the grouped form is head_dim 128, cache blocks of 16, partitions of 128";
     else if (a.gq * a.max_parts > 4096) why = "gq * max_parts <= 4096";
     else if (a.nblocks > (uint32_t)(a.max_parts * (a.NH / a.gq))) why = "the grid is at most max_parts * NH / gq tasks";
   } else {
@@ -120,8 +123,45 @@ static int32_t check_attnf_block(const etxb_attnf_args& a) {
   snprintf(m, sizeof m, "attn_fused block (NH=%d, NKV=%d, HD=%d, BS=%d, max_parts=%d, gq=%d) outside the tile: %s", a.NH, a.NKV, a.HD, a.BS, a.max_parts, a.gq, why);
   return fail(ETXB_E_UNSUPPORTED, m);
 }
+// the tiles of a batched step (several columns): the GEMV block with its column strides / the routing block
+static int32_t check_batch_block(int body, const unsigned char* blk, size_t bytes) {
+  const char* why = nullptr;
+  char m[256];
+  if (body == ETXB_BODY_ROUTE) {
+    if (bytes < sizeof(etxb::etxb_route_args)) return fail(ETXB_E_ARG, "route tile: the argument block is 88 bytes");
+    etxb::etxb_route_args a;
+    memcpy(&a, blk, sizeof a);
+    if (a.E < 1 || a.E > 256 || a.K < 1 || a.K > 16 || a.K > a.E) why = "1 <= K <= min(16, E), E <= 256";
+    else if (a.nb < 1 || a.nb > 64 || a.nb * a.K > 2048 || a.cap < 1) why = "1 <= nb <= 64 columns, cap >= 1";
+    else if (!a.logits || !a.wts || !a.ids || !a.ecount || !a.elist) why = "null pointer";
+    if (!why) return ETXB_OK;
+    snprintf(m, sizeof m, "route block (E=%d, K=%d, nb=%d, cap=%d) outside the tile: %s", a.E, a.K, a.nb, a.cap, why);
+    return fail(ETXB_E_UNSUPPORTED, m);
+  }
+  if (body == ETXB_BODY_PROLOGUE_NB || body == ETXB_BODY_ARGMAX_NB) {
+    if (bytes < sizeof(etxb::etxb_batch_args)) return fail(ETXB_E_ARG, "per-column prologue / argmax: the argument block is 32 bytes");
+    etxb::etxb_batch_args a;
+    memcpy(&a, blk, sizeof a);
+    if (a.nb < 1 || a.nb > 64 || a.slot_span < 0) return fail(ETXB_E_UNSUPPORTED, "per-column prologue / argmax: 1 <= nb <= 64 columns");
+    return ETXB_OK;
+  }
+  if (bytes < sizeof(etxb_gemv_args)) return fail(ETXB_E_ARG, "batched GEMV-family tile: the argument block is 160 bytes");
+  etxb_gemv_args a;
+  memcpy(&a, blk, sizeof a);
+  if (a.K <= 0 || (a.K % 8) || a.M < 0) why = "K > 0, K % 8 == 0";
+  else if (a.nb < 1 || a.nb > 64) why = "1 <= nb <= 64 columns";
+  else if (body == ETXB_BODY_NORM_COL && (a.K > ETXB_XF_FLOATS || a.R < 0 || a.R > 64 || !a.resid_in || !a.x || !a.ln)) why = "norm of a column: K <= 8192, 0 <= R <= 64, resid_in / x / ln set";
+  else if (body != ETXB_BODY_NORM_COL && (size_t)a.K * 2 + ETXB_NB_PAD > ETXB_NBX_BYTES) why = "one token vector must fit the 40 KB activation stage";
+  else if (body != ETXB_BODY_NORM_COL && (a.rpt < 1 || a.M < 1 || !a.W || !a.x || !a.out)) why = "rpt >= 1, M >= 1, W / x / out set";
+  else if ((body == ETXB_BODY_MOE_UP_G || body == ETXB_BODY_MOE_DOWN_G) && (a.tpe < 1 || a.R < 1 || a.R > 255 || !a.rows || !a.resid_in)) why = "expert-grouped tile: tpe >= 1, 1 <= R <= 255, token lists (rows) and their lengths (resid_in) set";
+  if (!why) return ETXB_OK;
+  snprintf(m, sizeof m, "batched block (body %d, M=%d, K=%d, rpt=%d, tpe=%d, R=%d, nb=%d) outside the tile: %s", body, a.M, a.K, a.rpt, a.tpe, a.R, a.nb, why);
+  return fail(ETXB_E_UNSUPPORTED, m);
+}
+
 // A block of `body` at `blk` (`bytes` readable).  Tiles whose blocks carry no loop bound the device depends on pass.
 static int32_t check_block(int body, const unsigned char* blk, size_t bytes) {
+  if (body >= ETXB_BODY_NORM_COL && body <= ETXB_BODY_ARGMAX_NB) return check_batch_block(body, blk, bytes);
   if (body == ETXB_BODY_GEMV || body == ETXB_BODY_MOE_UP || body == ETXB_BODY_MOE_DOWN) {
     if (bytes < sizeof(etxb_gemv_args)) return fail(ETXB_E_ARG, "GEMV-family tile: the argument block is 160 bytes");
     etxb_gemv_args a;
@@ -154,7 +194,7 @@ static int select_variant(const etxb_session* s, const std::vector<unsigned char
       if (off + sizeof(etxb_attnf_args) > pool.size()) return 0;
       etxb_attnf_args a;
       memcpy(&a, pool.data() + off, sizeof a);
-      if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || a.HD != 128 || a.BS != 16 || a.part_len != 128) return 0;
+      if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || a.HD != 128 || a.BS != 16 || (a.part_len & 0xffff) != 128) return 0;
       if (any_attn && a.gq != gq) return 0;
       gq = a.gq; any_attn = true;
     } else {
@@ -612,10 +652,11 @@ static int32_t recover(etxb_session* s) {
   std::vector<int32_t> ev((size_t)s->h.n_events * ETXB_EV_STRIDE, 0);
   for (uint32_t e = 0; e < s->h.n_events; ++e) ev[(size_t)e * ETXB_EV_STRIDE] = (int32_t)(s->epoch * (uint32_t)s->evcount[e]);
   if (!ev.empty()) CU(cudaMemcpy(s->d_events, ev.data(), ev.size() * 4, cudaMemcpyHostToDevice));
-  // The merge election of the fused attention grids counts arrivals in the caller's counters buffer (one int32 per kv
-  // head or q group, max_parts arrivals per step, elected when the count reaches a multiple of max_parts): a step
-  // abandoned in the middle of an attention phase leaves them off a multiple, and every later step would then elect
-  // its merging task too early.  Zero is a multiple: clear the counters of every fused attention grid of the pool.
+  // The merge election of the general fused attention tile counts arrivals in the caller's counters buffer (one int32
+  // per kv head, max_parts arrivals per step, elected when the count reaches a multiple of max_parts): a step abandoned
+  // in the middle of an attention phase leaves them off a multiple, and every later step would then elect its merging
+  // task too early.  Zero is a multiple: clear the counters of every fused attention grid of the pool.  (The grouped
+  // form has no counters: its partials carry the step number, which only grows.)
   for (const etxb_type& ty : s->types) {
     if (ty.body != ETXB_BODY_ATTN_FUSED || ty.args[0] != 0 || ty.cst[0] < 0 || (size_t)ty.cst[0] + sizeof(etxb_attnf_args) > s->h_pool.size()) continue;
     etxb_attnf_args a;
@@ -816,7 +857,9 @@ extern "C" int32_t etxb_op_launch(int device, int32_t body, const void* argblock
   if (bytes) CU(cudaMemcpyAsync(c.d_pool, argblock, bytes, cudaMemcpyHostToDevice, st));
   etxb_params p; memset(&p, 0, sizeof p);
   p.tasks = c.d_tasks; p.recs = c.d_recs; p.qbegin = c.d_qbegin; p.types = c.d_type; p.type_args = c.d_targs; p.events = c.d_events;
-  p.evcount = c.d_zero; p.inwords = c.d_zero; p.outwords = c.d_zero; p.ctrl = c.d_ctrl; p.timeout_ns = 2000000000ull; p.epoch = 1;
+  p.evcount = c.d_zero; p.inwords = c.d_zero; p.outwords = c.d_zero; p.ctrl = c.d_ctrl; p.timeout_ns = 2000000000ull;
+  static uint32_t op_epoch[64];                                    // a new step number per launch: flags a tile derives from it never repeat
+  p.epoch = ++op_epoch[device];
   p.n_workers = W;
   if (step) memcpy(&p.step, step, sizeof(p.step));
   return launch_kernel(p, W, st);

@@ -15,16 +15,32 @@
 #define ETXB_NWARPS ETXB_CONSUMER_WARPS
 #define ETXB_MAX_ARGS 4              // tensor pointers a task type may name (Graph.call_device(args=[...]))
 // shared memory of the persistent CTA
+#ifndef ETXB_STAGE_BYTES
 #define ETXB_STAGE_BYTES 24576       // one ring stage: whole weight rows, so a row is at most 24 KB (K <= 12288); 24 KB holds 6 / 3 / 1
+#endif
                                      // rows of K = 2048 / 4096 / 12288 and 16 rows of K = 768 without a remainder
+#ifndef ETXB_NSTAGE
 #define ETXB_NSTAGE 6                // 144 KB of weights in flight per SM (measured against 5 x 32 KB: 0.8 % / 2.3 % faster on the MoE / dense model)
+#endif
 #define ETXB_RING_BYTES (ETXB_STAGE_BYTES * ETXB_NSTAGE)
+#ifndef ETXB_GEN_BYTES
 #define ETXB_GEN_BYTES 65536         // activations: fp32 scratch [0,32K), bf16 x [32K,56K), row results [56K,64K); attention tiles use all of it
+#endif
+#ifndef ETXB_XF_FLOATS
 #define ETXB_XF_FLOATS 8192          // norm fold works on K <= 8192 floats
+#endif
+#ifndef ETXB_XB_OFF
 #define ETXB_XB_OFF 32768
+#endif
+#ifndef ETXB_XB_ELEMS
 #define ETXB_XB_ELEMS 12288          // streamed GEMV rows are at most 12288 elements long
+#endif
+#ifndef ETXB_G_OFF
 #define ETXB_G_OFF 57344
+#endif
+#ifndef ETXB_G_FLOATS
 #define ETXB_G_FLOATS 2048
+#endif
 #define ETXB_SCR_FLOATS 256
 #define ETXB_CTX_BYTES 288           // one prefetched task context: 96-byte record + 192 bytes of argument block
 #define ETXB_CTX_SLOTS 4
@@ -183,7 +199,8 @@ struct etxb_attnf_args {
   const int32_t* block_tables; const int32_t* seq_lens; const int64_t* positions; const int64_t* slot_mapping;  // 48..79
   float* exp_sums; float* max_logits; float* tmp_out; void* out; int32_t* counters;                             // 80..119
   float scale, eps; int32_t NH, NKV, HD, BS, X, max_parts;                                                      // 120..151
-  int32_t gq, part_len;   // 152..159: gq > 0 selects the grouped form (gq q heads x part_len = 128 positions per task, task = part * (NH / gq) + group; counters: one per group)
+  int32_t gq, part_len;   // 152..159: gq > 0 selects the grouped form (gq q heads x 128 positions per task, task = part * (NH / gq) + group);
+                          // part_len: bits 0..15 = 128, bits 16..23 = a tag that tells the grids sharing the partial buffers apart (the layer)
   uint32_t grid[3], nblocks;                                                                                    // 160..175
 };
 

@@ -18,6 +18,45 @@
 namespace etxb {
 
 #define ETXB_GQ_PART 128   // positions per task
+#define ETXB_GQ_PW 136     // 8-byte (value, flag) pairs a task publishes per q head and partition: 128 outputs, max, sum, padding
+
+// Partial results travel as FLAGGED PAIRS: every fp32 value is stored together with a 32-bit flag derived from the step
+// (one aligned 8-byte store: value and flag become visible together), into `tmp_out` viewed as
+// [NH][max_parts][ETXB_GQ_PW] pairs.  The merge is run by a task that is known beforehand -- the one of the context's LAST
+// partition (the partition of the new position: it has the fewest cached positions, so it is the first to finish and
+// polls while the others work) -- which re-reads a pair until its flag is this step's.  No counter, no election, no
+// fence: the producers only store, the merger's loads are its wait.  Nothing has to be reset between steps or after an
+// abandoned step; a buffer that was zeroed once never shows a current flag by accident (flags are never 0, differ
+// from grid to grid within a step and grow with the step).  Bounded like every wait: on a give-up the step is abandoned with the timeout status.
+// The flag names the step AND the grid: the layers of a step share the partial buffers, and a merger must not take the
+// previous layer's partials of the same step for its own.  The grid's tag travels in the upper half of the block's
+// part_len word (the builder puts the layer index there).
+__device__ __forceinline__ uint32_t pair_flag(uint32_t epoch, int part_len) { return ((epoch << 8) | (((uint32_t)part_len >> 16) & 0xffu)) | 0x80000000u; }
+__device__ __forceinline__ void st_pair(uint2* p, float v, uint32_t fl) {
+  asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(fl) : "memory");
+}
+__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// value of the pair at `p` once its flag is `fl`; gives up (step abandoned, 0 returned) at the deadline or on an abort
+__device__ __forceinline__ float poll_pair(const uint2* p, uint32_t fl, const Smem& sm) {
+  uint32_t spins = 0;
+  for (;;) {
+    const uint2 v = ld_pair(p);
+    if (v.y == fl) return __uint_as_float(v.x);
+    if ((++spins & 63u) == 0) {
+      if (ld_relaxed(sm.ctrl) != 0) { *(volatile int*)sm.stop = 1; return 0.f; }
+      if ((spins & 1023u) == 0 && globaltimer() > *sm.deadline) {
+        if (atomicOr(sm.ctrl, ETXB_CTRL_TIMEOUT) == 0) { sm.ctrl[1] = sm.cur; sm.ctrl[2] = -3; sm.ctrl[3] = (int32_t)v.y; sm.ctrl[4] = (int32_t)fl; }
+        *(volatile int*)sm.stop = 1;
+        return 0.f;
+      }
+      __nanosleep(32);
+    }
+  }
+}
 
 template <int GQ>
 struct GqSmem {
@@ -36,21 +75,49 @@ struct GqSmem {
     ph = vnew + HD; sc = ph + 4 * GQ * PL; st = sc + GQ * PL; po = st + 32;
   }
 };
+#ifndef ETXB_LAYOUT_EXPERIMENT
 static_assert(((8 + 2) + 3 + 8 + 2 + 32 + 8 + 32) * 128 * 4 + 128 <= ETXB_GEN_BYTES, "GQ = 8 layout fits the general region");
+#endif
 
 // out[hq][:] = bf16(sum_p w_p * tmp[p][:] / sum_p w_p * l_p), w_p = exp(m_p - max m), for q heads hq0 .. hq0 + GQ - 1.
-// Run by the last task of the q group; reads the partials the other CTAs wrote (L2).  GQ * np <= 4096.
+// Run by the task of the last partition; polls the flagged partials the other CTAs publish (L2).  GQ * np <= 4096.
+// The statistics AND the partial outputs are requested in one round (up to ETXB_GQ_NPR partitions out of registers), so the
+// tail of the attention phase is one L2 round trip after the slowest partition has published.
 template <int GQ>
-__device__ __noinline__ void attn_gq_merge(const etxb_attnf_args& d, const Smem& sm, int hq0, int np) {
-  constexpr int HD = 128;
+__device__ __noinline__ void attn_gq_merge(const etxb_attnf_args& d, const Smem& sm, int hq0, int np, uint32_t fl) {
+#ifndef ETXB_GQ_NPR
+#define ETXB_GQ_NPR 12               // partitions merged out of registers in one round (a 1.5K context); measured against 16: 0.8 % faster
+#endif
+  constexpr int HD = 128, NPR = ETXB_GQ_NPR, NR = (GQ * HD + ETXB_CONSUMERS - 1) / ETXB_CONSUMERS;   // output values per thread
   const int lane = tidx() & 31, warp = tidx() >> 5;
   float* wl = sm.xs;                                              // [GQ][np] max logits, then weights
   float* es = sm.xs + 4096;                                       // [GQ][np] exp sums
   float* red = sm.scr + 200;                                      // [GQ] denominators
+  const uint2* pw = (const uint2*)d.tmp_out;
+  const int idx0 = tidx();                                        // this thread's output values (GQ * HD <= 1024: one or two)
+  float pv[NR][NPR];
+  const bool in_regs = np <= NPR;
+  if (in_regs) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      const int idx = idx0 + r * ETXB_CONSUMERS;
+      if (idx < GQ * HD) {
+        const int g = idx >> 7, dd = idx & (HD - 1);
+        const uint2* tp = pw + (size_t)(hq0 + g) * d.max_parts * ETXB_GQ_PW + dd;
+        uint2 first[NPR];
+#pragma unroll
+        for (int u = 0; u < NPR; ++u) first[u] = ld_pair(tp + (size_t)min(u, np - 1) * ETXB_GQ_PW);   // all requests in flight at once
+#pragma unroll
+        for (int u = 0; u < NPR; ++u)
+          pv[r][u] = (u >= np || first[u].y == fl) ? __uint_as_float(first[u].x) : poll_pair(tp + (size_t)u * ETXB_GQ_PW, fl, sm);
+      }
+    }
+  }
   for (int i = tidx(); i < GQ * np; i += ETXB_CONSUMERS) {
     const int g = i / np, pp = i - g * np;
-    wl[i] = __ldcg(d.max_logits + (size_t)(hq0 + g) * d.max_parts + pp);
-    es[i] = __ldcg(d.exp_sums + (size_t)(hq0 + g) * d.max_parts + pp);
+    const uint2* st = pw + ((size_t)(hq0 + g) * d.max_parts + pp) * ETXB_GQ_PW + HD;
+    wl[i] = poll_pair(st, fl, sm);
+    es[i] = poll_pair(st + 1, fl, sm);
   }
   csync();
   mark(sm, 0);
@@ -70,19 +137,37 @@ __device__ __noinline__ void attn_gq_merge(const etxb_attnf_args& d, const Smem&
   }
   csync();
   mark(sm, 1);
-  for (int idx = tidx(); idx < GQ * HD; idx += ETXB_CONSUMERS) {    // one output value per thread, partitions in ascending order
-    const int g = idx >> 7, dd = idx & (HD - 1);
-    const float* tp = d.tmp_out + (size_t)(hq0 + g) * d.max_parts * HD + dd;
-    const float* wg = wl + g * np;
-    float o = 0.f;
-    for (int p0 = 0; p0 < np; p0 += 8) {
-      float v[8];
+  if (in_regs) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = __ldcg(tp + (size_t)min(p0 + u, np - 1) * HD);   // clamped: a padded load gets weight 0
+    for (int r = 0; r < NR; ++r) {
+      const int idx = idx0 + r * ETXB_CONSUMERS;
+      if (idx < GQ * HD) {
+        const int g = idx >> 7;
+        const float* wg = wl + g * np;
+        float o = 0.f;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) o = __fmaf_rn(p0 + u < np ? wg[p0 + u] : 0.f, v[u], o);
+        for (int u = 0; u < NPR; ++u) o = __fmaf_rn(u < np ? wg[u] : 0.f, u < np ? pv[r][u] : 0.f, o);   // partitions in ascending order
+        ((__nv_bfloat16*)d.out)[(size_t)hq0 * HD + idx] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
+      }
     }
-    ((__nv_bfloat16*)d.out)[(size_t)(hq0 + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
+  } else {
+    // a long context: the partials in rounds of NPR requests per output value, partitions still in ascending order
+    for (int idx = tidx(); idx < GQ * HD; idx += ETXB_CONSUMERS) {
+      const int g = idx >> 7, dd = idx & (HD - 1);
+      const uint2* tp = pw + (size_t)(hq0 + g) * d.max_parts * ETXB_GQ_PW + dd;
+      const float* wg = wl + g * np;
+      float o = 0.f;
+      for (int p0 = 0; p0 < np; p0 += NPR) {
+        uint2 first[NPR];
+#pragma unroll
+        for (int u = 0; u < NPR; ++u) first[u] = ld_pair(tp + (size_t)min(p0 + u, np - 1) * ETXB_GQ_PW);
+#pragma unroll
+        for (int u = 0; u < NPR; ++u)
+          if (p0 + u < np)
+            o = __fmaf_rn(wg[p0 + u], first[u].y == fl ? __uint_as_float(first[u].x) : poll_pair(tp + (size_t)(p0 + u) * ETXB_GQ_PW, fl, sm), o);
+      }
+      ((__nv_bfloat16*)d.out)[(size_t)(hq0 + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
+    }
   }
   mark(sm, 2);
 }
@@ -100,7 +185,7 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
   const int seq = (const void*)d.seq_lens == (const void*)S.seq_lens ? S.pos + 1 : __ldcg(d.seq_lens);
   const int t0 = part * PL;
   const int tid = tidx(), lane = tid & 31, warp = tid >> 5;
-  int* flag = (int*)(sm.scr + 130);
+  const uint32_t fl = pair_flag(sm.epoch, d.part_len);
   if (t0 < seq) {
     const GqSmem<GQ> s(sm.xs);
     const bool owner = pos >= t0 && pos < t0 + PL;                // this partition holds the position being written
@@ -262,23 +347,18 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
       const int g = idx >> 7, dd = idx & (HD - 1);
       float o = __fadd_rn(__fadd_rn(__fadd_rn(s.po[g * HD + dd], s.po[(GQ + g) * HD + dd]), s.po[(2 * GQ + g) * HD + dd]), s.po[(3 * GQ + g) * HD + dd]);
       if (owner) o = __fmaf_rn(s.st[2 * GQ + g], s.vnew[dd], o);
-      d.tmp_out[((size_t)(hq0 + g) * d.max_parts + part) * HD + dd] = o;
-      if (dd == 0) {
-        d.max_logits[(size_t)(hq0 + g) * d.max_parts + part] = s.st[g];
-        d.exp_sums[(size_t)(hq0 + g) * d.max_parts + part] = s.st[GQ + g];
-      }
+      uint2* pw = (uint2*)d.tmp_out + ((size_t)(hq0 + g) * d.max_parts + part) * ETXB_GQ_PW;
+      st_pair(pw + dd, o, fl);
+      if (dd == 0) { st_pair(pw + HD, s.st[g], fl); st_pair(pw + HD + 1, s.st[GQ + g], fl); }
     }
   }
-  csync();                                                         // the partials of this task are issued
-  if (tid == 0) {
-    __threadfence();
-    const int old = atomicAdd(d.counters + qg, 1);                 // monotonic: max_parts arrivals per step and q group
-    *flag = ((old + 1) % d.max_parts) == 0;
-    if (*flag) __threadfence();
-  }
-  csync();
   mark(sm, 3);
-  if (*flag) attn_gq_merge<GQ>(d, sm, hq0, min((seq + PL - 1) / PL, d.max_parts));   // never past the partials the grid computed
+  // the context's last partition merges (never past the partitions the grid computed, whatever seq_lens says)
+  const int np = min((seq + PL - 1) / PL, d.max_parts);
+  if (part == np - 1) {
+    csync();                                                       // every thread is done with the tile's shared memory
+    attn_gq_merge<GQ>(d, sm, hq0, np, fl);
+  }
 }
 
 // Fused attention, either form: gq > 0 in the argument block selects the grouped form above (head_dim 128, cache

@@ -212,8 +212,9 @@ __device__ __forceinline__ const unsigned char* gemv_range_base(int body, const 
 
 // ---------------------------------------------------------------------------------------------- producer side
 // Issue the bulk copies of one task.  One warp; lane 0 issues.  n = running stage counter of this CTA.
+// ptr: the task's trace row when tracing (slot 7 <- time the first stage was issued, slot 6 <- the last), else null.
 __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, const GemvTask& t, const int32_t* lids, uint32_t& n,
-                                             const Smem& sm, int where) {
+                                             const Smem& sm, int where, uint64_t* ptr = nullptr) {
   const int total = t.nranges * t.n;
   if (total <= 0) return true;
   const int rps = ETXB_STAGE_BYTES / t.row_bytes;
@@ -239,6 +240,7 @@ __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, 
                       (uint32_t)(cnt * t.row_bytes), sm.full + st, pol);
         q += cnt;
       }
+      if (ptr != nullptr) { if (q0 == 0) ptr[7] = globaltimer(); ptr[6] = globaltimer(); }
       ++n;
     }
   }
@@ -259,6 +261,9 @@ __device__ __forceinline__ float dot8(const uint4 w, const uint4 x, float a) {
 // Consume the stages of one task: row q (0 .. total-1, range q / rows_per_range) . its activation vector -> epi(q, value),
 // called by lane 0 of the owning warp.  Range i uses the vector at xb + i * xstride (xstride = 0: one vector for all).
 // Every consumer warp walks every stage (so the stage counter stays in step) and arrives on its `empty` barrier.
+// (Measured and not kept: the packed fma.rn.f32x2 form of the inner loop, +1.3 % step time; a lane's share of the
+// activations held in registers as fp32 pairs, which spills at the 96 registers this kernel gets, +45 %; a ring of
+// 7 stages instead of 6, +0.6 %.  The step is bound by the latency chain of its phases, not by this loop.)
 template <typename Epi>
 __device__ __forceinline__ void consume_task(int total, int rows_per_range, int row_bytes, uint32_t& n, const Smem& sm, const __nv_bfloat16* xb,
                                              int xstride, int where, Epi epi) {
@@ -499,9 +504,21 @@ __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, c
     } else {
       gemv_routing<LEAN>(d, lids, lwts);
     }
+    // the slots in ascending expert id, for the summed form: known as soon as the routing is, so it is worked out here,
+    // under the weight stream, and not after it (the barrier that follows the stream publishes it to the other warps)
+    if ((d.mode & ETXB_MODE_SUM_SLOTS) && tidx() < t.spt) {
+      const int mine = lids[t.group * t.spt + tidx()];
+      int rank = 0;
+      for (int j = 0; j < t.spt; ++j) {
+        const int o = lids[t.group * t.spt + j];
+        rank += (o < mine) || (o == mine && j < tidx());
+      }
+      ((int*)(sm.scr + 64))[rank] = tidx();
+    }
   }
   __nv_bfloat16* xb = smem_xb(sm);
   const int K = d.K, rows = t.n;
+  const int* order = (const int*)(sm.scr + 64);
   for (int i = tidx(); i < t.spt * (K >> 3); i += ETXB_CONSUMERS) {          // the task's slots' activation vectors
     const int s = i / (K >> 3), v = i - s * (K >> 3);
     ((uint4*)xb)[i] = ld_act16((const __nv_bfloat16*)d.x + (size_t)(t.group * t.spt + s) * K + 8 * v);
@@ -521,17 +538,6 @@ __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, c
   if (!sum) return;
   csync();
   mark(sm, 2);
-  int* order = (int*)(sm.scr + 64);                                // slots in ascending expert id
-  if (tidx() < t.spt) {
-    const int mine = lids[t.group * t.spt + tidx()];
-    int rank = 0;
-    for (int j = 0; j < t.spt; ++j) {
-      const int o = lids[t.group * t.spt + j];
-      rank += (o < mine) || (o == mine && j < tidx());
-    }
-    order[rank] = tidx();
-  }
-  csync();
   for (int r = tidx(); r < rows; r += ETXB_CONSUMERS) {
     float acc = 0.f;
     for (int k = 0; k < t.spt; ++k) acc = bfr(__fadd_rn(acc, g[order[k] * rows + r]));

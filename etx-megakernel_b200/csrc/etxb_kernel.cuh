@@ -6,6 +6,7 @@
 #pragma once
 #include "etxb_attn.cuh"
 #include "etxb_attn_gq.cuh"
+#include "etxb_batch.cuh"
 #include "etxb_gemv.cuh"
 #include "etxb_prims.cuh"
 
@@ -71,11 +72,12 @@ __device__ __noinline__ void argmax_exchange(const etxb_params& p, const Smem& s
   }
 }
 
+// col / ncols: column `col` of a batched step (logits [ncols][V], token_in / token_out [step][ncols]); (0, 1) otherwise.
 template <bool XCH>
-__device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm) {
+__device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm, int col = 0, int ncols = 1) {
   const etxb_stepv& S = p.step;
   float bv = -INFINITY; int bi = 0x7fffffff;
-  const uint4* lg4 = (const uint4*)S.logits;
+  const uint4* lg4 = (const uint4*)((const __nv_bfloat16*)S.logits + (size_t)col * S.V);
   const int n4 = S.V / 8;
   auto scan = [&](const uint4 w, int base) {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};
@@ -94,7 +96,7 @@ __device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm
   }
   for (; j < n4; j += B) scan(ld_act16(lg4 + j), 8 * j);
   for (int i = 8 * n4 + tidx(); i < S.V; i += B) {
-    const float v = ld_bf(S.logits, i);
+    const float v = ld_bf(lg4, i);
     if (v > bv) { bv = v; bi = i; }
   }
 #pragma unroll
@@ -111,9 +113,9 @@ __device__ __forceinline__ void tile_argmax(const etxb_params& p, const Smem& sm
       if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
     if constexpr (XCH) { if (p.n_peers > 0 && p.xargmax != 0u) argmax_exchange(p, sm, bv, bi); }
     const int t = S.tok;
-    S.token_out[t] = bi;
-    if (S.write_next) S.token_in[t + 1] = bi;
-    if (S.token_time) S.token_time[2 * t + 1] = globaltimer();
+    S.token_out[(size_t)t * ncols + col] = bi;
+    if (S.write_next) S.token_in[(size_t)(t + 1) * ncols + col] = bi;
+    if (S.token_time && col == ncols - 1) S.token_time[2 * t + 1] = globaltimer();
   }
 }
 
@@ -192,6 +194,14 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
     case 9: if constexpr (!LEAN) { tile_attn_reduce(args, c0, sm, p.step); break; }
     case 10: if constexpr (!LEAN) { tile_splitk_part(args, c0, c1, sm); break; }
     case 11: if constexpr (!LEAN) { tile_splitk_sum(args, c0); break; }
+    // batched decode (several columns per step): full kernel only
+    case 13: if constexpr (!LEAN) { tile_norm_col(args, c0, sm); break; }
+    case 14: if constexpr (!LEAN) { tile_gemv_nb(args, c0, sm); break; }
+    case 15: if constexpr (!LEAN) { tile_route(args, c0, sm); break; }
+    case 16: if constexpr (!LEAN) { tile_moe_up_g(args, c0, sm); break; }
+    case 17: if constexpr (!LEAN) { tile_moe_down_g(args, c0, sm); break; }
+    case 18: if constexpr (!LEAN) { tile_prologue_nb(args, c0, p.step); break; }
+    case 19: if constexpr (!LEAN) { if (c0 < ((const etxb_batch_args*)args)->nb) tile_argmax<false>(p, sm, c0, ((const etxb_batch_args*)args)->nb); break; }
     default:
       if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);
       break;
@@ -232,7 +242,7 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
     }
     const GemvTask gt = gemv_task(body, *pa, t->c0);
     if (gt.n > 0 && body != 3) gemv_routing<LEAN>(*pa, sm.prod, (float*)(sm.prod + 16));
-    ok = produce_task(body, *pa, gt, sm.prod, n, sm, cur);
+    ok = produce_task(body, *pa, gt, sm.prod, n, sm, cur, p.trace ? p.trace + 8 * (size_t)t->id : nullptr);
   }
   // Nothing is left in flight on a normal exit (the consumers waited for every stage).  When the step was abandoned,
   // wait (bounded) for the copies already issued before the CTA's shared memory goes away.

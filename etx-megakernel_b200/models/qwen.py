@@ -258,7 +258,7 @@ def buffer_shapes(d: Dims, maxlen: int, steps: int, parts: int) -> dict:
          "logits": ((d.V,), "bf16"), "positions": ((1,), "i64"), "seq_lens": ((1,), "i32"), "slot_mapping": ((1,), "i64"),
          "block_tables": ((nblk,), "i32"), "token_in": ((steps + 2,), "i32"), "token_out": ((steps + 1,), "i32"),
          "token_time": ((2 * (steps + 1),), "i64"),
-         "exp_sums": ((d.NH, parts), "f32"), "max_logits": ((d.NH, parts), "f32"), "tmp_out": ((d.NH, parts, d.HD), "f32"),
+         "exp_sums": ((d.NH, parts), "f32"), "max_logits": ((d.NH, parts), "f32"), "tmp_out": ((d.NH, parts, max(d.HD, op_attn.GQ_PARTIAL_FLOATS)), "f32"),
          "kc": ((d.L, nblk, d.NKV, d.HD // X, BS, X), "bf16"), "vc": ((d.L, nblk, d.NKV, d.HD, BS), "bf16"),
          "attn_counters": ((d.L, d.NH), "i32"), "moe_out": ((d.H,), "bf16")}
     if d.moe:
@@ -450,7 +450,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                                        positions=ptr("positions"), slot_mapping=ptr("slot_mapping"), exp_sums=ptr("exp_sums"),
                                        max_logits=ptr("max_logits"), tmp_out=ptr("tmp_out"), out=ptr("attn_out"),
                                        counters=ptr("attn_counters") + 4 * L * d.NH, scale=scale, eps=d.eps, NH=d.NH, NKV=d.NKV, HD=d.HD,
-                                       BS=BS, X=X, max_parts=nparts, gq=gq, part_len=plen)
+                                       BS=BS, X=X, max_parts=nparts, gq=gq, part_len=op_attn.tagged_part_len(L) if gq else plen)
             prev = add(f"attn_{L}", "attn_fused", "attn_fused", L, blob, ntask, (ntask,), prev, "i->(0)",
                        f"E_red_{L}", "i->(0)", (1,), ntask)
         else:

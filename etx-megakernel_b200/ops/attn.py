@@ -18,7 +18,10 @@ PARAMS = [("q", "ptr addrspace(1)", 0, 8), ("kc", "ptr addrspace(1)", 8, 8), ("v
 
 
 # the fused phase (export attn_fused): q/k norm + rope + cache write of the new position, attention over the partition,
-# and the merge by the last task of each kv head (counters: one int32 per kv head, monotonic, never reset)
+# and the merge.  General form: by the last task of each kv head to finish (counters: one int32 per kv head, monotonic,
+# never reset).  Grouped form: by the task of the context's last partition, which polls the partials the others publish
+# as flagged (value, step flag) pairs in `tmp_out` -- [NH][max_parts][GQ_PARTIAL_FLOATS] floats, zeroed once by the
+# caller; exp_sums, max_logits and counters are not used by it
 F_ARG_BYTES, F_GRID_OFF = 176, 160
 F_PARAMS = [("qkv", "ptr addrspace(1)", 0, 8), ("qw", "ptr addrspace(1)", 8, 8), ("kw", "ptr addrspace(1)", 16, 8),
             ("cos_sin", "ptr addrspace(1)", 24, 8), ("kc", "ptr addrspace(1)", 32, 8), ("vc", "ptr addrspace(1)", 40, 8),
@@ -31,6 +34,13 @@ F_PARAMS = [("qkv", "ptr addrspace(1)", 0, 8), ("qw", "ptr addrspace(1)", 8, 8),
             # part * (NH / gq) + group, one counter per group; gq = 0: the general form (32 positions x one kv head)
             ("gq", "i32", 152, 4), ("part_len", "i32", 156, 4)]
 GQ_PART = 128
+def tagged_part_len(tag: int) -> int:
+    """part_len word of a grouped attention block: 128 positions per task, and in bits 16..23 a tag that differs between the
+    grids of a step that share the partial buffers (the layer index): a merger only accepts partials carrying its own."""
+    return GQ_PART | ((tag & 0xff) << 16)
+
+
+GQ_PARTIAL_FLOATS = 272   # grouped form: floats of `tmp_out` per (q head, partition) -- 136 (value, flag) pairs: 128 outputs, max, sum, padding
 
 
 def import_entries(threads: int = 544) -> dict:
@@ -46,7 +56,7 @@ def check_fused(NH: int, NKV: int, HD: int, BS: int, X: int, max_parts: int, gq:
     check_shape(NH, NKV, HD, BS, X, max_parts)
     G = NH // NKV
     if gq:
-        if gq not in (1, 2, 4, 8) or G % gq or HD != 128 or BS != 16 or part_len != GQ_PART:
+        if gq not in (1, 2, 4, 8) or G % gq or HD != 128 or BS != 16 or (part_len & 0xffff) != GQ_PART or part_len >> 24:
             raise ValueError(f"attn_fused grouped form: needs gq in (1, 2, 4, 8) dividing G={G}, head_dim 128, block size 16 and "
                              f"part_len {GQ_PART} (gq={gq}, HD={HD}, BS={BS}, part_len={part_len})")
         if gq * max_parts > 4096:

@@ -58,7 +58,16 @@ enum {
   ETXB_BODY_SPLITK_PART = 10, /* demo: partial sums of a split-K reduction (etx/operators/splitk_sum.py) */
   ETXB_BODY_SPLITK_SUM = 11,
   ETXB_BODY_ATTN_FUSED = 12,  /* prep + split-KV attention + merge by the last task to finish, one phase (general and grouped form) */
-  ETXB_BODY_COUNT = 13
+  /* batched decode (several sequences per step; the reference's column batching, etx/ops/gemv.py:40-73, and request batching,
+   * examples/vllm_llm/model.py:194-211): tensor-core tiles that read a weight row once for up to 8 tokens per pass */
+  ETXB_BODY_NORM_COL = 13,    /* residual add (+ expert combine in ascending expert id) + RMSNorm of one column */
+  ETXB_BODY_GEMV_NB = 14,     /* dsl_gemv with nb activation columns (dsl_gemv_rows_nb, etx/ops/gemv.py:176-289) */
+  ETXB_BODY_ROUTE = 15,       /* softmax top-k of every column + per-expert token lists */
+  ETXB_BODY_MOE_UP_G = 16,    /* expert-grouped gate+up: an expert's rows read once for all the tokens that selected it */
+  ETXB_BODY_MOE_DOWN_G = 17,  /* expert-grouped down, scaled by the routing weight */
+  ETXB_BODY_PROLOGUE_NB = 18, /* vl_prologue for column c of a batch */
+  ETXB_BODY_ARGMAX_NB = 19,   /* vl_argmax for column c of a batch */
+  ETXB_BODY_COUNT = 20
 };
 
 /* The per-step scalars and buffers of the prologue / argmax tiles: field for field the reference's VlParams

@@ -55,7 +55,7 @@ class DeviceWeights:
             self.room -= n * 4
             return t.float().cpu().numpy()
         view = self.stage[:n].view(t.shape)
-        view.copy_(t, non_blocking=False)                               # bf16 -> fp32 on the way, through pinned memory
+        view.copy_(t.float() if t.is_cuda else t)                       # widened on the device, then one copy into pinned memory
         self._staged = True
         return view.numpy()
 

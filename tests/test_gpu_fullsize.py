@@ -4,9 +4,12 @@ provider (tests/device_weights.py), so it runs the very model the kernel runs.
 
 Per model: (1) a short random prompt and greedy tokens, free-running on both sides -- identical, or where a token
 differs the oracle's own logit margin between the two candidates is at most 2 bf16 ulps (the reference's tie rule,
-examples/vllm_llm/host.hip:930-946) and the comparison goes on teacher-forced; (2) three teacher-forced steps at context
-1024 over the same random KV cache: final hidden state and logits within 2e-2 of their largest magnitude.  What matched
+examples/vllm_llm/host.hip:930-946) and the comparison goes on teacher-forced; (2) teacher-forced steps at context
+1024 over the same random KV cache, layer by layer on the oracle's own inputs (first, middle, last layer): layer output
+within 2e-2 of its largest magnitude and >= 50 % of the elements bit-identical (what is left are single bf16 roundings
+that fell the other way), KV slot written in place.  What matched
 and every margin are printed (pytest -s / the captured output of a failing run)."""
+import os
 import time
 
 import numpy as np
@@ -66,42 +69,77 @@ def greedy_against_oracle(name, d, w, n_prompt, n_gen, maxlen=128):
     prog.close()
 
 
-def hidden_state_at_context(name, d, w, context=1024, steps=3):
+def layers_at_context(name, d, w, context=1024, steps=2):
+    """Layer by layer at a long context.  A random-init MoE stack amplifies a one-ulp difference (a flipped 8th expert)
+    from layer to layer, so the whole 48-layer hidden state is not a meaningful comparison at any tolerance (measured:
+    bit-identical after 2 layers, 0.6 % off after 4, unrelated after 16 -- and the same between any two correct
+    implementations).  Instead every checked layer gets the ORACLE's input for that layer: a one-layer program holding
+    that layer's weights and KV cache, with the oracle's hidden state as its embedding row.  First, middle and last layer;
+    the last one also checks the final norm + lm_head rows it is given.  The full-depth error is printed for the record."""
+    from dataclasses import replace
     od = O.dims_from_config(CFG[name], name)
     maxlen = context + 16
-    prog = D.DecodeProgram(d, w, device=0, maxlen=maxlen)
-    ref = O.Ref(od, DeviceWeights(d, w), maxlen)
+    W = DeviceWeights(d, w)
+    ref = O.Ref(od, W, maxlen)
     rng = np.random.default_rng(17)
     for L in range(d.L):
-        K = O.bfr(rng.standard_normal((context, d.NKV, d.HD), dtype=np.float32) * np.float32(0.02))
-        V = O.bfr(rng.standard_normal((context, d.NKV, d.HD), dtype=np.float32) * np.float32(0.02))
-        ref.kc[L, :context], ref.vc[L, :context] = K, V
-        prog.load_kv(L, K, V)
+        ref.kc[L, :context] = O.bfr(rng.standard_normal((context, d.NKV, d.HD), dtype=np.float32) * np.float32(0.02))
+        ref.vc[L, :context] = O.bfr(rng.standard_normal((context, d.NKV, d.HD), dtype=np.float32) * np.float32(0.02))
+    whole = D.DecodeProgram(d, w, device=0, maxlen=maxlen)
+    for L in range(d.L):
+        whole.load_kv(L, ref.kc[L, :context], ref.vc[L, :context])
+    d1 = replace(d, L=1, V=8, tie=False)
     toks = rng.integers(0, d.V, steps)
     for i, tok in enumerate(toks):
+        pos = context + i
         dump = []
-        want_tok, want_logits = ref.step(int(tok), context + i, dump=dump, return_logits=True)
-        prog.buf["token_in"][i] = int(tok)
-        prog.step(i, context + i, write_next=False)
-        hid, lg = prog.read("resid"), prog.read("logits")
-        eh = float(np.abs(hid - dump[-1]).max() / np.abs(dump[-1]).max())
-        el = float(np.abs(lg - want_logits).max() / np.abs(want_logits).max())
-        same = float(np.mean(hid == dump[-1]))
-        got_tok = int(prog.buf["token_out"][i].item())
-        print(f"[{name}] context {context + i}: hidden max err {eh:.2e} of scale ({same:.1%} of elements identical), logits max err {el:.2e}, "
-              f"token {got_tok} vs oracle {want_tok}")
-        assert eh <= BF16_REL and el <= BF16_REL
-        if got_tok != want_tok:
-            margin, ulp = float(want_logits[want_tok] - want_logits[got_tok]), float(abs(want_logits[want_tok])) * 2.0 ** -7
-            assert margin <= 2 * ulp, f"step {i}: device {got_tok}, oracle {want_tok}, margin {margin} > 2 ulps ({ulp})"
-    prog.close()
+        want_tok, want_logits = ref.step(int(tok), pos, dump=dump, return_logits=True)
+        inputs = [W.get("model.embed_tokens.weight")[int(tok)]] + dump[:-1]
+        for L in sorted({0, d.L // 2, d.L - 1}):
+            w1 = {k: w[k] for k in ("final_norm", "cos_sin")}
+            w1["lm_head"] = w["lm_head"][:8].contiguous()
+            emb = torch.zeros((8, d.H), dtype=torch.bfloat16, device="cuda:0")
+            emb[0] = torch.from_numpy(inputs[L]).to("cuda:0").to(torch.bfloat16)
+            w1["embed"] = emb
+            for k in w:
+                if k.startswith(f"{L}."):
+                    w1["0." + k.split(".", 1)[1]] = w[k]
+            one = D.DecodeProgram(d1, w1, device=0, maxlen=maxlen)
+            one.load_kv(0, ref.kc[L, :pos], ref.vc[L, :pos])
+            one.buf["token_in"][0] = 0
+            torch.cuda.synchronize()                                      # the session launches on its own stream
+            one.step(0, pos, write_next=False)
+            got, want = one.read("resid"), dump[L]
+            err, same = float(np.abs(got - want).max() / np.abs(want).max()), float(np.mean(got == want))
+            msg = f"[{name}] context {pos}, layer {L} on the oracle's input: max err {err:.2e} of scale, {same:.1%} of elements identical"
+            if L == d.L - 1:
+                el = float(np.abs(one.read("logits")[:8] - want_logits[:8]).max() / np.abs(want_logits).max())
+                msg += f"; first 8 logits max err {el:.2e}"
+                assert el <= BF16_REL
+            print(msg)
+            assert err <= BF16_REL and same >= 0.5, msg
+            Kd, Vd = one.read_kv(0, pos + 1)
+            assert np.array_equal(Kd[:pos], ref.kc[L, :pos]) and np.mean(Kd[pos] == ref.kc[L, pos]) > 0.97 and np.mean(Vd[pos] == ref.vc[L, pos]) > 0.97
+            one.close()
+        whole.buf["token_in"][i] = int(tok)
+        torch.cuda.synchronize()
+        whole.step(i, pos, write_next=False)
+        hid = whole.read("resid")
+        print(f"[{name}] context {pos}, all {d.L} layers free-running (for the record, not asserted): hidden max err "
+              f"{float(np.abs(hid - dump[-1]).max() / np.abs(dump[-1]).max()):.2e}, token {int(whole.buf['token_out'][i].item())} vs oracle {want_tok}")
+    whole.close()
 
 
-@pytest.mark.parametrize("name,n_prompt,n_gen", [("qwen3-30b-a3b", 16, 32), ("qwen3-8b", 8, 24)])
+# The oracle takes a few seconds per token at these sizes (numpy on the host, weights fetched from the device), so the
+# default run is short; ETXB_FULLSIZE_LONG=1 runs 16 prompt + 32 greedy tokens per model (several minutes each).
+LONG = os.environ.get("ETXB_FULLSIZE_LONG", "0") == "1"
+
+
+@pytest.mark.parametrize("name,n_prompt,n_gen", [("qwen3-30b-a3b", 16 if LONG else 6, 32 if LONG else 10), ("qwen3-8b", 16 if LONG else 4, 32 if LONG else 8)])
 def test_full_size_model_against_the_oracle(name, n_prompt, n_gen):
     d = Q.load_dims(name)
     w = D.random_packed_weights(d, 1040, torch.device("cuda:0"), seed=0, gamma="ones")
     greedy_against_oracle(name, d, w, n_prompt, n_gen, maxlen=1040)
-    hidden_state_at_context(name, d, w, context=1024, steps=3)
+    layers_at_context(name, d, w, context=1024, steps=3 if LONG else 2)
     del w
     torch.cuda.empty_cache()

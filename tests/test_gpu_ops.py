@@ -228,9 +228,10 @@ def test_paged_attention(NH, NKV, HD, seq):
     (32, 4, 128, True, 1025, 2), (32, 4, 128, True, 1024, 2), (32, 4, 128, True, 1041, 8), (8, 2, 128, True, 1, 1), (8, 2, 128, True, 129, 4),
     (32, 8, 128, False, 640, 2), (32, 8, 128, True, 128, 4), (16, 2, 128, True, 257, 8), (4, 4, 128, True, 77, 1)])
 def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq, gq):
-    """The one-phase attention tile (norm + rope + cache write of the new position, split-KV attention, merge by the last
-    task to finish) against the oracle, in its general and its grouped form: new cache slot bit-exact, output within bf16
-    tolerance; run twice with the same never-reset counters to cover the modulo arithmetic of the merge election."""
+    """The one-phase attention tile (norm + rope + cache write of the new position, split-KV attention, merge) against the
+    oracle, in its general form (merge by the last task to finish) and its grouped form (merge by the last partition's
+    task over flagged partials): new cache slot bit-exact, output within bf16 tolerance; run twice on the same buffers to
+    cover the modulo arithmetic of the election counters and the step flags of the partials."""
     rng = np.random.default_rng(seq + NH)
     G = NH // NKV
     pos = seq - 1
@@ -264,7 +265,8 @@ def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq, gq):
     bt = torch.arange(nblk, dtype=torch.int32, device=DEV); sl = torch.tensor([seq], dtype=torch.int32, device=DEV)
     p64 = torch.tensor([pos], dtype=torch.int64, device=DEV)
     es = torch.zeros((NH, parts), dtype=torch.float32, device=DEV); ml = torch.zeros_like(es)
-    tmp = torch.zeros((NH, parts, HD), dtype=torch.float32, device=DEV); out = torch.zeros((NH, HD), dtype=torch.bfloat16, device=DEV)
+    tmp = torch.zeros((NH, parts, ops.attn.GQ_PARTIAL_FLOATS if gq else HD), dtype=torch.float32, device=DEV)
+    out = torch.zeros((NH, HD), dtype=torch.bfloat16, device=DEV)
     cnt = torch.zeros(ncnt, dtype=torch.int32, device=DEV)
     blob = argblock.pack_named(ENT["attn_fused"], (ntask, 1, 1), qkv=d_qkv.data_ptr(), qw=d_qn.data_ptr() if qk_norm else 0,
                                kw=d_kn.data_ptr() if qk_norm else 0, cos_sin=cs.data_ptr(), kc=d_kc.data_ptr(), vc=d_vc.data_ptr(),
@@ -277,7 +279,7 @@ def test_attention_phase_fused(NH, NKV, HD, qk_norm, seq, gq):
         op_launch("attn_fused", blob, ntask)
         assert np.array_equal(host(d_kc), kc_ref) and np.array_equal(host(d_vc), vc_ref)
         assert_bf16_close(host(out), want, f"fused attention seq={seq} run {rerun}", min_exact=0.9)
-        assert host(cnt).tolist() == [parts * (rerun + 1)] * ncnt
+        assert host(cnt).tolist() == [0 if gq else parts * (rerun + 1)] * ncnt        # (the grouped form elects nobody: its merger is fixed)
         assert np.array_equal(host(d_qkv), qkv)                          # the fused tile leaves qkv as the GEMV wrote it
 
 
@@ -375,19 +377,26 @@ def test_blocks_outside_the_tile_limits_are_refused_before_launch(bad):
     """A GEMV-family block a device loop could not get through (a row longer than a ring stage, a zero row length, more
     results than the tile holds ...) never reaches the GPU: the C entry point answers E_UNSUPPORTED from its host-side
     check.  Nothing is launched, so the test needs no valid pointers."""
+    import struct
     from etx_megakernel_b200.runtime import EtxbError
     f = dict(W=4096, x=4096, out=4096, M=64, K=2048, rpt=1, tpe=64, nb=1, mode=0, E=0, R=0, logits=4096)
-    f.update(bad)
-    body = "moe_up" if f["mode"] & 0xff0000 else "gemv"
-    blob = argblock.pack_named(ENT["dsl_moe_up" if body == "moe_up" else "dsl_gemv"], (64, 1, 1), **f)
+    body = "moe_up" if bad.get("mode", 0) & 0xff0000 else "gemv"
+    blob = bytearray(argblock.pack_named(ENT["dsl_moe_up" if body == "moe_up" else "dsl_gemv"], (64, 1, 1), **f))
+    # the Python packer has its own guard (ops.gemv.check_shape), so the out-of-range values are patched into the packed
+    # bytes: what a C or C++ host that fills the 160-byte block by hand could pass
+    offsets = {name: off for name, _, off, _ in ops.gemv.PARAMS}
+    for name, value in bad.items():
+        struct.pack_into("<i", blob, offsets[name], value)
     with pytest.raises(EtxbError) as e:
-        op_launch(body, blob, 64)
+        op_launch(body, bytes(blob), 64)
     assert e.value.status == "E_UNSUPPORTED" and "outside the tile" in str(e.value)
     fa = dict(qkv=4096, cos_sin=4096, kc=4096, vc=4096, block_tables=4096, seq_lens=4096, positions=4096, slot_mapping=4096, exp_sums=4096,
               max_logits=4096, tmp_out=4096, out=4096, counters=4096, scale=1.0, eps=1e-6, NH=32, NKV=4, HD=128, BS=16, X=8, max_parts=9,
-              gq=3, part_len=128)
-    with pytest.raises(EtxbError) as e:                                     # gq must divide the q heads of a kv head
-        op_launch("attn_fused", argblock.pack_named(ENT["attn_fused"], (9 * 10, 1, 1), **fa), 90)
+              gq=2, part_len=128)
+    ablob = bytearray(argblock.pack_named(ENT["attn_fused"], (9 * 16, 1, 1), **fa))
+    struct.pack_into("<i", ablob, 152, 3)                                   # gq = 3 does not divide the 8 q heads of a kv head
+    with pytest.raises(EtxbError) as e:
+        op_launch("attn_fused", bytes(ablob), 144)
     assert e.value.status == "E_UNSUPPORTED"
     assert torch.zeros(2, device=DEV).sum().item() == 0.0
 

@@ -135,3 +135,32 @@ def test_weight_pack_round_trip():
     cos, sin = O.rope_tables(d.theta, d.HD, 64)
     tab = (packed["cos_sin"].astype(np.uint32) << 16).view(np.float32)
     assert np.array_equal(tab[:, :d.HD // 2], cos) and np.array_equal(tab[:, d.HD // 2:], sin)
+
+
+def test_batched_graph_phases_and_argument_blocks():
+    """The batched step (several sequences per launch): phase order, one argument block per sequence for the attention grid
+    (addressed by the grid's second coordinate), expert-grouped grids of E x chunks tasks, a valid plan."""
+    from etx_megakernel_b200.models import batched as BT
+    from etx_megakernel_b200.ops import attn as op_attn
+    from etx_megakernel_b200.sim.protocol import simulate
+    d = Q.load_dims("qwen3-30b-a3b", layers=2)
+    B = 8
+    g, pool, info = BT.build_graph(d, _fake_ptr, B, 1072)
+    names = [gr.name for gr in g.grids]
+    assert names[:11] == ["prologue", "norm1_0", "qkv_0", "attn_0", "o_proj_0", "norm2_0", "router_0", "route_0", "moe_up_0", "moe_down_0", "norm1_1"]
+    assert names[-3:] == ["norm_f", "lm_head", "argmax"]
+    plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
+    assert verify_plan(plan) == [] and not simulate(plan).deadlock
+    shape = plan.inst.grid_shapes
+    assert shape["attn_0"] == (info["attn_tasks"], B) and info["attn"] == (8, 128, 9) and shape["norm1_0"] == (B,) and shape["route_0"] == (1,)
+    assert shape["moe_up_0"] == (128 * 3,) and shape["moe_down_0"] == (128 * 4,)
+    rows = {r[0]: r for r in pool.rows}
+    off = rows["attn_1"][4]
+    pb = pool.bytes()
+    for b in range(B):                                       # block b of the attention grid: sequence b's q rows and partial buffers
+        blk = pb[off + b * op_attn.F_ARG_BYTES: off + (b + 1) * op_attn.F_ARG_BYTES]
+        assert struct.unpack_from("<Q", blk, 0)[0] == _fake_ptr("qkv") + b * d.NQKV * 2
+        assert struct.unpack_from("<Q", blk, 104)[0] == _fake_ptr("attn_out") + b * d.NH * d.HD * 2
+        assert struct.unpack_from("<4I", blk, 160) == (info["attn_tasks"], 1, 1, info["attn_tasks"])
+    with pytest.raises(ValueError, match="MoE"):
+        BT.build_graph(Q.load_dims("qwen3-8b", layers=1), _fake_ptr, 4, 1072)
