@@ -263,7 +263,11 @@ __device__ __forceinline__ float dot8(const uint4 w, const uint4 x, float a) {
 // Every consumer warp walks every stage (so the stage counter stays in step) and arrives on its `empty` barrier.
 // (Measured and not kept: the packed fma.rn.f32x2 form of the inner loop, +1.3 % step time; a lane's share of the
 // activations held in registers as fp32 pairs, which spills at the 96 registers this kernel gets, +45 %; a ring of
-// 7 stages instead of 6, +0.6 %.  The step is bound by the latency chain of its phases, not by this loop.)
+// 7 stages instead of 6, +0.6 %; the short tasks (a projection's 14 .. 42 rows per SM, resident in the ring before they
+// are needed) multiplied with mma.sync m16n8k16 from the ring, the activation vector as column 0 of B, +25 % -- the
+// legacy tensor path is slow on this part, and with one bulk copy per row padded for conflict-free fragment reads +60 %,
+// because a bulk copy costs the copy engine about 0.3 us whatever its size.  This loop runs at about 21 bytes of
+// weights per clock and SM, HBM delivers 22.5.)
 template <typename Epi>
 __device__ __forceinline__ void consume_task(int total, int rows_per_range, int row_bytes, uint32_t& n, const Smem& sm, const __nv_bfloat16* xb,
                                              int xstride, int where, Epi epi) {

@@ -116,6 +116,42 @@ OPERATORS = {
 }
 
 
+# ---- the tiles of a batched step (several sequences per launch; ops/batch.py)
+from ..ops import batch as _batch  # noqa: E402
+
+ARGUMENTS.update({
+    "norm_col": _gemv_recipe(x="hn | o_norm", rows="mc3 | o", resid_in="resid2 | resid", resid_out="resid | resid2", ln='W(pl + "ln1" | "ln2")', ids="ti",
+                             R="TOPK | 1 | 0", K="H", M="H", rpt="1", nb="B", sx="H", srows="TOPK * H | H", srin="H", srout="H"),
+    "gemv_nb": _gemv_recipe(W='W(pl + "wqkv" | "wo" | "wr") | W("lm_head")', x="hn | attn_out | o_norm", out="qkv | o | rlog | logits", M="rows", K="H | NH * HD",
+                            nb="B", sx="K", sout="M"),
+    "moe_up_g": _gemv_recipe(W='W(pl + "w13")', x="o_norm", out="mc2", estride="2 * MI * H", M="MI", K="H", tpe="tpe", rows="elist", resid_in="ecount", nb="B",
+                             R="TOPK", sx="H"),
+    "moe_down_g": _gemv_recipe(W='W(pl + "w2")', x="mc2", out="mc3", wts="tw", estride="H * MI", M="H", K="MI", tpe="tpe", rows="elist", resid_in="ecount",
+                               nb="B", R="TOPK"),
+    "route": [("ptr", "rlog"), ("ptr", "tw"), ("ptr", "ti"), ("ptr", "ecount"), ("ptr", "elist"), ("ptr", "active + layer"), ("i32", "E"), ("i32", "TOPK"),
+              ("i32", "norm_topk | 0x100"), ("i32", "B"), ("i32", "B")],
+    "cols": [("i32", "B"), ("i32", "nblk * BS")],
+})
+
+
+def _batch_op(name, tile, grid, shape, reads, writes):
+    return Operator(name, f"etxb::{tile}", grid, shape, dict(NB_MAX=_batch.NB_MAX, XBYTES=_batch.XBYTES, GROUP_ROWS=_batch.GROUP_ROWS), reads, writes,
+                    layouts="column b of a batched buffer at base + b * stride (element counts, the reference's sx / sout / srows / srin / srout)",
+                    arguments={name: ARGUMENTS[name]})
+
+
+OPERATORS.update({
+    "norm_col": _batch_op("norm_col", "tile_norm_col", ("B", "1", "1"), "K <= 8192, R <= 64, B <= 64", ("rows", "residual", "norm_weight", "expert_ids"),
+                          ("residual_out", "normed")),
+    "gemv_nb": _batch_op("gemv_nb", "tile_gemv_nb", ("CU", "1", "1"), "K % 8 == 0, 2 K + 64 <= 40960, B <= 64", ("weights", "input", "bias"), ("output",)),
+    "route": _batch_op("route", "tile_route", ("1", "1", "1"), "E <= 256, TOPK <= 16, B <= 64", ("logits",), ("routing_weights", "expert_ids", "expert_lists")),
+    "moe_up_g": _batch_op("moe_up_g", "tile_moe_up_g", ("E*tpe", "1", "1"), "as gemv_nb", ("weights", "input", "expert_lists"), ("activation",)),
+    "moe_down_g": _batch_op("moe_down_g", "tile_moe_down_g", ("E*tpe", "1", "1"), "as gemv_nb", ("weights", "activation", "expert_lists", "routing_weights"),
+                            ("expert_output",)),
+    "cols": _batch_op("cols", "tile_prologue_nb / tile_argmax", ("B", "1", "1"), "B <= 64", ("token_in", "embedding", "logits"), ("residual", "positions", "token_out")),
+})
+
+
 def grid_for(export, dims, *, role, cu, parts, tpe=1):
     """The launch grid of `export` for a model (etx/importer/spec.py:372-389)."""
     spec = OPERATORS[export]

@@ -173,6 +173,15 @@ def test_two_ranks_on_two_gpus_match_the_whole_model(od_name):
     top2 = np.sort(wl)[-2:]
     if top2[1] - top2[0] > 4e-2 * np.abs(wl).max():
         assert out[0][3][0] == wtok
+    # and against the ORACLE with every input token given (teacher forcing): the ranks' hidden state and logits within the
+    # bf16 tolerance of the CPU numerical path
+    ref = O.Ref(od, W, MAXLEN)
+    for t, tok in enumerate(long_prompt(od)):
+        dump = []
+        otok, ol = ref.step(int(tok), t, dump=dump, return_logits=True)
+    eo_l, eo_h = np.abs(fl - ol).max() / np.abs(ol).max(), np.abs(fr - dump[-1]).max() / np.abs(dump[-1]).max()
+    print("against the oracle: logits", eo_l, "hidden", eo_h, "token", out[0][3][0], "oracle", otok)
+    assert eo_l <= 2e-2 and eo_h <= 2e-2, f"against the oracle: logits off by {eo_l:.4f}, hidden state by {eo_h:.4f}"
     # sampled tokens: equal to the whole model's until a step whose top-2 margin is inside that tolerance
     want = whole.generate(prompt_of(od), N_GEN).tolist()
     whole.close()
