@@ -428,6 +428,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
     g.etensor("E_pro", (1,), wait_count=1)
     g.call_device("prologue", (1,), tile("vl_prologue"), resource=res, args=["vl"], consts=(0,), out_edges={"E_pro": "i->i"}, duration_us=3.8)
     prev = "E_pro"
+    before_x = prev
     for L in range(d.L):
         W = lambda n, L=L: ptr(f"{L}.{n}")                                  # noqa: E731
         # ---- qkv with the input-norm fold
@@ -438,7 +439,9 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                           resid_out=0 if first else ptr("resid"), ln=W("ln1"), R=0 if first else ranks, eps=d.eps,
                           ids=0, wts=W("bqkv") if d.bias else 0,
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0) | (0 if first else xmode), nb=1)
-        prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), prev, "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
+        # (sharded: the fold polls the step flags of the rows the ranks publish, which says more than the exchanged grid's
+        # event -- that only counts this rank's tasks -- so it waits for the event BEFORE that grid and starts polling at once)
+        prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), (before_x if ranks > 1 and not first else prev), "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
         if fused_attn:
             # ---- the attention phase as one grid: prep + split-KV partitions + merge by the last task to finish
             gq, plen, gparts = (0, 0, 0) if fused_attn == "general" else sz.attn
@@ -474,13 +477,15 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         t, rpt = sz.o
         blob = gemv_block("dsl_gemv", t, W=W("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.HD, rpt=rpt, tpe=1, eps=d.eps, nb=1,
                           rows=xblock(L, 0), mode=xmode)
+        before_x = prev
         prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD, after="", exchange=True)
+        fold_in = before_x if ranks > 1 else prev
         if d.moe:
             # ---- router with the post-attention norm fold: task 0 stores resid2 and the normed vector
             t, rpt = sz.router
             blob = gemv_block("dsl_gemv_fold", t, W=W("wr"), x=ptr("o_norm"), out=ptr("rlog"), M=d.E, K=d.H, rpt=rpt, tpe=1, rows=xblock(L, 0) or ptr("o"),
                               resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps, mode=op_gemv.MODE_NORM | xmode, nb=1)
-            prev = add(f"router_{L}", "dsl_gemv_fold", "router", L, blob, t, (t,), prev, "i->(0)", f"E_rt_{L}", "i->(0)", (1,), t, d.E, d.H, after="")
+            prev = add(f"router_{L}", "dsl_gemv_fold", "router", L, blob, t, (t,), fold_in, "i->(0)", f"E_rt_{L}", "i->(0)", (1,), t, d.E, d.H, after="")
             topk_mode = (op_gemv.MODE_TOPK_RENORM if d.norm_topk else op_gemv.MODE_TOPK) | hf_mode
             if not fold_topk:
                 from ..ops import topk as op_topk2
@@ -503,6 +508,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                               estride=d.H * d.MI, M=d.H, K=d.MI, rpt=rpt, tpe=tpe, R=d.TOPK, eps=d.eps,
                               mode=(topk_mode | op_gemv.MODE_ROUTE_READY if fold_topk else 0) | op_gemv.mode_spt(slots) | op_gemv.MODE_SUM_SLOTS | xmode, E=d.E, logits=ptr("rlog"), nb=1)
             # expert weights depend on the routing only: with the top-k folded in, the stream may start once the router is done
+            before_x = prev
             prev = add(f"moe_down_{L}", dn_export, "moe_down", L, blob, tpe, (tpe,), prev, "i->(0)",
                        f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.MI, after=f"E_rt_{L}" if fold_topk else None, exchange=True)
         else:
@@ -511,10 +517,11 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
             blob = gemv_block("dsl_moe_up", tpe, W=W("wgu"), x=ptr("o_norm"), out=ptr("mc2"), estride=0, M=d.INTER, K=d.H, rpt=rpt, tpe=tpe,
                               rows=xblock(L, 0) or ptr("o"), resid_in=ptr("resid"), resid_out=ptr("resid2"), ln=W("ln2"), R=ranks, eps=d.eps,
                               mode=op_gemv.MODE_NORM | xmode, nb=1)
-            prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H, after="")
+            prev = add(f"gate_up_{L}", "dsl_moe_up", "gate_up", L, blob, tpe, (tpe,), fold_in, "i->(0)", f"E_up_{L}", "i->(0)", (1,), tpe, d.INTER, d.H, after="")
             tpe, rpt = sz.down
             blob = gemv_block("dsl_moe_down", tpe, W=W("wd"), x=ptr("mc2"), out=ptr("moe_out"), estride=0, M=d.H, K=d.INTER, rpt=rpt, tpe=tpe,
                               eps=d.eps, nb=1, rows=xblock(L, 1), mode=xmode)
+            before_x = prev
             prev = add(f"down_{L}", "dsl_moe_down", "down", L, blob, tpe, (tpe,), prev, "i->(0)", f"E_dn_{L}", "i->(0)", (1,), tpe, d.H, d.INTER, after="", exchange=True)
     # ---- lm_head with the final-norm fold, then greedy sampling
     t, rpt = sz.lm
@@ -523,7 +530,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                       out=ptr("logits"), M=d.lm_rows, K=d.H, rpt=rpt,
                       tpe=1, rows=xblock(d.L - 1, 1) or ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=ranks, eps=d.eps,
                       ids=0, mode=op_gemv.MODE_NORM | xmode, nb=1)
-    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), prev, "i->(0)", "E_lm", "i->(0)", (1,), t, d.lm_rows, d.H, after="")
+    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), (before_x if ranks > 1 else prev), "i->(0)", "E_lm", "i->(0)", (1,), t, d.lm_rows, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},
                   out_edges={"E_argmax": "i->i"}, duration_us=8.5)

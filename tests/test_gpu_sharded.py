@@ -137,15 +137,16 @@ def _rank(rank, world, port, od_name, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("od_name", ["moe", "dense"])
-def test_two_ranks_on_two_gpus_match_the_whole_model(od_name):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("od_name,world", [("moe", 2), ("dense", 2), ("moe", 4), ("dense", 4)])
+def test_two_ranks_on_two_gpus_match_the_whole_model(od_name, world):
+    """world = 4 on these models (2 kv heads) is the case with more ranks than kv heads: every kv head lives on two ranks."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     od = {"moe": SMALL_MOE, "dense": SMALL_DENSE}[od_name]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_rank, args=(r, 2, 29641 + (od_name == "dense"), od_name, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rank, args=(r, world, 29641 + (od_name == "dense") + 2 * world, od_name, q)) for r in range(world)]
     for p in procs:
         p.start()
     out = sorted((q.get(timeout=300) for _ in procs), key=lambda t: t[0])
@@ -156,8 +157,9 @@ def test_two_ranks_on_two_gpus_match_the_whole_model(od_name):
         assert logits is not None, f"rank {rank}: {toks}"
     # both ranks hold bit-identical hidden states (same rows added in the same order) and agree on every token
     # (the lm_head is split by vocabulary: a rank's logits are its half, the token is agreed on through the argmax exchange)
-    assert out[0][1] == out[1][1]
-    assert out[0][3][0] == out[1][3][0] and np.array_equal(out[0][3][2], out[1][3][2])
+    for r in range(1, world):
+        assert out[0][1] == out[r][1]
+        assert out[0][3][0] == out[r][3][0] and np.array_equal(out[0][3][2], out[r][3][2])
     # against the whole model on one GPU with every input token given: hidden state and logits within the bf16 tolerance
     # (a rank rounds its partial rows to bf16 before they are added, the whole model rounds the whole row once)
     d = qdims(od)
@@ -165,9 +167,9 @@ def test_two_ranks_on_two_gpus_match_the_whole_model(od_name):
     whole = D.DecodeProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, MAXLEN), "cuda:0"), device=0, maxlen=MAXLEN)
     wtok = whole.generate(long_prompt(od), 1).tolist()
     wl, wr = whole.read("logits"), whole.read("resid")
-    vl = Q.shard_dims(d, 2).VL
-    assert vl == d.V // 2
-    fl, fr = np.concatenate([out[0][3][1][:vl], out[1][3][1][:vl]]), out[0][3][2]
+    vl = Q.shard_dims(d, world).VL
+    assert vl == d.V // world
+    fl, fr = np.concatenate([out[r][3][1][:vl] for r in range(world)]), out[0][3][2]
     el, er = np.abs(fl - wl).max() / np.abs(wl).max(), np.abs(fr - wr).max() / np.abs(wr).max()
     assert el <= 2e-2 and er <= 2e-2, f"logits off by {el:.4f}, hidden state by {er:.4f} (relative to the largest value)"
     top2 = np.sort(wl)[-2:]
