@@ -4,6 +4,7 @@
 //
 // Takes over the reference's host launcher etx/runtime/include/etx/host.h (setup 79-210, launch 339-347, watchdog
 // wait 351-417, event dump 545-587) and the token loop of examples/vllm_llm/host.hip:819-894.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
 #include <string.h>
@@ -70,6 +71,8 @@ struct etxb_session {
   unsigned char* xpeer[ETXB_MAX_PEERS] = {};
   uint32_t xargmax = 0;                // byte offset of the sharded argmax block in a region (0: the lm_head is whole on every rank)
   bool has_exchange = false;           // the plan is one rank's step of a sharded model (some grid is marked exchanged)
+  bool tc_on = false;                  // the plan has tensor-core tiles (tcgen05): the kernel allocates tensor memory
+  void* d_maps = nullptr;              // their TMA tensor maps, one per grid (128 bytes each)
 };
 
 static int g_kernel_ready[64];
@@ -151,9 +154,12 @@ static int32_t check_batch_block(int body, const unsigned char* blk, size_t byte
   if (a.K <= 0 || (a.K % 8) || a.M < 0) why = "K > 0, K % 8 == 0";
   else if (a.nb < 1 || a.nb > 64) why = "1 <= nb <= 64 columns";
   else if (body == ETXB_BODY_NORM_COL && (a.K > ETXB_XF_FLOATS || a.R < 0 || a.R > 64 || !a.resid_in || !a.x || !a.ln)) why = "norm of a column: K <= 8192, 0 <= R <= 64, resid_in / x / ln set";
-  else if (body != ETXB_BODY_NORM_COL && (size_t)a.K * 2 + ETXB_NB_PAD > ETXB_NBX_BYTES) why = "one token vector must fit the 40 KB activation stage";
+  else if (body != ETXB_BODY_NORM_COL && body < ETXB_BODY_GEMV_TC && (size_t)a.K * 2 + ETXB_NB_PAD > ETXB_NBX_BYTES) why = "one token vector must fit the 40 KB activation stage";
   else if (body != ETXB_BODY_NORM_COL && (a.rpt < 1 || a.M < 1 || !a.W || !a.x || !a.out)) why = "rpt >= 1, M >= 1, W / x / out set";
-  else if ((body == ETXB_BODY_MOE_UP_G || body == ETXB_BODY_MOE_DOWN_G) && (a.tpe < 1 || a.R < 1 || a.R > 255 || !a.rows || !a.resid_in)) why = "expert-grouped tile: tpe >= 1, 1 <= R <= 255, token lists (rows) and their lengths (resid_in) set";
+  else if ((body == ETXB_BODY_MOE_UP_G || body == ETXB_BODY_MOE_DOWN_G || body == ETXB_BODY_MOE_UP_TC || body == ETXB_BODY_MOE_DOWN_TC) &&
+           (a.tpe < 1 || a.R < 1 || a.R > 255 || !a.rows || !a.resid_in)) why = "expert-grouped tile: tpe >= 1, 1 <= R <= 255, token lists (rows) and their lengths (resid_in) set";
+  else if (body >= ETXB_BODY_GEMV_TC && (a.K % 64 || ((uintptr_t)a.W & 15))) why = "tensor-core tile: K % 64 == 0 and W 16-byte aligned (TMA tensor copies of 64-wide chunks)";
+  else if ((body == ETXB_BODY_MOE_UP_TC || body == ETXB_BODY_MOE_DOWN_TC) && (a.E < 1 || a.estride <= 0 || a.estride % a.K)) why = "tensor-core expert tile: E >= 1 and estride a multiple of K (the experts form one [E * rows][K] matrix)";
   if (!why) return ETXB_OK;
   snprintf(m, sizeof m, "batched block (body %d, M=%d, K=%d, rpt=%d, tpe=%d, R=%d, nb=%d) outside the tile: %s", body, a.M, a.K, a.rpt, a.tpe, a.R, a.nb, why);
   return fail(ETXB_E_UNSUPPORTED, m);
@@ -161,7 +167,7 @@ static int32_t check_batch_block(int body, const unsigned char* blk, size_t byte
 
 // A block of `body` at `blk` (`bytes` readable).  Tiles whose blocks carry no loop bound the device depends on pass.
 static int32_t check_block(int body, const unsigned char* blk, size_t bytes) {
-  if (body >= ETXB_BODY_NORM_COL && body <= ETXB_BODY_ARGMAX_NB) return check_batch_block(body, blk, bytes);
+  if (body >= ETXB_BODY_NORM_COL && body <= ETXB_BODY_MOE_DOWN_TC) return check_batch_block(body, blk, bytes);
   if (body == ETXB_BODY_GEMV || body == ETXB_BODY_MOE_UP || body == ETXB_BODY_MOE_DOWN) {
     if (bytes < sizeof(etxb_gemv_args)) return fail(ETXB_E_ARG, "GEMV-family tile: the argument block is 160 bytes");
     etxb_gemv_args a;
@@ -369,7 +375,7 @@ extern "C" int32_t etxb_destroy(etxb_session* s) {
   cudaSetDevice(s->device);
   if (s->launched) cudaDeviceSynchronize();
   void* ptrs[] = {s->d_tasks, s->d_recs, s->d_urecs, s->d_uqbegin, s->d_qbegin, s->d_types, s->d_type_args, s->d_events, s->d_evcount, s->d_inwords, s->d_outwords,
-                  s->d_ctrl, s->d_trace, s->d_exec, s->d_pool};
+                  s->d_ctrl, s->d_trace, s->d_exec, s->d_pool, s->d_maps};
   for (void* p : ptrs) if (p) cudaFree(p);
   if (s->h_ctrl) cudaFreeHost(s->h_ctrl);
   if (s->h_tok) cudaFreeHost(s->h_tok);
@@ -512,6 +518,55 @@ static int32_t exchange_rows(const etxb_session* s, const etxb_type& ty, const e
   return ETXB_OK;
 }
 
+typedef CUresult (*etxb_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int32_t build_tensor_maps(etxb_session* s) {
+  std::vector<size_t> blocks;                                       // pool offsets of the argument blocks of tensor-core grids
+  for (const etxb_type& ty : s->types)
+    if (ty.body >= ETXB_BODY_GEMV_TC && ty.body <= ETXB_BODY_MOE_DOWN_TC) {
+      if (ty.args[0] != 0 || ty.cst[0] < 0 || (size_t)ty.cst[0] + sizeof(etxb_gemv_args) > s->h_pool.size())
+        return fail(ETXB_E_UNSUPPORTED, "a tensor-core grid keeps its argument block in the pool");
+      blocks.push_back((size_t)ty.cst[0]);
+    }
+  s->tc_on = !blocks.empty();
+  if (blocks.empty()) return ETXB_OK;
+  static etxb_encode_fn encode = nullptr;
+  if (!encode) {
+    cudaDriverEntryPointQueryResult q;
+    void* fn = nullptr;
+    CU(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) return fail(ETXB_E_CUDA, "the driver does not offer cuTensorMapEncodeTiled");
+    encode = (etxb_encode_fn)fn;
+  }
+  std::vector<CUtensorMap> maps(blocks.size());
+  if (s->d_maps) { CU(cudaFree(s->d_maps)); s->d_maps = nullptr; }
+  CU(cudaMalloc(&s->d_maps, maps.size() * sizeof(CUtensorMap)));
+  size_t i = 0;
+  for (const etxb_type& ty : s->types) {
+    if (!(ty.body >= ETXB_BODY_GEMV_TC && ty.body <= ETXB_BODY_MOE_DOWN_TC)) continue;
+    etxb_gemv_args a;
+    memcpy(&a, s->h_pool.data() + ty.cst[0], sizeof a);
+    const cuuint64_t rows = ty.body == ETXB_BODY_GEMV_TC ? (cuuint64_t)a.M : (cuuint64_t)a.E * (cuuint64_t)(a.estride / a.K);
+    cuuint64_t gdim[2] = {(cuuint64_t)a.K, rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)a.K * 2};
+    cuuint32_t box[2] = {64, ETXB_TC_ROWS};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)a.W, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+      char m[160];
+      snprintf(m, sizeof m, "cuTensorMapEncodeTiled failed (%d) for a [%llu][%d] bf16 weight tensor", (int)r, (unsigned long long)rows, a.K);
+      return fail(ETXB_E_CUDA, m);
+    }
+    const void* dev = (const unsigned char*)s->d_maps + i * sizeof(CUtensorMap);
+    CU(cudaMemcpy(s->d_pool + ty.cst[0] + offsetof(etxb_gemv_args, ln), &dev, sizeof dev, cudaMemcpyHostToDevice));
+    ++i;
+  }
+  CU(cudaMemcpy(s->d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
+  return ETXB_OK;
+}
+
 static int32_t upload_type_args(etxb_session* s) {
   std::vector<void*> ta((size_t)s->h.n_types * ETXB_MAX_ARGS, nullptr);
   for (size_t t = 0; t < s->types.size(); ++t)
@@ -527,6 +582,13 @@ static int32_t upload_type_args(etxb_session* s) {
   for (const etxb_type& ty : s->types) {
     if (ty.args[0] != 0 || ty.cst[0] < 0 || (size_t)ty.cst[0] >= s->h_pool.size()) continue;
     int32_t rc = check_block(ty.body, s->h_pool.data() + ty.cst[0], s->h_pool.size() - (size_t)ty.cst[0]);
+    if (rc) return rc;
+  }
+  // tensor-core tiles: one TMA tensor map per grid -- the weight tensor as a [rows][K] bf16 matrix, box 64 k x 128 rows,
+  // 128-byte swizzle -- built here because only the library knows the driver entry point; its device address goes into
+  // the `ln` field of the grid's argument block (in the device copy of the pool)
+  {
+    int32_t rc = build_tensor_maps(s);
     if (rc) return rc;
   }
   // per-task records in queue order (the consumer loop prefetches them)
@@ -585,7 +647,7 @@ static void fill_params(etxb_session* s, etxb_params& p) {
   p.ctrl = s->d_ctrl; p.trace = s->trace ? s->d_trace : nullptr; p.exec_count = s->trace ? s->d_exec : nullptr;
   p.step_dev = nullptr; p.timeout_ns = s->timeout_ns; p.epoch = s->epoch; p.n_workers = (int32_t)s->h.n_workers;
   p.step = s->step;
-  p.n_peers = s->n_ranks - 1; p.rank = s->rank; p.xargmax = s->xargmax; p.pad = 0; p.xbase = s->xbase;
+  p.n_peers = s->n_ranks - 1; p.rank = s->rank; p.xargmax = s->xargmax; p.tc_on = s->tc_on ? 1u : 0u; p.xbase = s->xbase;
   for (int q = 0; q < ETXB_MAX_PEERS; ++q) p.xpeer[q] = s->xpeer[q];
 }
 
@@ -889,7 +951,7 @@ __global__ void __launch_bounds__(ETXB_CONSUMERS, 1) etxb_attn_static_kernel(con
   Smem sm;
   sm.xs = (float*)st_smem;
   sm.scr = (float*)(st_smem + ETXB_GEN_BYTES);
-  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.stop = nullptr; sm.tr = nullptr; sm.epoch = 0; sm.cur = 0;
+  sm.ring = nullptr; sm.full = nullptr; sm.empty = nullptr; sm.prod = nullptr; sm.deadline = nullptr; sm.ctrl = nullptr; sm.stop = nullptr; sm.tr = nullptr; sm.tc = nullptr; sm.epoch = 0; sm.cur = 0;
   tile_attn_fused((const unsigned char*)&d, (int)blockIdx.x, sm, S);
 }
 }  // namespace etxb

@@ -127,7 +127,7 @@ struct etxb_params {
   // sharded model (etxb_set_exchange): this rank's exchange region and the other ranks' as mapped into this process;
   // the blocks of flagged rows sit at the same offsets in every rank's region.
   int32_t n_peers, rank;
-  uint32_t xargmax, pad;                           // byte offset in a region of the [ranks][2] 8-byte (payload, flag) slots of the sharded
+  uint32_t xargmax, tc_on;                         // byte offset in a region of the [ranks][2] 8-byte (payload, flag) slots of the sharded
                                                    // argmax (lm_head split by vocabulary); 0 = every rank holds all logits
   unsigned char* xbase;
   unsigned char* xpeer[ETXB_MAX_PEERS];

@@ -34,6 +34,7 @@ struct Smem {
   int32_t* ctrl;
   int* stop;                 // CTA-local: a wait inside a body gave up (the body's results are not to be announced)
   uint64_t* tr;              // 8 stamps of the running task when tracing, else null (slots 4..7 are in-body marks)
+  struct TcShared* tc;       // state of the tensor-core tiles of a batched step (null where the kernel has none)
   uint32_t epoch;            // the step (sharded sessions: the flag of this step's exchanged words derives from it)
   int cur;                   // the running task's index in the queue order (reported when a wait gives up)
 };

@@ -7,6 +7,7 @@
 #include "etxb_attn.cuh"
 #include "etxb_attn_gq.cuh"
 #include "etxb_batch.cuh"
+#include "etxb_tc.cuh"
 #include "etxb_gemv.cuh"
 #include "etxb_prims.cuh"
 
@@ -201,6 +202,9 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
     case 16: if constexpr (!LEAN) { tile_moe_up_g(args, c0, sm); break; }
     case 17: if constexpr (!LEAN) { tile_moe_down_g(args, c0, sm); break; }
     case 18: if constexpr (!LEAN) { tile_prologue_nb(args, c0, p.step); break; }
+    case 20: if constexpr (!LEAN && !XCH) { tile_gemv_tc(args, c0, sm, *sm.tc, cur); break; }
+    case 21: if constexpr (!LEAN && !XCH) { tile_moe_up_tc(args, c0, sm, *sm.tc, cur); break; }
+    case 22: if constexpr (!LEAN && !XCH) { tile_moe_down_tc(args, c0, sm, *sm.tc, cur); break; }
     case 19: if constexpr (!LEAN) { if (c0 < ((const etxb_batch_args*)args)->nb) tile_argmax<false>(p, sm, c0, ((const etxb_batch_args*)args)->nb); break; }
     default:
       if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);
@@ -260,6 +264,8 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ int s_stop;
   __shared__ unsigned long long s_deadline;
+  __shared__ __align__(8) TcShared s_tc;                           // (used by the full kernel of a batched plan only)
+  constexpr bool TC = GQV == 0 && !XCH;
   Smem sm;
   sm.ring = smem_raw;
   sm.xs = (float*)(smem_raw + ETXB_RING_BYTES);
@@ -271,12 +277,18 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   sm.ctrl = p.ctrl;
   sm.stop = &s_stop;
   sm.tr = nullptr;
+  sm.tc = &s_tc;
   sm.epoch = p.epoch;
   sm.cur = 0;
   if (threadIdx.x == 0) {
     s_stop = 0;
     s_deadline = globaltimer() + p.timeout_ns;
     for (int i = 0; i < ETXB_NSTAGE; ++i) { mbar_init(sm.full + i, 1); mbar_init(sm.empty + i, ETXB_CONSUMER_WARPS); }
+    if constexpr (TC) {
+      for (int i = 0; i < ETXB_TC_NSTAGE; ++i) { mbar_init(s_tc.full + i, 1); mbar_init(s_tc.empty + i, 1); }
+      mbar_init(&s_tc.acc, 1);
+      s_tc.n = 0; s_tc.nacc = 0; s_tc.tmem = 0;
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -288,6 +300,12 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   }
   TaskCtx* ctx = (TaskCtx*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512);
   const bool fetcher = threadIdx.x >= ETXB_CONSUMERS - 32;          // the last consumer warp keeps the contexts coming
+  if constexpr (TC) {
+    // tensor memory for the tensor-core tiles of a batched plan: allocated once per launch by warp 0 (one CTA per SM, so
+    // the columns are always there), freed by the same warp after the last task on every path out of the loop below
+    if (p.tc_on != 0u && threadIdx.x < 32) tc_alloc(&s_tc.tmem);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
   if (fetcher && q0 < q1) {
     fetch_ctx(p, ctx, q0, q0, -1);
     fetch_ctx(p, ctx, q0, q0 + 1 < q1 ? q0 + 1 : -1, -1);
@@ -346,6 +364,13 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
         }
       if (p.trace) { p.trace[8 * (size_t)id + 2] = globaltimer(); p.trace[8 * (size_t)id + 3] = blockIdx.x; }
       if (p.exec_count) atomicAdd(p.exec_count + id, 1);
+    }
+  }
+  if constexpr (TC) {
+    if (p.tc_on != 0u) {
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      csync();                                                     // nobody reads an accumulator any more
+      if (threadIdx.x < 32) tc_dealloc(s_tc.tmem);
     }
   }
 }

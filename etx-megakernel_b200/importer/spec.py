@@ -135,9 +135,10 @@ ARGUMENTS.update({
 
 
 def _batch_op(name, tile, grid, shape, reads, writes):
+    recipe = {"gemv_tc": "gemv_nb", "moe_up_tc": "moe_up_g", "moe_down_tc": "moe_down_g"}.get(name, name)
     return Operator(name, f"etxb::{tile}", grid, shape, dict(NB_MAX=_batch.NB_MAX, XBYTES=_batch.XBYTES, GROUP_ROWS=_batch.GROUP_ROWS), reads, writes,
                     layouts="column b of a batched buffer at base + b * stride (element counts, the reference's sx / sout / srows / srin / srout)",
-                    arguments={name: ARGUMENTS[name]})
+                    arguments={recipe: ARGUMENTS[recipe]})
 
 
 OPERATORS.update({
@@ -148,6 +149,10 @@ OPERATORS.update({
     "moe_up_g": _batch_op("moe_up_g", "tile_moe_up_g", ("E*tpe", "1", "1"), "as gemv_nb", ("weights", "input", "expert_lists"), ("activation",)),
     "moe_down_g": _batch_op("moe_down_g", "tile_moe_down_g", ("E*tpe", "1", "1"), "as gemv_nb", ("weights", "activation", "expert_lists", "routing_weights"),
                             ("expert_output",)),
+    "gemv_tc": _batch_op("gemv_tc", "tile_gemv_tc", ("CU", "1", "1"), "K % 64 == 0, B <= 64 (32 columns per pass)", ("weights", "input", "bias"), ("output",)),
+    "moe_up_tc": _batch_op("moe_up_tc", "tile_moe_up_tc", ("E*tpe", "1", "1"), "as gemv_tc", ("weights", "input", "expert_lists"), ("activation",)),
+    "moe_down_tc": _batch_op("moe_down_tc", "tile_moe_down_tc", ("E*tpe", "1", "1"), "as gemv_tc", ("weights", "activation", "expert_lists", "routing_weights"),
+                             ("expert_output",)),
     "cols": _batch_op("cols", "tile_prologue_nb / tile_argmax", ("B", "1", "1"), "B <= 64", ("token_in", "embedding", "logits"), ("residual", "positions", "token_out")),
 })
 

@@ -51,9 +51,19 @@ def buffer_shapes(d: Q.Dims, B: int, maxlen: int, steps: int, parts: int) -> dic
             "mc2": ((B, d.TOPK, d.MI), "bf16"), "mc3": ((B, d.TOPK, d.H), "bf16"), "ecount": ((d.E,), "i32"), "elist": ((d.E, B), "i32"), "active": ((d.L,), "i32")}
 
 
-def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineModel | str = "b200"):
+def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineModel | str = "b200", engine: str = "tc"):
     """The batched decode step of `d` for B sequences as a Graph plus its argument pool.  ptr(name) -> device address of
-    a buffer (buffer_shapes) or packed weight (models.qwen.weight_shapes).  Returns (graph, pool, info)."""
+    a buffer (buffer_shapes) or packed weight (models.qwen.weight_shapes).  Returns (graph, pool, info).
+
+    engine: what multiplies the batched grids (dense projections, expert gate+up / down) -- "tc": tcgen05.mma with TMA tensor
+    copies and accumulators in tensor memory (needs every K a multiple of 64); "mma": the mma.sync tiles that read their
+    weights straight from global memory.  Same grids, same argument blocks, same results up to fp32 summation order."""
+    if engine not in ("tc", "mma"):
+        raise ValueError("engine is 'tc' or 'mma'")
+    if engine == "tc" and any(k % 64 for k in (d.H, d.NH * d.HD, d.MI)):
+        engine = "mma"
+    sfx = "_tc" if engine == "tc" else "_nb"
+    gsfx = "_tc" if engine == "tc" else "_g"
     if not d.moe:
         raise ValueError("the batched step is built for the softmax top-k MoE models")
     if d.HD != 128 or d.G not in (1, 2, 4, 8):
@@ -97,7 +107,7 @@ def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineMode
 
     def dense(name, Wp, x, out, M, K, bias=0):
         t, rpt = m.gemv_tasks(M)
-        add(name, "etx_tile_gemv_nb", gb("gemv_nb", t, W=Wp, x=ptr(x), out=ptr(out), M=M, K=K, rpt=rpt, tpe=1, nb=B, sx=K, sout=M, wts=bias,
+        add(name, "etx_tile_gemv" + sfx, gb("gemv" + sfx, t, W=Wp, x=ptr(x), out=ptr(out), M=M, K=K, rpt=rpt, tpe=1, nb=B, sx=K, sout=M, wts=bias,
                                          mode=op_gemv.MODE_BIAS if bias else 0), (t,), t)
 
     cols = argblock.pack_named(ent["cols"], (B, 1, 1), nb=B, slot_span=nblk * BS)
@@ -127,23 +137,24 @@ def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineMode
                                                                 elist=ptr("elist"), active=ptr("active") + 4 * L, E=d.E, K=d.TOPK, mode=(1 if d.norm_topk else 0) | op_gemv.MODE_BF16_WTS,
                                                                 nb=B, cap=B), (1,), 1)
         tpe = -(-d.MI // UP_ROWS)
-        add(f"moe_up_{L}", "etx_tile_moe_up_g", gb("moe_up_g", d.E * tpe, W=Wl("w13"), x=ptr("o_norm"), out=ptr("mc2"), estride=2 * d.MI * d.H, M=d.MI, K=d.H,
+        add(f"moe_up_{L}", "etx_tile_moe_up" + gsfx, gb("moe_up" + gsfx, d.E * tpe, E=d.E, W=Wl("w13"), x=ptr("o_norm"), out=ptr("mc2"), estride=2 * d.MI * d.H, M=d.MI, K=d.H,
                                                   rpt=UP_ROWS, tpe=tpe, rows=ptr("elist"), resid_in=ptr("ecount"), nb=B, R=d.TOPK, sx=d.H, eps=d.eps),
             (d.E * tpe,), d.E * tpe)
         tpe = -(-d.H // DOWN_ROWS)
-        add(f"moe_down_{L}", "etx_tile_moe_down_g", gb("moe_down_g", d.E * tpe, W=Wl("w2"), x=ptr("mc2"), out=ptr("mc3"), wts=ptr("tw"), estride=d.H * d.MI,
+        add(f"moe_down_{L}", "etx_tile_moe_down" + gsfx, gb("moe_down" + gsfx, d.E * tpe, E=d.E, W=Wl("w2"), x=ptr("mc2"), out=ptr("mc3"), wts=ptr("tw"), estride=d.H * d.MI,
                                                       M=d.H, K=d.MI, rpt=DOWN_ROWS, tpe=tpe, rows=ptr("elist"), resid_in=ptr("ecount"), nb=B, R=d.TOPK, eps=d.eps),
             (d.E * tpe,), d.E * tpe)
     norm("norm_f", "mc3", d.TOPK, "ti", d.TOPK * d.H, "resid2", "resid", "hn", ptr("final_norm"))
     dense("lm_head", ptr("embed") if d.tie else ptr("lm_head"), "hn", "logits", d.V, d.H)
     add("argmax", "vl_argmax_nb", cols, (B,), B)
-    return g, pool, {"workers": W, "attn": (gq, plen, gparts), "attn_tasks": ntask}
+    return g, pool, {"workers": W, "attn": (gq, plen, gparts), "attn_tasks": ntask, "engine": engine}
 
 
 class BatchProgram:
     """B sequences decoded in lock step on one GPU: weights, per-sequence buffers and KV blocks, plan, session."""
 
-    def __init__(self, dims: Q.Dims, weights: dict, batch: int, device: int = 0, maxlen: int = 1072, steps: int | None = None, machine="b200"):
+    def __init__(self, dims: Q.Dims, weights: dict, batch: int, device: int = 0, maxlen: int = 1072, steps: int | None = None, machine="b200",
+                 engine: str = "tc"):
         self.d, self.B, self.maxlen = dims, int(batch), maxlen
         self.dev = torch.device("cuda", device)
         self.machine = load_machine(machine) if isinstance(machine, str) else machine
@@ -162,7 +173,7 @@ class BatchProgram:
             if t is None:
                 t = self.w[name]
             return t.data_ptr()
-        self.graph, self.pool, self.info = build_graph(dims, ptr, self.B, maxlen, self.machine)
+        self.graph, self.pool, self.info = build_graph(dims, ptr, self.B, maxlen, self.machine, engine=engine)
         pool = self.pool.bytes()
         self.plan = compile_graph(self.graph, self.machine, {"POOL": len(pool)}, options=PassOptions())
         self.session = Session(self.plan, {}, pool, device)

@@ -12,6 +12,8 @@ prologue / argmax have small blocks of their own.
                 *active += the number of experts with a non-empty list (what the byte ledger of a batched step needs)
   moe_up_g      task (expert e, row chunk): act[b][slot][r] for every (b, slot) of e's list
   moe_down_g    task (expert e, row chunk): y[b][slot][r] = bf16(bf16(W2_e[r,:] . act[b][slot]) * wts[b][slot])
+  gemv_tc, moe_up_tc, moe_down_tc   the same three grids on tcgen05.mma (K % 64 == 0; the expert blocks also carry E); `ln` is
+                filled by the library with the address of the grid's TMA tensor map
   prologue_nb   task b: residual <- embedding row of column b's token, positions / slot of column b
   argmax_nb     task b: greedy token of column b
 """
@@ -35,7 +37,9 @@ def import_entries(threads: int = 544) -> dict:
     out = {e: entry(e, e, _gemv.PARAMS, _gemv.ARG_BYTES, _gemv.GRID_OFF, threads, spec)
            for e, spec in (("norm_col", "residual add + expert combine + RMSNorm of one column"),
                            ("gemv_nb", "bf16 GEMV, nb activation columns per weight read (mma.sync)"),
-                           ("moe_up_g", "expert-grouped gate+up with SiLU*mul"), ("moe_down_g", "expert-grouped down, scaled"))}
+                           ("moe_up_g", "expert-grouped gate+up with SiLU*mul"), ("moe_down_g", "expert-grouped down, scaled"),
+                           ("gemv_tc", "bf16 GEMV, up to 32 columns per weight read (tcgen05.mma, TMA, tensor memory)"),
+                           ("moe_up_tc", "expert-grouped gate+up on tcgen05"), ("moe_down_tc", "expert-grouped down on tcgen05"))}
     out["route"] = entry("route", "route", ROUTE_PARAMS, ROUTE_BYTES, ROUTE_GRID, threads, "softmax top-k per column + per-expert token lists")
     out["cols"] = entry("cols", "cols", COLS_PARAMS, COLS_BYTES, COLS_GRID, threads, "per-column prologue / argmax of a batched step")
     return out

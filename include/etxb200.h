@@ -67,7 +67,12 @@ enum {
   ETXB_BODY_MOE_DOWN_G = 17,  /* expert-grouped down, scaled by the routing weight */
   ETXB_BODY_PROLOGUE_NB = 18, /* vl_prologue for column c of a batch */
   ETXB_BODY_ARGMAX_NB = 19,   /* vl_argmax for column c of a batch */
-  ETXB_BODY_COUNT = 20
+  /* the same three batched grids on the Blackwell tensor cores: tcgen05.mma, weights through TMA tensor copies, fp32 accumulators
+   * in tensor memory (the library builds the tensor maps when the plan is bound) */
+  ETXB_BODY_GEMV_TC = 20,
+  ETXB_BODY_MOE_UP_TC = 21,
+  ETXB_BODY_MOE_DOWN_TC = 22,
+  ETXB_BODY_COUNT = 23
 };
 
 /* The per-step scalars and buffers of the prologue / argmax tiles: field for field the reference's VlParams

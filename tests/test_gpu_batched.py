@@ -24,9 +24,11 @@ def qdims(od):
     return Q.Dims(**{f: getattr(od, f) for f in FIELDS})
 
 
-def program(od, W, B, maxlen):
+def program(od, W, B, maxlen, engine="tc"):
     d = qdims(od)
-    return BT.BatchProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, maxlen), "cuda:0"), B, device=0, maxlen=maxlen)
+    prog = BT.BatchProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, maxlen), "cuda:0"), B, device=0, maxlen=maxlen, engine=engine)
+    assert prog.info["engine"] == engine
+    return prog
 
 
 def oracle_column(od, W, prompt, n_gen, ctx):
@@ -58,14 +60,16 @@ def check_columns(name, got, od, W, prompts, n_gen, ctx):
     return identical
 
 
-@pytest.mark.parametrize("od,B", [(SMALL_MOE, 4), (MID, 8), (MID, 32)])
-def test_batched_greedy_tokens_per_column(od, B):
+@pytest.mark.parametrize("od,B,engine", [(SMALL_MOE, 4, "tc"), (MID, 8, "tc"), (MID, 32, "tc"), (MID, 40, "tc"), (SMALL_MOE, 4, "mma"), (MID, 32, "mma")])
+def test_batched_greedy_tokens_per_column(od, B, engine):
+    """Both engines of the batched grids: tcgen05.mma (TMA tensor copies, accumulators in tensor memory; 40 columns = two
+    passes of the dense grids) and the mma.sync tiles."""
     W = O.SyntheticWeights(od, seed=31, gamma="ones")
     prompts = np.random.default_rng(B).integers(0, od.V, (B, 12))
-    prog = program(od, W, B, 64)
+    prog = program(od, W, B, 64, engine)
     got = prog.generate(prompts, 12)
     prog.close()
-    identical = check_columns(f"{od.name} x{B}", got, od, W, prompts, 12, 64)
+    identical = check_columns(f"{od.name} x{B} {engine}", got, od, W, prompts, 12, 64)
     assert identical >= (B + 1) // 2, f"only {identical} of {B} columns identical"
 
 
@@ -88,8 +92,8 @@ def test_columns_do_not_depend_on_their_neighbours():
 
 
 def test_one_batched_step_against_the_oracle_state():
-    """One teacher-forced step at a short context, B = 8: routing ids of the last layer bit-exact, routing weights within a
-    bf16 ulp, final hidden state and logits of every column within 2e-2 of the oracle's."""
+    """One teacher-forced step at a short context, B = 8: routing ids of the last layer exact (a swap of two experts only inside the oracle's own near tie), routing weights
+    within 2e-2, final hidden state and logits of every column within 2e-2 of the oracle's."""
     od, B, P = MID, 8, 9
     W = O.SyntheticWeights(od, seed=33, gamma="ones")
     prompts = np.random.default_rng(6).integers(0, od.V, (B, P))
@@ -113,7 +117,7 @@ def test_one_batched_step_against_the_oracle_state():
                 print(f"[batched step] column {b}: one expert swapped, oracle logits {a:.5f} / {c:.5f}")
                 assert abs(a - c) <= 2 * max(abs(a), abs(c)) * 2.0 ** -7, f"column {b}: routing ids differ beyond a near tie"
         else:
-            assert np.all(np.abs(wts[b] - tr["wts"]) <= np.abs(tr["wts"]) * 2.0 ** -7)
+            assert np.all(np.abs(wts[b] - tr["wts"]) <= BF16_REL * np.abs(tr["wts"]).max())      # (a smooth function of logits that carry three layers of summation-order noise)
         eh = np.abs(hid[b] - dump[-1]).max() / np.abs(dump[-1]).max()
         el = np.abs(logits[b] - lg).max() / np.abs(lg).max()
         assert eh <= BF16_REL and el <= BF16_REL, f"column {b}: hidden {eh:.4f}, logits {el:.4f}"
