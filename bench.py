@@ -231,7 +231,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         RD.connect_ranks(prog, dist)
     else:
         weights = D.random_packed_weights(d, maxlen, dev, seed=rank, gamma="ones")
-        prog = D.DecodeProgram(d, weights, device=local_rank, maxlen=maxlen, steps=maxlen)
+        prog = D.DecodeProgram(d, weights, device=local_rank, maxlen=maxlen, steps=maxlen, flagged=args.flagged)
     prompt = np.random.default_rng(1000 + (0 if tp > 1 else rank)).integers(0, d.V, P)
     # prefill: the prompt token by token through the same kernel (fills the KV caches), plus W warm-up decode steps
     tin = torch.zeros_like(prog.buf["token_in"]); tin[:P] = torch.tensor(prompt, dtype=torch.int32)
@@ -455,6 +455,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (debugging only; 0 = all)")
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--flagged", type=int, default=0, help="one GPU: hand o_proj / down outputs to the next norm fold as flagged words (1) or through events (0)")
     ap.add_argument("--batch", type=int, default=1, help="sequences per step (1: the headline ms/token; 8 / 32: tok/s through the batched step)")
     ap.add_argument("--shard", default="auto", choices=["auto", "tp", "replicas"],
                     help="N > 1: ONE request sharded over the N GPUs (tp; auto = tp when the model splits N ways, else replicas) or N independent requests (replicas)")

@@ -468,9 +468,9 @@ extern "C" int32_t etxb_exchange_close(int device, void* peer_ptr) {
 }
 
 extern "C" int32_t etxb_set_exchange(etxb_session* s, int32_t rank, int32_t n_ranks, void* local_base, size_t bytes, void* const* peer_bases) {
-  if (!s || !local_base || !peer_bases) return fail(ETXB_E_ARG, "null argument");
-  if (n_ranks < 2 || n_ranks > ETXB_MAX_PEERS + 1 || rank < 0 || rank >= n_ranks) return fail(ETXB_E_ARG, "set_exchange: 2 <= n_ranks <= 8, 0 <= rank < n_ranks");
-  if (s->epoch != 0 || s->launched || s->n_ranks != 1) return fail(ETXB_E_ARG, "set_exchange: once, before the first step");
+  if (!s || !local_base || (!peer_bases && n_ranks > 1)) return fail(ETXB_E_ARG, "null argument");
+  if (n_ranks < 1 || n_ranks > ETXB_MAX_PEERS + 1 || rank < 0 || rank >= n_ranks) return fail(ETXB_E_ARG, "set_exchange: 1 <= n_ranks <= 8, 0 <= rank < n_ranks");
+  if (s->epoch != 0 || s->launched || s->xbase != nullptr) return fail(ETXB_E_ARG, "set_exchange: once, before the first step");
   if (bytes < 4 || bytes > (size_t(1) << 24) || ((uintptr_t)local_base & 15)) return fail(ETXB_E_ARG, "set_exchange: a region is 16-byte aligned and at most 16 MiB");
   if (!s->has_exchange) return fail(ETXB_E_PLAN, "set_exchange: the plan marks no grid as exchanged");
   int q = 0;
@@ -607,7 +607,7 @@ static int32_t upload_type_args(etxb_session* s) {
     r.args = has_block ? (uint64_t)(uintptr_t)ta[(size_t)t.type * ETXB_MAX_ARGS] + (uint64_t)ty.cst[0] + (uint64_t)t.coord[1] * (uint64_t)ty.cst[1]
                        : (uint64_t)(uintptr_t)s->d_pool;
     r.stream_word = ty.stream_word;
-    if (s->n_ranks > 1 && ty.exchange) {
+    if (s->xbase != nullptr && ty.exchange) {
       int32_t rc = exchange_rows(s, ty, t, &r.mirror);
       if (rc) return rc;
     }
@@ -660,7 +660,7 @@ static int32_t launch_kernel(const etxb_params& p, int grid, cudaStream_t st, in
 extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   if (!s) return fail(ETXB_E_ARG, "null session");
   CU(cudaSetDevice(s->device));
-  if (s->has_exchange && s->n_ranks < 2) return fail(ETXB_E_ARG, "the plan is one rank of a sharded model: etxb_set_exchange comes before the first step");
+  if (s->has_exchange && s->xbase == nullptr) return fail(ETXB_E_ARG, "the plan is one rank of a sharded model: etxb_set_exchange comes before the first step");
   if (s->args_dirty) { int32_t rc = upload_type_args(s); if (rc) return rc; }
   s->stream = cuda_stream ? (cudaStream_t)cuda_stream : s->own_stream;
   if (s->trace && s->d_exec) CU(cudaMemsetAsync(s->d_exec, 0, (size_t)s->h.n_tasks * 4, s->stream));
@@ -668,7 +668,7 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   etxb_params p;
   fill_params(s, p);
   CU(cudaEventRecord(s->ev0, s->stream));
-  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->n_ranks > 1 ? 5 : 0));
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->xbase != nullptr ? 5 : 0));
   if (rc) return rc;
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
@@ -684,7 +684,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaSetDevice(s->device));
   if (s->args_dirty) { int32_t rc = upload_type_args(s); if (rc) return rc; }
   if (!s->grid_order_ok) return fail(ETXB_E_UNSUPPORTED, "a grid waits for a grid that comes later in the plan: no launch-per-grid order");
-  if (s->n_ranks > 1) return fail(ETXB_E_UNSUPPORTED, "a sharded model runs as the single launch only");
+  if (s->n_ranks > 1) return fail(ETXB_E_UNSUPPORTED, "a sharded session runs as the single launch only");   // (its grids wait for peers: launches of two ranks could not be ordered)
   s->stream = cuda_stream ? (cudaStream_t)cuda_stream : s->own_stream;
   if (s->trace && s->d_exec) CU(cudaMemsetAsync(s->d_exec, 0, (size_t)s->h.n_tasks * 4, s->stream));
   ++s->epoch;
@@ -694,7 +694,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   for (uint32_t t = 0; t < s->h.n_types; ++t) {
     p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
-    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->n_ranks > 1 ? 5 : 0));
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->xbase != nullptr ? 5 : 0));
     if (rc) return rc;
   }
   CU(cudaEventRecord(s->ev1, s->stream));

@@ -285,9 +285,9 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
     s_deadline = globaltimer() + p.timeout_ns;
     for (int i = 0; i < ETXB_NSTAGE; ++i) { mbar_init(sm.full + i, 1); mbar_init(sm.empty + i, ETXB_CONSUMER_WARPS); }
     if constexpr (TC) {
-      for (int i = 0; i < ETXB_TC_NSTAGE; ++i) { mbar_init(s_tc.full + i, 1); mbar_init(s_tc.empty + i, 1); }
-      mbar_init(&s_tc.acc, 1);
-      s_tc.n = 0; s_tc.nacc = 0; s_tc.tmem = 0;
+      for (int i = 0; i < ETXB_TC_MAXSTAGE; ++i) { mbar_init(s_tc.full + i, 1); mbar_init(s_tc.empty + i, 1); s_tc.lu[i] = 0; s_tc.mu[i] = 0; }
+      for (int i = 0; i < 2; ++i) { mbar_init(s_tc.acc_full + i, 1); mbar_init(s_tc.acc_free + i, 4); s_tc.nfull[i] = 0; s_tc.nfree[i] = 0; }
+      s_tc.tmem = 0;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }

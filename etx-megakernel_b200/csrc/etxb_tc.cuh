@@ -11,14 +11,16 @@
 // the 22.5 the HBM delivers, and all of a batch's tokens (up to 32 here) ride along for free -- mma.sync m16n8k16, the
 // legacy path, managed about a third of that with 8 tokens per pass.
 //
-// A job = one tile of 128 weight rows (or two: an expert's gate rows and up rows, accumulated side by side) x all of K x
-// up to 32 tokens.  Roles inside the CTA's consumer warps: every thread stages the tokens' vectors into the swizzled
-// layout; one thread issues the TMA loads of the weight tile, k-chunk by k-chunk, through a ring of three 16 KB stages;
-// one thread issues the MMAs (four k16 steps per 64-wide chunk) and commits each stage back to the loader; when the
-// last MMA has completed, four warps read the accumulators (one token per TMEM lane) and run the epilogue.  The weight
-// ring of the one-token tiles is not in use during a batched step (their producer warp has nothing to stream), so its
-// shared memory holds the tokens here.  Every wait is bounded by the step's deadline; tensor memory is allocated once
-// per launch by the kernel and freed on every exit path.
+// A task = a few tiles of 128 weight rows (or pairs: an expert's gate rows and up rows, accumulated side by side) x all
+// of K x up to 32 tokens.  Roles inside the CTA's consumer warps: every thread stages the tokens' vectors into the
+// swizzled layout, once per task; one thread issues the TMA loads of the weight tiles, k-chunk by k-chunk, through a
+// ring of 16 KB stages (as many as fit beside the tokens: 4 with 32 tokens of 2048 columns, 10 with up to 8); one
+// thread issues the MMAs (four k16 steps per 64-wide chunk) and commits each stage back to the loader; when the last
+// MMA of a tile has completed, four warps read its accumulators (one token per TMEM lane) and run the epilogue while
+// the next tile's MMAs fill the other accumulator buffer.  The weight ring of the one-token tiles is not in use during
+// a batched step (their producer warp has nothing to stream), so its shared memory and the general region form one
+// area for tokens and stages here.  Every wait is bounded by the step's deadline; tensor memory is allocated once per
+// launch by the kernel and freed on every exit path.
 #pragma once
 #include <cuda.h>
 
@@ -26,17 +28,20 @@
 
 namespace etxb {
 
-#define ETXB_TC_ROWS 128               // weight rows per tile (the N of the instruction)
-#define ETXB_TC_STAGE 16384            // one k-chunk of a tile: 128 rows x 64 k x 2 bytes
-#define ETXB_TC_NSTAGE 3
-#define ETXB_TC_XBYTES 143360          // shared memory for the tokens (the idle weight ring), 1024-byte aligned inside it
+#define ETXB_TC_ROWS 128               // weight rows per TMA box; an instruction takes one or two boxes (N = 128 or 256)
+#define ETXB_TC_BOX 16384              // one box: 128 rows x 64 k x 2 bytes
+#define ETXB_TC_STAGE (2 * ETXB_TC_BOX)   // one k-chunk of a tile: up to 256 rows
+#define ETXB_TC_MAXSTAGE 6
+#define ETXB_TC_AREA (ETXB_RING_BYTES + ETXB_GEN_BYTES - 1024)   // the idle weight ring and the general region, 1024-byte aligned inside
+#define ETXB_TC_XBYTES 131072          // at most this much of it holds tokens (32 tokens x 2048 columns); the rest are weight stages
 #define ETXB_TC_MAXTOK 32              // tokens per job (M = 64 up to 8 tokens, 128 above)
-#define ETXB_TC_COLS 256               // tensor-memory columns the kernel allocates: two accumulators of 128
+#define ETXB_TC_COLS 512               // tensor-memory columns the kernel allocates: two accumulator buffers of 256
 
 struct TcShared {                      // per-CTA state of the tensor-core tiles (static shared memory of the kernel)
-  uint64_t full[ETXB_TC_NSTAGE], empty[ETXB_TC_NSTAGE], acc;
-  uint32_t n;                          // stages used so far (both role threads count from it)
-  uint32_t nacc;                       // completions of `acc` so far
+  uint64_t full[ETXB_TC_MAXSTAGE], empty[ETXB_TC_MAXSTAGE];
+  uint64_t acc_full[2], acc_free[2];   // accumulator buffer b: MMAs complete / epilogue done with it
+  uint32_t lu[ETXB_TC_MAXSTAGE], mu[ETXB_TC_MAXSTAGE];   // how often the loader / the MMA issuer has used each stage (its barriers' phase)
+  uint32_t nfull[2], nfree[2];         // completions of acc_full / acc_free so far
   uint32_t tmem;                       // base address of the allocation
   uint32_t pad;
 };
@@ -78,82 +83,139 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// One job: D[tok][j] (+)= sum_k x_tok[k] * W[row[a] + j][k], j < 128, for `nacc` (1 or 2) tiles that share the tokens;
-// then epi(tok, j, v0, v1) for every tok < ntok and j < 128 (v1 = 0 with one tile).  xsrc(n): the K bf16 values of token n.
+// One task: for every tile i < ntiles, D_i[tok][j] = sum_k x_tok[k] * W[boxrow(i, j / 128) + j % 128][k] for j < 128 nbox(i),
+// then epi(i, tok, j, v0, v1) for every tok < ntok, j < 128, with v0 = D_i[tok][j] and v1 = D_i[tok][128 + j] (0 when the tile
+// has one box).  A tile is one or two TMA boxes of 128 weight rows that one instruction multiplies (N = 128 or 256): two
+// neighbouring row blocks of a matrix, or an expert's gate rows and up rows.  xsrc(n): the K bf16 values of token n;
 // map: the tensor map of the weight tensor (rows x K, box 64 x 128).  All consumer threads call; ends with a barrier.
-template <typename XSrc, typename Epi>
-__device__ __forceinline__ void tc_job(const Smem& sm, TcShared& tc, const void* map, int nacc, int row0, int row1, int K, int ntok, int where,
-                                       XSrc xsrc, Epi epi) {
+//
+// The tokens are staged ONCE per task (the tiles of a task share them) whenever all of K fits the token area; the tiles
+// then stream back to back through the stage ring, their accumulators alternating between two buffers of tensor
+// memory, so that the epilogue of tile i overlaps the MMAs of tile i + 1.  When K does not fit (4096 columns x 32
+// tokens) the tokens go in windows of K and a task handles its tiles one by one, accumulating across the windows.
+template <typename XSrc, typename NBox, typename BoxRow, typename Epi>
+__device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void* map, int ntiles, int K, int ntok, int where,
+                                        XSrc xsrc, NBox nbox, BoxRow boxrow, Epi epi) {
   const int tid = tidx(), warp = tid >> 5, lane = tid & 31;
-  unsigned char* xs = (unsigned char*)(((uintptr_t)sm.ring + 1023) & ~(uintptr_t)1023);
-  unsigned char* ws = (unsigned char*)(((uintptr_t)sm.xs + 1023) & ~(uintptr_t)1023);
+  unsigned char* area = (unsigned char*)(((uintptr_t)sm.ring + 1023) & ~(uintptr_t)1023);
   const int M = ntok <= 8 ? 64 : 128, groups = (ntok + 7) >> 3, nchunk = K >> 6;
-  const int wc = min(nchunk, (ETXB_TC_XBYTES - (M / 8 - groups) * 1024) / (groups * 1024));      // k-chunks of the tokens that fit at once
-  const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ETXB_TC_ROWS >> 3) << 17) | ((uint32_t)(M >> 4) << 24);   // fp32 D, bf16 A / B, K-major
-  const uint32_t n0 = tc.n, a0 = tc.nacc;                          // (the previous job ended with a barrier)
-  uint32_t used = 0, windows = 0;
-  bool alive = *(volatile int*)sm.stop == 0;
-  for (int w0 = 0; w0 < nchunk; w0 += wc, ++windows) {
-    const int nc = min(wc, nchunk - w0);
+  // (an instruction reads M / 8 row groups of its k-chunk: the ones past the tokens' groups are the next chunks' rows or,
+  // at the end, the first stage's -- whatever they hold only reaches accumulator rows that nobody reads)
+  const int wc = min(nchunk, ETXB_TC_XBYTES / (groups * 1024));    // k-chunks of the tokens that fit at once
+  const int nwin = (nchunk + wc - 1) / wc;
+  const int xbytes = wc * groups * 1024;
+  unsigned char* ws = area + xbytes;
+  const int nst = min(ETXB_TC_MAXSTAGE, (ETXB_TC_AREA - xbytes) / ETXB_TC_STAGE);
+  const uint32_t idesc0 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(M >> 4) << 24);   // fp32 D, bf16 A / B, K-major; N goes in per tile
+  const bool alive0 = *(volatile int*)sm.stop == 0;
+  const uint32_t f0[2] = {tc.nfull[0], tc.nfull[1]}, r0[2] = {tc.nfree[0], tc.nfree[1]};     // (the previous task ended with a barrier)
+  // one pass = one staging of tokens + the tiles that use it: all tiles x all of K, or (K in windows) one tile x one window
+  const int npass = nwin == 1 ? 1 : ntiles * nwin;
+  uint32_t tile_seq = 0;                                           // tiles finished before this pass (their buffer = tile_seq & 1)
+  for (int pass = 0; pass < npass; ++pass) {
+    const int i0 = nwin == 1 ? 0 : pass / nwin, i1 = nwin == 1 ? ntiles : i0 + 1, win = nwin == 1 ? 0 : pass - i0 * nwin;
+    const int w0 = win * wc, nc = min(wc, nchunk - w0);
+    const bool first_win = win == 0, last_win = win == nwin - 1;
     // the tokens' slice [64 w0, 64 (w0 + nc)) -> swizzled rows: token n is row n % 8 of group n / 8 of its k-chunk
     for (int i = tid; i < ntok * nc * 8; i += ETXB_CONSUMERS) {
       const int n = i / (nc * 8), v = i - n * (nc * 8), c = v >> 3, j = v & 7, r = n & 7;
       const uint4 val = ld_act16((const __nv_bfloat16*)xsrc(n) + (size_t)(w0 * 64 + v * 8));
-      *(uint4*)(xs + (size_t)(c * groups + (n >> 3)) * 1024 + r * 128 + ((j ^ r) << 4)) = val;
+      *(uint4*)(area + (size_t)(c * groups + (n >> 3)) * 1024 + r * 128 + ((j ^ r) << 4)) = val;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
     csync();
-    if (warp == 1 && lane == 0 && alive) {                         // loader
+    if (sm.tr != nullptr && tid == 0 && pass == 0) sm.tr[4] = globaltimer();
+    if (warp == 1 && lane == 0 && alive0) {                        // loader: every tile of the pass, chunk by chunk
       bool ok = true;
-      uint32_t n = n0 + used;
-      for (int a = 0; a < nacc && ok; ++a)
-        for (int c = 0; c < nc && ok; ++c, ++n) {
-          const uint32_t st = n % ETXB_TC_NSTAGE, par = (n / ETXB_TC_NSTAGE) & 1;
-          ok = mbar_wait(tc.empty + st, par ^ 1, sm, where);
+      int st = 0;
+      for (int i = i0; i < i1 && ok; ++i) {
+        const int nb = nbox(i), y0 = boxrow(i, 0), y1 = nb > 1 ? boxrow(i, 1) : 0;
+        for (int c = 0; c < nc && ok; ++c) {
+          const uint32_t uu = tc.lu[st];
+          ok = mbar_wait(tc.empty + st, (uu & 1) ^ 1, sm, where);
           if (!ok) break;
-          mbar_expect_tx(tc.full + st, ETXB_TC_STAGE);
-          tma_load_2d(ws + (size_t)st * ETXB_TC_STAGE, map, (w0 + c) * 64, a == 0 ? row0 : row1, tc.full + st);
+          mbar_expect_tx(tc.full + st, (uint32_t)nb * ETXB_TC_BOX);
+          unsigned char* dst = ws + (size_t)st * ETXB_TC_STAGE;
+          tma_load_2d(dst, map, (w0 + c) * 64, y0, tc.full + st);
+          if (nb > 1) tma_load_2d(dst + ETXB_TC_BOX, map, (w0 + c) * 64, y1, tc.full + st);
+          tc.lu[st] = uu + 1;
+          st = st + 1 == nst ? 0 : st + 1;
         }
-    } else if (warp == 2 && lane == 0 && alive) {                  // MMA issuer
+      }
+    } else if (warp == 2 && lane == 0 && alive0) {                 // MMA issuer
       bool ok = true;
-      uint32_t n = n0 + used;
-      for (int a = 0; a < nacc && ok; ++a)
-        for (int c = 0; c < nc && ok; ++c, ++n) {
-          const uint32_t st = n % ETXB_TC_NSTAGE, par = (n / ETXB_TC_NSTAGE) & 1;
-          ok = mbar_wait(tc.full + st, par, sm, where);
+      int st = 0;
+      for (int i = i0; i < i1 && ok; ++i) {
+        const uint32_t seq = tile_seq + (uint32_t)(i - i0), bsel = seq & 1;
+        const uint32_t idesc = idesc0 | ((uint32_t)(nbox(i) * ETXB_TC_ROWS >> 3) << 17);
+        if (first_win) {                                           // a fresh accumulator buffer: the epilogue of the tile two back must be done with it
+          const uint32_t nth = r0[bsel] + (seq >> 1);              // acc_free[bsel] completions expected before this use
+          if (nth > 0) ok = mbar_wait(tc.acc_free + bsel, (nth - 1) & 1, sm, where);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t aaddr = smem_u32(xs + (size_t)c * groups * 1024), baddr = smem_u32(ws + (size_t)st * ETXB_TC_STAGE);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma(tc.tmem + (uint32_t)a * ETXB_TC_ROWS, tc_desc(aaddr + 32 * k), tc_desc(baddr + 32 * k), idesc, (w0 + c + k) > 0 ? 1u : 0u);
-          tc_commit(tc.empty + st);                                // the stage is free once these MMAs have read it
         }
-      tc_commit(&tc.acc);                                          // this window's MMAs are complete (tokens may be restaged, accumulators read)
+        const uint32_t dcol = tc.tmem + bsel * 2 * ETXB_TC_ROWS;
+        for (int c = 0; c < nc && ok; ++c) {
+          const uint32_t uu = tc.mu[st];
+          ok = mbar_wait(tc.full + st, uu & 1, sm, where);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t aaddr = smem_u32(area + (size_t)c * groups * 1024), baddr = smem_u32(ws + (size_t)st * ETXB_TC_STAGE);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) tc_mma(dcol, tc_desc(aaddr + 32 * k), tc_desc(baddr + 32 * k), idesc, (w0 + c + k) > 0 ? 1u : 0u);
+          tc_commit(tc.empty + st);                                // the stage is free once these MMAs have read it
+          tc.mu[st] = uu + 1;
+          st = st + 1 == nst ? 0 : st + 1;
+        }
+        if (ok) tc_commit(tc.acc_full + bsel);                     // the tile's MMAs (of this window) are complete
+      }
+      if (sm.tr != nullptr && pass == npass - 1) sm.tr[5] = globaltimer();
     }
     __syncwarp();                                                  // the role threads' warp-mates wait here, not in a spin beside them
-    used += (uint32_t)(nacc * nc);
-    if (alive) alive = mbar_wait(&tc.acc, (a0 + windows) & 1, sm, where);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  }
-  // epilogue: warps 0, 4, 8, 12 own TMEM lanes 0..31 (one token per lane), a quarter of the 128 columns each
-  alive = __all_sync(0xffffffffu, alive);
-  if ((warp & 3) == 0 && alive) {
-    const int q = warp >> 2;
+    // epilogue: warps 0, 4, 8, 12 own TMEM lanes 0..31 (one token per lane), a quarter of each box's 128 columns each.  Only
+    // they wait for the accumulators: the issuer runs at most one tile ahead of the slowest of them (it needs their four
+    // arrivals to reuse a buffer), so none of them can miss a phase; the other warps go on to the barrier below.
+    if ((warp & 3) == 0) {
+      for (int i = i0; i < i1; ++i) {
+        const uint32_t seq = tile_seq + (uint32_t)(i - i0), bsel = seq & 1;
+        // completions of acc_full[bsel] before this one: one per tile on that buffer (per window, when K goes in windows)
+        const uint32_t done = f0[bsel] + (nwin == 1 ? (seq >> 1) : (seq >> 1) * (uint32_t)nwin + (uint32_t)win);
+        bool alive = alive0;
+        if (alive) alive = mbar_wait(tc.acc_full + bsel, done & 1, sm, where);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        alive = __all_sync(0xffffffffu, alive);
+        if (!last_win) continue;
+        if (alive) {
+          const int q = warp >> 2;
+          const bool two = nbox(i) > 1;
 #pragma unroll 1
-    for (int c8 = 0; c8 < 4; ++c8) {
-      const int col = 32 * q + 8 * c8;
-      float v0[8], v1[8];
-      tc_ld8(tc.tmem + (uint32_t)col, v0);
-      if (nacc > 1) tc_ld8(tc.tmem + (uint32_t)(ETXB_TC_ROWS + col), v1);
-      if (lane < ntok)
+          for (int c8 = 0; c8 < 4; ++c8) {
+            const int col = 32 * q + 8 * c8;
+            float v0[8], v1[8];
+            tc_ld8(tc.tmem + bsel * 2 * ETXB_TC_ROWS + (uint32_t)col, v0);
+            if (two) tc_ld8(tc.tmem + bsel * 2 * ETXB_TC_ROWS + (uint32_t)(ETXB_TC_ROWS + col), v1);
+            if (lane < ntok)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) epi(lane, col + j, v0[j], nacc > 1 ? v1[j] : 0.f);
+              for (int j = 0; j < 8; ++j) epi(i, lane, col + j, v0[j], two ? v1[j] : 0.f);
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tc.acc_free + bsel);            // four arrivals per tile: the buffer may be overwritten
+      }
+    }
+    if (last_win) tile_seq += (uint32_t)(i1 - i0);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    csync();                                                       // the tokens may be restaged
+  }
+  if (tid == 0) {
+    const uint32_t nt = (uint32_t)ntiles;
+    for (int b = 0; b < 2; ++b) {
+      const uint32_t tiles_b = (nt + (b == 0 ? 1u : 0u)) >> 1;     // tiles that used buffer b
+      tc.nfull[b] = f0[b] + tiles_b * (uint32_t)nwin;
+      tc.nfree[b] = r0[b] + tiles_b;
     }
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  csync();
-  if (tid == 0) { tc.n = n0 + used; tc.nacc = a0 + windows; }
   csync();
 }
 
@@ -167,15 +229,20 @@ __device__ __forceinline__ void tile_gemv_tc(const unsigned char* a, int blk, co
   if (r0 >= r1) return;
   const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
   __nv_bfloat16* out = (__nv_bfloat16*)d.out;
-  for (int c0 = r0; c0 < r1; c0 += ETXB_TC_ROWS)
-    for (int b0 = 0; b0 < d.nb; b0 += ETXB_TC_MAXTOK) {
-      const int nt = min(ETXB_TC_MAXTOK, d.nb - b0), nr = min(ETXB_TC_ROWS, r1 - c0);
-      tc_job(sm, tc, d.ln, 1, c0, 0, d.K, nt, where,
-             [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(b0 + n) * d.sx; },
-             [&](int tok, int j, float v, float) {
-               if (j < nr) out[(size_t)(b0 + tok) * d.sout + c0 + j] = __float2bfloat16_rn(bias ? __fadd_rn(v, __bfloat162float(bias[c0 + j])) : v);
-             });
-    }
+  const int ntiles = (r1 - r0 + 2 * ETXB_TC_ROWS - 1) / (2 * ETXB_TC_ROWS);
+  for (int b0 = 0; b0 < d.nb; b0 += ETXB_TC_MAXTOK) {
+    const int nt = min(ETXB_TC_MAXTOK, d.nb - b0);
+    tc_task(sm, tc, d.ln, ntiles, d.K, nt, where,
+            [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(b0 + n) * d.sx; },
+            [&](int i) { return r1 - r0 - i * 2 * ETXB_TC_ROWS > ETXB_TC_ROWS ? 2 : 1; },
+            [&](int i, int b) { return r0 + (2 * i + b) * ETXB_TC_ROWS; },
+            [&](int i, int tok, int j, float v0, float v1) {
+              const int r = r0 + 2 * i * ETXB_TC_ROWS + j, rb = r + ETXB_TC_ROWS;
+              __nv_bfloat16* o = out + (size_t)(b0 + tok) * d.sout;
+              if (r < r1) o[r] = __float2bfloat16_rn(bias ? __fadd_rn(v0, __bfloat162float(bias[r])) : v0);
+              if (rb < r1) o[rb] = __float2bfloat16_rn(bias ? __fadd_rn(v1, __bfloat162float(bias[rb])) : v1);
+            });
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- expert-grouped gate+up / down
@@ -190,20 +257,23 @@ __device__ __forceinline__ void tile_moe_up_tc(const unsigned char* a, int blk, 
   const int32_t* list = (const int32_t*)d.rows + (size_t)e * d.nb;
   int32_t* ent = (int32_t*)(sm.scr + 96);                          // [32] entries of the pass
   const int erow = (int)((long long)e * d.estride / d.K);          // first row of expert e in the [E * 2M][K] view
-  for (int c0 = r0; c0 < r1; c0 += ETXB_TC_ROWS)
-    for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
-      const int nt = min(ETXB_TC_MAXTOK, cnt - p0), nr = min(ETXB_TC_ROWS, r1 - c0);
-      if (tidx() < nt) ent[tidx()] = __ldcg(list + p0 + tidx());
-      csync();
-      tc_job(sm, tc, d.ln, 2, erow + c0, erow + d.M + c0, d.K, nt, where,
-             [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(ent[n] >> 8) * d.sx; },
-             [&](int tok, int j, float g, float u) {
-               if (j < nr) {
-                 const int en = ent[tok];
-                 ((__nv_bfloat16*)d.out)[((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M + c0 + j] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(bfr(g))), bfr(u)));
-               }
-             });
-    }
+  const int ntiles = (r1 - r0 + ETXB_TC_ROWS - 1) / ETXB_TC_ROWS;
+  for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
+    const int nt = min(ETXB_TC_MAXTOK, cnt - p0);
+    if (tidx() < nt) ent[tidx()] = __ldcg(list + p0 + tidx());
+    csync();
+    tc_task(sm, tc, d.ln, ntiles, d.K, nt, where,
+            [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(ent[n] >> 8) * d.sx; },
+            [&](int) { return 2; },                                                            // 128 gate rows and their 128 up rows: one instruction
+            [&](int i, int b) { return erow + (b ? d.M : 0) + r0 + i * ETXB_TC_ROWS; },          // up rows follow the M gate rows
+            [&](int i, int tok, int j, float g, float u) {
+              const int r = r0 + i * ETXB_TC_ROWS + j;
+              if (r < r1) {
+                const int en = ent[tok];
+                ((__nv_bfloat16*)d.out)[((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M + r] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(bfr(g))), bfr(u)));
+              }
+            });
+  }
 }
 
 __device__ __forceinline__ void tile_moe_down_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) {
@@ -216,25 +286,27 @@ __device__ __forceinline__ void tile_moe_down_tc(const unsigned char* a, int blk
   int32_t* ent = (int32_t*)(sm.scr + 96);
   float* wt = sm.scr + 128;
   const int erow = (int)((long long)e * d.estride / d.K);
-  for (int c0 = r0; c0 < r1; c0 += ETXB_TC_ROWS)
-    for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
-      const int nt = min(ETXB_TC_MAXTOK, cnt - p0), nr = min(ETXB_TC_ROWS, r1 - c0);
-      if (tidx() < nt) {
-        const int en = __ldcg(list + p0 + tidx());
-        ent[tidx()] = en;
-        wt[tidx()] = d.wts ? __ldcg(d.wts + (size_t)(en >> 8) * d.R + (en & 0xff)) : 1.f;
-      }
-      csync();
-      tc_job(sm, tc, d.ln, 1, erow + c0, 0, d.K, nt, where,
-             [&](int n) { return (const __nv_bfloat16*)d.x + ((size_t)(ent[n] >> 8) * d.R + (ent[n] & 0xff)) * d.K; },
-             [&](int tok, int j, float v, float) {
-               if (j < nr) {
-                 const int en = ent[tok];
-                 const float y = bfr(v);
-                 ((__nv_bfloat16*)d.out)[((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M + c0 + j] = __float2bfloat16_rn(d.wts ? bfr(__fmul_rn(y, wt[tok])) : y);
-               }
-             });
+  const int ntiles = (r1 - r0 + 2 * ETXB_TC_ROWS - 1) / (2 * ETXB_TC_ROWS);
+  for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
+    const int nt = min(ETXB_TC_MAXTOK, cnt - p0);
+    if (tidx() < nt) {
+      const int en = __ldcg(list + p0 + tidx());
+      ent[tidx()] = en;
+      wt[tidx()] = d.wts ? __ldcg(d.wts + (size_t)(en >> 8) * d.R + (en & 0xff)) : 1.f;
     }
+    csync();
+    tc_task(sm, tc, d.ln, ntiles, d.K, nt, where,
+            [&](int n) { return (const __nv_bfloat16*)d.x + ((size_t)(ent[n] >> 8) * d.R + (ent[n] & 0xff)) * d.K; },
+            [&](int i) { return r1 - r0 - i * 2 * ETXB_TC_ROWS > ETXB_TC_ROWS ? 2 : 1; },
+            [&](int i, int b) { return erow + r0 + (2 * i + b) * ETXB_TC_ROWS; },
+            [&](int i, int tok, int j, float v0, float v1) {
+              const int r = r0 + 2 * i * ETXB_TC_ROWS + j, rb = r + ETXB_TC_ROWS;
+              const int en = ent[tok];
+              __nv_bfloat16* o = (__nv_bfloat16*)d.out + ((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M;
+              if (r < r1) { const float y = bfr(v0); o[r] = __float2bfloat16_rn(d.wts ? bfr(__fmul_rn(y, wt[tok])) : y); }
+              if (rb < r1) { const float y = bfr(v1); o[rb] = __float2bfloat16_rn(d.wts ? bfr(__fmul_rn(y, wt[tok])) : y); }
+            });
+  }
 }
 
 }  // namespace etxb

@@ -44,7 +44,8 @@ def to_device_weights(packed: dict, device) -> dict:
 
 class DecodeProgram:
     def __init__(self, dims: Q.Dims, weights: dict, device: int = 0, maxlen: int = 1072, steps: int | None = None, machine="b200",
-                 fold_topk: bool = True, fused_attn: bool | str = True, workers: int | None = None, ranks: int = 1, rank: int = 0):
+                 fold_topk: bool = True, fused_attn: bool | str = True, workers: int | None = None, ranks: int = 1, rank: int = 0,
+                 flagged: bool = False):
         """ranks > 1: rank `rank` of a model sharded `ranks` ways -- `dims` and `weights` are the rank's shard
         (Q.shard_dims / Q.shard_weights); call connect() with every rank's `region.handle` before the first step."""
         self.d, self.maxlen = dims, maxlen
@@ -62,7 +63,7 @@ class DecodeProgram:
         self.buf["block_tables"].copy_(torch.arange(self.buf["block_tables"].numel(), dtype=torch.int32))
         self.vl = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
-        if ranks > 1:
+        if ranks > 1 or flagged:
             self.region = ExchangeRegion(Q.exchange_bytes(dims, ranks), device)      # the blocks of flagged rows the ranks publish into
             self.xaddr = {"xrows": self.region.ptr}
 
@@ -74,7 +75,7 @@ class DecodeProgram:
                 t = self.w[name]
             return t.data_ptr()
         self.graph, self.pool, self.sizing = Q.build_graph(dims, ptr, maxlen, self.machine, fold_topk=fold_topk, fused_attn=fused_attn,
-                                                              ranks=ranks, rank=rank)
+                                                              ranks=ranks, rank=rank, flagged=flagged)
         pool = self.pool.bytes()
         self.plan = compile_graph(self.graph, self.machine, {"POOL": len(pool)}, options=PassOptions(workers=workers))
         self.session = Session(self.plan, {"vl": self.vl}, pool, device)
@@ -82,6 +83,8 @@ class DecodeProgram:
         self.session.set_step(tok=0, pos=0, write_next=0, H=dims.H, V=dims.lm_rows, nrep=1, embed=self.w["embed"], resid=b["resid"],
                               positions=b["positions"], seq_lens=b["seq_lens"], slot_mapping=b["slot_mapping"], logits=b["logits"],
                               token_in=b["token_in"], token_out=b["token_out"], token_time=b["token_time"])
+        if flagged and ranks == 1:
+            self.session.set_exchange(0, 1, self.region)            # one rank: nothing to connect, the region is its own
 
     def connect(self, handles: list):
         """handles[r] = rank r's `region.handle` (all-gathered by the caller).  After this, and a barrier so that no

@@ -370,8 +370,12 @@ class ArgPool:
 
 
 def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = "b200", *, fold_topk: bool = True,
-                fused_attn: bool | str = True, ranks: int = 1, rank: int = 0):
+                fused_attn: bool | str = True, ranks: int = 1, rank: int = 0, flagged: bool = False):
     """The decode step of `d` as a Graph plus its argument pool.
+
+    flagged (one rank): hand the row-parallel grids' outputs (o_proj, down) to the norm folds that follow as flagged words
+    in an exchange region of one row per block -- the single-GPU form of the sharded hand-off below: the fold polls the
+    data itself instead of waiting for the producing grid's event and then loading.
 
     ranks > 1: the step of ONE rank of a model sharded `ranks` ways (`d` = shard_dims(full, ranks): its share of the
     heads and of the MLP / expert rows).  ptr("xrows") then names the rank's exchange region: 2 * L blocks of
@@ -403,11 +407,12 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
 
     if not (1 <= ranks <= 8 and 0 <= rank < ranks):
         raise ValueError("1 <= ranks <= 8 and 0 <= rank < ranks")
-    xmode = op_gemv.MODE_FLAGGED if ranks > 1 else 0
+    exch = ranks > 1 or flagged
+    xmode = op_gemv.MODE_FLAGGED if exch else 0
 
     def xblock(layer, kind):
         """The block of flagged rows o_proj (kind 0) / down (kind 1) of `layer` publish into; 0 when not sharded."""
-        return ptr("xrows") + (2 * layer + kind) * ranks * d.H * 4 if ranks > 1 else 0
+        return ptr("xrows") + (2 * layer + kind) * ranks * d.H * 4 if exch else 0
 
     def tile(symbol, stream_after=None, exchange=False):
         return cuda_link(SRC, symbol, stream_after=stream_after, exchange=exchange)
@@ -417,7 +422,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
         pool.rows.append((name, export, role, layer, off, tasks, M, K))
         g.etensor(out_ev, out_shape, wait_count=out_count)
         slots = (d.TOPK if role in ("moe_up", "moe_down") else 1) * (2 if role in ("moe_up", "gate_up") else 1)
-        g.call_device(name, grid, tile("etx_tile_" + export, after, exchange and ranks > 1), resource=res, args=["impargs"], consts=(off,),
+        g.call_device(name, grid, tile("etx_tile_" + export, after, exchange and exch), resource=res, args=["impargs"], consts=(off,),
                       in_edges={in_ev: in_map}, out_edges={out_ev: out_map},
                       duration_us=round(m.tile_duration_us(role, 2.0 * slots * M * K / max(1, tasks)), 2))
         return out_ev
@@ -441,7 +446,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                           mode=op_gemv.MODE_NORM | (op_gemv.MODE_BIAS if d.bias else 0) | (0 if first else xmode), nb=1)
         # (sharded: the fold polls the step flags of the rows the ranks publish, which says more than the exchanged grid's
         # event -- that only counts this rank's tasks -- so it waits for the event BEFORE that grid and starts polling at once)
-        prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), (before_x if ranks > 1 and not first else prev), "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
+        prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, (t,), (before_x if exch and not first else prev), "i->(0)", f"E_qkv_{L}", "i->(0)", (1,), t, d.NQKV, d.H, after="")
         if fused_attn:
             # ---- the attention phase as one grid: prep + split-KV partitions + merge by the last task to finish
             gq, plen, gparts = (0, 0, 0) if fused_attn == "general" else sz.attn
@@ -479,7 +484,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                           rows=xblock(L, 0), mode=xmode)
         before_x = prev
         prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, (t,), prev, "i->(0)", f"E_o_{L}", "i->(0)", (1,), t, d.H, d.NH * d.HD, after="", exchange=True)
-        fold_in = before_x if ranks > 1 else prev
+        fold_in = before_x if exch else prev
         if d.moe:
             # ---- router with the post-attention norm fold: task 0 stores resid2 and the normed vector
             t, rpt = sz.router
@@ -530,7 +535,7 @@ def build_graph(d: Dims, ptr, maxlen: int = 1072, machine: MachineModel | str = 
                       out=ptr("logits"), M=d.lm_rows, K=d.H, rpt=rpt,
                       tpe=1, rows=xblock(d.L - 1, 1) or ptr("moe_out"), resid_in=ptr("resid2"), resid_out=ptr("resid"), ln=ptr("final_norm"), R=ranks, eps=d.eps,
                       ids=0, mode=op_gemv.MODE_NORM | xmode, nb=1)
-    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), (before_x if ranks > 1 else prev), "i->(0)", "E_lm", "i->(0)", (1,), t, d.lm_rows, d.H, after="")
+    prev = add("lm_head", "dsl_gemv_fold", "lm_head", -1, blob, t, (t,), (before_x if exch else prev), "i->(0)", "E_lm", "i->(0)", (1,), t, d.lm_rows, d.H, after="")
     g.etensor("E_argmax", (1,), wait_count=1)
     g.call_device("argmax", (1,), tile("vl_argmax"), resource=res, args=["vl"], consts=(0,), in_edges={prev: "i->(0)"},
                   out_edges={"E_argmax": "i->i"}, duration_us=8.5)

@@ -51,9 +51,10 @@ class Session:
         L.check(self.lib.etxb_set_step(self._h, C.byref(self.step_params)))
 
     def set_exchange(self, rank: int, n_ranks: int, region: "ExchangeRegion"):
-        """Make this session rank `rank` of a model sharded over `n_ranks` processes: counters move into `region`, the
-        grids the graph marks `exchange=True` deliver their rows and arrivals to every peer (region.connect first)."""
-        bases = (C.c_void_p * n_ranks)(*[region.peers.get(r, 0) or None for r in range(n_ranks)])
+        """Make this session rank `rank` of a model sharded over `n_ranks` processes: the grids the graph marks
+        `exchange=True` publish the rows they write, as flagged words, into `region` and into every peer's region
+        (region.connect first); the norm folds that follow poll them there.  n_ranks = 1: the same hand-off on one GPU."""
+        bases = (C.c_void_p * max(n_ranks, 1))(*[region.peers.get(r, 0) or None for r in range(n_ranks)])
         L.check(self.lib.etxb_set_exchange(self._h, rank, n_ranks, C.c_void_p(region.ptr), region.nbytes, bases))
         self._keep["__exchange__"] = region
 

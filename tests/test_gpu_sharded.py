@@ -70,6 +70,25 @@ def test_rank_looped_back_to_itself_equals_the_plain_program(od):
         prog.close()
 
 
+@pytest.mark.parametrize("od", [SMALL_MOE, SMALL_DENSE])
+def test_flagged_hand_off_on_one_rank_equals_the_plain_program(od):
+    """One rank with the flagged hand-off (the folds poll the rows o_proj / down publish instead of waiting for those grids'
+    events): the same arithmetic on the same values, so tokens, logits and hidden state are bit-identical to the plain
+    program, on the lean and on the full kernel."""
+    d = qdims(od)
+    w = D.to_device_weights(Q.pack_hf(d, O.SyntheticWeights(od, seed=2, gamma="ones").get, MAXLEN), "cuda:0")
+    plain = D.DecodeProgram(d, w, device=0, maxlen=MAXLEN)
+    want, want_logits, want_resid = plain.generate(prompt_of(od), N_GEN), plain.read("logits"), plain.read("resid")
+    plain.close()
+    for full_kernel in (0, 1):
+        prog = D.DecodeProgram(d, w, device=0, maxlen=MAXLEN, flagged=True)
+        prog.session.set_option("full_kernel", full_kernel)
+        got = prog.generate(prompt_of(od), N_GEN)
+        assert got.tolist() == want.tolist()
+        assert np.array_equal(prog.read("logits"), want_logits) and np.array_equal(prog.read("resid"), want_resid)
+        prog.close()
+
+
 def test_exchange_region_and_argument_checks():
     reg = ExchangeRegion(4096, 0)
     assert reg.ptr % 256 == 0 and len(reg.handle) == 64 and any(reg.handle)
