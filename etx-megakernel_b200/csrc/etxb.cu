@@ -114,6 +114,9 @@ static int32_t check_attnf_block(const etxb_attnf_args& a) {
     if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || G % a.gq) why = "gq is 1, 2, 4 or 8 and divides NH / NKV";
     else if (a.HD != 128 || a.BS != 16 || (a.part_len & 0xffff) != 128) why = "the grouped form is head_dim 128, cache blocks of 16, partitions of 128";
     else if (a.gq * a.max_parts > 4096) why = "gq * max_parts <= 4096";
+    else if ((a.part_len >> 24) & ~1) why = "part_len bits 25..31 are zero";
+    else if ((a.part_len >> 24) && (a.nblocks > (uint32_t)(a.NH / a.gq) || (size_t)a.max_parts * a.gq * 130 * 4 > ETXB_RING_BYTES))
+      why = "whole-sequence form: the grid is NH / gq tasks and max_parts * gq * 130 floats fit the idle weight ring";
     else if (a.nblocks > (uint32_t)(a.max_parts * (a.NH / a.gq))) why = "the grid is at most max_parts * NH / gq tasks";
   } else {
     const int G = a.NH / a.NKV;
@@ -136,7 +139,7 @@ static int32_t check_batch_block(int body, const unsigned char* blk, size_t byte
     memcpy(&a, blk, sizeof a);
     if (a.E < 1 || a.E > 256 || a.K < 1 || a.K > 16 || a.K > a.E) why = "1 <= K <= min(16, E), E <= 256";
     else if (a.nb < 1 || a.nb > 64 || a.nb * a.K > 2048 || a.cap < 1) why = "1 <= nb <= 64 columns, cap >= 1";
-    else if (!a.logits || !a.wts || !a.ids || !a.ecount || !a.elist) why = "null pointer";
+    else if (!a.logits || !a.wts || !a.ids || (a.elist != nullptr && !a.ecount)) why = "null pointer";
     if (!why) return ETXB_OK;
     snprintf(m, sizeof m, "route block (E=%d, K=%d, nb=%d, cap=%d) outside the tile: %s", a.E, a.K, a.nb, a.cap, why);
     return fail(ETXB_E_UNSUPPORTED, m);
@@ -156,9 +159,12 @@ static int32_t check_batch_block(int body, const unsigned char* blk, size_t byte
   else if (body == ETXB_BODY_NORM_COL && (a.K > ETXB_XF_FLOATS || a.R < 0 || a.R > 64 || !a.resid_in || !a.x || !a.ln)) why = "norm of a column: K <= 8192, 0 <= R <= 64, resid_in / x / ln set";
   else if (body != ETXB_BODY_NORM_COL && body < ETXB_BODY_GEMV_TC && (size_t)a.K * 2 + ETXB_NB_PAD > ETXB_NBX_BYTES) why = "one token vector must fit the 40 KB activation stage";
   else if (body != ETXB_BODY_NORM_COL && (a.rpt < 1 || a.M < 1 || !a.W || !a.x || !a.out)) why = "rpt >= 1, M >= 1, W / x / out set";
-  else if ((body == ETXB_BODY_MOE_UP_G || body == ETXB_BODY_MOE_DOWN_G || body == ETXB_BODY_MOE_UP_TC || body == ETXB_BODY_MOE_DOWN_TC) &&
+  else if ((body == ETXB_BODY_MOE_UP_G || body == ETXB_BODY_MOE_DOWN_G) &&
            (a.tpe < 1 || a.R < 1 || a.R > 255 || !a.rows || !a.resid_in)) why = "expert-grouped tile: tpe >= 1, 1 <= R <= 255, token lists (rows) and their lengths (resid_in) set";
+  else if ((body == ETXB_BODY_MOE_UP_TC || body == ETXB_BODY_MOE_DOWN_TC) && (a.R < 1 || a.R > 16 || a.nb * a.R > 1024 || !a.ids || a.E > 256))
+    why = "share-scheduled expert tile: 1 <= R <= 16, nb * R <= 1024, E <= 256, the step's routing ids set";
   else if (body >= ETXB_BODY_GEMV_TC && (a.K % 64 || ((uintptr_t)a.W & 15))) why = "tensor-core tile: K % 64 == 0 and W 16-byte aligned (TMA tensor copies of 64-wide chunks)";
+  else if (body == ETXB_BODY_GEMV_TC && a.tpe > 1 && (a.K % (64 * a.tpe) || !a.rows || !a.resid_in)) why = "split-K dense tile: K a multiple of 64 x the split, partial sums (rows) and arrival counters (resid_in) set";
   else if ((body == ETXB_BODY_MOE_UP_TC || body == ETXB_BODY_MOE_DOWN_TC) && (a.E < 1 || a.estride <= 0 || a.estride % a.K)) why = "tensor-core expert tile: E >= 1 and estride a multiple of K (the experts form one [E * rows][K] matrix)";
   if (!why) return ETXB_OK;
   snprintf(m, sizeof m, "batched block (body %d, M=%d, K=%d, rpt=%d, tpe=%d, R=%d, nb=%d) outside the tile: %s", body, a.M, a.K, a.rpt, a.tpe, a.R, a.nb, why);
@@ -200,7 +206,7 @@ static int select_variant(const etxb_session* s, const std::vector<unsigned char
       if (off + sizeof(etxb_attnf_args) > pool.size()) return 0;
       etxb_attnf_args a;
       memcpy(&a, pool.data() + off, sizeof a);
-      if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || a.HD != 128 || a.BS != 16 || (a.part_len & 0xffff) != 128) return 0;
+      if (!(a.gq == 1 || a.gq == 2 || a.gq == 4 || a.gq == 8) || a.HD != 128 || a.BS != 16 || (a.part_len & 0xffff) != 128 || (a.part_len >> 24)) return 0;
       if (any_attn && a.gq != gq) return 0;
       gq = a.gq; any_attn = true;
     } else {

@@ -200,7 +200,9 @@ struct etxb_attnf_args {
   float* exp_sums; float* max_logits; float* tmp_out; void* out; int32_t* counters;                             // 80..119
   float scale, eps; int32_t NH, NKV, HD, BS, X, max_parts;                                                      // 120..151
   int32_t gq, part_len;   // 152..159: gq > 0 selects the grouped form (gq q heads x 128 positions per task, task = part * (NH / gq) + group);
-                          // part_len: bits 0..15 = 128, bits 16..23 = a tag that tells the grids sharing the partial buffers apart (the layer)
+                          // part_len: bits 0..15 = 128, bits 16..23 = a tag that tells the grids sharing the partial buffers apart (the layer),
+                          // bit 24 = whole-sequence form: task = q group, walks every partition, partials in the idle weight ring
+                          // (plans without streamed tiles only: the batched step)
   uint32_t grid[3], nblocks;                                                                                    // 160..175
 };
 

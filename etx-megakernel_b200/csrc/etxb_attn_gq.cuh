@@ -18,6 +18,7 @@
 namespace etxb {
 
 #define ETXB_GQ_PART 128   // positions per task
+#define ETXB_GQ_WHOLE (1 << 24)   // part_len bit: one task per (sequence, q group) walks all partitions (plans without streamed tiles)
 #define ETXB_GQ_PW 136     // 8-byte (value, flag) pairs a task publishes per q head and partition: 128 outputs, max, sum, padding
 
 // Partial results travel as FLAGGED PAIRS: every fp32 value is stored together with a 32-bit flag derived from the step
@@ -361,12 +362,256 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
   }
 }
 
+// ---------------------------------------------------------------------------------------------- a whole sequence per task
+// The same attention with one task per (sequence, group of GQ q heads): the task walks the context's partitions itself,
+// keeps every partition's partial output and statistics in shared memory and merges them at the end with the merge's
+// arithmetic (same partition boundaries, same order of sums: the results are those of the one-partition-per-task form bit
+// for bit).  This is the form of a batched step with enough sequences to fill the workers (sequences x kv heads x groups
+// tasks): the q rows are prepared once per sequence instead of once per partition, the next partition's K (then V) is
+// requested as soon as the registers of the current one are free, so the cache latency hides behind the softmax and
+// the output sums, and nothing is published, polled or merged through global memory.
+// The partials live in the weight ring, which is idle in a batched plan (no streamed tiles): part_len bit 24 selects
+// this form, and only builders of plans without streamed tiles may set it.  (np * GQ * 130 floats <= the ring.)
+template <int GQ>
+__device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, const Smem& sm, const etxb_stepv& S) {
+  constexpr int HD = 128, BS = 16, X = 8, PL = ETXB_GQ_PART, HV = HD / 8;
+  const int NKV = d.NKV, G = d.NH / NKV;
+  const int hq0 = blk * GQ, h = hq0 / G;
+  const bool writer = hq0 - h * G == 0;
+  const long long pos = (const void*)d.positions == (const void*)S.positions ? (long long)S.pos : __ldcg((const long long*)d.positions);
+  const long long slot = (const void*)d.slot_mapping == (const void*)S.slot_mapping ? (long long)S.pos : __ldcg((const long long*)d.slot_mapping);
+  const int seq = (const void*)d.seq_lens == (const void*)S.seq_lens ? S.pos + 1 : __ldcg(d.seq_lens);
+  const int np = min(min((seq + PL - 1) / PL, d.max_parts), ETXB_RING_BYTES / (GQ * (HD + 2) * 4));
+  if (np < 1) return;
+  const int tid = tidx(), lane = tid & 31, warp = tid >> 5;
+  const GqSmem<GQ> s(sm.xs);
+  float* PO = (float*)sm.ring;                                     // [np][GQ][HD] partial outputs
+  float* PS = PO + (size_t)np * GQ * HD;                           // [np][GQ][2] max logit, exp sum
+  const int t = tid & (PL - 1), qr = tid >> 7;                     // K: position t, dims [32 qr, 32 qr + 32);  V: dim t, blocks 2 qr, 2 qr + 1
+  uint4 kreg[4], vreg[4];
+  // cache blocks of a partition for this thread: [0] the block of its K position, [1], [2] the blocks of its V positions
+  // (requested a phase before the rows themselves, so that the row loads do not wait for the table)
+  int pbn[3];
+  auto load_tab = [&](int part) {
+    const int lb = part * (PL / BS) + (t >> 4), lv = part * (PL / BS) + 2 * qr;
+    pbn[0] = lb * BS < seq ? __ldg(d.block_tables + lb) : 0;
+    pbn[1] = lv * BS < seq ? __ldg(d.block_tables + lv) : 0;
+    pbn[2] = (lv + 1) * BS < seq ? __ldg(d.block_tables + lv + 1) : 0;
+  };
+  auto load_k = [&](int part) {
+    const int lb = part * (PL / BS) + (t >> 4);
+    const bool live = lb * BS < seq;
+    const long long pb = pbn[0];
+    const __nv_bfloat16* kp = (const __nv_bfloat16*)d.kc + ((((size_t)pb * NKV + h) * HV + qr * 4) * BS + (t & 15)) * X;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) kreg[j] = live ? ld_act16(kp + (size_t)j * BS * X) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  auto load_v = [&](int part) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int lv = part * (PL / BS) + 2 * qr + u;
+      const bool lv_live = lv * BS < seq;
+      const long long pv = pbn[1 + u];
+      const __nv_bfloat16* vp = (const __nv_bfloat16*)d.vc + (((size_t)pv * NKV + h) * HD + t) * BS;
+      vreg[2 * u] = lv_live ? ld_act16(vp) : make_uint4(0u, 0u, 0u, 0u);
+      vreg[2 * u + 1] = lv_live ? ld_act16(vp + 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  load_tab(0);
+  load_k(0);
+  load_v(0);
+  // ---- this step's rows: raw q heads, new k and v rows; rotary row and norm weights
+  {
+    const __nv_bfloat16* qkv = (const __nv_bfloat16*)d.qkv;
+    const int nq = GQ * HV, nrow = nq + 2 * HV;
+    for (int i = tid; i < nrow + 3 * HV; i += ETXB_CONSUMERS) {
+      if (i < nrow) {
+        const __nv_bfloat16* src = i < nq ? qkv + (size_t)hq0 * HD + 8 * i
+                                          : (i < nq + HV ? qkv + (size_t)(d.NH + h) * HD + 8 * (i - nq)
+                                                         : qkv + (size_t)(d.NH + NKV + h) * HD + 8 * (i - nq - HV));
+        unpack8(ld_act16(src), s.raw + (i < nq ? 8 * i : GQ * HD + 8 * (i - nq)));
+      } else {
+        const int c = i - nrow, which = c / HV, v = c - which * HV;
+        const __nv_bfloat16* src = which == 0 ? (const __nv_bfloat16*)d.cos_sin + (size_t)pos * HD
+                                              : (const __nv_bfloat16*)(which == 1 ? d.qw : d.kw);
+        if (src != nullptr) unpack8(__ldg((const uint4*)src + v), s.cw + which * HD + 8 * v);
+      }
+    }
+  }
+  csync();
+  mark(sm, 0);
+  if (warp < GQ) {
+    float o[8];
+    head_norm_rope_s<128>(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s.qs[warp * HD + lane * 4 + j] = o[j];
+  } else if (warp == GQ) {
+    float o[8];
+    head_norm_rope_s<128>(s.raw + GQ * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
+    const long long cb = slot / BS; const int off = (int)(slot % BS);
+    __nv_bfloat16* kc = (__nv_bfloat16*)d.kc;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int dd = lane * 4 + j;
+      s.knew[dd] = o[j];
+      if (writer) kc[((((size_t)cb * NKV + h) * HV + dd / X) * BS + off) * X + dd % X] = __float2bfloat16_rn(o[j]);
+    }
+  } else if (warp == GQ + 1) {
+    const long long cb = slot / BS; const int off = (int)(slot % BS);
+    __nv_bfloat16* vc = (__nv_bfloat16*)d.vc;
+    for (int dd = lane; dd < HD; dd += 32) {
+      const float v = s.raw[(GQ + 1) * HD + dd];
+      s.vnew[dd] = v;
+      if (writer) vc[(((size_t)cb * NKV + h) * HD + dd) * BS + off] = __float2bfloat16_rn(v);
+    }
+  }
+  csync();
+  mark(sm, 1);
+  for (int part = 0; part < np; ++part) {
+    const int t0 = part * PL;
+    const bool owner = pos >= t0 && pos < t0 + PL;
+    const int tpos = owner ? (int)(pos - t0) : -1;
+    const int ntok = min(PL, seq - t0);
+    auto cached = [&](int tt) { return tt < ntok && tt != tpos; };
+    if (part + 1 < np) load_tab(part + 1);
+    // ---- scores
+    {
+      float acc[GQ];
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) acc[g] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float kf[8];
+        unpack8(kreg[j], kf);
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          const float4 qa = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8), qb = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8 + 4);
+          acc[g] = __fmaf_rn(kf[0], qa.x, acc[g]); acc[g] = __fmaf_rn(kf[1], qa.y, acc[g]);
+          acc[g] = __fmaf_rn(kf[2], qa.z, acc[g]); acc[g] = __fmaf_rn(kf[3], qa.w, acc[g]);
+          acc[g] = __fmaf_rn(kf[4], qb.x, acc[g]); acc[g] = __fmaf_rn(kf[5], qb.y, acc[g]);
+          acc[g] = __fmaf_rn(kf[6], qb.z, acc[g]); acc[g] = __fmaf_rn(kf[7], qb.w, acc[g]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) s.ph[(qr * GQ + g) * PL + t] = acc[g];
+    }
+    if (part + 1 < np) load_k(part + 1);                           // the K registers are free: the next partition's rows travel during the softmax
+    csync();
+    // ---- softmax statistics: one warp per q head, lane holds positions lane + 32 k
+    if (warp < GQ) {
+      const int g = warp;
+      float sv[4], m = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int tt = lane + 32 * k;
+        const float dot = __fadd_rn(__fadd_rn(__fadd_rn(s.ph[g * PL + tt], s.ph[(GQ + g) * PL + tt]), s.ph[(2 * GQ + g) * PL + tt]), s.ph[(3 * GQ + g) * PL + tt]);
+        sv[k] = cached(tt) ? __fmul_rn(dot, d.scale) : -INFINITY;
+        m = fmaxf(m, sv[k]);
+      }
+      float snew = -INFINITY;
+      if (owner) {
+        float a = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a = __fmaf_rn(s.qs[g * HD + lane * 4 + j], s.knew[lane * 4 + j], a);
+        snew = __fmul_rn(warp_sum(a), d.scale);
+      }
+      m = fmaxf(warp_max(m), snew);
+      float l = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float pr = cached(lane + 32 * k) ? expf(__fsub_rn(sv[k], m)) : 0.f;
+        s.sc[g * PL + lane + 32 * k] = pr;
+        l = __fadd_rn(l, pr);
+      }
+      l = warp_sum(l);
+      const float pn = owner ? expf(__fsub_rn(snew, m)) : 0.f;
+      if (lane == 0) { s.st[g] = m; s.st[GQ + g] = __fadd_rn(l, pn); s.st[2 * GQ + g] = pn; }
+    }
+    csync();
+    // ---- output
+    {
+      float acc[GQ];
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) acc[g] = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int tb = (2 * qr + u) * BS;
+        if (tb < ntok) {
+          float f[16];
+          unpack8(vreg[2 * u], f); unpack8(vreg[2 * u + 1], f + 8);
+#pragma unroll
+          for (int o = 0; o < 16; ++o) f[o] = cached(tb + o) ? f[o] : 0.f;
+#pragma unroll
+          for (int g = 0; g < GQ; ++g) {
+#pragma unroll
+            for (int o4 = 0; o4 < 4; ++o4) {
+              const float4 pr = *(const float4*)(s.sc + g * PL + tb + 4 * o4);
+              acc[g] = __fmaf_rn(pr.x, f[4 * o4], acc[g]); acc[g] = __fmaf_rn(pr.y, f[4 * o4 + 1], acc[g]);
+              acc[g] = __fmaf_rn(pr.z, f[4 * o4 + 2], acc[g]); acc[g] = __fmaf_rn(pr.w, f[4 * o4 + 3], acc[g]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) s.po[(qr * GQ + g) * HD + t] = acc[g];
+    }
+    if (part + 1 < np) load_v(part + 1);
+    csync();
+    for (int idx = tid; idx < GQ * HD; idx += ETXB_CONSUMERS) {
+      const int g = idx >> 7, dd = idx & (HD - 1);
+      float o = __fadd_rn(__fadd_rn(__fadd_rn(s.po[g * HD + dd], s.po[(GQ + g) * HD + dd]), s.po[(2 * GQ + g) * HD + dd]), s.po[(3 * GQ + g) * HD + dd]);
+      if (owner) o = __fmaf_rn(s.st[2 * GQ + g], s.vnew[dd], o);
+      PO[((size_t)part * GQ + g) * HD + dd] = o;
+      if (dd == 0) { PS[(part * GQ + g) * 2] = s.st[g]; PS[(part * GQ + g) * 2 + 1] = s.st[GQ + g]; }
+    }
+    // (the next partition's score sums go to s.ph, its statistics to s.sc / s.st only after the barrier that follows them:
+    // nothing this loop still reads is overwritten early)
+  }
+  csync();
+  mark(sm, 2);
+  // ---- merge, with the arithmetic of attn_gq_merge: weights exp(m_p - max m), sums in ascending partition order
+  float* wl = s.ph;                                                // [GQ][np]
+  float* red = s.st + 24;                                          // [GQ]
+  if (warp < GQ) {
+    const int g = warp;
+    float m = -INFINITY;
+    for (int pp = lane; pp < np; pp += 32) m = fmaxf(m, PS[(pp * GQ + g) * 2]);
+    m = warp_max(m);
+    float L = 0.f;
+    for (int pp = lane; pp < np; pp += 32) {
+      const float w = expf(__fsub_rn(PS[(pp * GQ + g) * 2], m));
+      wl[g * np + pp] = w;
+      L = __fmaf_rn(w, PS[(pp * GQ + g) * 2 + 1], L);
+    }
+    L = warp_sum(L);
+    if (lane == 0) red[g] = L;
+  }
+  csync();
+  for (int idx = tid; idx < GQ * HD; idx += ETXB_CONSUMERS) {
+    const int g = idx >> 7, dd = idx & (HD - 1);
+    float o = 0.f;
+    for (int pp = 0; pp < np; ++pp) o = __fmaf_rn(wl[g * np + pp], PO[((size_t)pp * GQ + g) * HD + dd], o);
+    ((__nv_bfloat16*)d.out)[(size_t)(hq0 + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
+  }
+  mark(sm, 3);
+  csync();                                                         // the next task may overwrite the partials
+}
+
 // Fused attention, either form: gq > 0 in the argument block selects the grouped form above (head_dim 128, cache
 // blocks of 16, partitions of 128 positions), else the general tile.
 __device__ __forceinline__ void tile_attn_any(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
   const etxb_attnf_args& d = *(const etxb_attnf_args*)a;
   if (d.gq == 0) { tile_attn_fused(a, blk, sm, S); return; }
   if (blk >= (int)d.nblocks) return;
+  if (d.part_len & ETXB_GQ_WHOLE) {
+    switch (d.gq) {
+      case 1: attn_gq_seq<1>(d, blk, sm, S); break;
+      case 2: attn_gq_seq<2>(d, blk, sm, S); break;
+      case 4: attn_gq_seq<4>(d, blk, sm, S); break;
+      default: attn_gq_seq<8>(d, blk, sm, S); break;
+    }
+    return;
+  }
   switch (d.gq) {
     case 1: attn_gq_impl<1>(d, blk, sm, S); break;
     case 2: attn_gq_impl<2>(d, blk, sm, S); break;

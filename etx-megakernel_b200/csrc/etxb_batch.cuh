@@ -137,7 +137,9 @@ __device__ __forceinline__ void tile_gemv_nb(const unsigned char* a, int blk, co
 
 // ---------------------------------------------------------------------------------------------- routing of a batch
 // One task: softmax top-k of every column (a warp per column), then the per-expert token lists: elist[e][0 .. ecount[e])
-// holds the (column << 8 | slot) pairs that selected expert e, in ascending (column, slot) order.
+// holds the (column << 8 | slot) pairs that selected expert e, in ascending (column, slot) order.  With elist == null the
+// grid has one task per column, which only writes its column's ids / wts (the share-scheduled expert tiles build
+// their lists themselves).
 struct etxb_route_args {
   const void* logits; float* wts; int32_t* ids; int32_t* ecount; int32_t* elist;      // 0..39
   int32_t* active;                                                                    // 40..47: optional counter, += the experts with a non-empty list (the byte ledger of a batched step)
@@ -146,8 +148,14 @@ struct etxb_route_args {
 };
 __device__ __forceinline__ void tile_route(const unsigned char* a, int blk, const Smem& sm) {
   const etxb_route_args& d = *(const etxb_route_args*)a;
-  if (blk != 0) return;
   const int warp = tidx() >> 5, lane = tidx() & 31;
+  if (d.elist == nullptr) {
+    if (blk < d.nb && warp == 0)
+      warp_topk<false>((const __nv_bfloat16*)d.logits + (size_t)blk * d.E, d.E, d.K, (d.mode & 0xff) == 1, (d.mode & ETXB_MODE_BF16_WTS) != 0,
+                       d.ids + (size_t)blk * d.K, d.wts + (size_t)blk * d.K, nullptr);
+    return;
+  }
+  if (blk != 0) return;
   int32_t* sids = (int32_t*)sm.xs;                                 // [nb][K]
   float* swts = sm.xs + 2048;
   for (int b = warp; b < d.nb; b += ETXB_CONSUMER_WARPS) {
@@ -245,7 +253,11 @@ __device__ __forceinline__ void tile_moe_down_g(const unsigned char* a, int blk,
 // ---------------------------------------------------------------------------------------------- per-column prologue
 // Columns of a batched step: token_in / token_out are [step][nb]; every column is at the step's position; column b owns
 // the cache slots [b * slot_span, (b + 1) * slot_span) of the shared block pool.
-struct etxb_batch_args { int32_t nb, slot_span, pad[2]; uint32_t grid[3], nblocks; };
+// `zero`: optional, ETXB_SPLITK_COUNTERS int32 counters that column 0's prologue task clears (the arrival counters of the
+// split-K dense grids: they return to a multiple of the split in every completed step, and an abandoned step must not
+// leave them off one).
+#define ETXB_SPLITK_COUNTERS 768
+struct etxb_batch_args { int32_t nb, slot_span; int32_t* zero; uint32_t grid[3], nblocks; };
 __device__ __forceinline__ void tile_prologue_nb(const unsigned char* a, int b, const etxb_stepv& S) {
   const etxb_batch_args& d = *(const etxb_batch_args*)a;
   if (b >= d.nb) return;
@@ -254,6 +266,8 @@ __device__ __forceinline__ void tile_prologue_nb(const unsigned char* a, int b, 
     if (S.token_time && b == 0) S.token_time[2 * t] = globaltimer();
     S.positions[b] = S.pos; S.seq_lens[b] = S.pos + 1; S.slot_mapping[b] = (long long)b * d.slot_span + S.pos;
   }
+  if (b == 0 && d.zero != nullptr)
+    for (int i = tidx(); i < ETXB_SPLITK_COUNTERS; i += ETXB_CONSUMERS) d.zero[i] = 0;
   const int id = __ldcg(S.token_in + (size_t)t * d.nb + b);
   const uint4* src = (const uint4*)((const __nv_bfloat16*)S.embed + (size_t)id * S.H);
   uint4* dst = (uint4*)((__nv_bfloat16*)S.resid + (size_t)b * S.H);

@@ -32,7 +32,8 @@ namespace etxb {
 #define ETXB_TC_BOX 16384              // one box: 128 rows x 64 k x 2 bytes
 #define ETXB_TC_STAGE (2 * ETXB_TC_BOX)   // one k-chunk of a tile: up to 256 rows
 #define ETXB_TC_MAXSTAGE 6
-#define ETXB_TC_AREA (ETXB_RING_BYTES + ETXB_GEN_BYTES - 1024)   // the idle weight ring and the general region, 1024-byte aligned inside
+#define ETXB_TC_TAIL 8192              // end of the area: the routing tables of the expert tiles
+#define ETXB_TC_AREA (ETXB_RING_BYTES + ETXB_GEN_BYTES - 1024 - ETXB_TC_TAIL)   // the idle weight ring and the general region, 1024-byte aligned inside
 #define ETXB_TC_XBYTES 131072          // at most this much of it holds tokens (32 tokens x 2048 columns); the rest are weight stages
 #define ETXB_TC_MAXTOK 32              // tokens per job (M = 64 up to 8 tokens, 128 above)
 #define ETXB_TC_COLS 512               // tensor-memory columns the kernel allocates: two accumulator buffers of 256
@@ -83,18 +84,31 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 8 consecutive bf16 results of one token: one 16-byte store when all of them are inside [.., r1), else one by one
+__device__ __forceinline__ void tc_store8(__nv_bfloat16* o, int r, int r1, const float (&y)[8]) {
+  if (r + 8 <= r1 && (((uintptr_t)(o + r)) & 15) == 0) {
+    uint4 pk;
+    pk.x = pack_bf(y[0], y[1]); pk.y = pack_bf(y[2], y[3]); pk.z = pack_bf(y[4], y[5]); pk.w = pack_bf(y[6], y[7]);
+    *(uint4*)(o + r) = pk;
+  } else {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) if (r + u < r1) o[r + u] = __float2bfloat16_rn(y[u]);
+  }
+}
+
 // One task: for every tile i < ntiles, D_i[tok][j] = sum_k x_tok[k] * W[boxrow(i, j / 128) + j % 128][k] for j < 128 nbox(i),
-// then epi(i, tok, j, v0, v1) for every tok < ntok, j < 128, with v0 = D_i[tok][j] and v1 = D_i[tok][128 + j] (0 when the tile
-// has one box).  A tile is one or two TMA boxes of 128 weight rows that one instruction multiplies (N = 128 or 256): two
-// neighbouring row blocks of a matrix, or an expert's gate rows and up rows.  xsrc(n): the K bf16 values of token n;
-// map: the tensor map of the weight tensor (rows x K, box 64 x 128).  All consumer threads call; ends with a barrier.
+// then epi(i, tok, j, v0, v1, two) for every tok < ntok and j = 0, 8, .. 120, with v0[u] = D_i[tok][j + u] and (two: the tile has
+// a second box) v1[u] = D_i[tok][128 + j + u].  A tile is one or two TMA boxes of 128 weight rows that one instruction multiplies (N = 128 or 256): two
+// neighbouring row blocks of a matrix, or an expert's gate rows and up rows.  The sum runs over the K columns from
+// `kofs` on (a K-slice of the matrix: both multiples of 64).  xsrc(n): the bf16 row of token n (column 0);
+// map: the tensor map of the weight tensor (rows x all columns, box 64 x 128).  All consumer threads call; ends with a barrier.
 //
 // The tokens are staged ONCE per task (the tiles of a task share them) whenever all of K fits the token area; the tiles
 // then stream back to back through the stage ring, their accumulators alternating between two buffers of tensor
 // memory, so that the epilogue of tile i overlaps the MMAs of tile i + 1.  When K does not fit (4096 columns x 32
 // tokens) the tokens go in windows of K and a task handles its tiles one by one, accumulating across the windows.
 template <typename XSrc, typename NBox, typename BoxRow, typename Epi>
-__device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void* map, int ntiles, int K, int ntok, int where,
+__device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void* map, int ntiles, int kofs, int K, int ntok, int where,
                                         XSrc xsrc, NBox nbox, BoxRow boxrow, Epi epi) {
   const int tid = tidx(), warp = tid >> 5, lane = tid & 31;
   unsigned char* area = (unsigned char*)(((uintptr_t)sm.ring + 1023) & ~(uintptr_t)1023);
@@ -119,7 +133,7 @@ __device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void
     // the tokens' slice [64 w0, 64 (w0 + nc)) -> swizzled rows: token n is row n % 8 of group n / 8 of its k-chunk
     for (int i = tid; i < ntok * nc * 8; i += ETXB_CONSUMERS) {
       const int n = i / (nc * 8), v = i - n * (nc * 8), c = v >> 3, j = v & 7, r = n & 7;
-      const uint4 val = ld_act16((const __nv_bfloat16*)xsrc(n) + (size_t)(w0 * 64 + v * 8));
+      const uint4 val = ld_act16((const __nv_bfloat16*)xsrc(n) + (size_t)(kofs + w0 * 64 + v * 8));
       *(uint4*)(area + (size_t)(c * groups + (n >> 3)) * 1024 + r * 128 + ((j ^ r) << 4)) = val;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core's reads
@@ -136,8 +150,8 @@ __device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void
           if (!ok) break;
           mbar_expect_tx(tc.full + st, (uint32_t)nb * ETXB_TC_BOX);
           unsigned char* dst = ws + (size_t)st * ETXB_TC_STAGE;
-          tma_load_2d(dst, map, (w0 + c) * 64, y0, tc.full + st);
-          if (nb > 1) tma_load_2d(dst + ETXB_TC_BOX, map, (w0 + c) * 64, y1, tc.full + st);
+          tma_load_2d(dst, map, kofs + (w0 + c) * 64, y0, tc.full + st);
+          if (nb > 1) tma_load_2d(dst + ETXB_TC_BOX, map, kofs + (w0 + c) * 64, y1, tc.full + st);
           tc.lu[st] = uu + 1;
           st = st + 1 == nst ? 0 : st + 1;
         }
@@ -194,9 +208,7 @@ __device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void
             float v0[8], v1[8];
             tc_ld8(tc.tmem + bsel * 2 * ETXB_TC_ROWS + (uint32_t)col, v0);
             if (two) tc_ld8(tc.tmem + bsel * 2 * ETXB_TC_ROWS + (uint32_t)(ETXB_TC_ROWS + col), v1);
-            if (lane < ntok)
-#pragma unroll
-              for (int j = 0; j < 8; ++j) epi(i, lane, col + j, v0[j], two ? v1[j] : 0.f);
+            if (lane < ntok) epi(i, lane, col, v0, v1, two);
           }
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -220,93 +232,228 @@ __device__ __forceinline__ void tc_task(const Smem& sm, TcShared& tc, const void
 }
 
 // ---------------------------------------------------------------------------------------------- batched dense GEMV
-// out[b * sout + r] = bf16(W[r,:] . x[b] (+ bias[r])) for the nb columns b, rows [blk * rpt, ...).  The GEMV block of
-// gemv_nb; `ln` = the tensor map of W (rows M, box 64 x 128), put there by the host library when the plan is bound.
+// out[b * sout + r] = bf16(W[r,:] . x[b] (+ bias[r])) for the nb columns b.  The GEMV block of gemv_nb; `ln` = the tensor
+// map of W (rows M, box 64 x 128), put there by the host library when the plan is bound.
+//
+// tpe = the K-split S of the grid (1: none).  Task blk covers rows [(blk / S) * rpt, ...) and the K-slice blk % S.  A
+// matrix of a few thousand rows has too few 128-row tiles for 148 workers (qkv: 40, o_proj: 16, router: 1) and an
+// instruction cannot take fewer rows without paying the same time, so the narrow matrices are cut along K instead: every
+// slice task stores its fp32 partial sums to `rows` ([S][M][nb] floats) and counts itself in `resid_in` (one int32 per row
+// block); the S-th arrival adds the partials in slice order, adds the bias and writes the bf16 result -- the same sum
+// whoever comes last.
 __device__ __forceinline__ void tile_gemv_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   if (blk >= (int)d.nblocks) return;
-  const int r0 = blk * d.rpt, r1 = min(d.M, r0 + d.rpt);
+  const int S = max(1, d.tpe), rb = blk / S, ksl = blk - rb * S, Ks = d.K / S;
+  const int r0 = rb * d.rpt, r1 = min(d.M, r0 + d.rpt);
   if (r0 >= r1) return;
   const __nv_bfloat16* bias = (d.mode & ETXB_MODE_BIAS) ? (const __nv_bfloat16*)d.wts : nullptr;
   __nv_bfloat16* out = (__nv_bfloat16*)d.out;
+  float* part = S > 1 ? (float*)d.rows + (size_t)ksl * d.nb * d.M : nullptr;   // this slice's [M][nb] partial sums
   const int ntiles = (r1 - r0 + 2 * ETXB_TC_ROWS - 1) / (2 * ETXB_TC_ROWS);
   for (int b0 = 0; b0 < d.nb; b0 += ETXB_TC_MAXTOK) {
     const int nt = min(ETXB_TC_MAXTOK, d.nb - b0);
-    tc_task(sm, tc, d.ln, ntiles, d.K, nt, where,
+    tc_task(sm, tc, d.ln, ntiles, ksl * Ks, Ks, nt, where,
             [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(b0 + n) * d.sx; },
             [&](int i) { return r1 - r0 - i * 2 * ETXB_TC_ROWS > ETXB_TC_ROWS ? 2 : 1; },
             [&](int i, int b) { return r0 + (2 * i + b) * ETXB_TC_ROWS; },
-            [&](int i, int tok, int j, float v0, float v1) {
-              const int r = r0 + 2 * i * ETXB_TC_ROWS + j, rb = r + ETXB_TC_ROWS;
-              __nv_bfloat16* o = out + (size_t)(b0 + tok) * d.sout;
-              if (r < r1) o[r] = __float2bfloat16_rn(bias ? __fadd_rn(v0, __bfloat162float(bias[r])) : v0);
-              if (rb < r1) o[rb] = __float2bfloat16_rn(bias ? __fadd_rn(v1, __bfloat162float(bias[rb])) : v1);
-            });
-  }
-}
-
-// ---------------------------------------------------------------------------------------------- expert-grouped gate+up / down
-// The blocks of moe_up_g / moe_down_g (task = expert blk / tpe, row chunk blk % tpe; rows = token lists, resid_in = their
-// lengths, nb = entries per expert, R = top-k); `ln` = the tensor map of the expert tensor seen as one [E * rows][K] matrix.
-__device__ __forceinline__ void tile_moe_up_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) {
-  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  if (blk >= (int)d.nblocks) return;
-  const int e = blk / d.tpe, r0 = (blk - e * d.tpe) * d.rpt, r1 = min(d.M, r0 + d.rpt);
-  const int cnt = min(__ldcg((const int32_t*)d.resid_in + e), d.nb);
-  if (cnt <= 0 || r0 >= r1) return;
-  const int32_t* list = (const int32_t*)d.rows + (size_t)e * d.nb;
-  int32_t* ent = (int32_t*)(sm.scr + 96);                          // [32] entries of the pass
-  const int erow = (int)((long long)e * d.estride / d.K);          // first row of expert e in the [E * 2M][K] view
-  const int ntiles = (r1 - r0 + ETXB_TC_ROWS - 1) / ETXB_TC_ROWS;
-  for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
-    const int nt = min(ETXB_TC_MAXTOK, cnt - p0);
-    if (tidx() < nt) ent[tidx()] = __ldcg(list + p0 + tidx());
-    csync();
-    tc_task(sm, tc, d.ln, ntiles, d.K, nt, where,
-            [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(ent[n] >> 8) * d.sx; },
-            [&](int) { return 2; },                                                            // 128 gate rows and their 128 up rows: one instruction
-            [&](int i, int b) { return erow + (b ? d.M : 0) + r0 + i * ETXB_TC_ROWS; },          // up rows follow the M gate rows
-            [&](int i, int tok, int j, float g, float u) {
-              const int r = r0 + i * ETXB_TC_ROWS + j;
-              if (r < r1) {
-                const int en = ent[tok];
-                ((__nv_bfloat16*)d.out)[((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M + r] = __float2bfloat16_rn(__fmul_rn(bfr(silu_f(bfr(g))), bfr(u)));
+            [&](int i, int tok, int j, const float (&v0)[8], const float (&v1)[8], bool two) {
+              const int r = r0 + 2 * i * ETXB_TC_ROWS + j;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                if (h == 1 && !two) break;
+                const int rr = r + h * ETXB_TC_ROWS;
+                const float (&v)[8] = h ? v1 : v0;
+                if (part != nullptr) {                              // [slice][row][column]: the 32 lanes of a store are 32 consecutive floats
+#pragma unroll
+                  for (int u = 0; u < 8; ++u) if (rr + u < r1) __stcg(part + (size_t)(rr + u) * d.nb + b0 + tok, v[u]);
+                } else {
+                  float y[8];
+#pragma unroll
+                  for (int u = 0; u < 8; ++u) y[u] = (bias && rr + u < r1) ? __fadd_rn(v[u], __bfloat162float(bias[rr + u])) : v[u];
+                  tc_store8(out + (size_t)(b0 + tok) * d.sout, rr, r1, y);
+                }
               }
             });
   }
+  if (S == 1) return;
+  // (tc_task ended with a barrier: every partial of this task is stored)
+  int* last = (int*)(sm.scr + 90);
+  if (tidx() == 0) {
+    __threadfence();
+    const int old = atomicAdd((int*)d.resid_in + rb, 1);
+    *last = ((old + 1) % S) == 0;
+    __threadfence();
+  }
+  csync();
+  if (*last == 0) return;
+  const float* p0 = (const float*)d.rows;
+  const size_t sstride = (size_t)d.nb * d.M;
+  // Sums with the column index fastest (the partials are [row][column]: coalesced reads), four outputs per thread and round
+  // with all their slices requested before the first is added; every output is the sum of its slices in slice order.
+  // The sums go through shared memory ([row][nb + 1] floats in the area the tile's tokens and stages have left) so that
+  // the bf16 results leave with the row index fastest: rows of `out` are contiguous, columns are sout apart.
+  const int nr = r1 - r0, nout = d.nb * nr, ld = d.nb + 1;
+  float* tile = (float*)(((uintptr_t)sm.ring + 1023) & ~(uintptr_t)1023);
+  for (int i0 = tidx(); i0 < nout; i0 += 4 * ETXB_CONSUMERS) {
+    float t[4][8];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int i = min(i0 + w * ETXB_CONSUMERS, nout - 1);
+      const int r = r0 + i / d.nb, tok = i - (i / d.nb) * d.nb;
+      const float* src = p0 + (size_t)r * d.nb + tok;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) t[w][u] = u < S ? __ldcg(src + (size_t)u * sstride) : 0.f;
+    }
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int i = i0 + w * ETXB_CONSUMERS;
+      if (i >= nout) break;
+      const int rl = i / d.nb, tok = i - rl * d.nb;
+      float v = 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) if (u < S) v = __fadd_rn(v, t[w][u]);
+      for (int q = 8; q < S; ++q) v = __fadd_rn(v, __ldcg(p0 + (size_t)q * sstride + (size_t)(r0 + rl) * d.nb + tok));   // (a split beyond 8: the rest one by one)
+      tile[rl * ld + tok] = v;
+    }
+  }
+  csync();
+  for (int i = tidx(); i < nout; i += ETXB_CONSUMERS) {
+    const int tok = i / nr, rl = i - tok * nr, r = r0 + rl;
+    const float v = tile[rl * ld + tok];
+    out[(size_t)tok * d.sout + r] = __float2bfloat16_rn(bias ? __fadd_rn(v, __bfloat162float(bias[r])) : v);
+  }
+  csync();
 }
 
-__device__ __forceinline__ void tile_moe_down_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) {
-  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
-  if (blk >= (int)d.nblocks) return;
-  const int e = blk / d.tpe, r0 = (blk - e * d.tpe) * d.rpt, r1 = min(d.M, r0 + d.rpt);
-  const int cnt = min(__ldcg((const int32_t*)d.resid_in + e), d.nb);
-  if (cnt <= 0 || r0 >= r1) return;
-  const int32_t* list = (const int32_t*)d.rows + (size_t)e * d.nb;
-  int32_t* ent = (int32_t*)(sm.scr + 96);
-  float* wt = sm.scr + 128;
-  const int erow = (int)((long long)e * d.estride / d.K);
-  const int ntiles = (r1 - r0 + 2 * ETXB_TC_ROWS - 1) / (2 * ETXB_TC_ROWS);
-  for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
-    const int nt = min(ETXB_TC_MAXTOK, cnt - p0);
-    if (tidx() < nt) {
-      const int en = __ldcg(list + p0 + tidx());
-      ent[tidx()] = en;
-      wt[tidx()] = d.wts ? __ldcg(d.wts + (size_t)(en >> 8) * d.R + (en & 0xff)) : 1.f;
+// ---------------------------------------------------------------------------------------------- expert-grouped gate+up / down
+// The expert phases of a batched step, scheduled by SHARE: the grid has one task per worker, and task blk of S takes
+// tiles [blk * total / S, (blk + 1) * total / S) of the step's active experts (total = active experts x tiles per expert,
+// experts in ascending id, an expert's tiles in row order) -- every worker streams the same number of weight rows (+-1
+// tile) however the routing falls, where a grid of (expert, row chunk) tasks leaves the workers of unselected experts idle
+// and gives others three chunks.  Every task derives the routing tables itself from the step's top-k ids (nb x R int32,
+// one L2 read): per-expert counts, the active list, and per expert the (column << 8 | slot) pairs that selected it in
+// ascending (column, slot) order.
+//
+// The GEMV block, read this way: W / estride / M / K / E as in the one-token MoE tiles (gate+up: M gate rows then M up
+// rows per expert; down: M rows), ids = the routing ids [nb][R], nb columns, R = top-k, nblocks = S;
+// gate+up: x[b * sx ..] the columns' normed vectors, out = act [nb][R][M], resid_out = optional int32 counter that
+// share 0 increases by the number of active experts; down: x = act [nb][R][K], wts [nb][R] routing weights, out = y [nb][R][M].
+// `ln` = the tensor map of the expert tensor seen as one [E * rows][K] matrix.
+struct TcRoute {
+  int32_t* sids;     // [nb * R] expert ids of the step
+  int32_t* scnt;     // [E] entries per expert
+  int32_t* ent;      // [<= nb] entries of the current expert
+  float* wt;         // [<= nb] their routing weights (down)
+  uint16_t* alist;   // [nact] active experts, ascending
+  int32_t* nact;
+};
+__device__ __forceinline__ TcRoute tc_route_tables(const Smem& sm) {
+  unsigned char* tail = (unsigned char*)(((uintptr_t)sm.ring + 1023) & ~(uintptr_t)1023) + ETXB_TC_AREA;
+  TcRoute r;
+  r.sids = (int32_t*)tail; r.scnt = r.sids + 1024; r.ent = r.scnt + 256; r.wt = (float*)(r.ent + 64); r.alist = (uint16_t*)(r.wt + 64);
+  r.nact = (int32_t*)(r.alist + 256);
+  return r;
+}
+// counts and the active list (all consumer threads; ends with a barrier)
+__device__ __forceinline__ void tc_route_build(const etxb_gemv_args& d, const TcRoute& rt) {
+  const int tid = tidx(), n = d.nb * d.R;
+  for (int i = tid; i < n; i += ETXB_CONSUMERS) { const int e = __ldcg(d.ids + i); rt.sids[i] = (unsigned)e < (unsigned)d.E ? e : 0; }
+  for (int e = tid; e < d.E; e += ETXB_CONSUMERS) rt.scnt[e] = 0;
+  csync();
+  for (int i = tid; i < n; i += ETXB_CONSUMERS) atomicAdd(rt.scnt + rt.sids[i], 1);
+  csync();
+  if (tid < 32) {
+    int na = 0;
+    for (int e0 = 0; e0 < d.E; e0 += 32) {
+      const bool on = e0 + tid < d.E && rt.scnt[e0 + tid] > 0;
+      const uint32_t m = __ballot_sync(0xffffffffu, on);
+      if (on) rt.alist[na + __popc(m & ((1u << tid) - 1u))] = (uint16_t)(e0 + tid);
+      na += __popc(m);
     }
-    csync();
-    tc_task(sm, tc, d.ln, ntiles, d.K, nt, where,
-            [&](int n) { return (const __nv_bfloat16*)d.x + ((size_t)(ent[n] >> 8) * d.R + (ent[n] & 0xff)) * d.K; },
-            [&](int i) { return r1 - r0 - i * 2 * ETXB_TC_ROWS > ETXB_TC_ROWS ? 2 : 1; },
-            [&](int i, int b) { return erow + r0 + (2 * i + b) * ETXB_TC_ROWS; },
-            [&](int i, int tok, int j, float v0, float v1) {
-              const int r = r0 + 2 * i * ETXB_TC_ROWS + j, rb = r + ETXB_TC_ROWS;
-              const int en = ent[tok];
-              __nv_bfloat16* o = (__nv_bfloat16*)d.out + ((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M;
-              if (r < r1) { const float y = bfr(v0); o[r] = __float2bfloat16_rn(d.wts ? bfr(__fmul_rn(y, wt[tok])) : y); }
-              if (rb < r1) { const float y = bfr(v1); o[rb] = __float2bfloat16_rn(d.wts ? bfr(__fmul_rn(y, wt[tok])) : y); }
-            });
+    if (tid == 0) *rt.nact = na;
+  }
+  csync();
+}
+// the entries of expert e, in (column, slot) order (warp 0; the caller syncs)
+__device__ __forceinline__ void tc_route_entries(const etxb_gemv_args& d, const TcRoute& rt, int e, const float* wts) {
+  const int tid = tidx(), n = d.nb * d.R;
+  if (tid >= 32) return;
+  int cnt = 0;
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    const int i = i0 + tid;
+    const bool hit = i < n && rt.sids[i] == e;
+    const uint32_t m = __ballot_sync(0xffffffffu, hit);
+    const int at = cnt + __popc(m & ((1u << tid) - 1u));
+    if (hit && at < 64) {
+      rt.ent[at] = ((i / d.R) << 8) | (i % d.R);
+      if (wts != nullptr) rt.wt[at] = __ldcg(wts + i);
+    }
+    cnt += __popc(m);
   }
 }
+
+template <bool UP>
+__device__ __forceinline__ void tile_moe_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) {
+  const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
+  if (blk >= (int)d.nblocks) return;
+  const TcRoute rt = tc_route_tables(sm);
+  tc_route_build(d, rt);
+  const int nact = *rt.nact;
+  constexpr int TROWS = UP ? ETXB_TC_ROWS : 2 * ETXB_TC_ROWS;       // rows of M one tile covers (gate+up: 128 gate rows and their 128 up rows)
+  const int T = (d.M + TROWS - 1) / TROWS;
+  const long long total = (long long)nact * T;
+  int t = (int)(total * blk / (long long)d.nblocks);
+  const int hi = (int)(total * (blk + 1) / (long long)d.nblocks);
+  if (UP && blk == 0 && tidx() == 0 && d.resid_out != nullptr) atomicAdd((int32_t*)d.resid_out, nact);
+  while (t < hi) {
+    const int ai = t / T, t0 = t - ai * T, t1 = min(T, t0 + (hi - t));
+    const int e = rt.alist[ai];
+    const int cnt = min(min(rt.scnt[e], d.nb), 64);
+    tc_route_entries(d, rt, e, UP ? nullptr : d.wts);
+    csync();
+    const int erow = (int)((long long)e * d.estride / d.K);         // first row of expert e in the [E * rows][K] view
+    const int r0 = t0 * TROWS, r1 = min(d.M, t1 * TROWS);
+    for (int p0 = 0; p0 < cnt; p0 += ETXB_TC_MAXTOK) {
+      const int nt = min(ETXB_TC_MAXTOK, cnt - p0);
+      const int32_t* ent = rt.ent + p0;
+      if constexpr (UP) {
+        tc_task(sm, tc, d.ln, t1 - t0, 0, d.K, nt, where,
+                [&](int n) { return (const __nv_bfloat16*)d.x + (size_t)(ent[n] >> 8) * d.sx; },
+                [&](int) { return 2; },                                                          // 128 gate rows and their 128 up rows: one instruction
+                [&](int i, int b) { return erow + (b ? d.M : 0) + r0 + i * ETXB_TC_ROWS; },        // up rows follow the M gate rows
+                [&](int i, int tok, int j, const float (&g)[8], const float (&up)[8], bool) {
+                  const int r = r0 + i * ETXB_TC_ROWS + j, en = ent[tok];
+                  float y[8];
+#pragma unroll
+                  for (int u = 0; u < 8; ++u) y[u] = __fmul_rn(bfr(silu_f(bfr(g[u]))), bfr(up[u]));
+                  tc_store8((__nv_bfloat16*)d.out + ((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M, r, r1, y);
+                });
+      } else {
+        const float* wt = rt.wt + p0;
+        tc_task(sm, tc, d.ln, t1 - t0, 0, d.K, nt, where,
+                [&](int n) { return (const __nv_bfloat16*)d.x + ((size_t)(ent[n] >> 8) * d.R + (ent[n] & 0xff)) * d.K; },
+                [&](int i) { return r1 - r0 - i * 2 * ETXB_TC_ROWS > ETXB_TC_ROWS ? 2 : 1; },
+                [&](int i, int b) { return erow + r0 + (2 * i + b) * ETXB_TC_ROWS; },
+                [&](int i, int tok, int j, const float (&v0)[8], const float (&v1)[8], bool two) {
+                  const int r = r0 + 2 * i * ETXB_TC_ROWS + j, en = ent[tok];
+                  __nv_bfloat16* o = (__nv_bfloat16*)d.out + ((size_t)(en >> 8) * d.R + (en & 0xff)) * d.M;
+                  float y[8];
+#pragma unroll
+                  for (int u = 0; u < 8; ++u) { const float q = bfr(v0[u]); y[u] = d.wts ? bfr(__fmul_rn(q, wt[tok])) : q; }
+                  tc_store8(o, r, r1, y);
+                  if (two) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { const float q = bfr(v1[u]); y[u] = d.wts ? bfr(__fmul_rn(q, wt[tok])) : q; }
+                    tc_store8(o, r + ETXB_TC_ROWS, r1, y);
+                  }
+                });
+      }
+    }
+    t += t1 - t0;
+  }
+}
+__device__ __forceinline__ void tile_moe_up_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) { tile_moe_tc<true>(a, blk, sm, tc, where); }
+__device__ __forceinline__ void tile_moe_down_tc(const unsigned char* a, int blk, const Smem& sm, TcShared& tc, int where) { tile_moe_tc<false>(a, blk, sm, tc, where); }
 
 }  // namespace etxb

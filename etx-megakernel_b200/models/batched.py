@@ -33,7 +33,8 @@ from . import qwen as Q
 from .qwen import BS, SRC, X, ArgPool
 
 _DT = {"bf16": torch.bfloat16, "f32": torch.float32, "i32": torch.int32, "i64": torch.int64}
-UP_ROWS, DOWN_ROWS = 256, 512      # rows of one expert a gate+up / down task covers (blocks of 128 inside the tile)
+UP_ROWS, DOWN_ROWS = 256, 512      # mma.sync engine: rows of one expert a gate+up / down task covers (blocks of 128 inside the tile)
+SKP_FLOATS = 4 << 20               # fp32 partial sums of a split-K dense grid ([split][rows][B])
 
 
 def buffer_shapes(d: Q.Dims, B: int, maxlen: int, steps: int, parts: int) -> dict:
@@ -48,7 +49,8 @@ def buffer_shapes(d: Q.Dims, B: int, maxlen: int, steps: int, parts: int) -> dic
             "tmp_out": ((B, d.NH, parts, op_attn.GQ_PARTIAL_FLOATS), "f32"),
             "kc": ((d.L, B * nblk, d.NKV, d.HD // X, BS, X), "bf16"), "vc": ((d.L, B * nblk, d.NKV, d.HD, BS), "bf16"),
             "attn_counters": ((d.L, B, d.NH), "i32"), "rlog": ((B, d.E), "bf16"), "tw": ((B, d.TOPK), "f32"), "ti": ((B, d.TOPK), "i32"),
-            "mc2": ((B, d.TOPK, d.MI), "bf16"), "mc3": ((B, d.TOPK, d.H), "bf16"), "ecount": ((d.E,), "i32"), "elist": ((d.E, B), "i32"), "active": ((d.L,), "i32")}
+            "mc2": ((B, d.TOPK, d.MI), "bf16"), "mc3": ((B, d.TOPK, d.H), "bf16"), "ecount": ((d.E,), "i32"), "elist": ((d.E, B), "i32"), "active": ((d.L,), "i32"),
+            "skp": ((SKP_FLOATS,), "f32"), "skc": ((op_batch.SPLITK_COUNTERS,), "i32")}
 
 
 def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineModel | str = "b200", engine: str = "tc"):
@@ -62,8 +64,6 @@ def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineMode
         raise ValueError("engine is 'tc' or 'mma'")
     if engine == "tc" and any(k % 64 for k in (d.H, d.NH * d.HD, d.MI)):
         engine = "mma"
-    sfx = "_tc" if engine == "tc" else "_nb"
-    gsfx = "_tc" if engine == "tc" else "_g"
     if not d.moe:
         raise ValueError("the batched step is built for the softmax top-k MoE models")
     if d.HD != 128 or d.G not in (1, 2, 4, 8):
@@ -80,11 +80,13 @@ def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineMode
     res = Resource(threads=op_gemv.THREADS, vgpr=128, lds_bytes=0)
     nblk = -(-maxlen // BS)
     kv_layer_bytes = B * nblk * d.NKV * d.HD * BS * 2
+    W = m.workers()
     gq, plen, gparts = d.G, op_attn.GQ_PART, -(-maxlen // op_attn.GQ_PART)      # one task per (128 positions, kv head): K / V read once
-    ntask = gparts * (d.NH // gq)
+    # enough sequences to fill the workers: one task per (sequence, kv head) walks the whole context; else one per partition
+    whole = B * (d.NH // gq) >= W // 2 and op_attn.whole_sequence_fits(gq, gparts)
+    ntask = (d.NH // gq) if whole else gparts * (d.NH // gq)
     op_attn.check_fused(d.NH, d.NKV, d.HD, BS, X, gparts, gq, plen)
     scale = float(np.float32(1.0 / np.sqrt(d.HD)))
-    W = m.workers()
     state = {"prev": None}
 
     def add(name, symbol, blob, grid, n_out, two_d=False, stride=0):
@@ -105,12 +107,28 @@ def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineMode
                                           ln=ln, ids=ptr(ids) if ids else 0, R=R, K=d.H, M=d.H, rpt=1, tpe=1, eps=d.eps, nb=B, sx=d.H, srows=srows,
                                           srin=d.H, srout=d.H), (B,), B)
 
-    def dense(name, Wp, x, out, M, K, bias=0):
-        t, rpt = m.gemv_tasks(M)
-        add(name, "etx_tile_gemv" + sfx, gb("gemv" + sfx, t, W=Wp, x=ptr(x), out=ptr(out), M=M, K=K, rpt=rpt, tpe=1, nb=B, sx=K, sout=M, wts=bias,
-                                         mode=op_gemv.MODE_BIAS if bias else 0), (t,), t)
+    skc = {"n": 0}                                                     # arrival counters handed out so far; grids of one shape share theirs
 
-    cols = argblock.pack_named(ent["cols"], (B, 1, 1), nb=B, slot_span=nblk * BS)
+    def dense(name, Wp, x, out, M, K, bias=0):
+        mode = op_gemv.MODE_BIAS if bias else 0
+        if engine == "tc":
+            # row blocks of 256 (one instruction's worth); narrow matrices are also cut along K to fill the workers
+            t, rpt, S = op_batch.split_k(M, K, W)
+            blocks = t // S
+            if S > 1 and ((M, K, S) not in skc and skc["n"] + blocks > op_batch.SPLITK_COUNTERS or S * B * M > SKP_FLOATS):
+                t, rpt, S = blocks, rpt, 1
+            extra = {}
+            if S > 1:
+                if (M, K, S) not in skc:
+                    skc[(M, K, S)] = skc["n"]
+                    skc["n"] += blocks
+                extra = dict(rows=ptr("skp"), resid_in=ptr("skc") + 4 * skc[(M, K, S)])
+            add(name, "etx_tile_gemv_tc", gb("gemv_tc", t, W=Wp, x=ptr(x), out=ptr(out), M=M, K=K, rpt=rpt, tpe=S, nb=B, sx=K, sout=M, wts=bias, mode=mode, **extra), (t,), t)
+            return
+        t, rpt = m.gemv_tasks(M)
+        add(name, "etx_tile_gemv_nb", gb("gemv_nb", t, W=Wp, x=ptr(x), out=ptr(out), M=M, K=K, rpt=rpt, tpe=1, nb=B, sx=K, sout=M, wts=bias, mode=mode), (t,), t)
+
+    cols = argblock.pack_named(ent["cols"], (B, 1, 1), nb=B, slot_span=nblk * BS, zero=ptr("skc"))
     add("prologue", "vl_prologue_nb", cols, (B,), B)
     for L in range(d.L):
         Wl = lambda n, L=L: ptr(f"{L}.{n}")                                  # noqa: E731
@@ -128,26 +146,36 @@ def build_graph(d: Q.Dims, ptr, B: int, maxlen: int = 1072, machine: MachineMode
                 slot_mapping=ptr("slot_mapping") + 8 * b, exp_sums=ptr("exp_sums") + b * d.NH * gparts * 4, max_logits=ptr("max_logits") + b * d.NH * gparts * 4,
                 tmp_out=ptr("tmp_out") + b * d.NH * gparts * op_attn.GQ_PARTIAL_FLOATS * 4, out=ptr("attn_out") + b * d.NH * d.HD * 2,
                 counters=ptr("attn_counters") + 4 * (L * B + b) * d.NH, scale=scale, eps=d.eps, NH=d.NH, NKV=d.NKV, HD=d.HD, BS=BS, X=X,
-                max_parts=gparts, gq=gq, part_len=op_attn.tagged_part_len(L))
+                max_parts=gparts, gq=gq, part_len=op_attn.tagged_part_len(L, whole))
         add(f"attn_{L}", "etx_tile_attn_fused", blobs, (ntask, B), ntask * B, two_d=True, stride=op_attn.F_ARG_BYTES)
         dense(f"o_proj_{L}", Wl("wo"), "attn_out", "o", d.H, d.NH * d.HD)
         norm(f"norm2_{L}", "o", 1, None, d.H, "resid", "resid2", "o_norm", Wl("ln2"))
         dense(f"router_{L}", Wl("wr"), "o_norm", "rlog", d.E, d.H)
+        rmode = (1 if d.norm_topk else 0) | op_gemv.MODE_BF16_WTS
+        if engine == "tc":
+            # one routing task per column; the expert grids have one task per worker, which takes an equal share of the
+            # active experts' tiles and derives the token lists from the routing ids itself
+            add(f"route_{L}", "etx_tile_route", argblock.pack_named(ent["route"], (B, 1, 1), logits=ptr("rlog"), wts=ptr("tw"), ids=ptr("ti"), ecount=0, elist=0,
+                                                                    active=0, E=d.E, K=d.TOPK, mode=rmode, nb=B, cap=B), (B,), B)
+            add(f"moe_up_{L}", "etx_tile_moe_up_tc", gb("moe_up_tc", W, E=d.E, W=Wl("w13"), x=ptr("o_norm"), out=ptr("mc2"), estride=2 * d.MI * d.H, M=d.MI, K=d.H,
+                                                        rpt=128, tpe=-(-d.MI // 128), ids=ptr("ti"), resid_out=ptr("active") + 4 * L, nb=B, R=d.TOPK, sx=d.H, eps=d.eps), (W,), W)
+            add(f"moe_down_{L}", "etx_tile_moe_down_tc", gb("moe_down_tc", W, E=d.E, W=Wl("w2"), x=ptr("mc2"), out=ptr("mc3"), wts=ptr("tw"), estride=d.H * d.MI,
+                                                            M=d.H, K=d.MI, rpt=256, tpe=-(-d.H // 256), ids=ptr("ti"), nb=B, R=d.TOPK, eps=d.eps), (W,), W)
+            continue
         add(f"route_{L}", "etx_tile_route", argblock.pack_named(ent["route"], (1, 1, 1), logits=ptr("rlog"), wts=ptr("tw"), ids=ptr("ti"), ecount=ptr("ecount"),
-                                                                elist=ptr("elist"), active=ptr("active") + 4 * L, E=d.E, K=d.TOPK, mode=(1 if d.norm_topk else 0) | op_gemv.MODE_BF16_WTS,
-                                                                nb=B, cap=B), (1,), 1)
+                                                                elist=ptr("elist"), active=ptr("active") + 4 * L, E=d.E, K=d.TOPK, mode=rmode, nb=B, cap=B), (1,), 1)
         tpe = -(-d.MI // UP_ROWS)
-        add(f"moe_up_{L}", "etx_tile_moe_up" + gsfx, gb("moe_up" + gsfx, d.E * tpe, E=d.E, W=Wl("w13"), x=ptr("o_norm"), out=ptr("mc2"), estride=2 * d.MI * d.H, M=d.MI, K=d.H,
-                                                  rpt=UP_ROWS, tpe=tpe, rows=ptr("elist"), resid_in=ptr("ecount"), nb=B, R=d.TOPK, sx=d.H, eps=d.eps),
+        add(f"moe_up_{L}", "etx_tile_moe_up_g", gb("moe_up_g", d.E * tpe, E=d.E, W=Wl("w13"), x=ptr("o_norm"), out=ptr("mc2"), estride=2 * d.MI * d.H, M=d.MI, K=d.H,
+                                                   rpt=UP_ROWS, tpe=tpe, rows=ptr("elist"), resid_in=ptr("ecount"), nb=B, R=d.TOPK, sx=d.H, eps=d.eps),
             (d.E * tpe,), d.E * tpe)
         tpe = -(-d.H // DOWN_ROWS)
-        add(f"moe_down_{L}", "etx_tile_moe_down" + gsfx, gb("moe_down" + gsfx, d.E * tpe, E=d.E, W=Wl("w2"), x=ptr("mc2"), out=ptr("mc3"), wts=ptr("tw"), estride=d.H * d.MI,
-                                                      M=d.H, K=d.MI, rpt=DOWN_ROWS, tpe=tpe, rows=ptr("elist"), resid_in=ptr("ecount"), nb=B, R=d.TOPK, eps=d.eps),
+        add(f"moe_down_{L}", "etx_tile_moe_down_g", gb("moe_down_g", d.E * tpe, E=d.E, W=Wl("w2"), x=ptr("mc2"), out=ptr("mc3"), wts=ptr("tw"), estride=d.H * d.MI,
+                                                       M=d.H, K=d.MI, rpt=DOWN_ROWS, tpe=tpe, rows=ptr("elist"), resid_in=ptr("ecount"), nb=B, R=d.TOPK, eps=d.eps),
             (d.E * tpe,), d.E * tpe)
     norm("norm_f", "mc3", d.TOPK, "ti", d.TOPK * d.H, "resid2", "resid", "hn", ptr("final_norm"))
     dense("lm_head", ptr("embed") if d.tie else ptr("lm_head"), "hn", "logits", d.V, d.H)
     add("argmax", "vl_argmax_nb", cols, (B,), B)
-    return g, pool, {"workers": W, "attn": (gq, plen, gparts), "attn_tasks": ntask, "engine": engine}
+    return g, pool, {"workers": W, "attn": (gq, plen, gparts), "attn_tasks": ntask, "attn_whole": whole, "engine": engine}
 
 
 class BatchProgram:

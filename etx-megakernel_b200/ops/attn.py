@@ -34,10 +34,20 @@ F_PARAMS = [("qkv", "ptr addrspace(1)", 0, 8), ("qw", "ptr addrspace(1)", 8, 8),
             # part * (NH / gq) + group, one counter per group; gq = 0: the general form (32 positions x one kv head)
             ("gq", "i32", 152, 4), ("part_len", "i32", 156, 4)]
 GQ_PART = 128
-def tagged_part_len(tag: int) -> int:
+GQ_WHOLE = 1 << 24
+RING_BYTES = 6 * 24576     # shared memory of the weight ring, where the whole-sequence form keeps its partials
+
+
+def tagged_part_len(tag: int, whole: bool = False) -> int:
     """part_len word of a grouped attention block: 128 positions per task, and in bits 16..23 a tag that differs between the
-    grids of a step that share the partial buffers (the layer index): a merger only accepts partials carrying its own."""
-    return GQ_PART | ((tag & 0xff) << 16)
+    grids of a step that share the partial buffers (the layer index): a merger only accepts partials carrying its own.
+    whole: bit 24, the form with one task per (sequence, q group) that walks all partitions itself -- for plans without
+    streamed tiles (the batched step), whose idle weight ring holds the partials."""
+    return GQ_PART | ((tag & 0xff) << 16) | (GQ_WHOLE if whole else 0)
+
+
+def whole_sequence_fits(gq: int, max_parts: int) -> bool:
+    return max_parts * gq * 130 * 4 <= RING_BYTES
 
 
 GQ_PARTIAL_FLOATS = 272   # grouped form: floats of `tmp_out` per (q head, partition) -- 136 (value, flag) pairs: 128 outputs, max, sum, padding
@@ -56,7 +66,7 @@ def check_fused(NH: int, NKV: int, HD: int, BS: int, X: int, max_parts: int, gq:
     check_shape(NH, NKV, HD, BS, X, max_parts)
     G = NH // NKV
     if gq:
-        if gq not in (1, 2, 4, 8) or G % gq or HD != 128 or BS != 16 or (part_len & 0xffff) != GQ_PART or part_len >> 24:
+        if gq not in (1, 2, 4, 8) or G % gq or HD != 128 or BS != 16 or (part_len & 0xffff) != GQ_PART or part_len >> 25:
             raise ValueError(f"attn_fused grouped form: needs gq in (1, 2, 4, 8) dividing G={G}, head_dim 128, block size 16 and "
                              f"part_len {GQ_PART} (gq={gq}, HD={HD}, BS={BS}, part_len={part_len})")
         if gq * max_parts > 4096:

@@ -91,6 +91,28 @@ def test_columns_do_not_depend_on_their_neighbours():
     prog.close()
 
 
+def test_whole_sequence_attention_equals_the_partitioned_form():
+    """20 sequences of a 150-token prompt (two partitions of 128 positions): at B = 20 the attention grid has one task per
+    (sequence, kv head) that walks the partitions itself; at B = 10 it has one task per partition and a merge through
+    flagged partials.  Same partition boundaries and order of sums: tokens and logits are bit-identical."""
+    od = MID
+    W = O.SyntheticWeights(od, seed=35, gamma="ones")
+    prompts = np.random.default_rng(8).integers(0, od.V, (20, 150))
+    whole = program(od, W, 20, 192)
+    assert whole.info["attn_whole"] and whole.info["attn"][2] == 2
+    got = whole.generate(prompts, 6)
+    logits = whole.read("logits")
+    whole.close()
+    for half in range(2):
+        part = program(od, W, 10, 192)
+        assert not part.info["attn_whole"]
+        want = part.generate(prompts[10 * half: 10 * half + 10], 6)
+        plog = part.read("logits")
+        part.close()
+        assert np.array_equal(got[10 * half: 10 * half + 10], want)
+        assert np.array_equal(logits[10 * half: 10 * half + 10], plog)
+
+
 def test_one_batched_step_against_the_oracle_state():
     """One teacher-forced step at a short context, B = 8: routing ids of the last layer exact (a swap of two experts only inside the oracle's own near tie), routing weights
     within 2e-2, final hidden state and logits of every column within 2e-2 of the oracle's."""
@@ -123,21 +145,28 @@ def test_one_batched_step_against_the_oracle_state():
         assert eh <= BF16_REL and el <= BF16_REL, f"column {b}: hidden {eh:.4f}, logits {el:.4f}"
 
 
-def test_an_expert_with_more_tokens_than_one_pass():
+@pytest.mark.parametrize("engine", ["tc", "mma"])
+def test_an_expert_with_more_tokens_than_one_pass(engine):
     """Every column sees the same token, so all B = 12 columns select the same experts: each expert's list holds 12 entries,
-    more than the 8 a tensor-core pass takes.  Tokens equal the single-sequence program's (tie rule aside: compared on
-    logits) and the lists are complete."""
+    more than the 8 tokens of an mma.sync pass and of the tensor-core tile's M = 64 form.  Tokens equal the
+    single-sequence program's (tie rule aside: compared on logits); the routing is the same in every column, the active
+    experts counted per layer and step are the top-k ones, and (mma.sync engine, whose routing tile writes them) the
+    per-expert lists are complete."""
     od, B = SMALL_MOE, 12
     W = O.SyntheticWeights(od, seed=34, gamma="ones")
     prompt = np.random.default_rng(7).integers(0, od.V, 6)
-    prog = program(od, W, B, 64)
+    prog = program(od, W, B, 64, engine)
     got = prog.generate(np.tile(prompt, (B, 1)), 6)
     ecount, elist, ids = prog.read("ecount"), prog.read("elist"), prog.read("ti")
+    active = prog.active_experts()
     blog = prog.read("logits")
     prog.close()
-    assert sorted(np.nonzero(ecount)[0].tolist()) == sorted(ids[0].tolist()) and set(ecount[ecount > 0].tolist()) == {B}
-    for e in np.nonzero(ecount)[0]:
-        assert sorted((int(v) >> 8) for v in elist[e, :B]) == list(range(B))
+    assert all(sorted(ids[b].tolist()) == sorted(ids[0].tolist()) for b in range(B))
+    assert len(set(active.tolist())) == 1 and active[0] == od.TOPK * (len(prompt) + 6 - 1)      # top-k experts per layer and step
+    if engine == "mma":
+        assert sorted(np.nonzero(ecount)[0].tolist()) == sorted(ids[0].tolist()) and set(ecount[ecount > 0].tolist()) == {B}
+        for e in np.nonzero(ecount)[0]:
+            assert sorted((int(v) >> 8) for v in elist[e, :B]) == list(range(B))
     d = qdims(od)
     single = D.DecodeProgram(d, D.to_device_weights(Q.pack_hf(d, W.get, 64), "cuda:0"), device=0, maxlen=64)
     want = single.generate(prompt, 6)

@@ -139,7 +139,8 @@ def test_weight_pack_round_trip():
 
 def test_batched_graph_phases_and_argument_blocks():
     """The batched step (several sequences per launch): phase order, one argument block per sequence for the attention grid
-    (addressed by the grid's second coordinate), expert-grouped grids of E x chunks tasks, a valid plan."""
+    (addressed by the grid's second coordinate), a valid plan; tensor-core engine: one routing task per column, expert grids
+    of one share per worker, narrow dense grids cut along K; mma.sync engine: one routing task, E x chunks expert tasks."""
     from etx_megakernel_b200.models import batched as BT
     from etx_megakernel_b200.ops import attn as op_attn
     from etx_megakernel_b200.sim.protocol import simulate
@@ -152,11 +153,24 @@ def test_batched_graph_phases_and_argument_blocks():
     plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
     assert verify_plan(plan) == [] and not simulate(plan).deadlock
     shape = plan.inst.grid_shapes
-    assert shape["attn_0"] == (info["attn_tasks"], B) and info["attn"] == (8, 128, 9) and shape["norm1_0"] == (B,) and shape["route_0"] == (1,)
-    assert shape["moe_up_0"] == (128 * 3,) and shape["moe_down_0"] == (128 * 4,)
+    assert shape["attn_0"] == (info["attn_tasks"], B) and info["attn"] == (8, 128, 9) and shape["norm1_0"] == (B,) and shape["route_0"] == (B,)
+    assert shape["moe_up_0"] == (148,) and shape["moe_down_0"] == (148,)
+    assert shape["qkv_0"] == (80,) and shape["o_proj_0"] == (64,) and shape["router_0"] == (8,) and shape["lm_head"] == (132,)
     rows = {r[0]: r for r in pool.rows}
-    off = rows["attn_1"][4]
     pb = pool.bytes()
+    q0, q1, o0 = (pb[rows[n][4]: rows[n][4] + 160] for n in ("qkv_0", "qkv_1", "o_proj_0"))
+    assert struct.unpack_from("<2i", q0, 56) == (256, 4) and struct.unpack_from("<2i", o0, 56) == (256, 8)          # rows per task, K-split
+    assert struct.unpack_from("<Q", q0, 72)[0] == struct.unpack_from("<Q", q1, 72)[0] == _fake_ptr("skc")            # layers share a shape's counters
+    assert struct.unpack_from("<Q", o0, 72)[0] == _fake_ptr("skc") + 4 * 20 and struct.unpack_from("<Q", o0, 64)[0] == _fake_ptr("skp")
+    g3, pool3, info3 = BT.build_graph(d, _fake_ptr, 32, 1072)              # enough sequences: one attention task per (sequence, kv head)
+    shape3 = compile_graph(g3, "b200", {"POOL": len(pool3.bytes())}).inst.grid_shapes
+    assert info3["attn_whole"] and not info["attn_whole"] and shape3["attn_0"] == (4, 32)
+    blk3 = pool3.bytes()[{r[0]: r for r in pool3.rows}["attn_1"][4]:][:op_attn.F_ARG_BYTES]
+    assert struct.unpack_from("<i", blk3, 156)[0] == 128 | (1 << 16) | op_attn.GQ_WHOLE
+    g2, pool2, info2 = BT.build_graph(d, _fake_ptr, B, 1072, engine="mma")
+    shape2 = compile_graph(g2, "b200", {"POOL": len(pool2.bytes())}).inst.grid_shapes
+    assert shape2["route_0"] == (1,) and shape2["moe_up_0"] == (128 * 3,) and shape2["moe_down_0"] == (128 * 4,)
+    off = rows["attn_1"][4]
     for b in range(B):                                       # block b of the attention grid: sequence b's q rows and partial buffers
         blk = pb[off + b * op_attn.F_ARG_BYTES: off + (b + 1) * op_attn.F_ARG_BYTES]
         assert struct.unpack_from("<Q", blk, 0)[0] == _fake_ptr("qkv") + b * d.NQKV * 2
