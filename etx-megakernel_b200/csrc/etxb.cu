@@ -115,8 +115,8 @@ static int32_t check_attnf_block(const etxb_attnf_args& a) {
     else if (a.HD != 128 || a.BS != 16 || (a.part_len & 0xffff) != 128) why = "the grouped form is head_dim 128, cache blocks of 16, partitions of 128";
     else if (a.gq * a.max_parts > 4096) why = "gq * max_parts <= 4096";
     else if ((a.part_len >> 24) & ~1) why = "part_len bits 25..31 are zero";
-    else if ((a.part_len >> 24) && (a.nblocks > (uint32_t)(a.NH / a.gq) || (size_t)a.max_parts * a.gq * 130 * 4 > ETXB_RING_BYTES))
-      why = "whole-sequence form: the grid is NH / gq tasks and max_parts * gq * 130 floats fit the idle weight ring";
+    else if ((a.part_len >> 24) && (a.nblocks > (uint32_t)(a.NH / a.gq) || 65536 + (size_t)a.max_parts * a.gq * 130 * 4 > ETXB_RING_BYTES))
+      why = "whole-sequence form: the grid is NH / gq tasks and 64 KB + max_parts * gq * 130 floats fit the idle weight ring";
     else if (a.nblocks > (uint32_t)(a.max_parts * (a.NH / a.gq))) why = "the grid is at most max_parts * NH / gq tasks";
   } else {
     const int G = a.NH / a.NKV;

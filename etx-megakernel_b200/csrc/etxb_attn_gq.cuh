@@ -18,6 +18,7 @@
 namespace etxb {
 
 #define ETXB_GQ_PART 128   // positions per task
+#define ETXB_GQ_STAGE_BYTES 65536  // whole-sequence form: a partition's K and V pieces in shared memory (512 threads x 4 x 16 bytes each)
 #define ETXB_GQ_WHOLE (1 << 24)   // part_len bit: one task per (sequence, q group) walks all partitions (plans without streamed tiles)
 #define ETXB_GQ_PW 136     // 8-byte (value, flag) pairs a task publishes per q head and partition: 128 outputs, max, sum, padding
 
@@ -368,10 +369,10 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
 // arithmetic (same partition boundaries, same order of sums: the results are those of the one-partition-per-task form bit
 // for bit).  This is the form of a batched step with enough sequences to fill the workers (sequences x kv heads x groups
 // tasks): the q rows are prepared once per sequence instead of once per partition, the next partition's K (then V) is
-// requested as soon as the registers of the current one are free, so the cache latency hides behind the softmax and
-// the output sums, and nothing is published, polled or merged through global memory.
+// copied asynchronously into shared memory while the current one is being worked on, so the cache latency hides behind
+// the softmax and the output sums, and nothing is published, polled or merged through global memory.
 // The partials live in the weight ring, which is idle in a batched plan (no streamed tiles): part_len bit 24 selects
-// this form, and only builders of plans without streamed tiles may set it.  (np * GQ * 130 floats <= the ring.)
+// this form, and only builders of plans without streamed tiles may set it.  (64 KB of K / V pieces + np * GQ * 130 floats <= the ring.)
 template <int GQ>
 __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, const Smem& sm, const etxb_stepv& S) {
   constexpr int HD = 128, BS = 16, X = 8, PL = ETXB_GQ_PART, HV = HD / 8;
@@ -381,45 +382,59 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
   const long long pos = (const void*)d.positions == (const void*)S.positions ? (long long)S.pos : __ldcg((const long long*)d.positions);
   const long long slot = (const void*)d.slot_mapping == (const void*)S.slot_mapping ? (long long)S.pos : __ldcg((const long long*)d.slot_mapping);
   const int seq = (const void*)d.seq_lens == (const void*)S.seq_lens ? S.pos + 1 : __ldcg(d.seq_lens);
-  const int np = min(min((seq + PL - 1) / PL, d.max_parts), ETXB_RING_BYTES / (GQ * (HD + 2) * 4));
+  const int np = min(min((seq + PL - 1) / PL, d.max_parts), (ETXB_RING_BYTES - ETXB_GQ_STAGE_BYTES) / (GQ * (HD + 2) * 4));
   if (np < 1) return;
   const int tid = tidx(), lane = tid & 31, warp = tid >> 5;
   const GqSmem<GQ> s(sm.xs);
-  float* PO = (float*)sm.ring;                                     // [np][GQ][HD] partial outputs
+  // the weight ring: [4][512] 16-byte K pieces, [4][512] V pieces (piece j of thread tid at [j][tid]: every thread copies
+  // and reads only its own), then the partitions' partial outputs and statistics
+  uint4* KB = (uint4*)sm.ring;
+  uint4* VB = KB + 4 * ETXB_CONSUMERS;
+  float* PO = (float*)(sm.ring + ETXB_GQ_STAGE_BYTES);            // [np][GQ][HD] partial outputs
   float* PS = PO + (size_t)np * GQ * HD;                           // [np][GQ][2] max logit, exp sum
   const int t = tid & (PL - 1), qr = tid >> 7;                     // K: position t, dims [32 qr, 32 qr + 32);  V: dim t, blocks 2 qr, 2 qr + 1
-  uint4 kreg[4], vreg[4];
-  // cache blocks of a partition for this thread: [0] the block of its K position, [1], [2] the blocks of its V positions
-  // (requested a phase before the rows themselves, so that the row loads do not wait for the table)
-  int pbn[3];
-  auto load_tab = [&](int part) {
+  // Asynchronous copies (cp.async, 16 bytes each, zero-filled where the context ends) bring a partition's K and V pieces
+  // from the cache to shared memory while the previous partition is being worked on: K of the next partition as soon as
+  // the scores have consumed this one's, V of the next as soon as the output sums have.  One commit group per request, in
+  // that order, so "all but the latest group" is always the piece about to be read.  Nothing waits in registers: a
+  // 17-warp CTA has 96 of them per thread, and a partition of K and V ahead would take 32.
+  // (the block-table entries a request needs are fetched a phase earlier: tab[0] the block of the thread's K position,
+  // tab[1], tab[2] the blocks of its V positions, of the partition that is requested next)
+  int tab[3];
+  auto fetch_tab = [&](int part) {
     const int lb = part * (PL / BS) + (t >> 4), lv = part * (PL / BS) + 2 * qr;
-    pbn[0] = lb * BS < seq ? __ldg(d.block_tables + lb) : 0;
-    pbn[1] = lv * BS < seq ? __ldg(d.block_tables + lv) : 0;
-    pbn[2] = (lv + 1) * BS < seq ? __ldg(d.block_tables + lv + 1) : 0;
+    tab[0] = part < np && lb * BS < seq ? __ldg(d.block_tables + lb) : 0;
+    tab[1] = part < np && lv * BS < seq ? __ldg(d.block_tables + lv) : 0;
+    tab[2] = part < np && (lv + 1) * BS < seq ? __ldg(d.block_tables + lv + 1) : 0;
   };
-  auto load_k = [&](int part) {
-    const int lb = part * (PL / BS) + (t >> 4);
-    const bool live = lb * BS < seq;
-    const long long pb = pbn[0];
-    const __nv_bfloat16* kp = (const __nv_bfloat16*)d.kc + ((((size_t)pb * NKV + h) * HV + qr * 4) * BS + (t & 15)) * X;
+  auto request_k = [&](int part) {
+    if (part < np) {
+      const int lb = part * (PL / BS) + (t >> 4);
+      const bool live = lb * BS < seq;
+      const long long pb = tab[0];
+      const __nv_bfloat16* kp = (const __nv_bfloat16*)d.kc + ((((size_t)pb * NKV + h) * HV + qr * 4) * BS + (t & 15)) * X;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) kreg[j] = live ? ld_act16(kp + (size_t)j * BS * X) : make_uint4(0u, 0u, 0u, 0u);
-  };
-  auto load_v = [&](int part) {
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int lv = part * (PL / BS) + 2 * qr + u;
-      const bool lv_live = lv * BS < seq;
-      const long long pv = pbn[1 + u];
-      const __nv_bfloat16* vp = (const __nv_bfloat16*)d.vc + (((size_t)pv * NKV + h) * HD + t) * BS;
-      vreg[2 * u] = lv_live ? ld_act16(vp) : make_uint4(0u, 0u, 0u, 0u);
-      vreg[2 * u + 1] = lv_live ? ld_act16(vp + 8) : make_uint4(0u, 0u, 0u, 0u);
+      for (int j = 0; j < 4; ++j) cp_async16(KB + j * ETXB_CONSUMERS + tid, kp + (size_t)j * BS * X, live);
     }
+    cp_async_commit();
   };
-  load_tab(0);
-  load_k(0);
-  load_v(0);
+  auto request_v = [&](int part) {
+    if (part < np) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int lv = part * (PL / BS) + 2 * qr + u;
+        const bool live = lv * BS < seq;
+        const long long pv = tab[1 + u];
+        const __nv_bfloat16* vp = (const __nv_bfloat16*)d.vc + (((size_t)pv * NKV + h) * HD + t) * BS;
+        cp_async16(VB + (2 * u) * ETXB_CONSUMERS + tid, vp, live);
+        cp_async16(VB + (2 * u + 1) * ETXB_CONSUMERS + tid, vp + 8, live);
+      }
+    }
+    cp_async_commit();
+  };
+  fetch_tab(0);
+  request_k(0);
+  request_v(0);
   // ---- this step's rows: raw q heads, new k and v rows; rotary row and norm weights
   {
     const __nv_bfloat16* qkv = (const __nv_bfloat16*)d.qkv;
@@ -473,8 +488,9 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
     const int tpos = owner ? (int)(pos - t0) : -1;
     const int ntok = min(PL, seq - t0);
     auto cached = [&](int tt) { return tt < ntok && tt != tpos; };
-    if (part + 1 < np) load_tab(part + 1);
+    fetch_tab(part + 1);
     // ---- scores
+    cp_async_wait1();                                              // this partition's K pieces have landed (its V may still travel)
     {
       float acc[GQ];
 #pragma unroll
@@ -482,7 +498,7 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float kf[8];
-        unpack8(kreg[j], kf);
+        unpack8(KB[j * ETXB_CONSUMERS + tid], kf);
 #pragma unroll
         for (int g = 0; g < GQ; ++g) {
           const float4 qa = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8), qb = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8 + 4);
@@ -495,7 +511,7 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
 #pragma unroll
       for (int g = 0; g < GQ; ++g) s.ph[(qr * GQ + g) * PL + t] = acc[g];
     }
-    if (part + 1 < np) load_k(part + 1);                           // the K registers are free: the next partition's rows travel during the softmax
+    request_k(part + 1);                                           // (this thread's own K pieces are consumed: no barrier needed before overwriting them)
     csync();
     // ---- softmax statistics: one warp per q head, lane holds positions lane + 32 k
     if (warp < GQ) {
@@ -529,6 +545,7 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
     }
     csync();
     // ---- output
+    cp_async_wait1();                                              // this partition's V pieces have landed (the next K may still travel)
     {
       float acc[GQ];
 #pragma unroll
@@ -538,9 +555,11 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
         const int tb = (2 * qr + u) * BS;
         if (tb < ntok) {
           float f[16];
-          unpack8(vreg[2 * u], f); unpack8(vreg[2 * u + 1], f + 8);
+          unpack8(VB[(2 * u) * ETXB_CONSUMERS + tid], f); unpack8(VB[(2 * u + 1) * ETXB_CONSUMERS + tid], f + 8);
+          if (part == np - 1) {                                    // (only the last partition has slots that are not cached yet)
 #pragma unroll
-          for (int o = 0; o < 16; ++o) f[o] = cached(tb + o) ? f[o] : 0.f;
+            for (int o = 0; o < 16; ++o) f[o] = cached(tb + o) ? f[o] : 0.f;
+          }
 #pragma unroll
           for (int g = 0; g < GQ; ++g) {
 #pragma unroll
@@ -555,7 +574,7 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
 #pragma unroll
       for (int g = 0; g < GQ; ++g) s.po[(qr * GQ + g) * HD + t] = acc[g];
     }
-    if (part + 1 < np) load_v(part + 1);
+    request_v(part + 1);
     csync();
     for (int idx = tid; idx < GQ * HD; idx += ETXB_CONSUMERS) {
       const int g = idx >> 7, dd = idx & (HD - 1);
@@ -594,6 +613,7 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
     ((__nv_bfloat16*)d.out)[(size_t)(hq0 + g) * HD + dd] = __float2bfloat16_rn(__fdiv_rn(o, red[g]));
   }
   mark(sm, 3);
+  cp_async_wait0();
   csync();                                                         // the next task may overwrite the partials
 }
 

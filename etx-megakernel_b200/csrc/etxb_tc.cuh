@@ -289,31 +289,49 @@ __device__ __forceinline__ void tile_gemv_tc(const unsigned char* a, int blk, co
   if (*last == 0) return;
   const float* p0 = (const float*)d.rows;
   const size_t sstride = (size_t)d.nb * d.M;
-  // Sums with the column index fastest (the partials are [row][column]: coalesced reads), four outputs per thread and round
-  // with all their slices requested before the first is added; every output is the sum of its slices in slice order.
+  // Sums with the column index fastest (the partials are [row][column]: coalesced reads), eight loads of four columns in
+  // flight per thread (the partials come from L2, a microsecond away); every output is the sum of its slices in slice order.
   // The sums go through shared memory ([row][nb + 1] floats in the area the tile's tokens and stages have left) so that
   // the bf16 results leave with the row index fastest: rows of `out` are contiguous, columns are sout apart.
   const int nr = r1 - r0, nout = d.nb * nr, ld = d.nb + 1;
   float* tile = (float*)(((uintptr_t)sm.ring + 1023) & ~(uintptr_t)1023);
-  for (int i0 = tidx(); i0 < nout; i0 += 4 * ETXB_CONSUMERS) {
-    float t[4][8];
+  if ((d.nb & 3) == 0 && (((uintptr_t)p0) & 15) == 0) {
+    // four columns per 16-byte load; two such groups x four slices in flight per thread and round
+    const int gpr = d.nb >> 2, ngrp = nr * gpr;
+    for (int g0 = tidx(); g0 < ngrp; g0 += 2 * ETXB_CONSUMERS) {
+      float4 acc[2];
+      acc[0] = acc[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q0 = 0; q0 < S; q0 += 4) {
+        float4 t[2][4];
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const int i = min(i0 + w * ETXB_CONSUMERS, nout - 1);
-      const int r = r0 + i / d.nb, tok = i - (i / d.nb) * d.nb;
-      const float* src = p0 + (size_t)r * d.nb + tok;
+        for (int w = 0; w < 2; ++w) {
+          const int gi = min(g0 + w * ETXB_CONSUMERS, ngrp - 1);
+          const float4* src = (const float4*)(p0 + (size_t)(r0 + gi / gpr) * d.nb) + (gi - (gi / gpr) * gpr);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) t[w][u] = u < S ? __ldcg(src + (size_t)u * sstride) : 0.f;
+          for (int u = 0; u < 4; ++u) t[w][u] = q0 + u < S ? __ldcg((const float4*)((const float*)src + (size_t)(q0 + u) * sstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int w = 0; w < 2; ++w)
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (q0 + u < S) {
+              acc[w].x = __fadd_rn(acc[w].x, t[w][u].x); acc[w].y = __fadd_rn(acc[w].y, t[w][u].y);
+              acc[w].z = __fadd_rn(acc[w].z, t[w][u].z); acc[w].w = __fadd_rn(acc[w].w, t[w][u].w);
+            }
+      }
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const int gi = g0 + w * ETXB_CONSUMERS;
+        if (gi >= ngrp) break;
+        float* dst = tile + (gi / gpr) * ld + 4 * (gi - (gi / gpr) * gpr);
+        dst[0] = acc[w].x; dst[1] = acc[w].y; dst[2] = acc[w].z; dst[3] = acc[w].w;
+      }
     }
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const int i = i0 + w * ETXB_CONSUMERS;
-      if (i >= nout) break;
+  } else {
+    for (int i = tidx(); i < nout; i += ETXB_CONSUMERS) {
       const int rl = i / d.nb, tok = i - rl * d.nb;
       float v = 0.f;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) if (u < S) v = __fadd_rn(v, t[w][u]);
-      for (int q = 8; q < S; ++q) v = __fadd_rn(v, __ldcg(p0 + (size_t)q * sstride + (size_t)(r0 + rl) * d.nb + tok));   // (a split beyond 8: the rest one by one)
+      for (int q = 0; q < S; ++q) v = __fadd_rn(v, __ldcg(p0 + (size_t)q * sstride + (size_t)(r0 + rl) * d.nb + tok));
       tile[rl * ld + tok] = v;
     }
   }

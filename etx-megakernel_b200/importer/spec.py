@@ -203,7 +203,7 @@ def validate_values(export, values, grid):
         _attn.check_fused(*values[17:25])
         whole = bool(values[23]) and bool(values[24] & _attn.GQ_WHOLE)
         if whole and not _attn.whole_sequence_fits(values[23], values[22]):
-            raise ValueError(f"{spec.name}: whole-sequence form: max_parts * gq * 130 floats must fit the weight ring")
+            raise ValueError(f"{spec.name}: whole-sequence form: 64 KB + max_parts * gq * 130 floats must fit the weight ring")
         want = (1 if whole else values[22]) * (values[17] // values[23] if values[23] else values[18])
         if gx * gy * gz != want:
             raise ValueError(f"{spec.name}: grid must be max_parts * NKV tasks (grouped form: max_parts * NH / gq; whole-sequence form: NH / gq)")

@@ -47,7 +47,7 @@ def tagged_part_len(tag: int, whole: bool = False) -> int:
 
 
 def whole_sequence_fits(gq: int, max_parts: int) -> bool:
-    return max_parts * gq * 130 * 4 <= RING_BYTES
+    return 65536 + max_parts * gq * 130 * 4 <= RING_BYTES      # a partition of K / V pieces + the partials
 
 
 GQ_PARTIAL_FLOATS = 272   # grouped form: floats of `tmp_out` per (q head, partition) -- 136 (value, flag) pairs: 128 outputs, max, sum, padding
