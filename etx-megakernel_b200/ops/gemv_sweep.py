@@ -3,7 +3,9 @@
 Shapes: M in {1, 2, 4, 8}, K = 4096, N = 12288; M = 1, K = 12288, N = 4096; M = 1, K = 4096, N = 151936 (lm_head).
 Weights ~ N(0, 0.02), activations ~ N(0, 1), fp32 accumulation, seed 1.  M = 1 runs as a one-grid graph through the
 persistent kernel (plan -> session -> launches, the path a decode program takes); M > 1 runs the column-batched kernel
-through `etxb_op_launch`.  Between timed launches a buffer larger than L2 is written, so every launch streams its
+through `etxb_op_launch`; the rows marked "tc" (M = 8, 32) run the tcgen05 tile of the batched decode step as a one-grid
+graph through the persistent kernel (TMA tensor copies, accumulators in tensor memory, K cut in slices where the matrix
+has too few 256-row blocks for the workers).  Between timed launches a buffer larger than L2 is written, so every launch streams its
 weights from HBM.  Algorithmic bytes per launch: 2 N K + 2 M K + 2 M N.
 
     python -m etx_megakernel_b200.ops.gemv_sweep            # prints one line per shape
@@ -14,7 +16,8 @@ import json
 
 import numpy as np
 
-SHAPES = [(1, 4096, 12288), (2, 4096, 12288), (4, 4096, 12288), (8, 4096, 12288), (1, 12288, 4096), (1, 4096, 151936)]
+SHAPES = [(1, 4096, 12288), (2, 4096, 12288), (4, 4096, 12288), (8, 4096, 12288), (1, 12288, 4096), (1, 4096, 151936),
+          (8, 4096, 12288, "tc"), (32, 4096, 12288, "tc"), (32, 2048, 151936, "tc")]
 
 
 def run(shapes=SHAPES, iters: int = 12, device: int = 0, peak_gbs: float | None = None) -> list:
@@ -34,7 +37,9 @@ def run(shapes=SHAPES, iters: int = 12, device: int = 0, peak_gbs: float | None 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.Stream(dev)                                # launches and the timing events share this stream
     out_rows = []
-    for M, K, N in shapes:
+    for shape in shapes:
+        M, K, N = shape[:3]
+        tc = len(shape) > 3 and shape[3] == "tc"
         W = torch.empty((N, K), dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g0)
         x = torch.randn((M, K), device=dev, generator=g0).bfloat16()
         out = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
@@ -42,7 +47,23 @@ def run(shapes=SHAPES, iters: int = 12, device: int = 0, peak_gbs: float | None 
         blob = argblock.pack_named(ent["dsl_gemv"], (tasks, 1, 1), W=W.data_ptr(), x=x.data_ptr(), out=out.data_ptr(), M=N, K=K, rpt=rpt,
                                    tpe=1, nb=M, sx=K, sout=N)
         session = None
-        if M == 1:
+        if tc:
+            from . import batch as _batch
+            tasks, rpt, S = _batch.split_k(N, K, m.workers())
+            part = torch.zeros((S * N * M,), dtype=torch.float32, device=dev)
+            count = torch.zeros((tasks // S,), dtype=torch.int32, device=dev)
+            blob = argblock.pack_named(ent["gemv_tc"], (tasks, 1, 1), W=W.data_ptr(), x=x.data_ptr(), out=out.data_ptr(), M=N, K=K, rpt=rpt, tpe=S, nb=M,
+                                       sx=K, sout=N, rows=part.data_ptr() if S > 1 else 0, resid_in=count.data_ptr() if S > 1 else 0)
+            g = Graph(f"gemv_tc_{M}x{K}x{N}")
+            g.tensor("impargs", (len(blob),), role="weight", bytes_per_elem=1)
+            g.etensor("E_done", (1,), wait_count=tasks)
+            g.call_device("gemv", (tasks,), cuda_link("", "etx_tile_gemv_tc", stream_after=""), args=["impargs"], consts=(0,),
+                          out_edges={"E_done": "i->(0)"})
+            session = Session(compile_graph(g, m, {}), {}, blob, device)
+
+            def launch():
+                session.launch(stream.cuda_stream)
+        elif M == 1:
             g = Graph(f"gemv_{K}x{N}")
             g.tensor("impargs", (len(blob),), role="weight", bytes_per_elem=1)
             g.etensor("E_done", (1,), wait_count=tasks)
@@ -71,7 +92,7 @@ def run(shapes=SHAPES, iters: int = 12, device: int = 0, peak_gbs: float | None 
         want = (x.float() @ W.float().t())
         err = float((out.float() - want).abs().max() / want.abs().max())
         nbytes = 2 * N * K + 2 * M * K + 2 * M * N
-        row = {"M": M, "K": K, "N": N, "tasks": tasks, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "bytes": nbytes,
+        row = {"M": M, "K": K, "N": N, "engine": "tcgen05" if tc else ("fma ring" if M == 1 else "mma.sync"), "tasks": tasks, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "bytes": nbytes,
                "max_rel_err_vs_fp32": err}
         if peak_gbs:
             row["of_peak"] = round(row["gbs"] / peak_gbs, 3)

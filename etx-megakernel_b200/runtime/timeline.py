@@ -154,6 +154,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--maxlen", type=int, default=1072)
     ap.add_argument("--warm", type=int, default=64, help="untraced steps before the traced one")
+    ap.add_argument("--batch", type=int, default=1, help="sequences per step (> 1: the batched step of models.batched)")
     ap.add_argument("--sim", action="store_true", help="simulate the schedule from the tile annotations instead of running on a GPU")
     ap.add_argument("--raw", help="also write the nine-int64-per-task rows to this file")
     a = ap.parse_args(argv)
@@ -174,6 +175,19 @@ def main(argv=None) -> int:
         dev = torch.device("cuda", local)
         torch.cuda.set_device(dev)
         w = D.random_packed_weights(d, a.maxlen, dev, seed=0)
+        if a.batch > 1:
+            from ..models import batched as BT
+            prog = BT.BatchProgram(d, w, a.batch, device=local, maxlen=a.maxlen)
+            prog.buf["kc"].normal_(0, 0.02); prog.buf["vc"].normal_(0, 0.02)
+            prog.buf["token_in"].random_(0, 1000)
+            torch.cuda.synchronize(dev)
+            for t in range(min(a.warm, 8)):
+                prog.step(0, a.context + t, False)
+            prog.session.set_option("trace", 1)
+            prog.step(1, a.context + 9, False)
+            print(Timeline.from_trace(prog.plan, prog.session.trace()).text())
+            prog.close()
+            return 0
         if world > 1:
             # under torchrun: ONE request sharded over the ranks (the timeline of rank 0 is printed)
             import torch.distributed as dist
