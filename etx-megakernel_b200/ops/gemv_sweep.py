@@ -43,10 +43,11 @@ def run(shapes=SHAPES, iters: int = 12, device: int = 0, peak_gbs: float | None 
         W = torch.empty((N, K), dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g0)
         x = torch.randn((M, K), device=dev, generator=g0).bfloat16()
         out = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
-        tasks, rpt = m.gemv_tasks(N, waves=4 if N > 65536 else 1)
-        blob = argblock.pack_named(ent["dsl_gemv"], (tasks, 1, 1), W=W.data_ptr(), x=x.data_ptr(), out=out.data_ptr(), M=N, K=K, rpt=rpt,
-                                   tpe=1, nb=M, sx=K, sout=N)
         session = None
+        if not tc:
+            tasks, rpt = m.gemv_tasks(N, waves=4 if N > 65536 else 1)
+            blob = argblock.pack_named(ent["dsl_gemv"], (tasks, 1, 1), W=W.data_ptr(), x=x.data_ptr(), out=out.data_ptr(), M=N, K=K, rpt=rpt,
+                                       tpe=1, nb=M, sx=K, sout=N)
         if tc:
             from . import batch as _batch
             tasks, rpt, S = _batch.split_k(N, K, m.workers())
