@@ -27,6 +27,7 @@ static_assert(ETXB_SMEM_BYTES + 256 <= 232448, "dynamic + static shared memory m
 static_assert(sizeof(etxb_task) == 40 && sizeof(etxb_type) == 48, "plan table layouts");
 static_assert(sizeof(etxb_stepv) == sizeof(etxb_step_params), "step parameter layouts must agree");
 static_assert(sizeof(etxb::etxb_route_args) == 88 && offsetof(etxb::etxb_route_args, grid) == 72, "route block layout");
+static_assert(sizeof(etxb::etxb_mla_args) == 112 && offsetof(etxb::etxb_mla_args, grid) == 96 && offsetof(etxb::etxb_mla_args, scale) == 80, "mla block layout");
 static_assert(sizeof(etxb::etxb_batch_args) == 32 && offsetof(etxb::etxb_batch_args, grid) == 16, "column block layout");
 static_assert(ETXB_NBR_OFF + 2 * ETXB_NB_ROWS * ETXB_NBC * 4 <= ETXB_GEN_BYTES && ETXB_NBP_OFF + ETXB_NBP_UNITS * 512 <= ETXB_NBR_OFF, "batched tiles fit the general region");
 
@@ -97,6 +98,7 @@ static int32_t check_gemv_block(int body, const etxb_gemv_args& a) {
   else if (fold > 3) why = "mode & 0xff is 0 (plain), 1 (norm fold), 2 or 3 (top-k fold)";
   else if (fold >= 2 && (a.E < 1 || a.E > 256 || a.R < 1 || a.R > 16 || a.R > a.E || a.logits == nullptr)) why = "a top-k fold needs logits, 1 <= E <= 256 and 1 <= R <= min(16, E)";
   else if (body == ETXB_BODY_GEMV && (a.mode & (ETXB_MODE_SUM_SLOTS | 0xff0000))) why = "slot bits are for the MoE forms only";
+  else if (fold >= 2 && ((a.mode >> 24) & 0xf) >= a.R) why = "the always-on experts (mode bits 24..27) leave at least one routed slot";
   else if (body == ETXB_BODY_MOE_UP && 2 * spt * a.rpt > ETXB_G_FLOATS) why = "gate + up results of a task: 2 * slots * rpt <= 2048";
   else if (body == ETXB_BODY_MOE_DOWN && ((long long)spt * a.K > ETXB_XB_ELEMS || spt * a.rpt > ETXB_G_FLOATS)) why = "down: slots * K <= 12288 activations and slots * rpt <= 2048 results per task";
   else if (body != ETXB_BODY_GEMV && spt > 16) why = "at most 16 expert slots per task";
@@ -171,9 +173,26 @@ static int32_t check_batch_block(int body, const unsigned char* blk, size_t byte
   return fail(ETXB_E_UNSUPPORTED, m);
 }
 
+static int32_t check_mla_block(const unsigned char* blk, size_t bytes) {
+  if (bytes < sizeof(etxb::etxb_mla_args)) return fail(ETXB_E_ARG, "mla_attn tile: the argument block is 112 bytes");
+  etxb::etxb_mla_args a;
+  memcpy(&a, blk, sizeof a);
+  const char* why = nullptr;
+  if (a.NH < 1 || a.C < 2 || a.C > 512 || (a.C & 1) || a.DR < 2 || a.DR > 64 || (a.DR & 1) || a.DN < 1 || a.DN + a.DR > 256 || a.C + a.DR > 640 || a.DV < 1)
+    why = "C <= 512 (even), DR <= 64 (even), DN + DR <= 256";
+  else if (a.maxlen < 1 || a.maxlen > ETXB_MLA_MAXCTX) why = "1 <= maxlen <= 8192";
+  else if (!a.qkv || !a.kvln || !a.cos_sin || !a.wkvb || !a.cache || !a.positions || !a.out) why = "null pointer";
+  else if (a.nblocks > (uint32_t)a.NH) why = "the grid is one task per head";
+  if (!why) return ETXB_OK;
+  char m[256];
+  snprintf(m, sizeof m, "mla_attn block (NH=%d, C=%d, DN=%d, DR=%d, DV=%d, maxlen=%d) outside the tile: %s", a.NH, a.C, a.DN, a.DR, a.DV, a.maxlen, why);
+  return fail(ETXB_E_UNSUPPORTED, m);
+}
+
 // A block of `body` at `blk` (`bytes` readable).  Tiles whose blocks carry no loop bound the device depends on pass.
 static int32_t check_block(int body, const unsigned char* blk, size_t bytes) {
   if (body >= ETXB_BODY_NORM_COL && body <= ETXB_BODY_MOE_DOWN_TC) return check_batch_block(body, blk, bytes);
+  if (body == ETXB_BODY_MLA_ATTN) return check_mla_block(blk, bytes);
   if (body == ETXB_BODY_GEMV || body == ETXB_BODY_MOE_UP || body == ETXB_BODY_MOE_DOWN) {
     if (bytes < sizeof(etxb_gemv_args)) return fail(ETXB_E_ARG, "GEMV-family tile: the argument block is 160 bytes");
     etxb_gemv_args a;

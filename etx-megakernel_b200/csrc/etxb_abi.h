@@ -165,6 +165,8 @@ struct etxb_gemv_args {
                                       // ids / wts, so the consumer warps read it there (one load) instead of redoing the top-k;
                                       // the producer warp, which runs ahead of the gate/up phase, still derives it from the logits
 // bits 16..23 of mode: expert slots per task of the MoE forms (0 = 1)
+// bits 24..27 of mode (top-k fold): ns always-on experts stored after the E routed ones (DeepSeek's shared experts as
+// experts E .. E + ns - 1): the fold picks R - ns experts from the logits and gives the last ns slots weight 1
 
 // top-k: the reference's 64-byte block (etx/ops/topk.py:16-23), grid words at 48.
 struct etxb_topk_args {

@@ -191,7 +191,14 @@ template <bool LEAN>
 __device__ __forceinline__ void gemv_routing(const etxb_gemv_args& d, int32_t* lids, float* lwts) {
   const int fold = d.mode & 0xff, lane = tidx() & 31;
   if (fold >= 2) {
-    warp_topk<LEAN>(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
+    // mode bits 24..27: experts that every token uses (shared experts), stored after the E routed ones: they take the
+    // last slots with weight 1, the top-k picks the others
+    const int ns = (d.mode >> 24) & 0xf;
+    warp_topk<LEAN>(d.logits, d.E, d.R - ns, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
+    if (ns > 0) {
+      if (lane < ns) { lids[d.R - ns + lane] = d.E + lane; lwts[d.R - ns + lane] = 1.f; }
+      __syncwarp();
+    }
   } else {
     if (lane < 16) {
       lids[lane] = (d.ids && lane < d.R) ? __ldcg(d.ids + lane) : 0;
@@ -205,7 +212,7 @@ __device__ __forceinline__ const unsigned char* gemv_range_base(int body, const 
   if (body == 3) return (const unsigned char*)d.W + (size_t)t.r0 * t.row_bytes;
   const int slot = t.group * t.spt + (body == 4 ? i >> 1 : i);
   int e = lids[slot];
-  if (d.E > 0 && (unsigned)e >= (unsigned)d.E) e = 0;                // "no candidate" (a NaN row): never an address
+  if (d.E > 0 && (unsigned)e >= (unsigned)(d.E + ((d.mode >> 24) & 0xf))) e = 0;   // "no candidate" (a NaN row): never an address
   const unsigned char* We = (const unsigned char*)d.W + (size_t)e * d.estride * 2;
   const int row = t.r0 + ((body == 4 && (i & 1)) ? d.M : 0);        // up rows follow the M gate rows
   return We + (size_t)row * t.row_bytes;

@@ -8,6 +8,7 @@
 #include "etxb_attn_gq.cuh"
 #include "etxb_batch.cuh"
 #include "etxb_tc.cuh"
+#include "etxb_mla.cuh"
 #include "etxb_gemv.cuh"
 #include "etxb_prims.cuh"
 
@@ -205,6 +206,7 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
     case 20: if constexpr (!LEAN && !XCH) { tile_gemv_tc(args, c0, sm, *sm.tc, cur); break; }
     case 21: if constexpr (!LEAN && !XCH) { tile_moe_up_tc(args, c0, sm, *sm.tc, cur); break; }
     case 22: if constexpr (!LEAN && !XCH) { tile_moe_down_tc(args, c0, sm, *sm.tc, cur); break; }
+    case 23: if constexpr (!LEAN) { tile_mla_attn(args, c0, sm, p.step); break; }
     case 19: if constexpr (!LEAN) { if (c0 < ((const etxb_batch_args*)args)->nb) tile_argmax<false>(p, sm, c0, ((const etxb_batch_args*)args)->nb); break; }
     default:
       if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);

@@ -34,6 +34,14 @@ MODE_NORM, MODE_TOPK, MODE_TOPK_RENORM, MODE_BF16_WTS, MODE_BIAS, MODE_SUM_SLOTS
 MODE_FLAGGED = 0x1000      # sharded model: `rows` is a [ranks][M or K] block of flagged words (see build_graph(ranks=...))
 
 
+def mode_shared(ns: int) -> int:
+    """Always-on experts of a top-k fold, carried in mode bits 24..27: ns experts stored after the E routed ones take the last
+    ns of the R slots with weight 1 (DeepSeek's shared experts); the fold picks the other R - ns from the logits."""
+    if not 0 <= ns <= 15:
+        raise ValueError("0 <= shared experts <= 15")
+    return ns << 24
+
+
 def mode_spt(spt: int) -> int:
     """Expert slots per task of the MoE forms, carried in mode bits 16..23 (0 and 1 both mean one slot per task)."""
     return (spt & 0xff) << 16

@@ -37,6 +37,7 @@ TILE_SYMBOLS = {
     "etx_tile_partial_sum": 10, "etx_tile_final_sum": 11,
     "etx_tile_norm_col": 13, "etx_tile_gemv_nb": 14, "etx_tile_route": 15, "etx_tile_moe_up_g": 16, "etx_tile_moe_down_g": 17,
     "vl_prologue_nb": 18, "vl_argmax_nb": 19, "etx_tile_gemv_tc": 20, "etx_tile_moe_up_tc": 21, "etx_tile_moe_down_tc": 22,
+    "etx_tile_mla_attn": 23,
 }
 
 

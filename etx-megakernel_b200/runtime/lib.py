@@ -15,14 +15,14 @@ PKG = Path(__file__).resolve().parents[1]
 CSRC = PKG / "csrc"
 LIB_PATH = PKG / "libetxb200.so"
 SOURCES = ["etxb.cu"]
-HEADERS = ["etxb_abi.h", "etxb_prims.cuh", "etxb_gemv.cuh", "etxb_gemv_nb.cuh", "etxb_attn.cuh", "etxb_attn_fused.cuh", "etxb_attn_gq.cuh", "etxb_batch.cuh", "etxb_tc.cuh", "etxb_kernel.cuh"]
+HEADERS = ["etxb_abi.h", "etxb_prims.cuh", "etxb_gemv.cuh", "etxb_gemv_nb.cuh", "etxb_attn.cuh", "etxb_attn_fused.cuh", "etxb_attn_gq.cuh", "etxb_batch.cuh", "etxb_tc.cuh", "etxb_mla.cuh", "etxb_kernel.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-fmad=false",
               "-shared", "-Xcompiler", "-fPIC"]
 
 STATUS = {0: "OK", 1: "E_ARG", 2: "E_PLAN", 3: "E_CUDA", 4: "E_RESIDENCY", 5: "E_TIMEOUT", 6: "E_ABORTED", 7: "E_UNSUPPORTED"}
 BODY = {"nop": 0, "prologue": 1, "argmax": 2, "gemv": 3, "moe_up": 4, "moe_down": 5, "topk": 6, "attnprep": 7, "attn": 8,
         "attn_reduce": 9, "splitk_part": 10, "splitk_sum": 11, "attn_fused": 12, "norm_col": 13, "gemv_nb": 14, "route": 15,
-        "moe_up_g": 16, "moe_down_g": 17, "prologue_nb": 18, "argmax_nb": 19, "gemv_tc": 20, "moe_up_tc": 21, "moe_down_tc": 22}
+        "moe_up_g": 16, "moe_down_g": 17, "prologue_nb": 18, "argmax_nb": 19, "gemv_tc": 20, "moe_up_tc": 21, "moe_down_tc": 22, "mla_attn": 23}
 
 # every symbol include/etxb200.h declares
 SYMBOLS = ["etxb_version", "etxb_last_error", "etxb_device_info", "etxb_create", "etxb_bind", "etxb_set_step", "etxb_set_option",

@@ -72,7 +72,8 @@ enum {
   ETXB_BODY_GEMV_TC = 20,
   ETXB_BODY_MOE_UP_TC = 21,
   ETXB_BODY_MOE_DOWN_TC = 22,
-  ETXB_BODY_COUNT = 23
+  ETXB_BODY_MLA_ATTN = 23,    /* absorbed multi-head latent attention of one head over the whole context (DeepSeek-V2 family) */
+  ETXB_BODY_COUNT = 24
 };
 
 /* The per-step scalars and buffers of the prologue / argmax tiles: field for field the reference's VlParams
