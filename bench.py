@@ -160,6 +160,8 @@ def run_reference(args, rank: int, world: int):
     """The reference's CPU implementation of the path (its numpy path restated in oracle/) on this box's host cores."""
     if rank != 0:
         return
+    if MODEL == "deepseek-v2-lite":
+        return run_reference_mla(args)
     from oracle import ref_decode as O
     use_all_cores()
     cfg = oracle_cfg(O)
@@ -190,6 +192,206 @@ def run_reference(args, rank: int, world: int):
                       "config": {"workload": work, "parallelism": "cpu", "norm_gamma": "ones"},
                       "cpu_baseline": {"value": v, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
                       "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ------------------------------------------------------------------------------------------------ DeepSeek-V2-Lite (latent attention)
+def run_mla(args, rank: int, world: int, local_rank: int):
+    """--model deepseek-v2-lite: the same measurement for the latent-attention / shared-expert model (one GPU per request;
+    N > 1 runs N independent requests)."""
+    import torch
+    import etx_megakernel_b200  # noqa: F401
+    from etx_megakernel_b200.models import dsv2 as M
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    d = M.load_dims("deepseek-v2-lite", layers=args.layers or None)
+    P, K, Wm = args.prompt, args.steps, args.warmup
+    maxlen = ((P + Wm + K + 40 + 15) // 16) * 16
+    weights = M.random_weights(d, maxlen, dev, seed=rank)
+    prog = M.MlaProgram(d, weights, device=local_rank, maxlen=maxlen, steps=maxlen)
+    prompt = np.random.default_rng(1000 + rank).integers(0, d.V, P)
+    tin = torch.zeros_like(prog.buf["token_in"]); tin[:P] = torch.tensor(prompt, dtype=torch.int32)
+    prog.buf["token_in"].copy_(tin)
+    clk = ClockSampler(local_rank)
+    clk.__enter__()
+    try:
+        t0 = time.perf_counter()
+        for t in range(P + Wm):
+            prog.step(t, t, write_next=t + 1 >= P, wait=(t % 128 == 127))
+        prog.session.wait(120.0)
+        torch.cuda.synchronize(dev)
+        prefill_s = time.perf_counter() - t0
+        stream = torch.cuda.Stream(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for i in range(K):
+                t = P + Wm + i
+                prog.session.set_step(tok=t, pos=t, write_next=1)
+                prog.session.launch(stream.cuda_stream)
+            e1.record(stream)
+        torch.cuda.synchronize(dev)
+        prog.session.wait(120.0)
+        if dist:
+            dist.barrier()
+        dev_ms = e0.elapsed_time(e1) / K
+        gen_dev = prog.buf["token_out"][P + Wm - 1:P + Wm + K].cpu().numpy()
+        h0 = time.perf_counter()
+        toks_host, _ = prog.session.decode_host(np.asarray([int(gen_dev[0])], np.int32), K, P + Wm)
+        host_ms = (time.perf_counter() - h0) * 1e3 / K
+    finally:
+        clk.__exit__(None, None, None)
+    clocks = clk.summary()
+    same_tokens = bool(np.array_equal(toks_host, gen_dev[1:K + 1]))
+    from etx_megakernel_b200.runtime.dist import slowest
+    dev_ms, host_ms = slowest([dev_ms, host_ms], dist, dev)
+    ctx = P + Wm + K // 2
+    ledger = M.step_bytes(d, ctx)
+    peak, peak_src = measured_peaks()
+    achieved = ledger["total"] / (dev_ms * 1e-3) / 1e9
+    line = {"metric": METRIC, "value": dev_ms, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": Wm, "ms_per_step": dev_ms, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"deepseek-v2-lite decode bs1, {d.L} layers ({d.DENSE_LAYERS} dense), prompt {P} random ids, then greedy tokens",
+                       "prefill": "the prompt is fed token by token through the same kernel", "context": ctx,
+                       "parallelism": "single" if world == 1 else f"replicas x{world} (independent requests)", "norm_gamma": "ones",
+                       "l2": f"each step streams {ledger['total'] / 1e9:.1f} GB (> 126 MB L2)", "prefill_s": round(prefill_s, 2),
+                       "host_tokens_equal_device_tokens": same_tokens},
+            "e2e": {"value": host_ms, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4}, "gpu_launches": K, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": ledger["total"], "kernel": "etxb_megakernel",
+                         "ledger": "per layer: q / kv_a / kv_b / o projections + latent cache + (router + (top-k + shared) experts | dense MLP); + lm_head"}}
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = mla_cpu_baseline(d, weights, ctx)
+    if rank == 0:
+        print(json.dumps(line))
+    prog.close()
+    if dist:
+        dist.destroy_process_group()
+
+
+def run_reference_mla(args):
+    """--impl reference --model deepseek-v2-lite: the oracle's layers on the host cores with random weights of the model's
+    shapes (a pool of 8 routed experts stands for the 64: what a step multiplies is the same)."""
+    import etx_megakernel_b200  # noqa: F401
+    from etx_megakernel_b200.models import dsv2 as M
+    from oracle import ref_mla as R
+    cores = use_all_cores()
+    d = M.load_dims("deepseek-v2-lite", layers=args.layers or None)
+    ctx = args.prompt + args.warmup + args.steps // 2
+    rng = np.random.default_rng(0)
+    w = lambda *shape: R.bfr(rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02))   # noqa: E731
+
+    class Pool:
+        def __init__(self, mats):
+            self.mats = mats
+
+        def __getitem__(self, e):
+            return self.mats[int(e) % len(self.mats)]
+    one = np.ones
+    att = lambda: (one(d.H, np.float32), w(d.NH * d.QH, d.H), w(d.ROW, d.H), one(d.C, np.float32), w(d.NH * (d.DN + d.DV), d.C), w(d.H, d.NH * d.DV),   # noqa: E731
+                   one(d.H, np.float32))
+    dense, moe = R.MlaLayer(*att()), R.MlaLayer(*att())
+    dense.mlp = {"gate": w(d.DENSE_INTER, d.H), "up": w(d.DENSE_INTER, d.H), "down": w(d.H, d.DENSE_INTER)}
+    si = d.MI * d.NS
+    moe.mlp = {"router": w(d.E, d.H), "egate": Pool([w(d.MI, d.H) for _ in range(8)]), "eup": Pool([w(d.MI, d.H) for _ in range(8)]),
+               "edown": Pool([w(d.H, d.MI) for _ in range(8)]), "sgate": w(si, d.H), "sup": w(si, d.H), "sdown": w(d.H, si)}
+    lm = w(d.V, d.H)
+    cos, sin = R.yarn_tables(mla_oracle_dims(R, d, False), ctx + 8)
+    cache = rng.standard_normal((ctx + 8, d.ROW)).astype(np.float32)
+    x = rng.standard_normal(d.H).astype(np.float32)
+
+    def step():
+        t0 = time.perf_counter()
+        R.layer(mla_oracle_dims(R, d, True), dense, x, cache, ctx, cos, sin)
+        t1 = time.perf_counter()
+        R.layer(mla_oracle_dims(R, d, False), moe, x, cache, ctx, cos, sin)
+        t2 = time.perf_counter()
+        lm @ x
+        t3 = time.perf_counter()
+        return 1e3 * (d.DENSE_LAYERS * (t1 - t0) + (d.L - d.DENSE_LAYERS) * (t2 - t1) + (t3 - t2))
+    for _ in range(args.warmup):
+        step()
+    v = float(np.mean([step() for _ in range(args.steps)]))
+    print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                      "ms_per_step": v, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"deepseek-v2-lite decode bs1, {d.L} layers ({d.DENSE_LAYERS} dense), prompt {args.prompt} random ids, then greedy tokens",
+                                 "parallelism": "cpu", "norm_gamma": "ones"},
+                      "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                       "sample": f"per step: the dense layer once, one MoE layer once, the lm_head product, at context {ctx}; scaled to {d.L} layers"},
+                      "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+class _LazyExperts:
+    """m["egate"][e]-style access to one expert's rows of a packed device tensor (fetched when asked for)."""
+
+    def __init__(self, t, rows):
+        self.t, self.rows = t, rows
+
+    def __getitem__(self, e):
+        a = self.t[e]
+        return (a[self.rows] if self.rows is not None else a).float().cpu().numpy()
+
+
+def mla_oracle_layer(R, d, weights, L):
+    """The oracle's layer object of layer L over the device's packed weights (experts fetched lazily)."""
+    g = lambda n: weights[f"{L}.{n}"].float().cpu().numpy()                 # noqa: E731
+    wqa = g("wqa")
+    lw = R.MlaLayer(g("ln1"), wqa[:d.NH * d.QH], wqa[d.NH * d.QH:], g("kvln"), g("wkvb"), g("wo"), g("ln2"))
+    if d.dense(L):
+        wgu = g("wgu")
+        lw.mlp = {"gate": wgu[:d.DENSE_INTER], "up": wgu[d.DENSE_INTER:], "down": g("wd")}
+    else:
+        w13, w2 = weights[f"{L}.w13"], weights[f"{L}.w2"]
+        sh = [w13[d.E + i].float().cpu().numpy() for i in range(d.NS)]
+        lw.mlp = {"router": g("wr"), "egate": _LazyExperts(w13, slice(0, d.MI)), "eup": _LazyExperts(w13, slice(d.MI, 2 * d.MI)), "edown": _LazyExperts(w2, None),
+                  "sgate": np.concatenate([s[:d.MI] for s in sh]), "sup": np.concatenate([s[d.MI:] for s in sh]),
+                  "sdown": np.concatenate([w2[d.E + i].float().cpu().numpy() for i in range(d.NS)], axis=1)}
+    return lw
+
+
+def mla_oracle_dims(R, d, dense):
+    return R.MlaDims(hidden=d.H, heads=d.NH, kv_lora=d.C, qk_nope=d.DN, qk_rope=d.DR, v_head=d.DV, moe_inter=d.MI, n_routed=d.E, top_k=d.TOPK, n_shared=d.NS,
+                     dense_inter=d.DENSE_INTER if dense else 0, eps=d.eps, theta=d.theta, rope_factor=d.rope_factor, rope_original_max=d.rope_original_max,
+                     beta_fast=d.beta_fast, beta_slow=d.beta_slow, mscale=d.mscale, mscale_all_dim=d.mscale_all_dim, norm_topk=d.norm_topk)
+
+
+def mla_cpu_baseline(d, weights, ctx, budget_s: float = 20.0):
+    """The oracle (oracle/ref_mla.py) on the host cores: a few decode steps of the dense layer and of one MoE layer at the
+    bench's context + the lm_head product, scaled to the model's layer counts."""
+    from oracle import ref_mla as R                                        # the checker, timed: the one CPU leg of this bench
+    cores = use_all_cores()
+    x = np.random.default_rng(0).standard_normal(d.H).astype(np.float32)
+    cos, sin = R.yarn_tables(mla_oracle_dims(R, d, False), ctx + 8)
+    per = {}
+    for kind, L in (("dense", 0 if d.DENSE_LAYERS else None), ("moe", d.DENSE_LAYERS if d.L > d.DENSE_LAYERS else None)):
+        if L is None:
+            per[kind] = 0.0
+            continue
+        od, lw = mla_oracle_dims(R, d, kind == "dense"), mla_oracle_layer(R, d, weights, L)
+        cache = np.random.default_rng(1).standard_normal((ctx + 8, d.ROW)).astype(np.float32)
+        ts = []
+        t_end = time.perf_counter() + budget_s / 2
+        while len(ts) < 3 or (time.perf_counter() < t_end and len(ts) < 12):
+            t0 = time.perf_counter()
+            R.layer(od, lw, x, cache, ctx, cos, sin)
+            ts.append(time.perf_counter() - t0)
+        per[kind] = float(np.median(ts))
+    lm = weights["lm_head"].float().cpu().numpy()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        lm @ x
+    t_lm = (time.perf_counter() - t0) / 3
+    ms = 1e3 * (d.DENSE_LAYERS * per["dense"] + (d.L - d.DENSE_LAYERS) * per["moe"] + t_lm)
+    return {"value": ms, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"median of a few decode steps of the dense layer and of one MoE layer at context {ctx} + the lm_head product, scaled to {d.L} layers"}
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
@@ -454,7 +656,8 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default=MODEL, choices=["qwen3-30b-a3b", "qwen3-8b"], help="qwen3-8b: the dense configuration (reported beside the headline)")
+    ap.add_argument("--model", default=MODEL, choices=["qwen3-30b-a3b", "qwen3-8b", "deepseek-v2-lite"],
+                    help="qwen3-8b: the dense configuration; deepseek-v2-lite: latent attention + shared-expert MoE (both reported beside the headline)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (debugging only; 0 = all)")
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
@@ -471,6 +674,8 @@ def main():
             import etx_megakernel_b200  # noqa: F401  (registers the package under its importable name)
             from etx_megakernel_b200.ops import gemv_sweep
             gemv_sweep.main()
+    elif a.model == "deepseek-v2-lite" and a.impl != "reference":
+        run_mla(a, rank, world, local)
     elif a.impl == "reference":
         run_reference(a, rank, world)
     elif a.batch > 1:

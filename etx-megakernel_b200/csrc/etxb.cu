@@ -27,7 +27,7 @@ static_assert(ETXB_SMEM_BYTES + 256 <= 232448, "dynamic + static shared memory m
 static_assert(sizeof(etxb_task) == 40 && sizeof(etxb_type) == 48, "plan table layouts");
 static_assert(sizeof(etxb_stepv) == sizeof(etxb_step_params), "step parameter layouts must agree");
 static_assert(sizeof(etxb::etxb_route_args) == 88 && offsetof(etxb::etxb_route_args, grid) == 72, "route block layout");
-static_assert(sizeof(etxb::etxb_mla_args) == 112 && offsetof(etxb::etxb_mla_args, grid) == 96 && offsetof(etxb::etxb_mla_args, scale) == 80, "mla block layout");
+static_assert(sizeof(etxb::etxb_mla_args) == 128 && offsetof(etxb::etxb_mla_args, grid) == 112 && offsetof(etxb::etxb_mla_args, tmp) == 88, "mla block layout");
 static_assert(sizeof(etxb::etxb_batch_args) == 32 && offsetof(etxb::etxb_batch_args, grid) == 16, "column block layout");
 static_assert(ETXB_NBR_OFF + 2 * ETXB_NB_ROWS * ETXB_NBC * 4 <= ETXB_GEN_BYTES && ETXB_NBP_OFF + ETXB_NBP_UNITS * 512 <= ETXB_NBR_OFF, "batched tiles fit the general region");
 
@@ -174,15 +174,16 @@ static int32_t check_batch_block(int body, const unsigned char* blk, size_t byte
 }
 
 static int32_t check_mla_block(const unsigned char* blk, size_t bytes) {
-  if (bytes < sizeof(etxb::etxb_mla_args)) return fail(ETXB_E_ARG, "mla_attn tile: the argument block is 112 bytes");
+  if (bytes < sizeof(etxb::etxb_mla_args)) return fail(ETXB_E_ARG, "mla_attn tile: the argument block is 128 bytes");
   etxb::etxb_mla_args a;
   memcpy(&a, blk, sizeof a);
   const char* why = nullptr;
-  if (a.NH < 1 || a.C < 2 || a.C > 512 || (a.C & 1) || a.DR < 2 || a.DR > 64 || (a.DR & 1) || a.DN < 1 || a.DN + a.DR > 256 || a.C + a.DR > 640 || a.DV < 1)
-    why = "C <= 512 (even), DR <= 64 (even), DN + DR <= 256";
+  if (a.NH < 1 || a.C < 8 || a.C > 512 || (a.C & 7) || a.DR < 8 || a.DR > 64 || (a.DR & 7) || a.DN < 1 || a.DN + a.DR > 256 || a.C + a.DR > 640 || a.DV < 1)
+    why = "C <= 512 and DR <= 64 (multiples of 8), DN + DR <= 256";
   else if (a.maxlen < 1 || a.maxlen > ETXB_MLA_MAXCTX) why = "1 <= maxlen <= 8192";
-  else if (!a.qkv || !a.kvln || !a.cos_sin || !a.wkvb || !a.cache || !a.positions || !a.out) why = "null pointer";
-  else if (a.nblocks > (uint32_t)a.NH) why = "the grid is one task per head";
+  else if (!a.qkv || !a.kvln || !a.cos_sin || !a.wkvb || !a.cache || !a.positions || !a.out || !a.tmp) why = "null pointer";
+  else if (a.max_parts < 1 || a.max_parts > 64 || (long long)a.max_parts * ETXB_MLA_PART < a.maxlen) why = "max_parts partitions of 128 positions cover maxlen (at most 64)";
+  else if (a.nblocks > (uint32_t)(a.NH * a.max_parts)) why = "the grid is max_parts * NH tasks";
   if (!why) return ETXB_OK;
   char m[256];
   snprintf(m, sizeof m, "mla_attn block (NH=%d, C=%d, DN=%d, DR=%d, DV=%d, maxlen=%d) outside the tile: %s", a.NH, a.C, a.DN, a.DR, a.DV, a.maxlen, why);

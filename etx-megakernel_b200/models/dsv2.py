@@ -8,8 +8,9 @@ tile bodies there are a third-party library; the arithmetic follows that model's
 Phases per layer (one event after each), all inside the one persistent launch of a decode step:
   qkv_a   q_proj and kv_a_proj as ONE streamed GEMV with the input-norm fold (rows: NH q heads of DN + DR, then the
           C + DR row of the latent projection)
-  attn    absorbed latent attention, one task per head: latent norm + rope + cache row, q W_UK, scores over the latent
-          cache, softmax, weighted latent, W_UV (csrc/etxb_mla.cuh)
+  attn    absorbed latent attention, one task per (head, 128 positions): latent norm + rope + cache row, q W_UK, scores
+          over the latent cache, softmax statistics, weighted latent; the last partition's task merges and applies W_UV
+          (csrc/etxb_mla.cuh)
   o_proj  streamed GEMV
   MoE layers:   router (post-attention norm fold) -> gate+up -> down.  The shared experts are stored as experts
           E .. E + NS - 1 of the same tensors and take the last NS slots of every token with weight 1 (top-k fold mode
@@ -227,7 +228,7 @@ def buffer_shapes(d: MlaDims, maxlen: int, steps: int) -> dict:
          "attn_out": ((d.NH * d.DV,), "bf16"), "o": ((d.H,), "bf16"), "o_norm": ((d.H,), "bf16"), "logits": ((d.V,), "bf16"),
          "positions": ((1,), "i64"), "seq_lens": ((1,), "i32"), "slot_mapping": ((1,), "i64"),
          "token_in": ((steps + 2,), "i32"), "token_out": ((steps + 1,), "i32"), "token_time": ((2 * (steps + 1),), "i64"),
-         "ckv": ((d.L, maxlen, d.ROW), "bf16"), "moe_out": ((d.H,), "bf16"),
+         "ckv": ((d.L, maxlen, d.ROW), "bf16"), "moe_out": ((d.H,), "bf16"), "mla_tmp": ((op_mla.tmp_pairs(d.NH, d.C, maxlen), 2), "f32"),
          "rlog": ((max(d.E, 1),), "bf16"), "tw": ((max(d.SLOTS, 1),), "f32"), "ti": ((max(d.SLOTS, 1),), "i32"),
          "mc2": ((max(d.SLOTS * mi, d.DENSE_INTER, 1),), "bf16")}
     return s
@@ -279,6 +280,7 @@ def build_graph(d: MlaDims, ptr, maxlen: int = 1072, machine: MachineModel | str
     g.call_device("prologue", (1,), cuda_link(SRC, "vl_prologue"), resource=res, args=["vl"], consts=(0,), out_edges={"E_pro": "i->i"}, duration_us=3.8)
     prev = "E_pro"
     cache_layer_bytes = maxlen * d.ROW * 2
+    nparts = op_mla.partitions(maxlen)
     for L in range(d.L):
         Wl = lambda n, L=L: ptr(f"{L}.{n}")                                  # noqa: E731
         first = L == 0
@@ -287,10 +289,10 @@ def build_graph(d: MlaDims, ptr, maxlen: int = 1072, machine: MachineModel | str
                   resid_in=ptr("resid") if first else ptr("resid2"), resid_out=0 if first else ptr("resid"), ln=Wl("ln1"), R=0 if first else 1, eps=d.eps,
                   mode=op_gemv.MODE_NORM, nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, prev, f"E_qkv_{L}", d.NQKV, d.H, after="")
-        blob = argblock.pack_named(ent["mla_attn"], (d.NH, 1, 1), qkv=ptr("qkv"), kvln=Wl("kvln"), cos_sin=ptr("cos_sin"), wkvb=Wl("wkvb"),
+        blob = argblock.pack_named(ent["mla_attn"], (d.NH * nparts, 1, 1), qkv=ptr("qkv"), kvln=Wl("kvln"), cos_sin=ptr("cos_sin"), wkvb=Wl("wkvb"),
                                    cache=ptr("ckv") + L * cache_layer_bytes, positions=ptr("positions"), out=ptr("attn_out"), NH=d.NH, C=d.C, DN=d.DN, DR=d.DR,
-                                   DV=d.DV, maxlen=maxlen, scale=d.scale, eps=d.eps)
-        prev = add(f"attn_{L}", "mla_attn", "attn_fused", L, blob, d.NH, prev, f"E_attn_{L}")
+                                   DV=d.DV, maxlen=maxlen, scale=d.scale, eps=d.eps, tmp=ptr("mla_tmp"), max_parts=nparts, tag=L & 0xff)
+        prev = add(f"attn_{L}", "mla_attn", "attn_fused", L, blob, d.NH * nparts, prev, f"E_attn_{L}")
         t, rpt = m.gemv_tasks(d.H)
         blob = gb("dsl_gemv", t, W=Wl("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.DV, rpt=rpt, tpe=1, eps=d.eps, nb=1)
         prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, prev, f"E_o_{L}", d.H, d.NH * d.DV, after="")

@@ -159,6 +159,22 @@ def main(argv=None) -> int:
     ap.add_argument("--raw", help="also write the nine-int64-per-task rows to this file")
     a = ap.parse_args(argv)
     from ..models import qwen as Q
+    if a.model == "deepseek-v2-lite":                                       # latent attention + shared-expert MoE: its own program
+        import torch
+        from ..models import dsv2 as M
+        d = M.load_dims(a.model, layers=a.layers)
+        dev = torch.device("cuda", 0)
+        prog = M.MlaProgram(d, M.random_weights(d, a.maxlen, dev, seed=0), device=0, maxlen=a.maxlen)
+        prog.buf["ckv"].normal_(0, 0.5)
+        torch.cuda.synchronize(dev)
+        for t in range(min(a.warm, 8)):
+            prog.buf["token_in"][0] = 7
+            prog.step(0, a.context + t, False)
+        prog.session.set_option("trace", 1)
+        prog.step(0, a.context + 9, False)
+        print(Timeline.from_trace(prog.plan, prog.session.trace()).text())
+        prog.close()
+        return 0
     d = Q.load_dims(a.model, layers=a.layers)
     if a.sim:
         from ..passes import compile_graph

@@ -125,3 +125,39 @@ class DeviceWeights:
         if keep and not self._staged:
             self.cache[k] = v
         return v
+
+
+# ---------------------------------------------------------------------------------------------- DeepSeek-V2 family
+class LazyExperts:
+    """m["egate"][e]-style access to one expert's rows of a packed device tensor, fetched when the oracle asks for them."""
+
+    def __init__(self, t, rows=None):
+        self.t, self.rows = t, rows
+
+    def __getitem__(self, e):
+        a = self.t[int(e)]
+        return (a[self.rows] if self.rows is not None else a).float().cpu().numpy()
+
+
+def mla_oracle_dims(R, d, dense: bool):
+    return R.MlaDims(hidden=d.H, heads=d.NH, kv_lora=d.C, qk_nope=d.DN, qk_rope=d.DR, v_head=d.DV, moe_inter=d.MI, n_routed=d.E, top_k=d.TOPK, n_shared=d.NS,
+                     dense_inter=d.DENSE_INTER if dense else 0, eps=d.eps, theta=d.theta, rope_factor=d.rope_factor, rope_original_max=d.rope_original_max,
+                     beta_fast=d.beta_fast, beta_slow=d.beta_slow, mscale=d.mscale, mscale_all_dim=d.mscale_all_dim, norm_topk=d.norm_topk)
+
+
+def mla_oracle_layer(R, d, weights: dict, L: int):
+    """oracle.ref_mla.MlaLayer of layer L over the device's packed weights (models.dsv2.weight_shapes): the shared experts are
+    experts E .. E + NS - 1 of the packed tensors, the routed experts are fetched one by one when the oracle selects them."""
+    g = lambda n: weights[f"{L}.{n}"].float().cpu().numpy()                 # noqa: E731
+    wqa = g("wqa")
+    lw = R.MlaLayer(g("ln1"), wqa[:d.NH * d.QH], wqa[d.NH * d.QH:], g("kvln"), g("wkvb"), g("wo"), g("ln2"))
+    if d.dense(L):
+        wgu = g("wgu")
+        lw.mlp = {"gate": wgu[:d.DENSE_INTER], "up": wgu[d.DENSE_INTER:], "down": g("wd")}
+    else:
+        w13, w2 = weights[f"{L}.w13"], weights[f"{L}.w2"]
+        sh = [w13[d.E + i].float().cpu().numpy() for i in range(d.NS)]
+        lw.mlp = {"router": g("wr"), "egate": LazyExperts(w13, slice(0, d.MI)), "eup": LazyExperts(w13, slice(d.MI, 2 * d.MI)), "edown": LazyExperts(w2),
+                  "sgate": np.concatenate([s[:d.MI] for s in sh]), "sup": np.concatenate([s[d.MI:] for s in sh]),
+                  "sdown": np.concatenate([w2[d.E + i].float().cpu().numpy() for i in range(d.NS)], axis=1)}
+    return lw

@@ -10,6 +10,7 @@ import etx_megakernel_b200  # noqa: E402,F401
 from etx_megakernel_b200 import ops  # noqa: E402
 from etx_megakernel_b200.importer import argblock  # noqa: E402
 from etx_megakernel_b200.models import dsv2 as M  # noqa: E402
+from etx_megakernel_b200.ops import mla as op_mla  # noqa: E402
 from etx_megakernel_b200.runtime import op_launch  # noqa: E402
 from oracle import ref_mla as R  # noqa: E402
 from oracle.ref_decode import bfr, f32_to_bf16_bits  # noqa: E402
@@ -29,11 +30,12 @@ def host(t):
     return (t.float() if t.dtype == torch.bfloat16 else t).cpu().numpy()
 
 
-@pytest.mark.parametrize("NH,ctx", [(4, 1), (4, 37), (16, 300)])
+@pytest.mark.parametrize("NH,ctx", [(4, 0), (4, 37), (16, 300), (16, 1027)])
 def test_latent_attention_tile_against_the_oracle(NH, ctx):
-    """One head per task over a context of `ctx` cached positions + the new one: the cache row the tile writes is the
-    oracle's bit for bit (latent RMSNorm in numpy's summation order, interleaved rope with fp32 YaRN tables), the
-    attention output within the bf16 tolerance of the oracle's (fp32 sums in another order)."""
+    """A task per (head, 128 positions) over a context of `ctx` cached positions + the new one (1, 3 and 9 partitions; the
+    new position first in its partition or in the middle): the cache row the tile writes is the oracle's bit for bit
+    (latent RMSNorm in numpy's summation order, interleaved rope with fp32 YaRN tables), the attention output within
+    the bf16 tolerance of the oracle's (fp32 sums in another order, softmax merged over partitions)."""
     d = M.MlaDims(name="t", H=NH * 128, NH=NH, C=512, DN=128, DR=64, DV=128, MI=128, E=4, TOPK=2, NS=0, DENSE_LAYERS=0, DENSE_INTER=0, L=1, V=256)
     od = oracle_dims(d)
     maxlen = ctx + 8
@@ -54,10 +56,12 @@ def test_latent_attention_tile_against_the_oracle(NH, ctx):
     t_cache = dev_bf16(before)
     t_pos = torch.tensor([ctx], dtype=torch.int64, device=DEV)
     t_out = torch.zeros(NH * d.DV, dtype=torch.bfloat16, device=DEV)
-    blob = argblock.pack_named(ENT["mla_attn"], (NH, 1, 1), qkv=t_qkv.data_ptr(), kvln=t_ln.data_ptr(), cos_sin=t_cs.data_ptr(), wkvb=t_w.data_ptr(),
+    nparts = op_mla.partitions(maxlen)
+    t_tmp = torch.zeros((op_mla.tmp_pairs(NH, d.C, maxlen), 2), dtype=torch.float32, device=DEV)
+    blob = argblock.pack_named(ENT["mla_attn"], (NH * nparts, 1, 1), qkv=t_qkv.data_ptr(), kvln=t_ln.data_ptr(), cos_sin=t_cs.data_ptr(), wkvb=t_w.data_ptr(),
                                cache=t_cache.data_ptr(), positions=t_pos.data_ptr(), out=t_out.data_ptr(), NH=NH, C=d.C, DN=d.DN, DR=d.DR, DV=d.DV,
-                               maxlen=maxlen, scale=d.scale, eps=d.eps)
-    op_launch("mla_attn", blob, NH)
+                               maxlen=maxlen, scale=d.scale, eps=d.eps, tmp=t_tmp.data_ptr(), max_parts=nparts, tag=3)
+    op_launch("mla_attn", blob, NH * nparts)
     got_cache, got = host(t_cache), host(t_out)
     assert np.array_equal(got_cache[ctx], cache[ctx]), "the new cache row differs from the oracle's"
     assert np.array_equal(got_cache[:ctx], before[:ctx]) and not got_cache[ctx + 1:].any()
@@ -139,9 +143,9 @@ def test_blocks_outside_the_tile_are_refused():
     t = torch.zeros(64, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(ValueError, match="mla_attn"):
         argblock.pack_named(ENT["mla_attn"], (2, 1, 1), qkv=t.data_ptr(), kvln=t.data_ptr(), cos_sin=t.data_ptr(), wkvb=t.data_ptr(), cache=t.data_ptr(),
-                            positions=t.data_ptr(), out=t.data_ptr(), NH=2, C=1024, DN=128, DR=64, DV=128, maxlen=64, scale=0.1, eps=1e-6)
+                            positions=t.data_ptr(), out=t.data_ptr(), NH=2, C=1024, DN=128, DR=64, DV=128, maxlen=64, scale=0.1, eps=1e-6, tmp=t.data_ptr(), max_parts=1, tag=0)
     good = argblock.pack_named(ENT["mla_attn"], (2, 1, 1), qkv=t.data_ptr(), kvln=t.data_ptr(), cos_sin=t.data_ptr(), wkvb=t.data_ptr(), cache=t.data_ptr(),
-                               positions=t.data_ptr(), out=t.data_ptr(), NH=2, C=512, DN=128, DR=64, DV=128, maxlen=64, scale=0.1, eps=1e-6)
+                               positions=t.data_ptr(), out=t.data_ptr(), NH=2, C=512, DN=128, DR=64, DV=128, maxlen=64, scale=0.1, eps=1e-6, tmp=t.data_ptr(), max_parts=1, tag=0)
     bad = bytearray(good)
     bad[60:64] = (2048).to_bytes(4, "little")                 # C beyond the tile's shared-memory layout, patched past the Python check
     with pytest.raises(EtxbError, match="mla_attn"):
