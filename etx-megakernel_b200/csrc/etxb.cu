@@ -215,10 +215,11 @@ static int32_t check_block(int body, const unsigned char* blk, size_t bytes) {
 // attention (head_dim 128, cache blocks of 16, partitions of 128) with the same group size everywhere.
 static int select_variant(const etxb_session* s, const std::vector<unsigned char>& pool) {
   int gq = 0;
-  bool any_attn = false;
+  bool any_attn = false, any_mla = false;
   for (const etxb_type& ty : s->types) {
     const int b = ty.body;
     if (b == ETXB_BODY_NOP || b == ETXB_BODY_PROLOGUE || b == ETXB_BODY_ARGMAX) continue;
+    if (b == ETXB_BODY_MLA_ATTN) { any_mla = true; continue; }
     if (!(b == ETXB_BODY_GEMV || b == ETXB_BODY_MOE_UP || b == ETXB_BODY_MOE_DOWN || b == ETXB_BODY_ATTN_FUSED)) return 0;
     if (ty.args[0] != 0 || ty.cst[1] != 0 || ty.cst[0] < 0) return 0;
     const size_t off = (size_t)ty.cst[0];
@@ -238,6 +239,7 @@ static int select_variant(const etxb_session* s, const std::vector<unsigned char
       if (fold >= 2 && a.E > 128) return 0;
     }
   }
+  if (any_mla) return any_attn ? 0 : 10;                           // latent attention: its own lean kernel (no GQA grids beside it)
   if (!any_attn) gq = 1;                                           // no attention grid: any lean kernel will do
   return gq == 1 ? 1 : gq == 2 ? 2 : gq == 4 ? 3 : 4;
 }
@@ -245,11 +247,17 @@ static int select_variant(const etxb_session* s, const std::vector<unsigned char
 // The kernel variants: index 0 = the full kernel, 1..4 = the lean decode kernels for grouped attention with 1, 2, 4, 8
 // q heads per task (etxb_kernel.cuh, run_body).
 // Entries 5..9: the same five with the exchange code of a sharded session compiled in (launch_kernel adds 5).
-static const void* const g_kernels[10] = {(const void*)etxb::etxb_megakernel<0>, (const void*)etxb::etxb_megakernel<1>, (const void*)etxb::etxb_megakernel<2>,
+// Entry 10: the lean decode kernel of a latent-attention model (no sharded form: such a session falls back to entry 5).
+static const void* const g_kernels[11] = {(const void*)etxb::etxb_megakernel<0>, (const void*)etxb::etxb_megakernel<1>, (const void*)etxb::etxb_megakernel<2>,
                                           (const void*)etxb::etxb_megakernel<4>, (const void*)etxb::etxb_megakernel<8>,
                                           (const void*)etxb::etxb_megakernel<0, true>, (const void*)etxb::etxb_megakernel<1, true>,
                                           (const void*)etxb::etxb_megakernel<2, true>, (const void*)etxb::etxb_megakernel<4, true>,
-                                          (const void*)etxb::etxb_megakernel<8, true>};
+                                          (const void*)etxb::etxb_megakernel<8, true>, (const void*)etxb::etxb_megakernel<ETXB_VARIANT_MLA>};
+static int kernel_index(const etxb_session* s) {
+  const int v = s->force_full ? 0 : s->variant;
+  if (s->xbase == nullptr) return v;
+  return (v == 10 ? 0 : v) + 5;
+}
 
 static int32_t prepare_kernel(int device, int* workers_out) {
   CU(cudaSetDevice(device));
@@ -694,7 +702,7 @@ extern "C" int32_t etxb_launch(etxb_session* s, void* cuda_stream) {
   etxb_params p;
   fill_params(s, p);
   CU(cudaEventRecord(s->ev0, s->stream));
-  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->xbase != nullptr ? 5 : 0));
+  int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, kernel_index(s));
   if (rc) return rc;
   CU(cudaEventRecord(s->ev1, s->stream));
   s->launched = true;
@@ -720,7 +728,7 @@ extern "C" int32_t etxb_launch_unfused(etxb_session* s, void* cuda_stream) {
   CU(cudaEventRecord(s->ev0, s->stream));
   for (uint32_t t = 0; t < s->h.n_types; ++t) {
     p.qbegin = s->d_uqbegin + (size_t)t * (s->h.n_workers + 1);
-    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, (s->force_full ? 0 : s->variant) + (s->xbase != nullptr ? 5 : 0));
+    int32_t rc = launch_kernel(p, (int)s->h.n_workers, s->stream, kernel_index(s));
     if (rc) return rc;
   }
   CU(cudaEventRecord(s->ev1, s->stream));

@@ -187,17 +187,22 @@ __device__ __forceinline__ GemvTask gemv_task(int body, const etxb_gemv_args& d,
 
 // Expert ids (and routing weights) of the task's slots into `lids` / `lwts` (indexed by global slot).  One warp, all
 // lanes call.  Top-k fold: recomputed from the logits; else read from the ids / wts buffers; no ids: expert 0.
-template <bool LEAN>
+// SH: the kernel variant supports always-on (shared) experts -- mode bits 24..27: ns experts that every token uses, stored
+// after the E routed ones; they take the last ns slots with weight 1, the top-k picks the others.  (A template parameter
+// and not a run-time branch: the lean kernels of the models without shared experts measured 1.4 % slower with it.)
+template <bool LEAN, bool SH = !LEAN>
 __device__ __forceinline__ void gemv_routing(const etxb_gemv_args& d, int32_t* lids, float* lwts) {
   const int fold = d.mode & 0xff, lane = tidx() & 31;
   if (fold >= 2) {
-    // mode bits 24..27: experts that every token uses (shared experts), stored after the E routed ones: they take the
-    // last slots with weight 1, the top-k picks the others
-    const int ns = (d.mode >> 24) & 0xf;
-    warp_topk<LEAN>(d.logits, d.E, d.R - ns, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
-    if (ns > 0) {
-      if (lane < ns) { lids[d.R - ns + lane] = d.E + lane; lwts[d.R - ns + lane] = 1.f; }
-      __syncwarp();
+    if constexpr (SH) {
+      const int ns = (d.mode >> 24) & 0xf;
+      warp_topk<LEAN>(d.logits, d.E, d.R - ns, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
+      if (ns > 0) {
+        if (lane < ns) { lids[d.R - ns + lane] = d.E + lane; lwts[d.R - ns + lane] = 1.f; }
+        __syncwarp();
+      }
+    } else {
+      warp_topk<LEAN>(d.logits, d.E, d.R, fold == 3, (d.mode & ETXB_MODE_BF16_WTS) != 0, lids, lwts, nullptr);
     }
   } else {
     if (lane < 16) {
@@ -208,11 +213,12 @@ __device__ __forceinline__ void gemv_routing(const etxb_gemv_args& d, int32_t* l
   }
 }
 
+template <bool SH = true>
 __device__ __forceinline__ const unsigned char* gemv_range_base(int body, const etxb_gemv_args& d, const GemvTask& t, int i, const int32_t* lids) {
   if (body == 3) return (const unsigned char*)d.W + (size_t)t.r0 * t.row_bytes;
   const int slot = t.group * t.spt + (body == 4 ? i >> 1 : i);
   int e = lids[slot];
-  if (d.E > 0 && (unsigned)e >= (unsigned)(d.E + ((d.mode >> 24) & 0xf))) e = 0;   // "no candidate" (a NaN row): never an address
+  if (d.E > 0 && (unsigned)e >= (unsigned)(d.E + (SH ? ((d.mode >> 24) & 0xf) : 0))) e = 0;   // "no candidate" (a NaN row): never an address
   const unsigned char* We = (const unsigned char*)d.W + (size_t)e * d.estride * 2;
   const int row = t.r0 + ((body == 4 && (i & 1)) ? d.M : 0);        // up rows follow the M gate rows
   return We + (size_t)row * t.row_bytes;
@@ -221,6 +227,7 @@ __device__ __forceinline__ const unsigned char* gemv_range_base(int body, const 
 // ---------------------------------------------------------------------------------------------- producer side
 // Issue the bulk copies of one task.  One warp; lane 0 issues.  n = running stage counter of this CTA.
 // ptr: the task's trace row when tracing (slot 7 <- time the first stage was issued, slot 6 <- the last), else null.
+template <bool SH = true>
 __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, const GemvTask& t, const int32_t* lids, uint32_t& n,
                                              const Smem& sm, int where, uint64_t* ptr = nullptr) {
   const int total = t.nranges * t.n;
@@ -244,7 +251,7 @@ __device__ __forceinline__ bool produce_task(int body, const etxb_gemv_args& d, 
       while (q < q0 + nr) {                                        // one copy per piece of a range that falls into this stage
         const int rg = q / t.n, r = q - rg * t.n;
         const int cnt = min(t.n - r, q0 + nr - q);
-        bulk_g2s_hint(dst + (size_t)(q - q0) * t.row_bytes, gemv_range_base(body, d, t, rg, lids) + (size_t)r * t.row_bytes,
+        bulk_g2s_hint(dst + (size_t)(q - q0) * t.row_bytes, gemv_range_base<SH>(body, d, t, rg, lids) + (size_t)r * t.row_bytes,
                       (uint32_t)(cnt * t.row_bytes), sm.full + st, pol);
         q += cnt;
       }
@@ -457,7 +464,7 @@ __device__ __forceinline__ void tile_gemv(const unsigned char* a, int blk, const
 // ---------------------------------------------------------------------------------------------- MoE gate+up
 // task blk: expert slots [group * spt, ...), row chunk j = blk % tpe; expert e = ids[slot] (no ids and no fold: expert
 // 0, the dense SwiGLU MLP); act[slot][r] = bf16(bf16(silu(bf16 g)) * bf16 u), g = W_e[r,:].x, u = W_e[M + r,:].x.
-template <bool LEAN, bool XCH = false>
+template <bool LEAN, bool XCH = false, bool SH = !LEAN>
 __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(4, d, blk);
@@ -466,7 +473,7 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
   const int fold = d.mode & 0xff;
   if (tidx() < 32) {
     if (fold >= 2) {
-      gemv_routing<LEAN>(d, lids, lwts);
+      gemv_routing<LEAN, SH>(d, lids, lwts);
       if (blk - t.group * d.tpe == 0 && tidx() < t.spt) {           // the group's first chunk publishes its slots' routing
         const int sl = t.group * t.spt + tidx();
         if (d.ids) ((int32_t*)d.ids)[sl] = lids[sl];
@@ -498,7 +505,7 @@ __device__ __forceinline__ void tile_moe_up(const unsigned char* a, int blk, con
 // Plain form: out[slot][r] = y.  Summed form (mode bit ETXB_MODE_SUM_SLOTS, the task covers every slot): out[r] = the
 // y of all slots added one by one in bf16 in ascending expert id -- the expert combine of the CPU path
 // (examples/llm/ref_numpy.py:142-148), which the reference leaves to the next layer's norm fold.
-template <bool LEAN>
+template <bool LEAN, bool SH = !LEAN>
 __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, const Smem& sm, uint32_t& n, int where) {
   const etxb_gemv_args& d = *(const etxb_gemv_args*)a;
   const GemvTask t = gemv_task(5, d, blk);
@@ -514,7 +521,7 @@ __device__ __forceinline__ void tile_moe_down(const unsigned char* a, int blk, c
       }
       __syncwarp();
     } else {
-      gemv_routing<LEAN>(d, lids, lwts);
+      gemv_routing<LEAN, SH>(d, lids, lwts);
     }
     // the slots in ascending expert id, for the summed form: known as soon as the routing is, so it is worked out here,
     // under the weight stream, and not after it (the barrier that follows the stream publishes it to the other warps)

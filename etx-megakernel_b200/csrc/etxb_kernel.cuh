@@ -169,25 +169,29 @@ __device__ __forceinline__ void fetch_ctx(const etxb_params& p, TaskCtx* ctx, in
 // Run the body of the task whose context is `c` on the consumer warps.
 // GQV: the kernel variant.  0 = every tile.  1, 2, 4, 8 = the lean decode kernel: only the tiles of a fused decode step
 // (prologue, argmax, the GEMV family with norm folds of at most one row and top-k folds over at most 128 experts, the
-// grouped attention tile with GQV q heads per task).  The host picks it from the plan (select_variant): the full
+// grouped attention tile with GQV q heads per task); ETXB_VARIANT_MLA = the lean kernel of a latent-attention model (the
+// same GEMV family with the latent-attention tile in place of the grouped one).  The host picks it from the plan (select_variant): the full
 // kernel is 550 KB of code, of which a decode step uses a fraction scattered through it, and the step runs about 10 %
 // faster from the 150 KB kernel (instruction fetch).
 // XCH: the variants a sharded session launches -- the same bodies plus the exchange code (flagged-row folds of R = ranks
 // rows, row publishing after the body, the argmax exchange); compiled out of the others.
+#define ETXB_VARIANT_MLA 16
 template <int GQV, bool XCH>
 __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c, int cur, const Smem& sm, uint32_t& n) {
   const unsigned char* args = c->args;
   const int c0 = c->r.c0, c1 = c->r.c1;
   constexpr bool LEAN = GQV != 0;
+  constexpr bool SH = GQV == 0 || GQV == ETXB_VARIANT_MLA;         // always-on (shared) experts: the full kernel and the latent-attention variant
   switch (c->r.body) {
     case 0: break;
     case 1: tile_prologue(p.step); break;
     case 2: tile_argmax<XCH>(p, sm); break;
     case 3: tile_gemv<LEAN, XCH>(args, c0, sm, n, cur); break;
-    case 4: tile_moe_up<LEAN, XCH>(args, c0, sm, n, cur); break;
-    case 5: tile_moe_down<LEAN>(args, c0, sm, n, cur); break;
+    case 4: tile_moe_up<LEAN, XCH, SH>(args, c0, sm, n, cur); break;
+    case 5: tile_moe_down<LEAN, SH>(args, c0, sm, n, cur); break;
     case 12:
-      if constexpr (LEAN) { if (c0 < (int)((const etxb_attnf_args*)args)->nblocks) attn_gq_impl<GQV ? GQV : 1>(*(const etxb_attnf_args*)args, c0, sm, p.step); }
+      if constexpr (GQV == ETXB_VARIANT_MLA) { if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK); }      // (the latent-attention variant has no GQA tile)
+      else if constexpr (LEAN) { if (c0 < (int)((const etxb_attnf_args*)args)->nblocks) attn_gq_impl<GQV ? GQV : 1>(*(const etxb_attnf_args*)args, c0, sm, p.step); }
       else tile_attn_any(args, c0, sm, p.step);
       break;
     case 6: if constexpr (!LEAN) { tile_topk(args, c0, sm); break; }
@@ -206,7 +210,7 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
     case 20: if constexpr (!LEAN && !XCH) { tile_gemv_tc(args, c0, sm, *sm.tc, cur); break; }
     case 21: if constexpr (!LEAN && !XCH) { tile_moe_up_tc(args, c0, sm, *sm.tc, cur); break; }
     case 22: if constexpr (!LEAN && !XCH) { tile_moe_down_tc(args, c0, sm, *sm.tc, cur); break; }
-    case 23: if constexpr (!LEAN) { tile_mla_attn(args, c0, sm, p.step); break; }
+    case 23: if constexpr (!LEAN || GQV == ETXB_VARIANT_MLA) { tile_mla_attn(args, c0, sm, p.step); break; }
     case 19: if constexpr (!LEAN) { if (c0 < ((const etxb_batch_args*)args)->nb) tile_argmax<false>(p, sm, c0, ((const etxb_batch_args*)args)->nb); break; }
     default:
       if (tidx() == 0) atomicOr(p.ctrl, ETXB_CTRL_BADTASK);
@@ -217,7 +221,7 @@ __device__ __forceinline__ void run_body(const etxb_params& p, const TaskCtx* c,
 // The producer warp: walks the same queue ahead of the consumers and streams the weight rows of every GEMV-family
 // task into the ring.  It waits only for what the weight ADDRESSES depend on (nothing for static weights, the router's
 // event for expert weights), never for the task's activations.
-template <bool LEAN>
+template <bool LEAN, bool SH = !LEAN>
 __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& sm, int q0, int q1) {
   uint32_t n = 0;
   const int lane = tidx() & 31;
@@ -247,8 +251,8 @@ __device__ __forceinline__ void producer_loop(const etxb_params& p, const Smem& 
       break;
     }
     const GemvTask gt = gemv_task(body, *pa, t->c0);
-    if (gt.n > 0 && body != 3) gemv_routing<LEAN>(*pa, sm.prod, (float*)(sm.prod + 16));
-    ok = produce_task(body, *pa, gt, sm.prod, n, sm, cur, p.trace ? p.trace + 8 * (size_t)t->id : nullptr);
+    if (gt.n > 0 && body != 3) gemv_routing<LEAN, SH>(*pa, sm.prod, (float*)(sm.prod + 16));
+    ok = produce_task<SH>(body, *pa, gt, sm.prod, n, sm, cur, p.trace ? p.trace + 8 * (size_t)t->id : nullptr);
   }
   // Nothing is left in flight on a normal exit (the consumers waited for every stage).  When the step was abandoned,
   // wait (bounded) for the copies already issued before the CTA's shared memory goes away.
@@ -297,7 +301,7 @@ __global__ void __launch_bounds__(ETXB_THREADS, 1) etxb_megakernel(const __grid_
   if ((int)blockIdx.x >= p.n_workers) return;
   const int q0 = p.qbegin[blockIdx.x], q1 = p.qbegin[blockIdx.x + 1];
   if (threadIdx.x >= ETXB_CONSUMERS) {
-    producer_loop<GQV != 0>(p, sm, q0, q1);
+    producer_loop<GQV != 0, GQV == 0 || GQV == ETXB_VARIANT_MLA>(p, sm, q0, q1);
     return;
   }
   TaskCtx* ctx = (TaskCtx*)(smem_raw + ETXB_RING_BYTES + ETXB_GEN_BYTES + ETXB_SCR_FLOATS * 4 + 512);
