@@ -373,6 +373,12 @@ __device__ __noinline__ void attn_gq_impl(const etxb_attnf_args& d, int blk, con
 // the softmax and the output sums, and nothing is published, polled or merged through global memory.
 // The partials live in the weight ring, which is idle in a batched plan (no streamed tiles): part_len bit 24 selects
 // this form, and only builders of plans without streamed tiles may set it.  (64 KB of K / V pieces + np * GQ * 130 floats <= the ring.)
+// D += A (16 x 16, row-major) * B (16 x 8, column-major), bf16 operands, fp32 accumulators (the warp-level tensor-core form)
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <int GQ>
 __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, const Smem& sm, const etxb_stepv& S) {
   constexpr int HD = 128, BS = 16, X = 8, PL = ETXB_GQ_PART, HV = HD / 8;
@@ -390,6 +396,12 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
   // and reads only its own), then the partitions' partial outputs and statistics
   uint4* KB = (uint4*)sm.ring;
   uint4* VB = KB + 4 * ETXB_CONSUMERS;
+  // bf16 operands of the tensor-core products, rows padded to 68 words (bank-conflict-free fragment loads): the q heads,
+  // and a partition's probabilities split into a bf16 value and the bf16 of what that rounding lost
+  uint32_t* QB = (uint32_t*)(s.po + 4 * GQ * HD);                  // [8][68] words = [8 heads][136] bf16 (heads >= GQ: zero)
+  uint32_t* PH = QB + 8 * 68;                                      // [8][68] high parts of the probabilities
+  uint32_t* PLo = PH + 8 * 68;                                     // [8][68] low parts
+  for (int i = tid; i < 3 * 8 * 68; i += ETXB_CONSUMERS) QB[i] = 0u;
   float* PO = (float*)(sm.ring + ETXB_GQ_STAGE_BYTES);            // [np][GQ][HD] partial outputs
   float* PS = PO + (size_t)np * GQ * HD;                           // [np][GQ][2] max logit, exp sum
   const int t = tid & (PL - 1), qr = tid >> 7;                     // K: position t, dims [32 qr, 32 qr + 32);  V: dim t, blocks 2 qr, 2 qr + 1
@@ -460,6 +472,8 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
     head_norm_rope_s<128>(s.raw + warp * HD, d.qw ? s.cw + HD : nullptr, s.cw, HD, d.eps, o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) s.qs[warp * HD + lane * 4 + j] = o[j];
+    QB[warp * 68 + 2 * lane] = pack_bf(o[0], o[1]);                // (the rotated q values are bf16 values already)
+    QB[warp * 68 + 2 * lane + 1] = pack_bf(o[2], o[3]);
   } else if (warp == GQ) {
     float o[8];
     head_norm_rope_s<128>(s.raw + GQ * HD, d.kw ? s.cw + 2 * HD : nullptr, s.cw, HD, d.eps, o);
@@ -489,30 +503,31 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
     const int ntok = min(PL, seq - t0);
     auto cached = [&](int tt) { return tt < ntok && tt != tpos; };
     fetch_tab(part + 1);
-    // ---- scores
-    cp_async_wait1();                                              // this partition's K pieces have landed (its V may still travel)
+    // ---- scores on the tensor cores: S[position][head] = K[position][:] . q[head][:].  Warp = (16 positions, half of the
+    //      128 dims): four m16n8k16 steps; A fragments straight from the staged K pieces (piece of dims chunk c and
+    //      position p sits at [c & 3][c >> 2][p]), B fragments from the bf16 q rows.  The two halves go to s.ph.
+    cp_async_wait1();                                              // this thread's K pieces have landed (its V may still travel)
+    csync();                                                       // .. and everybody else's: the fragments cross threads
     {
-      float acc[GQ];
+      const int mt = warp & 7, kh = warp >> 3, g8 = lane >> 2, t4 = lane & 3;
+      const uint32_t* KW = (const uint32_t*)KB;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const int p0 = 16 * mt + g8;
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) acc[g] = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float kf[8];
-        unpack8(KB[j * ETXB_CONSUMERS + tid], kf);
-#pragma unroll
-        for (int g = 0; g < GQ; ++g) {
-          const float4 qa = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8), qb = *(const float4*)(s.qs + g * HD + (qr * 4 + j) * 8 + 4);
-          acc[g] = __fmaf_rn(kf[0], qa.x, acc[g]); acc[g] = __fmaf_rn(kf[1], qa.y, acc[g]);
-          acc[g] = __fmaf_rn(kf[2], qa.z, acc[g]); acc[g] = __fmaf_rn(kf[3], qa.w, acc[g]);
-          acc[g] = __fmaf_rn(kf[4], qb.x, acc[g]); acc[g] = __fmaf_rn(kf[5], qb.y, acc[g]);
-          acc[g] = __fmaf_rn(kf[6], qb.z, acc[g]); acc[g] = __fmaf_rn(kf[7], qb.w, acc[g]);
-        }
+      for (int q = 0; q < 4; ++q) {
+        const int ks = 4 * kh + q, c0 = 2 * ks, c1 = 2 * ks + 1;
+        const uint32_t a0 = KW[(((c0 & 3) * ETXB_CONSUMERS + (c0 >> 2) * PL + p0) << 2) + t4];
+        const uint32_t a1 = KW[(((c0 & 3) * ETXB_CONSUMERS + (c0 >> 2) * PL + p0 + 8) << 2) + t4];
+        const uint32_t a2 = KW[(((c1 & 3) * ETXB_CONSUMERS + (c1 >> 2) * PL + p0) << 2) + t4];
+        const uint32_t a3 = KW[(((c1 & 3) * ETXB_CONSUMERS + (c1 >> 2) * PL + p0 + 8) << 2) + t4];
+        mma16816(c, a0, a1, a2, a3, QB[g8 * 68 + 8 * ks + t4], QB[g8 * 68 + 8 * ks + 4 + t4]);
       }
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) s.ph[(qr * GQ + g) * PL + t] = acc[g];
+      const int h0 = 2 * t4;
+      if (h0 < GQ) { s.ph[(kh * GQ + h0) * PL + p0] = c[0]; s.ph[(kh * GQ + h0) * PL + p0 + 8] = c[2]; }
+      if (h0 + 1 < GQ) { s.ph[(kh * GQ + h0 + 1) * PL + p0] = c[1]; s.ph[(kh * GQ + h0 + 1) * PL + p0 + 8] = c[3]; }
     }
-    request_k(part + 1);                                           // (this thread's own K pieces are consumed: no barrier needed before overwriting them)
     csync();
+    request_k(part + 1);                                           // every warp is done with the K pieces: the next partition's may land
     // ---- softmax statistics: one warp per q head, lane holds positions lane + 32 k
     if (warp < GQ) {
       const int g = warp;
@@ -520,7 +535,7 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int tt = lane + 32 * k;
-        const float dot = __fadd_rn(__fadd_rn(__fadd_rn(s.ph[g * PL + tt], s.ph[(GQ + g) * PL + tt]), s.ph[(2 * GQ + g) * PL + tt]), s.ph[(3 * GQ + g) * PL + tt]);
+        const float dot = __fadd_rn(s.ph[g * PL + tt], s.ph[(GQ + g) * PL + tt]);
         sv[k] = cached(tt) ? __fmul_rn(dot, d.scale) : -INFINITY;
         m = fmaxf(m, sv[k]);
       }
@@ -536,49 +551,62 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float pr = cached(lane + 32 * k) ? expf(__fsub_rn(sv[k], m)) : 0.f;
-        s.sc[g * PL + lane + 32 * k] = pr;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(pr), lo = __float2bfloat16_rn(__fsub_rn(pr, __bfloat162float(hi)));
+        ((__nv_bfloat16*)PH)[g * 136 + lane + 32 * k] = hi;
+        ((__nv_bfloat16*)PLo)[g * 136 + lane + 32 * k] = lo;
         l = __fadd_rn(l, pr);
       }
       l = warp_sum(l);
       const float pn = owner ? expf(__fsub_rn(snew, m)) : 0.f;
       if (lane == 0) { s.st[g] = m; s.st[GQ + g] = __fadd_rn(l, pn); s.st[2 * GQ + g] = pn; }
     }
-    csync();
-    // ---- output
-    cp_async_wait1();                                              // this partition's V pieces have landed (the next K may still travel)
+    // ---- output on the tensor cores: O[dim][head] = sum_pos V[dim][pos] P[head][pos].  Warp = (16 dims, half of the
+    //      partition's eight cache blocks): per block one m16n8k16 step for the high and one for the low part of the
+    //      probabilities; A fragments straight from the staged V pieces (block b, positions 8 v .. of dim d at
+    //      [2 (b & 1) + v][b >> 1][d]).  Slots that are not cached yet (last partition only) are zeroed first: a
+    //      probability of 0 does not neutralise whatever bits a stale slot holds.
+    cp_async_wait1();                                              // this thread's V pieces have landed (the next K may still travel)
+    if (part == np - 1) {
+      __nv_bfloat16* vb = (__nv_bfloat16*)VB;
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int v = 0; v < 2; ++v) {
+          const int base = (2 * qr + u) * BS + 8 * v;
+          if (base + 8 > ntok || (tpos >= base && tpos < base + 8))
+#pragma unroll
+            for (int o = 0; o < 8; ++o)
+              if (!cached(base + o)) vb[(((2 * u + v) * ETXB_CONSUMERS + tid) << 3) + o] = __float2bfloat16_rn(0.f);
+        }
+    }
+    csync();                                                       // the probabilities and everybody's V pieces are in place
     {
-      float acc[GQ];
+      const int mt = warp & 7, kh = warp >> 3, g8 = lane >> 2, t4 = lane & 3;
+      const uint32_t* VW = (const uint32_t*)VB;
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      const int d0 = 16 * mt + g8;
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) acc[g] = 0.f;
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int tb = (2 * qr + u) * BS;
-        if (tb < ntok) {
-          float f[16];
-          unpack8(VB[(2 * u) * ETXB_CONSUMERS + tid], f); unpack8(VB[(2 * u + 1) * ETXB_CONSUMERS + tid], f + 8);
-          if (part == np - 1) {                                    // (only the last partition has slots that are not cached yet)
-#pragma unroll
-            for (int o = 0; o < 16; ++o) f[o] = cached(tb + o) ? f[o] : 0.f;
-          }
-#pragma unroll
-          for (int g = 0; g < GQ; ++g) {
-#pragma unroll
-            for (int o4 = 0; o4 < 4; ++o4) {
-              const float4 pr = *(const float4*)(s.sc + g * PL + tb + 4 * o4);
-              acc[g] = __fmaf_rn(pr.x, f[4 * o4], acc[g]); acc[g] = __fmaf_rn(pr.y, f[4 * o4 + 1], acc[g]);
-              acc[g] = __fmaf_rn(pr.z, f[4 * o4 + 2], acc[g]); acc[g] = __fmaf_rn(pr.w, f[4 * o4 + 3], acc[g]);
-            }
-          }
+      for (int q = 0; q < 4; ++q) {
+        const int b = 4 * kh + q;
+        if (b * BS < ntok) {
+          const int pu = 2 * (b & 1), pq = (b >> 1) * PL;
+          const uint32_t a0 = VW[((pu * ETXB_CONSUMERS + pq + d0) << 2) + t4];
+          const uint32_t a1 = VW[((pu * ETXB_CONSUMERS + pq + d0 + 8) << 2) + t4];
+          const uint32_t a2 = VW[(((pu + 1) * ETXB_CONSUMERS + pq + d0) << 2) + t4];
+          const uint32_t a3 = VW[(((pu + 1) * ETXB_CONSUMERS + pq + d0 + 8) << 2) + t4];
+          mma16816(c, a0, a1, a2, a3, PH[g8 * 68 + 8 * b + t4], PH[g8 * 68 + 8 * b + 4 + t4]);
+          mma16816(c, a0, a1, a2, a3, PLo[g8 * 68 + 8 * b + t4], PLo[g8 * 68 + 8 * b + 4 + t4]);
         }
       }
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) s.po[(qr * GQ + g) * HD + t] = acc[g];
+      const int h0 = 2 * t4;
+      if (h0 < GQ) { s.po[(kh * GQ + h0) * HD + d0] = c[0]; s.po[(kh * GQ + h0) * HD + d0 + 8] = c[2]; }
+      if (h0 + 1 < GQ) { s.po[(kh * GQ + h0 + 1) * HD + d0] = c[1]; s.po[(kh * GQ + h0 + 1) * HD + d0 + 8] = c[3]; }
     }
-    request_v(part + 1);
     csync();
+    request_v(part + 1);                                           // every warp is done with the V pieces
     for (int idx = tid; idx < GQ * HD; idx += ETXB_CONSUMERS) {
       const int g = idx >> 7, dd = idx & (HD - 1);
-      float o = __fadd_rn(__fadd_rn(__fadd_rn(s.po[g * HD + dd], s.po[(GQ + g) * HD + dd]), s.po[(2 * GQ + g) * HD + dd]), s.po[(3 * GQ + g) * HD + dd]);
+      float o = __fadd_rn(s.po[g * HD + dd], s.po[(GQ + g) * HD + dd]);
       if (owner) o = __fmaf_rn(s.st[2 * GQ + g], s.vnew[dd], o);
       PO[((size_t)part * GQ + g) * HD + dd] = o;
       if (dd == 0) { PS[(part * GQ + g) * 2] = s.st[g]; PS[(part * GQ + g) * 2 + 1] = s.st[GQ + g]; }

@@ -91,26 +91,38 @@ def test_columns_do_not_depend_on_their_neighbours():
     prog.close()
 
 
-def test_whole_sequence_attention_equals_the_partitioned_form():
-    """20 sequences of a 150-token prompt (two partitions of 128 positions): at B = 20 the attention grid has one task per
-    (sequence, kv head) that walks the partitions itself; at B = 10 it has one task per partition and a merge through
-    flagged partials.  Same partition boundaries and order of sums: tokens and logits are bit-identical."""
-    od = MID
+def test_whole_sequence_attention_agrees_with_the_partitioned_form():
+    """20 sequences of a 150-token prompt (two partitions of 128 positions) through ONE layer, so that nothing but the
+    attention phase separates the two forms: at B = 20 the attention grid has one task per (sequence, kv head) that
+    walks the partitions itself with its products on the tensor cores (bf16 q / K / V, the probabilities as a bf16 value
+    plus the bf16 of its rounding error, fp32 accumulation); at B = 10 it has one task per partition on the fp32 pipes
+    and a merge through flagged partials.  Same partition boundaries and merge order, sums in another order: the KV
+    caches are bit-identical, the attention output agrees within 2 bf16 ulps per element with >= 90 % of the elements
+    identical.  (Through several MoE layers a one-ulp difference can flip a near-tie routing decision, which is why the
+    multi-layer comparisons are made against the oracle with its tie rule, not between the two forms.)"""
+    from dataclasses import replace
+    od = replace(MID, L=1)
     W = O.SyntheticWeights(od, seed=35, gamma="ones")
     prompts = np.random.default_rng(8).integers(0, od.V, (20, 150))
     whole = program(od, W, 20, 192)
     assert whole.info["attn_whole"] and whole.info["attn"][2] == 2
-    got = whole.generate(prompts, 6)
-    logits = whole.read("logits")
+    whole.generate(prompts, 1)
+    att, kc, vc = whole.read("attn_out"), whole.read("kc"), whole.read("vc")
     whole.close()
     for half in range(2):
         part = program(od, W, 10, 192)
         assert not part.info["attn_whole"]
-        want = part.generate(prompts[10 * half: 10 * half + 10], 6)
-        plog = part.read("logits")
+        part.generate(prompts[10 * half: 10 * half + 10], 1)
+        patt, pkc, pvc = part.read("attn_out"), part.read("kc"), part.read("vc")
         part.close()
-        assert np.array_equal(got[10 * half: 10 * half + 10], want)
-        assert np.array_equal(logits[10 * half: 10 * half + 10], plog)
+        nblk = pkc.shape[1] // 10
+        assert np.array_equal(kc[:, 10 * half * nblk: (10 * half + 10) * nblk], pkc) and np.array_equal(vc[:, 10 * half * nblk: (10 * half + 10) * nblk], pvc)
+        g, w = att[10 * half: 10 * half + 10], patt
+        scale = np.abs(w).max()
+        ulp = np.maximum(np.abs(w) * 2.0 ** -7, scale / 4096)
+        same = float(np.mean(g == w))
+        print(f"whole-sequence vs partitioned attention, columns {10 * half}..{10 * half + 9}: max diff {np.abs(g - w).max() / scale:.2e} of scale, {same:.1%} identical")
+        assert np.all(np.abs(g - w) <= 2 * ulp) and same >= 0.9
 
 
 def test_one_batched_step_against_the_oracle_state():
