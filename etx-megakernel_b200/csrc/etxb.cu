@@ -183,7 +183,7 @@ static int32_t check_mla_block(const unsigned char* blk, size_t bytes) {
   else if (a.maxlen < 1 || a.maxlen > ETXB_MLA_MAXCTX) why = "1 <= maxlen <= 8192";
   else if (!a.qkv || !a.kvln || !a.cos_sin || !a.wkvb || !a.cache || !a.positions || !a.out || !a.tmp) why = "null pointer";
   else if (a.max_parts < 1 || a.max_parts > 64 || (long long)a.max_parts * ETXB_MLA_PART < a.maxlen) why = "max_parts partitions of 128 positions cover maxlen (at most 64)";
-  else if (a.nblocks > (uint32_t)(a.NH * a.max_parts)) why = "the grid is max_parts * NH tasks";
+  else if (a.nblocks != (uint32_t)(a.NH * (a.max_parts + ETXB_MLA_FIN))) why = "the grid is (max_parts + 4) * NH tasks: the partitions, then four finishing tasks per head";
   if (!why) return ETXB_OK;
   char m[256];
   snprintf(m, sizeof m, "mla_attn block (NH=%d, C=%d, DN=%d, DR=%d, DV=%d, maxlen=%d) outside the tile: %s", a.NH, a.C, a.DN, a.DR, a.DV, a.maxlen, why);

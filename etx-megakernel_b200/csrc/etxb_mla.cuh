@@ -15,8 +15,9 @@
 // position's latent row from the kv_a row (576 values: cheaper than a phase of its own) and uses it from shared
 // memory -- the task (head 0, last partition) also stores it into the cache --, folds W_UK into its head's query, and
 // produces its partition's softmax statistics and weighted latent.  The partials travel as flagged (value, step) pairs
-// like those of the grouped GQA tile (etxb_attn_gq.cuh): the task of the context's last partition polls them, merges
-// them in ascending partition order and applies W_UV.  The cached rows come from L2 (all heads read the same rows).
+// like those of the grouped GQA tile (etxb_attn_gq.cuh); four finishing tasks per head, placed after the partition tasks
+// in the grid, poll them, merge them in ascending partition order and apply a quarter of W_UV's rows each.  The cached
+// rows come from L2 (all heads read the same rows).
 #pragma once
 #include "etxb_attn_gq.cuh"
 
@@ -24,6 +25,7 @@ namespace etxb {
 
 #define ETXB_MLA_MAXCTX 8192   // longest context (64 partitions)
 #define ETXB_MLA_PART 128      // positions per task
+#define ETXB_MLA_FIN 4         // finishing tasks per head: each merges the head's partials and applies a quarter of W_UV's rows
 
 struct etxb_mla_args {
   const void* qkv;             // 0   bf16 [NH * (DN + DR) + C + DR]: the q heads (nope | rope part each), then the kv_a row (c | k_pe)
@@ -36,20 +38,111 @@ struct etxb_mla_args {
   int32_t NH, C, DN, DR, DV, maxlen;   // 56..79
   float scale, eps;            // 80..87
   void* tmp;                   // 88  (value, flag) pairs [NH][max_parts][C + 8]: weighted latent, then max logit and exp sum
-  int32_t max_parts, tag;      // 96, 100: partitions the grid covers (tasks = max_parts * NH); tag tells the layers that share tmp apart
+  int32_t max_parts, tag;      // 96, 100: partitions the grid covers (tasks = (max_parts + 4) * NH: partitions, then finishing tasks); tag tells the layers that share tmp apart
   int32_t pad[2];              // 104..111
   uint32_t grid[3], nblocks;   // 112..127
 };
 
+// A finishing task of head h: waits (bounded) for the head's np partials, merges them -- weights exp(m_p - max m),
+// partitions in ascending order -- and applies rows [f * DV / FIN, ..) of W_UV.  The finishing tasks come after the
+// partition tasks in the grid, so whatever they wait for runs on another worker or ran before them on their own; the
+// partition tasks never wait.  Four tasks per head instead of one cut the tail of the phase (merge + all of W_UV by the
+// last partition's task: 15 us) to a third.
+__device__ __forceinline__ void mla_finish(const etxb_mla_args& d, const Smem& sm, int h, int f, int np) {
+  const int C = d.C, DN = d.DN, DV = d.DV, PW = C + 8;
+  const int tid = tidx(), lane = tid & 31, warp = tid >> 5;
+  const uint32_t fl = pair_flag(sm.epoch, d.tag << 16);
+  float* oc = sm.xs;                                               // [C] merged, normalised latent
+  float* wl = oc + 512;                                            // [np <= 64] max logits, then weights
+  float* es = wl + 64;                                             // [np] exp sums
+  float* red = es + 64;
+  const __nv_bfloat16* wuv = (const __nv_bfloat16*)d.wkvb + ((size_t)h * (DN + DV) + DN) * C;
+  const int v_lo = f * ((DV + ETXB_MLA_FIN - 1) / ETXB_MLA_FIN), v_hi = min(DV, v_lo + (DV + ETXB_MLA_FIN - 1) / ETXB_MLA_FIN);
+  // this task's rows of W_UV travel while it waits for the partials
+  uint4 w[2][2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int v = v_lo + warp + r * ETXB_CONSUMER_WARPS, j = 8 * lane + 256 * k;
+      w[r][k] = (v < v_hi && j < C) ? __ldg((const uint4*)(wuv + (size_t)v * C + j)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  const uint2* ph = (const uint2*)d.tmp + (size_t)h * d.max_parts * PW;
+  for (int q = tid; q < np; q += ETXB_CONSUMERS) {
+    wl[q] = poll_pair(ph + (size_t)q * PW + C, fl, sm);
+    es[q] = poll_pair(ph + (size_t)q * PW + C + 1, fl, sm);
+  }
+  csync();
+  if (warp == 0) {
+    float mm = -INFINITY;
+    for (int q = lane; q < np; q += 32) mm = fmaxf(mm, wl[q]);
+    mm = warp_max(mm);
+    float L = 0.f;
+    for (int q = lane; q < np; q += 32) {
+      const float wq = expf(__fsub_rn(wl[q], mm));
+      wl[q] = wq;
+      L = __fmaf_rn(wq, es[q], L);
+    }
+    L = warp_sum(L);
+    if (lane == 0) red[0] = L;
+  }
+  csync();
+  for (int j = tid; j < C; j += ETXB_CONSUMERS) {
+    float o = 0.f;
+    for (int q0 = 0; q0 < np; q0 += 8) {                             // eight partitions' pairs requested at once
+      uint2 first[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) first[u] = ld_pair(ph + (size_t)min(q0 + u, np - 1) * PW + j);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (q0 + u < np) o = __fmaf_rn(wl[q0 + u], first[u].y == fl ? __uint_as_float(first[u].x) : poll_pair(ph + (size_t)(q0 + u) * PW + j, fl, sm), o);
+    }
+    oc[j] = __fdiv_rn(o, red[0]);
+  }
+  csync();
+  // ---- out[v] = W_UV[h][v] . o_c: a warp per output row, lanes over the columns
+  for (int r = 0; r < 2; ++r) {
+    const int v = v_lo + warp + r * ETXB_CONSUMER_WARPS;
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int j = 8 * lane + 256 * k;
+      if (j < C) {
+        const uint4 x = w[r][k];
+        const float wf[8] = {bf_lo(x.x), bf_hi(x.x), bf_lo(x.y), bf_hi(x.y), bf_lo(x.z), bf_hi(x.z), bf_lo(x.w), bf_hi(x.w)};
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc = __fmaf_rn(wf[u], oc[j + u], acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0 && v < v_hi) ((__nv_bfloat16*)d.out)[(size_t)h * DV + v] = __float2bfloat16_rn(acc);
+  }
+  for (int v0 = v_lo + 2 * ETXB_CONSUMER_WARPS; v0 < v_hi; v0 += ETXB_CONSUMER_WARPS) {   // (more than 32 rows per finishing task: DV > 128)
+    const int v = v0 + warp;
+    float acc = 0.f;
+    if (v < v_hi)
+      for (int j = 8 * lane; j < C; j += 256) {
+        const uint4 x = __ldg((const uint4*)(wuv + (size_t)v * C + j));
+        const float wf[8] = {bf_lo(x.x), bf_hi(x.x), bf_lo(x.y), bf_hi(x.y), bf_lo(x.z), bf_hi(x.z), bf_lo(x.w), bf_hi(x.w)};
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc = __fmaf_rn(wf[u], oc[j + u], acc);
+      }
+    acc = warp_sum(acc);
+    if (lane == 0 && v < v_hi) ((__nv_bfloat16*)d.out)[(size_t)h * DV + v] = __float2bfloat16_rn(acc);
+  }
+  csync();
+}
+
 __device__ __noinline__ void tile_mla_attn(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
   const etxb_mla_args& d = *(const etxb_mla_args*)a;
-  if (blk >= (int)d.nblocks || blk >= d.NH * d.max_parts) return;
-  const int part_i = blk / d.NH, h = blk - part_i * d.NH;
+  if (blk >= (int)d.nblocks || blk >= d.NH * (d.max_parts + ETXB_MLA_FIN)) return;
+  const int part_i = blk / d.NH, h = blk - part_i * d.NH;            // part_i >= max_parts: finishing task part_i - max_parts of the head
   const int C = d.C, DN = d.DN, DR = d.DR, DV = d.DV, QH = DN + DR, ROW = C + DR, PW = C + 8;
   const long long pos = (const void*)d.positions == (const void*)S.positions ? (long long)S.pos : __ldcg((const long long*)d.positions);
   if (pos < 0 || pos >= d.maxlen || pos >= ETXB_MLA_MAXCTX) return;
   const int seq_all = (int)pos + 1;
   const int np = min((seq_all + ETXB_MLA_PART - 1) / ETXB_MLA_PART, d.max_parts);
+  if (part_i >= d.max_parts) { mla_finish(d, sm, h, part_i - d.max_parts, np); return; }
   if (part_i >= np) return;
   const int tbase = part_i * ETXB_MLA_PART;                        // first position of this task
   const int seq = min(seq_all - tbase, ETXB_MLA_PART);               // its positions: tbase .. tbase + seq - 1
@@ -221,74 +314,6 @@ __device__ __noinline__ void tile_mla_attn(const unsigned char* a, int blk, cons
     st_pair(pw + j, v, fl);
   }
   if (tid == 0) { st_pair(pw + C, m, fl); st_pair(pw + C + 1, l, fl); }
-  if (part_i != np - 1) return;
-  // ---- merge (the task of the context's last partition): weights exp(m_p - max m), partitions in ascending order
-  csync();
-  float* wl = sc;                                                  // [np] max logits, then weights
-  float* es = sc + 64;                                             // [np] exp sums
-  const uint2* ph = (const uint2*)d.tmp + (size_t)h * d.max_parts * PW;
-  for (int q = tid; q < np; q += ETXB_CONSUMERS) {
-    wl[q] = poll_pair(ph + (size_t)q * PW + C, fl, sm);
-    es[q] = poll_pair(ph + (size_t)q * PW + C + 1, fl, sm);
-  }
-  csync();
-  if (warp == 0) {
-    float mm = -INFINITY;
-    for (int q = lane; q < np; q += 32) mm = fmaxf(mm, wl[q]);
-    mm = warp_max(mm);
-    float L = 0.f;
-    for (int q = lane; q < np; q += 32) {
-      const float w = expf(__fsub_rn(wl[q], mm));
-      wl[q] = w;
-      L = __fmaf_rn(w, es[q], L);
-    }
-    L = warp_sum(L);
-    if (lane == 0) red[0] = L;
-  }
-  csync();
-  for (int j = tid; j < C; j += ETXB_CONSUMERS) {
-    float o = 0.f;
-    for (int q0 = 0; q0 < np; q0 += 8) {                             // eight partitions' pairs requested at once
-      uint2 first[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) first[u] = ld_pair(ph + (size_t)min(q0 + u, np - 1) * PW + j);
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (q0 + u < np) o = __fmaf_rn(wl[q0 + u], first[u].y == fl ? __uint_as_float(first[u].x) : poll_pair(ph + (size_t)(q0 + u) * PW + j, fl, sm), o);
-    }
-    oc[j] = __fdiv_rn(o, red[0]);
-  }
-  csync();
-  // ---- out[v] = W_UV[h][v] . o_c: a warp per output row, four rows' loads in flight, lanes over the columns
-  const __nv_bfloat16* wuv = wuk + (size_t)DN * C;
-  for (int v0 = warp; v0 < DV; v0 += 4 * ETXB_CONSUMER_WARPS) {
-    uint4 w[4][2];
-#pragma unroll
-    for (int r = 0; r < 4; ++r)
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int v = v0 + r * ETXB_CONSUMER_WARPS, j = 8 * lane + 256 * k;
-        w[r][k] = (v < DV && j < C) ? __ldg((const uint4*)(wuv + (size_t)v * C + j)) : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int v = v0 + r * ETXB_CONSUMER_WARPS;
-      float acc = 0.f;
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const int j = 8 * lane + 256 * k;
-        if (j < C) {
-          const uint4 x = w[r][k];
-          const float wf[8] = {bf_lo(x.x), bf_hi(x.x), bf_lo(x.y), bf_hi(x.y), bf_lo(x.z), bf_hi(x.z), bf_lo(x.w), bf_hi(x.w)};
-#pragma unroll
-          for (int u = 0; u < 8; ++u) acc = __fmaf_rn(wf[u], oc[j + u], acc);
-        }
-      }
-      acc = warp_sum(acc);
-      if (lane == 0 && v < DV) ((__nv_bfloat16*)d.out)[(size_t)h * DV + v] = __float2bfloat16_rn(acc);
-    }
-  }
-  csync();
 }
 
 }  // namespace etxb

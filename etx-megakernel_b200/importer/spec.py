@@ -163,7 +163,7 @@ from ..ops import mla as _mla  # noqa: E402
 ARGUMENTS["mla_attn"] = [("ptr", "qkv"), ("ptr", 'W(pl + "kvln")'), ("ptr", "cos_sin"), ("ptr", 'W(pl + "wkvb")'), ("ptr", "ckv + layer"), ("ptr", "positions"),
                          ("ptr", "attn_out"), ("i32", "NH"), ("i32", "C"), ("i32", "DN"), ("i32", "DR"), ("i32", "DV"), ("i32", "maxlen"), ("f32", "scale"), ("f32", "eps"), ("ptr", "mla_tmp"),
                          ("i32", "parts"), ("i32", "layer")]
-OPERATORS["mla_attn"] = Operator("mla_attn", "etxb::tile_mla_attn", ("parts*NH", "1", "1"), "C <= 512, DR <= 64, DN + DR <= 256, context <= 8192", dict(MAX_CTX=_mla.MAX_CTX),
+OPERATORS["mla_attn"] = Operator("mla_attn", "etxb::tile_mla_attn", ("(parts+4)*NH", "1", "1"), "C <= 512, DR <= 64, DN + DR <= 256, context <= 8192", dict(MAX_CTX=_mla.MAX_CTX),
                                  ("qkv", "latent_norm_weight", "cos_sin", "kv_b_proj", "latent_cache", "positions"), ("latent_cache", "output"),
                                  layouts="latent cache [position][C + DR] (normed latent | rotated k_pe), kv_b_proj [head][DN rows of W_UK, DV rows of W_UV][C]",
                                  arguments={"mla_attn": ARGUMENTS["mla_attn"]})
@@ -213,8 +213,8 @@ def validate_values(export, values, grid):
             raise ValueError(f"{spec.name}: grid must be one task per kv head")
     elif name == "mla_attn":
         _mla.check_shape(*values[7:13])
-        if values[16] != _mla.partitions(values[12]) or gx * gy * gz != values[7] * values[16]:
-            raise ValueError(f"{spec.name}: max_parts must cover maxlen in partitions of {_mla.PART} and the grid is max_parts * NH tasks")
+        if values[16] != _mla.partitions(values[12]) or gx * gy * gz != values[7] * (values[16] + _mla.FINISHERS):
+            raise ValueError(f"{spec.name}: max_parts must cover maxlen in partitions of {_mla.PART} and the grid is (max_parts + {_mla.FINISHERS}) * NH tasks")
     elif name == "attn_fused":
         _attn.check_fused(*values[17:25])
         whole = bool(values[23]) and bool(values[24] & _attn.GQ_WHOLE)

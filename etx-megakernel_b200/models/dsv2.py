@@ -289,10 +289,10 @@ def build_graph(d: MlaDims, ptr, maxlen: int = 1072, machine: MachineModel | str
                   resid_in=ptr("resid") if first else ptr("resid2"), resid_out=0 if first else ptr("resid"), ln=Wl("ln1"), R=0 if first else 1, eps=d.eps,
                   mode=op_gemv.MODE_NORM, nb=1)
         prev = add(f"qkv_{L}", "dsl_gemv_fold", "qkv", L, blob, t, prev, f"E_qkv_{L}", d.NQKV, d.H, after="")
-        blob = argblock.pack_named(ent["mla_attn"], (d.NH * nparts, 1, 1), qkv=ptr("qkv"), kvln=Wl("kvln"), cos_sin=ptr("cos_sin"), wkvb=Wl("wkvb"),
+        blob = argblock.pack_named(ent["mla_attn"], (d.NH * (nparts + op_mla.FINISHERS), 1, 1), qkv=ptr("qkv"), kvln=Wl("kvln"), cos_sin=ptr("cos_sin"), wkvb=Wl("wkvb"),
                                    cache=ptr("ckv") + L * cache_layer_bytes, positions=ptr("positions"), out=ptr("attn_out"), NH=d.NH, C=d.C, DN=d.DN, DR=d.DR,
                                    DV=d.DV, maxlen=maxlen, scale=d.scale, eps=d.eps, tmp=ptr("mla_tmp"), max_parts=nparts, tag=L & 0xff)
-        prev = add(f"attn_{L}", "mla_attn", "attn_fused", L, blob, d.NH * nparts, prev, f"E_attn_{L}")
+        prev = add(f"attn_{L}", "mla_attn", "attn_fused", L, blob, d.NH * (nparts + op_mla.FINISHERS), prev, f"E_attn_{L}")
         t, rpt = m.gemv_tasks(d.H)
         blob = gb("dsl_gemv", t, W=Wl("wo"), x=ptr("attn_out"), out=ptr("o"), M=d.H, K=d.NH * d.DV, rpt=rpt, tpe=1, eps=d.eps, nb=1)
         prev = add(f"o_proj_{L}", "dsl_gemv", "o_proj", L, blob, t, prev, f"E_o_{L}", d.H, d.NH * d.DV, after="")

@@ -10,8 +10,8 @@ It stands where the reference's DeepSeek-V2-Lite graph runs q_absorb, the chunke
   cache     bf16 [maxlen][C + DR]            the layer's latent cache (row `pos` is written by head 0's task)
   positions int64 [1],  out bf16 [NH * DV]
   tmp       (value, flag) pairs [NH][max_parts][C + 8] (8 bytes each): the partitions' partial results; the task of the
-            context's last partition merges them and applies W_UV.  max_parts * 128 >= maxlen; grid = max_parts * NH tasks
-            (task = partition * NH + head); tag = a number that differs between the grids sharing tmp (the layer)
+            four finishing tasks per head merge them and apply a quarter of W_UV each.  max_parts * 128 >= maxlen; grid =
+            (max_parts + 4) * NH tasks (task = partition * NH + head, then the finishing tasks); tag = a number that differs between the grids sharing tmp (the layer)
 """
 from __future__ import annotations
 
@@ -19,6 +19,7 @@ from ._layout import entry
 
 ARG_BYTES, GRID_OFF = 128, 112
 PART = 128
+FINISHERS = 4            # finishing tasks per head, after the partition tasks in the grid
 MAX_CTX = 8192
 PARAMS = [("qkv", "ptr addrspace(1)", 0, 8), ("kvln", "ptr addrspace(1)", 8, 8), ("cos_sin", "ptr addrspace(1)", 16, 8),
           ("wkvb", "ptr addrspace(1)", 24, 8), ("cache", "ptr addrspace(1)", 32, 8), ("positions", "ptr addrspace(1)", 40, 8),

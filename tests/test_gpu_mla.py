@@ -58,10 +58,10 @@ def test_latent_attention_tile_against_the_oracle(NH, ctx):
     t_out = torch.zeros(NH * d.DV, dtype=torch.bfloat16, device=DEV)
     nparts = op_mla.partitions(maxlen)
     t_tmp = torch.zeros((op_mla.tmp_pairs(NH, d.C, maxlen), 2), dtype=torch.float32, device=DEV)
-    blob = argblock.pack_named(ENT["mla_attn"], (NH * nparts, 1, 1), qkv=t_qkv.data_ptr(), kvln=t_ln.data_ptr(), cos_sin=t_cs.data_ptr(), wkvb=t_w.data_ptr(),
+    blob = argblock.pack_named(ENT["mla_attn"], (NH * (nparts + op_mla.FINISHERS), 1, 1), qkv=t_qkv.data_ptr(), kvln=t_ln.data_ptr(), cos_sin=t_cs.data_ptr(), wkvb=t_w.data_ptr(),
                                cache=t_cache.data_ptr(), positions=t_pos.data_ptr(), out=t_out.data_ptr(), NH=NH, C=d.C, DN=d.DN, DR=d.DR, DV=d.DV,
                                maxlen=maxlen, scale=d.scale, eps=d.eps, tmp=t_tmp.data_ptr(), max_parts=nparts, tag=3)
-    op_launch("mla_attn", blob, NH * nparts)
+    op_launch("mla_attn", blob, NH * (nparts + op_mla.FINISHERS))
     got_cache, got = host(t_cache), host(t_out)
     assert np.array_equal(got_cache[ctx], cache[ctx]), "the new cache row differs from the oracle's"
     assert np.array_equal(got_cache[:ctx], before[:ctx]) and not got_cache[ctx + 1:].any()
@@ -144,9 +144,9 @@ def test_blocks_outside_the_tile_are_refused():
     with pytest.raises(ValueError, match="mla_attn"):
         argblock.pack_named(ENT["mla_attn"], (2, 1, 1), qkv=t.data_ptr(), kvln=t.data_ptr(), cos_sin=t.data_ptr(), wkvb=t.data_ptr(), cache=t.data_ptr(),
                             positions=t.data_ptr(), out=t.data_ptr(), NH=2, C=1024, DN=128, DR=64, DV=128, maxlen=64, scale=0.1, eps=1e-6, tmp=t.data_ptr(), max_parts=1, tag=0)
-    good = argblock.pack_named(ENT["mla_attn"], (2, 1, 1), qkv=t.data_ptr(), kvln=t.data_ptr(), cos_sin=t.data_ptr(), wkvb=t.data_ptr(), cache=t.data_ptr(),
+    good = argblock.pack_named(ENT["mla_attn"], (2 * 5, 1, 1), qkv=t.data_ptr(), kvln=t.data_ptr(), cos_sin=t.data_ptr(), wkvb=t.data_ptr(), cache=t.data_ptr(),
                                positions=t.data_ptr(), out=t.data_ptr(), NH=2, C=512, DN=128, DR=64, DV=128, maxlen=64, scale=0.1, eps=1e-6, tmp=t.data_ptr(), max_parts=1, tag=0)
     bad = bytearray(good)
     bad[60:64] = (2048).to_bytes(4, "little")                 # C beyond the tile's shared-memory layout, patched past the Python check
     with pytest.raises(EtxbError, match="mla_attn"):
-        op_launch("mla_attn", bytes(bad), 2)
+        op_launch("mla_attn", bytes(bad), 2 * 5)

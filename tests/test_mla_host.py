@@ -64,7 +64,7 @@ def test_the_full_size_graph_verifies_and_simulates():
     plan = compile_graph(g, "b200", {"POOL": len(pool.bytes())})
     assert verify_plan(plan) == [] and not simulate(plan).deadlock
     shape = plan.inst.grid_shapes
-    assert shape["attn_1"] == (16 * 9,) and shape["moe_up_1"][0] <= 148 and shape["moe_down_1"][0] <= 148
+    assert shape["attn_1"] == (16 * (9 + 4),) and shape["moe_up_1"][0] <= 148 and shape["moe_down_1"][0] <= 148
     rows = {r[0]: r for r in pool.rows}
     blk = pool.bytes()[rows["moe_up_1"][4]: rows["moe_up_1"][4] + 160]
     import struct
