@@ -157,8 +157,7 @@ __device__ __noinline__ void tile_mla_attn(const unsigned char* a, int blk, cons
   float* qpe = kpn + 64;        // [DR] this head's rotated q_pe (bf16 values)
   float* cs = qpe + 64;         // [2 DR] cos | sin of the position
   float* qc = cs + 128;         // [C] q_nope W_UK
-  float* oc = qc + 512;         // [C] softmax-weighted latent
-  float* part = oc + 512;       // [8][C] partial sums of the eight thread groups (q_c, then o_c)
+  float* part = qc + 512;       // [8][C] partial sums of the eight thread groups (q_c, then o_c)
   float* red = part + 4096;     // [64]
   float* sc = red + 64;         // [128] the partition's scores, then exp(s - m); the merge keeps its weights and sums here
   const __nv_bfloat16* qkv = (const __nv_bfloat16*)d.qkv;

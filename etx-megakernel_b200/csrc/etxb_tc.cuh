@@ -1,21 +1,21 @@
 // Batched decode on the Blackwell tensor cores: tcgen05.mma with the tokens as the M side (A operand, shared memory,
-// SWIZZLE_128B K-major), 128 weight rows as the N side (B operand, loaded by TMA tensor copies -- cp.async.bulk.tensor.2d
-// with SWIZZLE_128B, one tensor map per weight tensor, box 64 k x 128 rows) and fp32 accumulators in tensor memory, read
-// back with tcgen05.ld for the epilogue.
+// SWIZZLE_128B K-major), 128 or 256 weight rows as the N side (B operand, loaded by TMA tensor copies --
+// cp.async.bulk.tensor.2d with SWIZZLE_128B, one tensor map per weight tensor, boxes of 64 k x 128 rows, one or two per
+// instruction) and fp32 accumulators in tensor memory, read back with tcgen05.ld for the epilogue.
 //
 // These tiles serve the same grids as the mma.sync tiles of etxb_batch.cuh (column-batched GEMV, expert-grouped gate+up
 // and down: etx/ops/gemv.py:40-73, 176-289 and examples/vllm_llm/model.py:194-211 of the reference) and are what the
 // batched step uses.  Sizing, measured on B200: one tcgen05.mma (cta_group::1, kind::f16) takes 156 clocks whatever its
-// M, N (8 .. 256) or the number of accumulators in flight, so its cost is per instruction: with N = 128 weight rows per
-// instruction (4 KB of weights per k16 step) the pipe moves 26 bytes of weights per clock and SM, a little more than
-// the 22.5 the HBM delivers, and all of a batch's tokens (up to 32 here) ride along for free -- mma.sync m16n8k16, the
-// legacy path, managed about a third of that with 8 tokens per pass.
+// M, N (8 .. 256) or the number of accumulators in flight, so its cost is per instruction: with N = 256 weight rows per
+// instruction (8 KB of weights per k16 step) the pipe moves 52 bytes of weights per clock and SM, twice what the HBM
+// delivers (22.5), and all of a batch's tokens (up to 32 here) ride along for free -- mma.sync m16n8k16, the legacy
+// path, managed about a sixth of that with 8 tokens per pass.
 //
-// A task = a few tiles of 128 weight rows (or pairs: an expert's gate rows and up rows, accumulated side by side) x all
-// of K x up to 32 tokens.  Roles inside the CTA's consumer warps: every thread stages the tokens' vectors into the
-// swizzled layout, once per task; one thread issues the TMA loads of the weight tiles, k-chunk by k-chunk, through a
-// ring of 16 KB stages (as many as fit beside the tokens: 4 with 32 tokens of 2048 columns, 10 with up to 8); one
-// thread issues the MMAs (four k16 steps per 64-wide chunk) and commits each stage back to the loader; when the last
+// A task = a few tiles of up to 256 weight rows (two neighbouring blocks of 128 rows of a matrix, or an expert's 128 gate
+// rows and their 128 up rows) x all of K (or a K-slice) x up to 32 tokens.  Roles inside the CTA's consumer warps: every
+// thread stages the tokens' vectors into the swizzled layout, once per task; one thread issues the TMA loads of the
+// weight tiles, k-chunk by k-chunk, through a ring of 32 KB stages (as many as fit beside the tokens: 2 with 32 tokens
+// of 2048 columns, 5 with up to 8); one thread issues the MMAs (four k16 steps per 64-wide chunk) and commits each stage back to the loader; when the last
 // MMA of a tile has completed, four warps read its accumulators (one token per TMEM lane) and run the epilogue while
 // the next tile's MMAs fill the other accumulator buffer.  The weight ring of the one-token tiles is not in use during
 // a batched step (their producer warp has nothing to stream), so its shared memory and the general region form one
