@@ -256,7 +256,7 @@ static const void* const g_kernels[11] = {(const void*)etxb::etxb_megakernel<0>,
 static int kernel_index(const etxb_session* s) {
   const int v = s->force_full ? 0 : s->variant;
   if (s->xbase == nullptr) return v;
-  return (v == 10 ? 0 : v) + 5;
+  return (v >= 10 ? 0 : v) + 5;
 }
 
 static int32_t prepare_kernel(int device, int* workers_out) {

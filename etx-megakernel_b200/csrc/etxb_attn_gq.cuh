@@ -645,12 +645,11 @@ __device__ __noinline__ void attn_gq_seq(const etxb_attnf_args& d, int blk, cons
   csync();                                                         // the next task may overwrite the partials
 }
 
-// Fused attention, either form: gq > 0 in the argument block selects the grouped form above (head_dim 128, cache
-// blocks of 16, partitions of 128 positions), else the general tile.
-__device__ __forceinline__ void tile_attn_any(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
+// The grouped forms (gq > 0 in the argument block; head_dim 128, cache blocks of 16, partitions of 128): one task per
+// partition, or (part_len bit 24) one task per sequence and q group.
+__device__ __forceinline__ void tile_attn_gq(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
   const etxb_attnf_args& d = *(const etxb_attnf_args*)a;
-  if (d.gq == 0) { tile_attn_fused(a, blk, sm, S); return; }
-  if (blk >= (int)d.nblocks) return;
+  if (blk >= (int)d.nblocks || d.gq <= 0) return;
   if (d.part_len & ETXB_GQ_WHOLE) {
     switch (d.gq) {
       case 1: attn_gq_seq<1>(d, blk, sm, S); break;
@@ -666,6 +665,13 @@ __device__ __forceinline__ void tile_attn_any(const unsigned char* a, int blk, c
     case 4: attn_gq_impl<4>(d, blk, sm, S); break;
     default: attn_gq_impl<8>(d, blk, sm, S); break;
   }
+}
+
+// Fused attention, either form: gq > 0 in the argument block selects the grouped forms above, else the general tile.
+__device__ __forceinline__ void tile_attn_any(const unsigned char* a, int blk, const Smem& sm, const etxb_stepv& S) {
+  const etxb_attnf_args& d = *(const etxb_attnf_args*)a;
+  if (d.gq == 0) { tile_attn_fused(a, blk, sm, S); return; }
+  tile_attn_gq(a, blk, sm, S);
 }
 
 }  // namespace etxb
