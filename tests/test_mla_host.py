@@ -72,3 +72,43 @@ def test_the_full_size_graph_verifies_and_simulates():
     assert (mode & 0xff) == 2 and (mode >> 24) & 0xf == 2 and E == 64 and struct.unpack_from("<i", blk, 96)[0] == 8       # no renorm, 2 shared, 8 slots
     with pytest.raises(ValueError, match="mla_attn"):
         M.build_graph(M.MlaDims(name="x", H=256, NH=2, C=1024, DN=64, DR=32, DV=64, MI=128, E=4, TOPK=2, NS=0, DENSE_LAYERS=0, DENSE_INTER=0, L=1, V=512), ptr, 64)
+
+
+def test_latent_attention_block_layout_and_checks():
+    """The 128-byte block: field offsets, the grid of (partitions + finishing tasks) x heads, and the refusals of the
+    packer (shape outside the tile's shared-memory layout, a grid that does not match max_parts)."""
+    import struct
+    from etx_megakernel_b200 import ops
+    from etx_megakernel_b200.importer import argblock
+    from etx_megakernel_b200.ops import mla as op_mla
+    ent = ops.all_entries()["mla_attn"]
+    kw = dict(qkv=0x1000, kvln=0x2000, cos_sin=0x3000, wkvb=0x4000, cache=0x5000, positions=0x6000, out=0x7000, NH=16, C=512, DN=128, DR=64, DV=128,
+              maxlen=1072, scale=0.125, eps=1e-6, tmp=0x8000, max_parts=9, tag=5)
+    blob = argblock.pack_named(ent, (16 * (9 + op_mla.FINISHERS), 1, 1), **kw)
+    assert len(blob) == op_mla.ARG_BYTES == 128
+    assert struct.unpack_from("<7Q", blob, 0) == (0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 0x6000, 0x7000)
+    assert struct.unpack_from("<6i", blob, 56) == (16, 512, 128, 64, 128, 1072)
+    assert struct.unpack_from("<Q2i", blob, 88) == (0x8000, 9, 5)
+    assert struct.unpack_from("<4I", blob, 112) == (16 * 13, 1, 1, 16 * 13)
+    assert op_mla.partitions(1072) == 9 and op_mla.tmp_pairs(16, 512, 1072) == 16 * 9 * 520
+    with pytest.raises(ValueError, match="max_parts"):
+        argblock.pack_named(ent, (16 * 9, 1, 1), **kw)                               # the finishing tasks are missing from the grid
+    with pytest.raises(ValueError, match="max_parts"):
+        argblock.pack_named(ent, (16 * 12, 1, 1), **dict(kw, max_parts=8))           # 8 partitions do not cover 1072 positions
+    with pytest.raises(ValueError, match="multiples of 8"):
+        argblock.pack_named(ent, (16 * 13, 1, 1), **dict(kw, DR=60))
+    with pytest.raises(ValueError, match="context"):
+        argblock.pack_named(ent, (16 * 13, 1, 1), **dict(kw, maxlen=9000, max_parts=71))
+
+
+def test_split_k_keeps_one_wave_and_whole_slices():
+    """The K-split of the dense tensor-core grids: tasks stay within one wave of the workers, slices are multiples of 64
+    columns and at least 256 wide, a matrix with a wave of row blocks of its own is not split."""
+    from etx_megakernel_b200.ops import batch as op_batch
+    for M, K in ((5120, 2048), (2048, 4096), (128, 2048), (151936, 2048), (3648, 2048), (64, 2048), (2048, 1408), (102400, 2048)):
+        tasks, rpt, S = op_batch.split_k(M, K, 148)
+        blocks = -(-M // rpt)
+        assert tasks == blocks * S and (tasks <= 148 or S == 1) and rpt % 128 == 0
+        assert K % (64 * S) == 0 and (S == 1 or K // S >= 256) and S in (1, 2, 4, 8)
+        if blocks * 2 <= 148 and K % 128 == 0 and K // 2 >= 256:
+            assert S >= 2
