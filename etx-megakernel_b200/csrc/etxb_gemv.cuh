@@ -336,7 +336,20 @@ __device__ __noinline__ void stage_norm_col(const void* rows, const void* rin, v
                                             uint32_t fl = 0u, const Smem* smp = nullptr) {
   int* order = (int*)(scr + 64);
   if (!LEAN && R > 1 && (!XCH || fl == 0u)) {
-    if (tidx() < R) {
+    if (R <= 32) {
+      // one load per lane, the other ids by shuffle (no loop of R loads from L2 in front of the rows)
+      if (tidx() < 32) {
+        const int lane = tidx();
+        const int mine = (ids && lane < R) ? __ldcg(ids + lane) : 0;
+        int rank = ids ? 0 : lane;
+        if (ids)
+          for (int j = 0; j < R; ++j) {
+            const int o = __shfl_sync(0xffffffffu, mine, j);
+            rank += (o < mine) || (o == mine && j < lane);
+          }
+        if (lane < R) order[rank] = lane;
+      }
+    } else if (tidx() < R) {
       int rank = tidx();
       if (ids) {
         const int mine = __ldcg(ids + tidx());
